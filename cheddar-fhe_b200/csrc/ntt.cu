@@ -1,0 +1,156 @@
+// Cluster NTT / INTT kernels for sm_100a: one 8-CTA thread-block cluster per
+// limb, one HBM read and one HBM write per word; the 256x256 transposition
+// between the row-pairing and the in-row stages goes through distributed
+// shared memory. The per-thread phases live in ntt_core.cuh.
+#include <cooperative_groups.h>
+
+#include "context.h"
+
+namespace cg = cooperative_groups;
+
+namespace cfhe {
+namespace {
+
+struct RemoteBuf {
+  cg::cluster_group cluster;
+  uint32_t *local;
+  __device__ __forceinline__ uint32_t *operator()(int rank) const {
+    return cluster.map_shared_rank(local, rank);
+  }
+};
+
+template <bool FAST>
+__device__ __forceinline__ void forward_body(const NttArgs &a, int c, int tid,
+                                             int l, const uint32_t *src,
+                                             uint32_t *dst, const Tw *tw,
+                                             uint32_t q, uint32_t *xbuf,
+                                             uint32_t *rbuf) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t q2 = 2 * q;
+  uint32_t v[16];
+  {
+    const int x = tid & 31, r0 = tid >> 5;
+    const uint32_t *p = src + r0 * kRowWords + kStripCols * c + x;
+#pragma unroll
+    for (int k = 0; k < 16; k++) v[k] = p[k * 16 * kRowWords];
+    if (a.premul) {
+      const Tw kc = a.kc[l];
+#pragma unroll
+      for (int k = 0; k < 16; k++) v[k] = shoup_mul(v[k], kc, q);
+    }
+  }
+  fwd_rows_a<FAST>(v, tid, xbuf, tw, q, q2);
+  // Also guarantees every CTA of the cluster is resident before its shared
+  // memory is written remotely.
+  cluster.sync();
+  fwd_rows_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, tw, q, q2);
+  cluster.sync();
+  fwd_cols_a<FAST>(c, tid, rbuf, xbuf, tw, q, q2);
+  __syncthreads();
+  fwd_cols_b<FAST>(v, c, tid, xbuf, tw, q, q2);
+  {
+    const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
+    uint4 *o = reinterpret_cast<uint4 *>(dst + R * kRowWords + 16 * g);
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      o[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  }
+}
+
+template <bool FAST>
+__device__ __forceinline__ void inverse_body(const NttArgs &a, int c, int tid,
+                                             int l, const uint32_t *src,
+                                             uint32_t *dst, const Tw *itw,
+                                             uint32_t q, uint32_t *xbuf,
+                                             uint32_t *rbuf) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t q2 = 2 * q;
+  uint32_t v[16];
+  {
+    const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
+    const uint4 *p =
+        reinterpret_cast<const uint4 *>(src + R * kRowWords + 16 * g);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint4 t = p[i];
+      v[4 * i] = t.x;
+      v[4 * i + 1] = t.y;
+      v[4 * i + 2] = t.z;
+      v[4 * i + 3] = t.w;
+    }
+  }
+  inv_cols_a<FAST>(v, c, tid, xbuf, itw, q, q2);
+  cluster.sync();
+  inv_cols_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, itw, q, q2);
+  cluster.sync();
+  inv_rows_a<FAST>(tid, rbuf, xbuf, itw, q, q2);
+  __syncthreads();
+  inv_rows_b<FAST>(v, tid, xbuf, itw, a.kc[l], a.centred != 0, q, q2);
+  {
+    const int x = tid & 31, r0 = tid >> 5;
+    uint32_t *o = dst + r0 * kRowWords + kStripCols * c + x;
+#pragma unroll
+    for (int k = 0; k < 16; k++) o[k * 16 * kRowWords] = v[k];
+  }
+}
+
+template <bool INV>
+__global__ void __cluster_dims__(kClusterSize, 1, 1)
+    __launch_bounds__(kNttThreads, 2)
+        ntt_cluster_kernel(const __grid_constant__ NttArgs a) {
+  extern __shared__ __align__(16) uint32_t smem[];
+  uint32_t *xbuf = smem;
+  uint32_t *rbuf = smem + kBufWords;
+  const int c = blockIdx.x;  // rank inside the cluster (gridDim.x == 8)
+  const int tid = threadIdx.x;
+  const int t = blockIdx.y;
+  const int p = t / a.n_limbs;
+  const int l = t - p * a.n_limbs;
+  const uint32_t q = a.q[l];
+  const Tw *tw = a.table + (size_t)a.g[l] * kN;
+  const uint32_t *src =
+      a.src + (size_t)p * a.src_poly_stride + (size_t)a.src_limb[l] * kN;
+  uint32_t *dst =
+      a.dst + (size_t)p * a.dst_poly_stride + (size_t)a.dst_limb[l] * kN;
+  if (q < (1u << 30)) {
+    if constexpr (INV)
+      inverse_body<true>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+    else
+      forward_body<true>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+  } else {
+    if constexpr (INV)
+      inverse_body<false>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+    else
+      forward_body<false>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+  }
+}
+
+}  // namespace
+
+int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse) {
+  static bool configured = false;
+  if (!configured) {
+    CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kNttSmemBytes));
+    CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kNttSmemBytes));
+    configured = true;
+  }
+  const int total = args.n_limbs * args.n_polys;
+  if (total <= 0) return 0;
+  if (total > 65535) {
+    set_error("ntt: more than 65535 limb transforms in one call");
+    return -1;
+  }
+  dim3 grid(kClusterSize, total), block(kNttThreads);
+  if (inverse)
+    ntt_cluster_kernel<true><<<grid, block, kNttSmemBytes, ctx.stream>>>(args);
+  else
+    ntt_cluster_kernel<false><<<grid, block, kNttSmemBytes, ctx.stream>>>(args);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace cfhe
