@@ -175,3 +175,163 @@ class Engine:
         d = self.torch.empty_like(s)
         self.intt_(d, s, gidx, consts, mont_keep, centred)
         return self.to_host(d)
+
+    def beta(self, level):
+        return self._check(self.L.cfhe_beta(self.h, level))
+
+    def galois(self, rot):
+        self.L.cfhe_galois_for_rotation.restype = C.c_uint32
+        return self.L.cfhe_galois_for_rotation(self.h, int(rot))
+
+    def _alpha(self, level):
+        return len(self.level_limbs(-1)) if level == -1 else self.alpha
+
+    def _ptrs(self, tensors):
+        arr = (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        return arr
+
+    # ---- device-resident operators
+    def binary_(self, op, dst, a, b, gidx):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_binary(self.h, op, self._p(dst), self._p(a),
+                                       self._p(b) if b is not None else None, gp, len(g)))
+
+    def const_op_(self, op, dst, a, b, consts, gidx):
+        g, gp = _ints(gidx)
+        k, kp = _u32s(consts)
+        self._check(self.L.cfhe_const_op(self.h, op, self._p(dst), self._p(a),
+                                         self._p(b) if b is not None else None, kp, gp, len(g)))
+
+    def tensor_(self, d0, d1, d2, b1, a1, b2, a2, gidx):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_tensor(self.h, *[self._p(t) for t in (d0, d1, d2, b1, a1, b2, a2)], gp, len(g)))
+
+    def permute_(self, dst, src, add, galois, gidx):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_permute(self.h, self._p(dst), self._p(src),
+                                        self._p(add) if add is not None else None,
+                                        C.c_uint32(int(galois)), gp, len(g)))
+
+    def modup_(self, level, dst, src):
+        self._check(self.L.cfhe_modup(self.h, level, self._p(dst), self._p(src)))
+
+    def moddown_(self, level, kind, dst, src):
+        """dst/src: [limbs, N] or [polys, limbs, N]."""
+        polys = 1 if src.dim() == 2 else src.shape[0]
+        ss = src.stride(0) if src.dim() == 3 else 0
+        ds = dst.stride(0) if dst.dim() == 3 else 0
+        self._check(self.L.cfhe_moddown(self.h, level, kind, self._p(dst), self._p(src), polys,
+                                        C.c_longlong(ds), C.c_longlong(ss)))
+
+    def evk_inner_(self, level, acc_b, acc_a, modup, c0, c1, evk_b, evk_a, key_main):
+        self._check(self.L.cfhe_evk_inner(self.h, level, self._p(acc_b), self._p(acc_a), self._p(modup),
+                                          self._p(c0) if c0 is not None else None,
+                                          self._p(c1) if c1 is not None else None,
+                                          self._ptrs(evk_b), self._ptrs(evk_a), int(key_main)))
+
+    def keyswitch_(self, level, out_b, out_a, d, bx, evk_b, evk_a, key_main):
+        self._check(self.L.cfhe_keyswitch(self.h, level, self._p(out_b), self._p(out_a), self._p(d),
+                                          self._p(bx) if bx is not None else None,
+                                          self._ptrs(evk_b), self._ptrs(evk_a), int(key_main)))
+
+    def hmult_(self, level, out_b, out_a, b1, a1, b2, a2, evk_b, evk_a, key_main, rescale=True):
+        self._check(self.L.cfhe_hmult(self.h, level, self._p(out_b), self._p(out_a),
+                                      self._p(b1), self._p(a1), self._p(b2), self._p(a2),
+                                      self._ptrs(evk_b), self._ptrs(evk_a), int(key_main), int(rescale)))
+
+    # ---- host-array operators with the golden model's signatures
+    def _bin(self, op, a, b, gidx):
+        da = self.to_dev(a)
+        db = self.to_dev(b) if b is not None else None
+        d = self.torch.empty_like(da)
+        self.binary_(op, d, da, db, gidx)
+        return self.to_host(d)
+
+    def add(self, a, b, gidx):
+        return self._bin(0, a, b, gidx)
+
+    def sub(self, a, b, gidx):
+        return self._bin(1, a, b, gidx)
+
+    def neg(self, a, gidx):
+        return self._bin(2, a, None, gidx)
+
+    def mul(self, a, b, gidx):
+        return self._bin(3, a, b, gidx)
+
+    def const_op(self, a, k, gidx, op, b=None):
+        da = self.to_dev(a)
+        db = self.to_dev(b) if b is not None else None
+        d = self.torch.empty_like(da)
+        self.const_op_(op, d, da, db, k, gidx)
+        return self.to_host(d)
+
+    def tensor(self, b1, a1, b2, a2, gidx):
+        ins = [self.to_dev(x) for x in (b1, a1, b2, a2)]
+        outs = [self.torch.empty_like(ins[0]) for _ in range(3)]
+        self.tensor_(*outs, *ins, gidx)
+        return tuple(self.to_host(o) for o in outs)
+
+    def permute(self, a, galois, gidx=None, add=None):
+        da = self.to_dev(a)
+        if gidx is None:
+            gidx = [0] * da.shape[0]
+        d = self.torch.empty_like(da)
+        self.permute_(d, da, self.to_dev(add) if add is not None else None, galois, gidx)
+        return self.to_host(d)
+
+    def mul_imag_unit(self, a, gidx):
+        da = self.to_dev(a)
+        d = self.torch.empty_like(da)
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_mul_imag_unit(self.h, self._p(d), self._p(da), gp, len(g)))
+        return self.to_host(d)
+
+    def bconv(self, y, src_gidx, dst_gidx):
+        dy = self.to_dev(np.ascontiguousarray(y, dtype=np.int32).view(np.uint32))
+        sg, sp = _ints(src_gidx)
+        dg, dp = _ints(dst_gidx)
+        d = self.empty(len(dg), self.n)
+        self._check(self.L.cfhe_bconv(self.h, self._p(d), self._p(dy), sp, len(sg), dp, len(dg)))
+        return self.to_host(d)
+
+    def modup(self, level, src):
+        ntot = len(self.level_limbs(level, self._alpha(level)))
+        d = self.torch.zeros((self.beta(level), ntot, self.n), dtype=self.torch.int32,
+                             device=f"cuda:{self.device}")
+        self.modup_(level, d, self.to_dev(src))
+        return self.to_host(d)
+
+    def moddown(self, level, kind, src):
+        s = self.to_dev(src)
+        nd = len(self.level_limbs(level if kind == 0 else level - 1))
+        shape = (nd, self.n) if s.dim() == 2 else (s.shape[0], nd, self.n)
+        d = self.empty(*shape)
+        self.moddown_(level, kind, d, s)
+        return self.to_host(d)
+
+    def evk_inner(self, level, modup, evk_b, evk_a, key_main, c0=None, c1=None):
+        mu = self.to_dev(modup)
+        kb = [self.to_dev(x) for x in evk_b]
+        ka = [self.to_dev(x) for x in evk_a]
+        ab = self.empty(mu.shape[1], self.n)
+        aa = self.empty(mu.shape[1], self.n)
+        self.evk_inner_(level, ab, aa, mu, self.to_dev(c0) if c0 is not None else None,
+                        self.to_dev(c1) if c1 is not None else None, kb, ka, key_main)
+        return self.to_host(ab), self.to_host(aa)
+
+    def keyswitch(self, level, d, bx, evk_b, evk_a, key_main):
+        kb = [self.to_dev(x) for x in evk_b]
+        ka = [self.to_dev(x) for x in evk_a]
+        nd = len(self.level_limbs(level))
+        ob, oa = self.empty(nd, self.n), self.empty(nd, self.n)
+        self.keyswitch_(level, ob, oa, self.to_dev(d), self.to_dev(bx), kb, ka, key_main)
+        return self.to_host(ob), self.to_host(oa)
+
+    def hmult(self, level, b1, a1, b2, a2, evk_b, evk_a, key_main, rescale=True):
+        kb = [self.to_dev(x) for x in evk_b]
+        ka = [self.to_dev(x) for x in evk_a]
+        nd = len(self.level_limbs(level - 1 if rescale else level))
+        ob, oa = self.empty(nd, self.n), self.empty(nd, self.n)
+        self.hmult_(level, ob, oa, *[self.to_dev(x) for x in (b1, a1, b2, a2)], kb, ka, key_main, rescale)
+        return self.to_host(ob), self.to_host(oa)

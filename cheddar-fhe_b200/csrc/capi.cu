@@ -7,6 +7,8 @@
 
 #include "context.h"
 #include "host_math.h"
+#include "kernels.h"
+#include "pipeline.h"
 
 struct cfhe_context {
   cfhe::Context c;
@@ -51,7 +53,7 @@ static int fill_limbs(const Context &c, NttArgs &a, const int *gidx,
     if (gidx[l] < 0 || gidx[l] >= c.NP) return fail("prime index out of range");
     a.g[l] = (uint8_t)gidx[l];
     a.q[l] = c.q[gidx[l]];
-    a.src_limb[l] = a.dst_limb[l] = (uint8_t)l;
+    a.src_limb[l] = a.dst_limb[l] = (uint16_t)l;
   }
   a.n_limbs = n_limbs;
   return 0;
@@ -128,6 +130,10 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
   if (e == cudaSuccess)
     e = cudaMemcpy(c.d_itw, inv.data(), tsz * sizeof(Tw), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return cleanup_fail(cudaGetErrorString(e));
+  if (build_plans(c) != 0) {
+    std::string m = get_error();
+    return cleanup_fail(m);
+  }
   *out = h;
   return 0;
 }
@@ -135,27 +141,35 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
 void cfhe_context_destroy(cfhe_context *h) {
   if (!h) return;
   Context &c = h->c;
+  free_plans(c);
   if (c.d_tw) cudaFree(c.d_tw);
   if (c.d_itw) cudaFree(c.d_itw);
   if (c.own_stream && c.stream) cudaStreamDestroy(c.stream);
   delete h;
 }
 
-int cfhe_set_stream(cfhe_context *h, void *cuda_stream) {
-  if (!h) return fail("null context");
-  Context &c = h->c;
+static void drop_own_stream(Context &c) {
   if (c.own_stream && c.stream) {
     cudaStreamSynchronize(c.stream);
     cudaStreamDestroy(c.stream);
-    c.stream = nullptr;
-    c.own_stream = false;
   }
-  if (cuda_stream) {
-    c.stream = (cudaStream_t)cuda_stream;
-  } else {
-    CFHE_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-    c.own_stream = true;
-  }
+  c.stream = nullptr;
+  c.own_stream = false;
+}
+
+int cfhe_set_stream(cfhe_context *h, void *cuda_stream) {
+  if (!h) return fail("null context");
+  drop_own_stream(h->c);
+  h->c.stream = (cudaStream_t)cuda_stream;
+  return 0;
+}
+
+int cfhe_use_own_stream(cfhe_context *h) {
+  if (!h) return fail("null context");
+  Context &c = h->c;
+  if (c.own_stream) return 0;
+  CFHE_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  c.own_stream = true;
   return 0;
 }
 
@@ -253,6 +267,234 @@ int cfhe_intt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
     a.kc[l] = make_tw(k, q);
   }
   return launch_ntt(c, a, true);
+}
+
+// ---------------------------------------------------------------------------
+// element-wise
+// ---------------------------------------------------------------------------
+static int fill_rows(const Context &c, EwArgs &e, uint32_t *dst,
+                     const uint32_t *a, const uint32_t *b,
+                     const uint32_t *consts, const int *gidx, int n_limbs) {
+  if (!dst || !a || !gidx) return fail("null argument");
+  if (n_limbs < 0 || n_limbs > kMaxRows) return fail("too many limbs");
+  e.n_rows = n_limbs;
+  for (int l = 0; l < n_limbs; l++) {
+    const int g = gidx[l];
+    if (g < 0 || g >= c.NP) return fail("prime index out of range");
+    const size_t o = (size_t)l * kN;
+    e.rows[l] = EwRow{dst + o, a + o, b ? b + o : nullptr, c.q[g], c.nqinv[g],
+                      consts ? consts[l] % c.q[g] : 0u, 0u};
+  }
+  return 0;
+}
+
+int cfhe_binary(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
+                const uint32_t *b, const int *gidx, int n_limbs) {
+  if (!h) return fail("null context");
+  static const int map[4] = {EW_ADD, EW_SUB, EW_NEG, EW_MUL};
+  if (op < 0 || op > 3) return fail("unknown binary op");
+  if (op != 2 && !b) return fail("null argument");
+  EwArgs e;
+  if (int r = fill_rows(h->c, e, dst, a, b, nullptr, gidx, n_limbs)) return r;
+  return launch_ew(h->c, map[op], e);
+}
+
+int cfhe_const_op(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
+                  const uint32_t *b, const uint32_t *consts, const int *gidx,
+                  int n_limbs) {
+  if (!h || !consts) return fail("null argument");
+  static const int map[5] = {EW_ADDC, EW_SUBC, EW_RSUBC, EW_MULC, EW_MULC_ADD};
+  if (op < 0 || op > 4) return fail("unknown const op");
+  if (op == 4 && !b) return fail("null argument");
+  EwArgs e;
+  if (int r = fill_rows(h->c, e, dst, a, b, consts, gidx, n_limbs)) return r;
+  return launch_ew(h->c, map[op], e);
+}
+
+int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
+                const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
+                const uint32_t *a2, const int *gidx, int n_limbs) {
+  if (!h || !d0 || !d1 || !d2 || !b1 || !a1 || !b2 || !a2 || !gidx)
+    return fail("null argument");
+  if (n_limbs < 0 || n_limbs > kMaxLimbs) return fail("too many limbs");
+  const Context &c = h->c;
+  TensorArgs t;
+  t.n_rows = n_limbs;
+  for (int l = 0; l < n_limbs; l++) {
+    const int g = gidx[l];
+    if (g < 0 || g >= c.NP) return fail("prime index out of range");
+    const size_t o = (size_t)l * kN;
+    t.rows[l] = TensorRow{d0 + o, d1 + o, d2 + o, b1 + o, a1 + o,
+                          b2 + o, a2 + o, c.q[g], c.nqinv[g]};
+  }
+  return launch_tensor(c, t);
+}
+
+int cfhe_permute(cfhe_context *h, uint32_t *dst, const uint32_t *src,
+                 const uint32_t *add, uint32_t galois, const int *gidx,
+                 int n_limbs) {
+  if (!h) return fail("null context");
+  if (dst == src) return fail("permute cannot run in place");
+  if ((galois & 1u) == 0 || galois >= 2u * kN) return fail("invalid Galois element");
+  EwArgs e;
+  if (int r = fill_rows(h->c, e, dst, src, add, nullptr, gidx, n_limbs)) return r;
+  return launch_permute(h->c, e, galois);
+}
+
+uint32_t cfhe_galois_for_rotation(const cfhe_context *h, int rot) {
+  if (!h) return 0;
+  const uint32_t m = 2u * h->c.n;
+  if (rot < 0) return m - 1;
+  uint32_t g = 1;
+  for (int i = 0; i < rot; i++) g = (uint32_t)(((uint64_t)g * 5u) % m);
+  return g;
+}
+
+int cfhe_mul_imag_unit(cfhe_context *h, uint32_t *dst, const uint32_t *src,
+                       const int *gidx, int n_limbs) {
+  if (!h || !gidx) return fail("null argument");
+  const Context &c = h->c;
+  if (n_limbs < 0 || n_limbs > kMaxRows) return fail("too many limbs");
+  std::vector<uint32_t> u(n_limbs);
+  for (int l = 0; l < n_limbs; l++) {
+    const int g = gidx[l];
+    if (g < 0 || g >= c.NP) return fail("prime index out of range");
+    // psi^(N/2) in M-form (the reference reuses twiddle entry 1,
+    // src/core/NTT.cu:1301-1310)
+    u[l] = to_mont(powmod(c.psi[g], (uint64_t)c.n / 2, c.q[g]), c.q[g]);
+  }
+  EwArgs e;
+  if (int r = fill_rows(c, e, dst, src, nullptr, u.data(), gidx, n_limbs)) return r;
+  return launch_ew(c, EW_IMAG, e);
+}
+
+// ---------------------------------------------------------------------------
+// mod-switch
+// ---------------------------------------------------------------------------
+int cfhe_bconv(cfhe_context *h, uint32_t *dst, const int32_t *y,
+               const int *src_gidx, int n_src, const int *dst_gidx, int n_dst) {
+  if (!h || !dst || !y || !src_gidx || !dst_gidx) return fail("null argument");
+  Context &c = h->c;
+  if (n_src < 1 || n_src > 16 || n_dst < 1 || n_dst > kMaxLimbs)
+    return fail("bconv: unsupported shape");
+  std::vector<int32_t> t((size_t)n_src * n_dst);
+  BconvArgs b;
+  memset(&b, 0, sizeof(b));
+  BconvJob &j = b.jobs[0];
+  for (int m = 0; m < n_dst; m++) {
+    const int gd = dst_gidx[m];
+    if (gd < 0 || gd >= c.NP) return fail("prime index out of range");
+    const uint32_t p = c.q[gd];
+    for (int k = 0; k < n_src; k++) {
+      uint32_t acc = 1;
+      for (int i = 0; i < n_src; i++) {
+        if (src_gidx[i] < 0 || src_gidx[i] >= c.NP)
+          return fail("prime index out of range");
+        if (i != k) acc = mulmod(acc, c.q[src_gidx[i]] % p, p);
+      }
+      acc = to_mont(to_mont(acc, p), p);
+      t[(size_t)m * n_src + k] = acc > (p >> 1) ? (int32_t)(acc - p) : (int32_t)acc;
+    }
+    j.dst_limb[m] = (uint8_t)m;
+    j.q[m] = p;
+    j.qinv[m] = 0u - c.nqinv[gd];
+  }
+  int32_t *d_t = nullptr;
+  CFHE_CUDA(cudaMalloc(&d_t, t.size() * sizeof(int32_t)));
+  CFHE_CUDA(cudaMemcpyAsync(d_t, t.data(), t.size() * sizeof(int32_t),
+                            cudaMemcpyHostToDevice, c.stream));
+  j.src = y;
+  j.dst = dst;
+  j.table = d_t;
+  j.ns = n_src;
+  j.nd = n_dst;
+  b.n_jobs = 1;
+  int r = launch_bconv(c, b);
+  cudaStreamSynchronize(c.stream);
+  cudaFree(d_t);
+  return r;
+}
+
+static const LevelPlan *get_plan(cfhe_context *h, int level) {
+  if (!h) {
+    fail("null context");
+    return nullptr;
+  }
+  const LevelPlan *lp = h->c.plan(level);
+  if (!lp) fail("invalid level");
+  return lp;
+}
+
+int cfhe_beta(const cfhe_context *h, int level) {
+  if (!h) return fail("null context");
+  const LevelPlan *lp = h->c.plan(level);
+  if (!lp) return fail("invalid level");
+  return lp->beta;
+}
+
+int cfhe_modup(cfhe_context *h, int level, uint32_t *dst, const uint32_t *src) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!dst || !src) return fail("null argument");
+  if (int r = ensure_workspace(h->c, modup_scratch_words(*lp))) return r;
+  return run_modup(h->c, *lp, dst, src, true, h->c.ws);
+}
+
+int cfhe_moddown(cfhe_context *h, int level, int type, uint32_t *dst,
+                 const uint32_t *src, int n_polys, long long dst_poly_stride,
+                 long long src_poly_stride) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!dst || !src) return fail("null argument");
+  if (type < 0 || type > 2) return fail("unknown ModDown type");
+  if (type != 0 && !lp->has_rescale) return fail("level cannot be rescaled");
+  if (n_polys < 1 || n_polys > kMaxBconvJobs) return fail("invalid n_polys");
+  const ConvPlan &cv = lp->down[type];
+  if (int r = ensure_workspace(h->c, moddown_scratch_words(cv, n_polys))) return r;
+  return run_moddown(h->c, cv, dst, src, n_polys, dst_poly_stride,
+                     src_poly_stride, h->c.ws);
+}
+
+int cfhe_evk_inner(cfhe_context *h, int level, uint32_t *acc_b, uint32_t *acc_a,
+                   const uint32_t *modup, const uint32_t *c0, const uint32_t *c1,
+                   const uint32_t *const *evk_b, const uint32_t *const *evk_a,
+                   int key_main) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!acc_b || !acc_a || !modup || !evk_b || !evk_a) return fail("null argument");
+  return run_inner(h->c, *lp, acc_b, acc_a, modup, nullptr, c0, c1, evk_b,
+                   evk_a, key_main);
+}
+
+int cfhe_keyswitch(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
+                   const uint32_t *d, const uint32_t *bx,
+                   const uint32_t *const *evk_b, const uint32_t *const *evk_a,
+                   int key_main) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!out_b || !out_a || !d || !evk_b || !evk_a) return fail("null argument");
+  if (int r = ensure_workspace(h->c, keyswitch_scratch_words(*lp, 0))) return r;
+  return run_keyswitch(h->c, *lp, 0, out_b, out_a, d, bx, nullptr, evk_b, evk_a,
+                       key_main, h->c.ws);
+}
+
+int cfhe_hmult(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
+               const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
+               const uint32_t *a2, const uint32_t *const *evk_b,
+               const uint32_t *const *evk_a, int key_main, int rescale) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!out_b || !out_a || !b1 || !a1 || !b2 || !a2 || !evk_b || !evk_a)
+    return fail("null argument");
+  const int type = rescale ? 2 : 0;
+  if (rescale && !lp->has_rescale) return fail("level cannot be rescaled");
+  const size_t tw = (size_t)lp->nq * kN;
+  if (int r = ensure_workspace(h->c, 3 * tw + keyswitch_scratch_words(*lp, type)))
+    return r;
+  uint32_t *d0 = h->c.ws, *d1 = d0 + tw, *d2 = d1 + tw, *scratch = d2 + tw;
+  if (int r = run_tensor(h->c, *lp, d0, d1, d2, b1, a1, b2, a2)) return r;
+  return run_keyswitch(h->c, *lp, type, out_b, out_a, d2, d0, d1, evk_b, evk_a,
+                       key_main, scratch);
 }
 
 }  // extern "C"

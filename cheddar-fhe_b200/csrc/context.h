@@ -13,8 +13,13 @@ namespace cfhe {
 
 constexpr int kMaxLimbs = 64;
 
+constexpr int kMaxJobs = 256;
+
 // One batched transform launch: limb l of polynomial p lives at
-// base + p * poly_stride + limb_pos[l] * N (strides in 32-bit words).
+// base + p * poly_stride + limb_pos[l] * N (strides in 32-bit words). A launch
+// may list up to kMaxJobs limbs (ModUp flattens every digit into one list);
+// per-limb constants and the epilogue are available for lists of at most
+// kMaxLimbs limbs.
 struct NttArgs {
   uint32_t *dst;
   const uint32_t *src;
@@ -23,11 +28,48 @@ struct NttArgs {
   int n_limbs, n_polys;
   int premul;   // forward: multiply the input by kc[l] first
   int centred;  // inverse: centred output
-  uint8_t g[kMaxLimbs];         // global prime index
-  uint8_t src_limb[kMaxLimbs];  // limb position inside the source polynomial
-  uint8_t dst_limb[kMaxLimbs];
-  uint32_t q[kMaxLimbs];
+  // forward epilogue (ModDown family): out = ((pad*x) - ntt) * scale, x read
+  // from ep_src limb ep_limb[l] (255: no such limb, x = 0)
+  int ep_mode;  // 0 none, 1 without padding constant, 2 with
+  const uint32_t *ep_src;
+  long long ep_poly_stride;
+  uint8_t g[kMaxJobs];          // global prime index
+  uint16_t src_limb[kMaxJobs];  // limb position inside the source polynomial
+  uint16_t dst_limb[kMaxJobs];
+  uint32_t q[kMaxJobs];
   Tw kc[kMaxLimbs];  // per-limb constant (Shoup pair)
+  uint8_t ep_limb[kMaxLimbs];
+  Tw ep_pad[kMaxLimbs], ep_scale[kMaxLimbs];
+};
+
+// One base conversion S -> D with everything its three kernels need.
+struct ConvPlan {
+  std::vector<int> src_g, dst_g;    // global prime indices
+  std::vector<int> src_pos;         // limb positions of S inside the source
+  std::vector<uint32_t> pre;        // per source limb: (S_hat_k * N)^-1 (* restored)
+  int32_t *d_table = nullptr;       // [nd][ns] centred, device
+  // ModDown-family epilogue, per destination limb
+  std::vector<int> ep_pos;          // position of the surviving limb in the source, -1 if restored
+  std::vector<uint32_t> ep_pad;     // product of restored primes mod d (plain)
+  std::vector<uint32_t> ep_scale;   // (prod S)^-1 mod d (plain)
+  bool has_pad = false;
+};
+
+struct DigitPlan {
+  int index = 0;    // absolute digit number (slot of its ModUp buffer)
+  int s0 = 0, s1 = 0;  // limb range inside the level's Q limbs
+  ConvPlan conv;    // dst limb positions are those of the (nq+alpha) layout
+  std::vector<int> dst_pos;
+};
+
+struct LevelPlan {
+  int level = 0, num_main = 0, num_ter = 0, alpha = 0, nq = 0, ntot = 0, beta = 0;
+  std::vector<int> q_g, full_g;     // global indices of Q limbs / Q+aux limbs
+  std::vector<DigitPlan> digits;    // active digits only
+  std::vector<int> own_digit;       // per Q limb: index into `digits`
+  std::vector<uint32_t> p_mont;     // per Q limb: (P mod q) * 2^32 mod q
+  ConvPlan down[3];                 // ModDown, Rescale, ModDownAndRescale
+  bool has_rescale = false;
 };
 
 struct Context {
@@ -43,7 +85,22 @@ struct Context {
   Tw *d_tw = nullptr, *d_itw = nullptr;  // [NP][N]
   cudaStream_t stream = nullptr;
   bool own_stream = false;
+
+  std::vector<uint32_t> nqinv;      // -q^-1 mod 2^32, global order
+  std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
+  // workspace arena for pipeline temporaries (grown on demand)
+  uint32_t *ws = nullptr;
+  size_t ws_words = 0;
+
+  const LevelPlan *plan(int level) const {
+    if (level < -1 || level + 1 >= (int)levels.size()) return nullptr;
+    return &levels[level + 1];
+  }
 };
+
+int build_plans(Context &ctx);
+void free_plans(Context &ctx);
+int ensure_workspace(Context &ctx, size_t words);
 
 void set_error(const std::string &msg);
 const std::string &get_error();

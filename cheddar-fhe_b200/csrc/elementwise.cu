@@ -1,0 +1,217 @@
+// Element-wise limb kernels: 128-bit accesses, one launch per operator over a
+// table of rows (a row = one limb of one polynomial). These are pure
+// streaming kernels; the values they produce are the canonical residues the
+// reference's kernels produce (reference src/core/ElementWise.cu:32-658).
+#include "context.h"
+#include "kernels.h"
+#include "modmath.cuh"
+
+namespace cfhe {
+namespace {
+
+constexpr int kEwThreads = 256;
+constexpr int kVecPerLimb = kN / 4;                    // uint4 per limb
+constexpr int kEwBlocksX = kVecPerLimb / kEwThreads;   // 64
+
+template <typename F>
+__device__ __forceinline__ uint4 map4(uint4 a, uint4 b, F f) {
+  return make_uint4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w));
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kEwThreads)
+    ew_kernel(const __grid_constant__ EwArgs args) {
+  const EwRow &r = args.rows[blockIdx.y];
+  const int v = blockIdx.x * kEwThreads + threadIdx.x;
+  const uint32_t q = r.q, nq = r.nqinv, k = r.k;
+  uint4 a = reinterpret_cast<const uint4 *>(r.a)[v];
+  uint4 b = make_uint4(0, 0, 0, 0);
+  if constexpr (OP == EW_ADD || OP == EW_SUB || OP == EW_MUL || OP == EW_MULC_ADD)
+    b = reinterpret_cast<const uint4 *>(r.b)[v];
+  uint4 o;
+  if constexpr (OP == EW_ADD)
+    o = map4(a, b, [=](uint32_t x, uint32_t y) { return add_mod(x, y, q); });
+  else if constexpr (OP == EW_SUB)
+    o = map4(a, b, [=](uint32_t x, uint32_t y) { return sub_mod(x, y, q); });
+  else if constexpr (OP == EW_NEG)
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return x ? q - x : 0u; });
+  else if constexpr (OP == EW_MUL)
+    o = map4(a, b, [=](uint32_t x, uint32_t y) { return mont_mul(x, y, q, nq); });
+  else if constexpr (OP == EW_ADDC)
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return add_mod(x, k, q); });
+  else if constexpr (OP == EW_SUBC)
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return sub_mod(x, k, q); });
+  else if constexpr (OP == EW_RSUBC)
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return sub_mod(k, x, q); });
+  else if constexpr (OP == EW_MULC)
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return mont_mul(x, k, q, nq); });
+  else if constexpr (OP == EW_MULC_ADD)
+    o = map4(a, b, [=](uint32_t x, uint32_t y) {
+      return add_mod(mont_mul(x, k, q, nq), y, q);
+    });
+  else if constexpr (OP == EW_IMAG) {
+    // multiply by X^(N/2): +u on the first half of the evaluation points,
+    // -u on the second (u = psi^(N/2) in M-form)
+    const uint32_t u = (4 * v < kN / 2) ? k : q - k;
+    o = map4(a, b, [=](uint32_t x, uint32_t) { return mont_mul(x, u, q, nq); });
+  } else
+    o = a;
+  reinterpret_cast<uint4 *>(r.dst)[v] = o;
+}
+
+__global__ void __launch_bounds__(kEwThreads)
+    tensor_kernel(const __grid_constant__ TensorArgs args) {
+  const TensorRow &r = args.rows[blockIdx.y];
+  const int v = blockIdx.x * kEwThreads + threadIdx.x;
+  const uint32_t q = r.q, nq = r.nqinv;
+  const uint4 b1 = reinterpret_cast<const uint4 *>(r.b1)[v];
+  const uint4 a1 = reinterpret_cast<const uint4 *>(r.a1)[v];
+  const uint4 b2 = reinterpret_cast<const uint4 *>(r.b2)[v];
+  const uint4 a2 = reinterpret_cast<const uint4 *>(r.a2)[v];
+  const uint64_t q32 = (uint64_t)q << 32;
+  auto cross = [=](uint32_t x1, uint32_t y1, uint32_t x2, uint32_t y2) {
+    uint64_t acc = (uint64_t)x1 * y2;  // b1*a2 + a1*b2, one reduction
+    mac_fold(acc, y1, x2, q32);
+    return mont_reduce(acc, q, nq);
+  };
+  auto mm = [=](uint32_t x, uint32_t y) { return mont_mul(x, y, q, nq); };
+  reinterpret_cast<uint4 *>(r.d0)[v] = map4(b1, b2, mm);
+  reinterpret_cast<uint4 *>(r.d2)[v] = map4(a1, a2, mm);
+  reinterpret_cast<uint4 *>(r.d1)[v] =
+      make_uint4(cross(b1.x, a1.x, b2.x, a2.x), cross(b1.y, a1.y, b2.y, a2.y),
+                 cross(b1.z, a1.z, b2.z, a2.z), cross(b1.w, a1.w, b2.w, a2.w));
+}
+
+// dst[i] = (add ? add[i] : 0) + src[pi(i)], pi the index map of the Galois
+// automorphism on bit-reversed evaluation order. Aligned blocks of 2^k
+// outputs read aligned blocks of 2^k inputs, so a warp's scattered 4-byte
+// loads stay inside one 512-byte block.
+__global__ void __launch_bounds__(kEwThreads)
+    permute_kernel(const __grid_constant__ EwArgs args, uint32_t galois) {
+  const EwRow &r = args.rows[blockIdx.y];
+  const int v = blockIdx.x * kEwThreads + threadIdx.x;
+  const uint32_t q = r.q;
+  uint32_t o[4];
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const uint32_t i = 4 * v + e;
+    const uint32_t ex = (__brev(i) >> (31 - kLogN)) + 1;  // 2*brev16(i)+1
+    const uint32_t s = __brev((ex * galois - 1) << (31 - kLogN));
+    o[e] = r.a[s & (kN - 1)];
+  }
+  uint4 out = make_uint4(o[0], o[1], o[2], o[3]);
+  if (r.b) {
+    const uint4 b = reinterpret_cast<const uint4 *>(r.b)[v];
+    out = map4(out, b, [=](uint32_t x, uint32_t y) { return add_mod(x, y, q); });
+  }
+  reinterpret_cast<uint4 *>(r.dst)[v] = out;
+}
+
+// Key-switch inner product: for every limb l of the extended basis
+//   acc_b[l] = sum_i x_i[l] * kb_i[l] (+ P * c0[l] on Q limbs), same for a.
+// x_i[l] is the digit's own limb read in place from `d` when limb l belongs
+// to digit i, else the ModUp output. One Montgomery reduction per output.
+__global__ void __launch_bounds__(kEwThreads)
+    inner_kernel(const __grid_constant__ InnerArgs a) {
+  const int l = blockIdx.y;
+  const int v = blockIdx.x * kEwThreads + threadIdx.x;
+  const uint32_t q = a.q[l], nq = a.nqinv[l];
+  const uint64_t q32 = (uint64_t)q << 32;
+  uint64_t sb[4] = {0, 0, 0, 0}, sa[4] = {0, 0, 0, 0};
+  const size_t koff = (size_t)a.kpos[l] * kN;
+#pragma unroll 1
+  for (int i = 0; i < a.n_digits; i++) {
+    const uint32_t *xp = (a.own_digit[l] == i && a.d)
+                             ? a.d + (size_t)l * kN
+                             : a.mu + ((size_t)a.mu_slot[i] * a.ntot + l) * kN;
+    const uint4 x = reinterpret_cast<const uint4 *>(xp)[v];
+    const uint4 kb = __ldcs(reinterpret_cast<const uint4 *>(a.kb[i] + koff) + v);
+    const uint4 ka = __ldcs(reinterpret_cast<const uint4 *>(a.ka[i] + koff) + v);
+    mac_fold(sb[0], x.x, kb.x, q32);
+    mac_fold(sb[1], x.y, kb.y, q32);
+    mac_fold(sb[2], x.z, kb.z, q32);
+    mac_fold(sb[3], x.w, kb.w, q32);
+    mac_fold(sa[0], x.x, ka.x, q32);
+    mac_fold(sa[1], x.y, ka.y, q32);
+    mac_fold(sa[2], x.z, ka.z, q32);
+    mac_fold(sa[3], x.w, ka.w, q32);
+  }
+  if (l < a.nq) {
+    const uint32_t pm = a.pm[l];
+    if (a.c0) {
+      const uint4 c = reinterpret_cast<const uint4 *>(a.c0 + (size_t)l * kN)[v];
+      mac_fold(sb[0], c.x, pm, q32);
+      mac_fold(sb[1], c.y, pm, q32);
+      mac_fold(sb[2], c.z, pm, q32);
+      mac_fold(sb[3], c.w, pm, q32);
+    }
+    if (a.c1) {
+      const uint4 c = reinterpret_cast<const uint4 *>(a.c1 + (size_t)l * kN)[v];
+      mac_fold(sa[0], c.x, pm, q32);
+      mac_fold(sa[1], c.y, pm, q32);
+      mac_fold(sa[2], c.z, pm, q32);
+      mac_fold(sa[3], c.w, pm, q32);
+    }
+  }
+  reinterpret_cast<uint4 *>(a.acc_b + (size_t)l * kN)[v] =
+      make_uint4(mont_reduce(sb[0], q, nq), mont_reduce(sb[1], q, nq),
+                 mont_reduce(sb[2], q, nq), mont_reduce(sb[3], q, nq));
+  reinterpret_cast<uint4 *>(a.acc_a + (size_t)l * kN)[v] =
+      make_uint4(mont_reduce(sa[0], q, nq), mont_reduce(sa[1], q, nq),
+                 mont_reduce(sa[2], q, nq), mont_reduce(sa[3], q, nq));
+}
+
+}  // namespace
+
+int launch_ew(const Context &ctx, int op, const EwArgs &args) {
+  if (args.n_rows <= 0) return 0;
+  dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
+  switch (op) {
+#define CASE(OP)                                            \
+  case OP:                                                  \
+    ew_kernel<OP><<<grid, block, 0, ctx.stream>>>(args);    \
+    break;
+    CASE(EW_ADD)
+    CASE(EW_SUB)
+    CASE(EW_NEG)
+    CASE(EW_MUL)
+    CASE(EW_ADDC)
+    CASE(EW_SUBC)
+    CASE(EW_RSUBC)
+    CASE(EW_MULC)
+    CASE(EW_MULC_ADD)
+    CASE(EW_IMAG)
+    CASE(EW_COPY)
+#undef CASE
+    default:
+      set_error("unknown element-wise op");
+      return -1;
+  }
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_tensor(const Context &ctx, const TensorArgs &args) {
+  if (args.n_rows <= 0) return 0;
+  dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
+  tensor_kernel<<<grid, block, 0, ctx.stream>>>(args);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois) {
+  if (args.n_rows <= 0) return 0;
+  dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
+  permute_kernel<<<grid, block, 0, ctx.stream>>>(args, galois);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_inner(const Context &ctx, const InnerArgs &args) {
+  dim3 grid(kEwBlocksX, args.ntot), block(kEwThreads);
+  inner_kernel<<<grid, block, 0, ctx.stream>>>(args);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace cfhe

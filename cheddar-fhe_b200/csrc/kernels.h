@@ -1,0 +1,81 @@
+// Argument blocks and launchers of the element-wise, inner-product and base
+// conversion kernels. Argument blocks travel as kernel parameters (constant
+// bank), so a launch needs no host-to-device copy.
+#pragma once
+#include <stdint.h>
+
+#include "context.h"
+
+namespace cfhe {
+
+enum EwOp {
+  EW_ADD = 0,
+  EW_SUB,
+  EW_NEG,
+  EW_MUL,
+  EW_ADDC,
+  EW_SUBC,
+  EW_RSUBC,
+  EW_MULC,
+  EW_MULC_ADD,
+  EW_IMAG,
+  EW_COPY
+};
+
+struct EwRow {
+  uint32_t *dst;
+  const uint32_t *a;
+  const uint32_t *b;
+  uint32_t q, nqinv, k, pad_;
+};
+constexpr int kMaxRows = 192;  // 3 polynomials x 59 limbs fit
+struct EwArgs {
+  int n_rows;
+  EwRow rows[kMaxRows];
+};
+
+struct TensorRow {
+  uint32_t *d0, *d1, *d2;
+  const uint32_t *b1, *a1, *b2, *a2;
+  uint32_t q, nqinv;
+};
+struct TensorArgs {
+  int n_rows;
+  TensorRow rows[kMaxLimbs];
+};
+
+constexpr int kMaxDigits = 8;
+struct InnerArgs {
+  uint32_t *acc_b, *acc_a;
+  const uint32_t *mu;  // ModUp buffers, slot s at mu + s*ntot*N
+  const uint32_t *d;   // polynomial being switched (own limbs), or null
+  const uint32_t *c0, *c1;  // optional P*c0 -> acc_b, P*c1 -> acc_a (Q limbs)
+  const uint32_t *kb[kMaxDigits], *ka[kMaxDigits];
+  int n_digits, ntot, nq;
+  uint8_t mu_slot[kMaxDigits];
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs], pm[kMaxLimbs];
+  uint8_t kpos[kMaxLimbs];       // limb position inside the key
+  uint8_t own_digit[kMaxLimbs];  // active-digit index owning limb l, or 255
+};
+
+struct BconvJob {
+  const int32_t *src;    // [ns][N] centred
+  uint32_t *dst;         // limb m stored at dst + dst_limb[m]*N
+  const int32_t *table;  // [nd][ns]
+  int ns, nd;
+  uint8_t dst_limb[kMaxLimbs];
+  uint32_t q[kMaxLimbs], qinv[kMaxLimbs];
+};
+constexpr int kMaxBconvJobs = 8;
+struct BconvArgs {
+  int n_jobs;
+  BconvJob jobs[kMaxBconvJobs];
+};
+
+int launch_ew(const Context &ctx, int op, const EwArgs &args);
+int launch_tensor(const Context &ctx, const TensorArgs &args);
+int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
+int launch_inner(const Context &ctx, const InnerArgs &args);
+int launch_bconv(const Context &ctx, const BconvArgs &args);
+
+}  // namespace cfhe

@@ -21,7 +21,7 @@ struct RemoteBuf {
 
 template <bool FAST>
 __device__ __forceinline__ void forward_body(const NttArgs &a, int c, int tid,
-                                             int l, const uint32_t *src,
+                                             int p, int l, const uint32_t *src,
                                              uint32_t *dst, const Tw *tw,
                                              uint32_t q, uint32_t *xbuf,
                                              uint32_t *rbuf) {
@@ -50,7 +50,44 @@ __device__ __forceinline__ void forward_body(const NttArgs &a, int c, int tid,
   fwd_cols_b<FAST>(v, c, tid, xbuf, tw, q, q2);
   {
     const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
-    uint4 *o = reinterpret_cast<uint4 *>(dst + R * kRowWords + 16 * g);
+    const int off = R * kRowWords + 16 * g;
+    if (a.ep_mode) {
+      // ModDown-family epilogue: ((pad * x) - ntt) * scale, canonical
+      const Tw scale = a.ep_scale[l];
+      uint32_t x[16];
+      if (a.ep_limb[l] != 255) {
+        const uint4 *xp = reinterpret_cast<const uint4 *>(
+            a.ep_src + (size_t)p * a.ep_poly_stride +
+            (size_t)a.ep_limb[l] * kN + off);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const uint4 t = xp[i];
+          x[4 * i] = t.x;
+          x[4 * i + 1] = t.y;
+          x[4 * i + 2] = t.z;
+          x[4 * i + 3] = t.w;
+        }
+        if (a.ep_mode == 2) {
+          const Tw pad = a.ep_pad[l];
+#pragma unroll
+          for (int k = 0; k < 16; k++) {
+            const uint32_t t = shoup_mul(x[k], pad, q);
+            x[k] = umin32(t, t - q);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) x[k] = 0;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; k++) {
+        uint32_t d = x[k] - v[k];
+        if (x[k] < v[k]) d += q;
+        d = shoup_mul(d, scale, q);
+        v[k] = umin32(d, d - q);
+      }
+    }
+    uint4 *o = reinterpret_cast<uint4 *>(dst + off);
 #pragma unroll
     for (int i = 0; i < 4; i++)
       o[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -116,12 +153,12 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1)
     if constexpr (INV)
       inverse_body<true>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
     else
-      forward_body<true>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+      forward_body<true>(a, c, tid, p, l, src, dst, tw, q, xbuf, rbuf);
   } else {
     if constexpr (INV)
       inverse_body<false>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
     else
-      forward_body<false>(a, c, tid, l, src, dst, tw, q, xbuf, rbuf);
+      forward_body<false>(a, c, tid, p, l, src, dst, tw, q, xbuf, rbuf);
   }
 }
 

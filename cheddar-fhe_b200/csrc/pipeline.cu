@@ -1,0 +1,263 @@
+// Level-aware pipelines: ModUp, the ModDown family, the evaluation-key inner
+// product, key switching and HMult, composed from the kernels of this library.
+// They follow the algebra of the reference's ModSwitchHandler
+// (src/core/ModSwitch.cu:429-684) and Context (src/core/Context.cpp:584-871)
+// with fewer launches: every digit's base conversion shares one launch, all
+// digits' forward transforms share one launch, the digit's own limbs are read
+// in place instead of copied, P*(b,a) is folded into the inner product, and
+// both polynomials of a ciphertext go through ModDown together.
+#include <string.h>
+
+#include "host_math.h"
+#include "pipeline.h"
+
+namespace cfhe {
+namespace {
+
+Tw inv_const(uint32_t pre, uint32_t q) {
+  // the kernel multiplies the raw inverse transform by pre * 2^-32 so that
+  // M-form evaluations come out as plain, pre-scaled coefficients
+  return make_tw(mulmod(pre % q, rinv_mod(q), q), q);
+}
+
+void fill_bconv_job(const Context &c, BconvJob &j, const ConvPlan &cv,
+                    const int32_t *src, uint32_t *dst,
+                    const std::vector<int> *dst_pos) {
+  j.src = src;
+  j.dst = dst;
+  j.table = cv.d_table;
+  j.ns = (int)cv.src_g.size();
+  j.nd = (int)cv.dst_g.size();
+  for (int m = 0; m < j.nd; m++) {
+    const int g = cv.dst_g[m];
+    j.dst_limb[m] = (uint8_t)(dst_pos ? (*dst_pos)[m] : m);
+    j.q[m] = c.q[g];
+    j.qinv[m] = 0u - c.nqinv[g];
+  }
+}
+
+}  // namespace
+
+size_t modup_scratch_words(const LevelPlan &lp) { return (size_t)lp.nq * kN; }
+
+int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
+              const uint32_t *src, bool copy_own, uint32_t *y) {
+  if (lp.digits.empty()) {
+    set_error("ModUp: level has no digits");
+    return -1;
+  }
+  // 1. inverse transform of every Q limb, pre-scaled and centred
+  NttArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dst = y;
+  a.src = src;
+  a.table = c.d_itw;
+  a.n_limbs = lp.nq;
+  a.n_polys = 1;
+  a.centred = 1;
+  for (const DigitPlan &d : lp.digits)
+    for (int k = d.s0; k < d.s1; k++) {
+      const int g = lp.q_g[k];
+      a.g[k] = (uint8_t)g;
+      a.q[k] = c.q[g];
+      a.src_limb[k] = a.dst_limb[k] = (uint16_t)k;
+      a.kc[k] = inv_const(d.conv.pre[k - d.s0], c.q[g]);
+    }
+  if (int r = launch_ntt(c, a, true)) return r;
+  // 2. every digit's base conversion in one launch, written straight to the
+  //    limb positions of its (nq + alpha)-limb ModUp buffer
+  BconvArgs b;
+  memset(&b, 0, sizeof(b));
+  for (const DigitPlan &d : lp.digits) {
+    if (b.n_jobs == kMaxBconvJobs) {
+      set_error("ModUp: too many digits");
+      return -1;
+    }
+    fill_bconv_job(c, b.jobs[b.n_jobs++], d.conv,
+                   reinterpret_cast<const int32_t *>(y) + (size_t)d.s0 * kN,
+                   mu + (size_t)d.index * lp.ntot * kN, &d.dst_pos);
+  }
+  if (int r = launch_bconv(c, b)) return r;
+  // 3. forward transforms of all converted limbs of all digits, in place
+  memset(&a, 0, sizeof(a));
+  a.dst = mu;
+  a.src = mu;
+  a.table = c.d_tw;
+  a.n_polys = 1;
+  int n = 0;
+  for (const DigitPlan &d : lp.digits)
+    for (size_t m = 0; m < d.dst_pos.size(); m++) {
+      if (n == kMaxJobs) {
+        set_error("ModUp: too many limb transforms");
+        return -1;
+      }
+      const int g = d.conv.dst_g[m];
+      a.g[n] = (uint8_t)g;
+      a.q[n] = c.q[g];
+      a.src_limb[n] = a.dst_limb[n] = (uint16_t)(d.index * lp.ntot + d.dst_pos[m]);
+      n++;
+    }
+  a.n_limbs = n;
+  if (int r = launch_ntt(c, a, false)) return r;
+  if (copy_own)
+    for (const DigitPlan &d : lp.digits)
+      CFHE_CUDA(cudaMemcpyAsync(
+          mu + ((size_t)d.index * lp.ntot + d.s0) * kN, src + (size_t)d.s0 * kN,
+          (size_t)(d.s1 - d.s0) * kN * sizeof(uint32_t),
+          cudaMemcpyDeviceToDevice, c.stream));
+  return 0;
+}
+
+size_t moddown_scratch_words(const ConvPlan &cv, int n_polys) {
+  return (size_t)n_polys * cv.src_g.size() * kN;
+}
+
+int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
+                const uint32_t *src, int n_polys, long long dst_stride,
+                long long src_stride, uint32_t *y) {
+  const int ns = (int)cv.src_g.size(), nd = (int)cv.dst_g.size();
+  if (ns == 0 || nd == 0 || ns > 16 || n_polys > kMaxBconvJobs) {
+    set_error("ModDown: unsupported shape");
+    return -1;
+  }
+  // 1. inverse transform of the limbs that disappear
+  NttArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dst = y;
+  a.src = src;
+  a.table = c.d_itw;
+  a.n_limbs = ns;
+  a.n_polys = n_polys;
+  a.dst_poly_stride = (long long)ns * kN;
+  a.src_poly_stride = src_stride;
+  a.centred = 1;
+  for (int k = 0; k < ns; k++) {
+    const int g = cv.src_g[k];
+    a.g[k] = (uint8_t)g;
+    a.q[k] = c.q[g];
+    a.src_limb[k] = (uint16_t)cv.src_pos[k];
+    a.dst_limb[k] = (uint16_t)k;
+    a.kc[k] = inv_const(cv.pre[k], c.q[g]);
+  }
+  if (int r = launch_ntt(c, a, true)) return r;
+  // 2. base conversion into the destination buffers
+  BconvArgs b;
+  memset(&b, 0, sizeof(b));
+  for (int p = 0; p < n_polys; p++)
+    fill_bconv_job(c, b.jobs[b.n_jobs++], cv,
+                   reinterpret_cast<const int32_t *>(y) + (size_t)p * ns * kN,
+                   dst + p * dst_stride, nullptr);
+  if (int r = launch_bconv(c, b)) return r;
+  // 3. forward transform in place with the fused (pad*x - t) * P^-1 epilogue
+  memset(&a, 0, sizeof(a));
+  a.dst = dst;
+  a.src = dst;
+  a.table = c.d_tw;
+  a.n_limbs = nd;
+  a.n_polys = n_polys;
+  a.dst_poly_stride = a.src_poly_stride = dst_stride;
+  a.ep_mode = cv.has_pad ? 2 : 1;
+  a.ep_src = src;
+  a.ep_poly_stride = src_stride;
+  for (int m = 0; m < nd; m++) {
+    const int g = cv.dst_g[m];
+    const uint32_t q = c.q[g];
+    a.g[m] = (uint8_t)g;
+    a.q[m] = q;
+    a.src_limb[m] = a.dst_limb[m] = (uint16_t)m;
+    a.ep_limb[m] = cv.ep_pos[m] < 0 ? 255 : (uint8_t)cv.ep_pos[m];
+    a.ep_pad[m] = make_tw(cv.ep_pad[m], q);
+    a.ep_scale[m] = make_tw(cv.ep_scale[m], q);
+  }
+  return launch_ntt(c, a, false);
+}
+
+int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+              uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+              const uint32_t *c0, const uint32_t *c1,
+              const uint32_t *const *kb, const uint32_t *const *ka,
+              int key_main) {
+  if ((int)lp.digits.size() > kMaxDigits) {
+    set_error("inner product: too many digits");
+    return -1;
+  }
+  const int key_ter = lp.level == -1 ? lp.num_ter : c.T;
+  if (key_main < lp.num_main || key_main > c.M) {
+    set_error("evaluation key holds fewer main limbs than the level needs");
+    return -1;
+  }
+  InnerArgs a;
+  memset(&a, 0, sizeof(a));
+  a.acc_b = acc_b;
+  a.acc_a = acc_a;
+  a.mu = mu;
+  a.d = d;
+  a.c0 = c0;
+  a.c1 = c1;
+  a.n_digits = (int)lp.digits.size();
+  a.ntot = lp.ntot;
+  a.nq = lp.nq;
+  for (int i = 0; i < a.n_digits; i++) {
+    const int slot = lp.digits[i].index;
+    a.kb[i] = kb[slot];
+    a.ka[i] = ka[slot];
+    a.mu_slot[i] = (uint8_t)slot;
+  }
+  for (int l = 0; l < lp.ntot; l++) {
+    const int g = lp.full_g[l];
+    a.q[l] = c.q[g];
+    a.nqinv[l] = c.nqinv[g];
+    a.kpos[l] = (uint8_t)(g < c.L ? g - (c.T - key_ter)
+                                  : key_ter + key_main + (g - c.L));
+    a.own_digit[l] = l < lp.nq ? (uint8_t)lp.own_digit[l] : 255;
+    a.pm[l] = l < lp.nq ? lp.p_mont[l] : 0;
+  }
+  return launch_inner(c, a);
+}
+
+int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
+               uint32_t *d1, uint32_t *d2, const uint32_t *b1,
+               const uint32_t *a1, const uint32_t *b2, const uint32_t *a2) {
+  TensorArgs t;
+  memset(&t, 0, sizeof(t));
+  t.n_rows = lp.nq;
+  for (int l = 0; l < lp.nq; l++) {
+    const size_t o = (size_t)l * kN;
+    const int g = lp.q_g[l];
+    t.rows[l] = TensorRow{d0 + o, d1 + o, d2 + o, b1 + o, a1 + o,
+                          b2 + o, a2 + o, c.q[g], c.nqinv[g]};
+  }
+  return launch_tensor(c, t);
+}
+
+int run_keyswitch(Context &c, const LevelPlan &lp, int down_type,
+                  uint32_t *out_b, uint32_t *out_a, const uint32_t *d,
+                  const uint32_t *c0, const uint32_t *c1,
+                  const uint32_t *const *kb, const uint32_t *const *ka,
+                  int key_main, uint32_t *scratch) {
+  const ConvPlan &cv = lp.down[down_type];
+  // scratch: y (max of the two inverse-transform outputs) | mu | acc_b | acc_a
+  const size_t y_words =
+      std::max(modup_scratch_words(lp), moddown_scratch_words(cv, 2));
+  uint32_t *y = scratch;
+  uint32_t *mu = y + y_words;
+  uint32_t *acc = mu + (size_t)lp.beta * lp.ntot * kN;
+  const size_t acc_words = (size_t)lp.ntot * kN;
+  if (int r = run_modup(c, lp, mu, d, false, y)) return r;
+  if (int r = run_inner(c, lp, acc, acc + acc_words, mu, d, c0, c1, kb, ka, key_main))
+    return r;
+  if (out_a - out_b == 0) {
+    set_error("key switch: output polynomials alias");
+    return -1;
+  }
+  return run_moddown(c, cv, out_b, acc, 2, (long long)(out_a - out_b),
+                     (long long)acc_words, y);
+}
+
+size_t keyswitch_scratch_words(const LevelPlan &lp, int down_type) {
+  const size_t y_words = std::max(modup_scratch_words(lp),
+                                  moddown_scratch_words(lp.down[down_type], 2));
+  return y_words + (size_t)(lp.beta + 2) * lp.ntot * kN;
+}
+
+}  // namespace cfhe

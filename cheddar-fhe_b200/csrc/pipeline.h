@@ -1,0 +1,35 @@
+// Level-aware pipelines built from the kernels (see pipeline.cu).
+#pragma once
+#include <algorithm>
+
+#include "context.h"
+#include "kernels.h"
+
+namespace cfhe {
+
+size_t modup_scratch_words(const LevelPlan &lp);
+size_t moddown_scratch_words(const ConvPlan &cv, int n_polys);
+size_t keyswitch_scratch_words(const LevelPlan &lp, int down_type);
+
+// mu: beta buffers of ntot limbs (slot = digit number); y: nq limbs scratch
+int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
+              const uint32_t *src, bool copy_own, uint32_t *y);
+int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
+                const uint32_t *src, int n_polys, long long dst_stride,
+                long long src_stride, uint32_t *y);
+int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+              uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+              const uint32_t *c0, const uint32_t *c1,
+              const uint32_t *const *kb, const uint32_t *const *ka,
+              int key_main);
+int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
+               uint32_t *d1, uint32_t *d2, const uint32_t *b1,
+               const uint32_t *a1, const uint32_t *b2, const uint32_t *a2);
+// (out_b, out_a) = Down( sum_i ModUp_i(d) * key_i + P * (c0, c1) )
+int run_keyswitch(Context &c, const LevelPlan &lp, int down_type,
+                  uint32_t *out_b, uint32_t *out_a, const uint32_t *d,
+                  const uint32_t *c0, const uint32_t *c1,
+                  const uint32_t *const *kb, const uint32_t *const *ka,
+                  int key_main, uint32_t *scratch);
+
+}  // namespace cfhe

@@ -54,10 +54,12 @@ CFHE_API int cfhe_context_create(cfhe_context **out, int device, int log_degree,
                         int add_ter);
 CFHE_API void cfhe_context_destroy(cfhe_context *ctx);
 
-/* Use an existing cudaStream_t (NULL restores the context's own stream). The
- * reference runs everything on the legacy default stream
- * (include/core/DeviceVector.h:88). */
+/* Enqueue on the caller's cudaStream_t; the handle is used as given, so NULL
+ * means the legacy default stream, which is what the reference runs on
+ * (include/core/DeviceVector.h:88). A new context starts on a non-blocking
+ * stream of its own; cfhe_use_own_stream() returns to it. */
 CFHE_API int cfhe_set_stream(cfhe_context *ctx, void *cuda_stream);
+CFHE_API int cfhe_use_own_stream(cfhe_context *ctx);
 CFHE_API int cfhe_synchronize(cfhe_context *ctx);
 
 CFHE_API int cfhe_degree(const cfhe_context *ctx);
@@ -95,6 +97,83 @@ CFHE_API int cfhe_intt(cfhe_context *ctx, uint32_t *dst, const uint32_t *src,
               const int *gidx, int n_limbs, int n_polys,
               long long dst_poly_stride, long long src_poly_stride,
               const uint32_t *consts, int mont_keep, int centred);
+
+/* ---- element-wise operators (ElementWiseHandler, src/core/ElementWise.cu).
+ * Operands are limb-major over exactly the limbs listed in gidx. ---- */
+/* op: 0 a+b (:687 Add), 1 a-b (:719 Sub), 2 -a (:751 Neg, b unused),
+ * 3 a*b Montgomery (:779 Mult / :813 PMult). */
+CFHE_API int cfhe_binary(cfhe_context *ctx, int op, uint32_t *dst,
+                         const uint32_t *a, const uint32_t *b, const int *gidx,
+                         int n_limbs);
+/* consts: HOST array, one word per limb. op: 0 a+k (:821 AddConst), 1 a-k
+ * (:852 SubConst), 2 k-a (:883 SubOppositeConst), 3 a*k Montgomery (:914
+ * MultConst), 4 a*k + b (CAccum with one term plus src0, :1356). */
+CFHE_API int cfhe_const_op(cfhe_context *ctx, int op, uint32_t *dst,
+                           const uint32_t *a, const uint32_t *b,
+                           const uint32_t *consts, const int *gidx, int n_limbs);
+/* (d0,d1,d2) = (b1*b2, b1*a2 + a1*b2, a1*a2): ElementWiseHandler::Tensor
+ * (:922, kernel :504-546). */
+CFHE_API int cfhe_tensor(cfhe_context *ctx, uint32_t *d0, uint32_t *d1,
+                         uint32_t *d2, const uint32_t *b1, const uint32_t *a1,
+                         const uint32_t *b2, const uint32_t *a2,
+                         const int *gidx, int n_limbs);
+/* dst = automorphism_galois(src) (+ add when add != NULL):
+ * ElementWiseHandler::Permute / PermuteAccum (:967, :1002; kernels :370-501).
+ * galois = 5^r mod 2N for a rotation by r slots, 2N-1 for conjugation. */
+CFHE_API int cfhe_permute(cfhe_context *ctx, uint32_t *dst, const uint32_t *src,
+                          const uint32_t *add, uint32_t galois,
+                          const int *gidx, int n_limbs);
+CFHE_API uint32_t cfhe_galois_for_rotation(const cfhe_context *ctx, int rot);
+/* dst = src * X^(N/2): ElementWiseHandler::MultImaginaryUnit (:1673). */
+CFHE_API int cfhe_mul_imag_unit(cfhe_context *ctx, uint32_t *dst,
+                                const uint32_t *src, const int *gidx,
+                                int n_limbs);
+
+/* ---- mod-switch (ModSwitchHandler, src/core/ModSwitch.cu) ---- */
+/* Base conversion of centred, pre-scaled coefficients y[n_src][N] (int32) to
+ * M-form coefficients on the destination primes: the kernel
+ * ModSwitchMatrixMult (:23-171) with its table built as in :353-366. */
+CFHE_API int cfhe_bconv(cfhe_context *ctx, uint32_t *dst, const int32_t *y,
+                        const int *src_gidx, int n_src, const int *dst_gidx,
+                        int n_dst);
+CFHE_API int cfhe_beta(const cfhe_context *ctx, int level);
+/* ModSwitchHandler::ModUp (:429-509). dst: beta buffers of (nq+alpha) limbs,
+ * back to back (digit i at dst + i*(nq+alpha)*N); digits holding no limb at
+ * this level are left untouched. */
+CFHE_API int cfhe_modup(cfhe_context *ctx, int level, uint32_t *dst,
+                        const uint32_t *src);
+/* type 0 ModDown (:511-527), 1 Rescale (:529-545), 2 ModDownAndRescale
+ * (:547-563), all through ModDownWorker (:566-684); n_polys polynomials with
+ * the given strides (words) are processed together. */
+CFHE_API int cfhe_moddown(cfhe_context *ctx, int level, int type, uint32_t *dst,
+                          const uint32_t *src, int n_polys,
+                          long long dst_poly_stride, long long src_poly_stride);
+/* Evaluation-key inner product, Context::MultKeyNoModDown(accum, a_modup,
+ * a_orig, key) (src/core/Context.cpp:609-647) -> ElementWiseHandler::PAccum.
+ * modup as produced by cfhe_modup; evk_b/evk_a: HOST arrays of beta device
+ * pointers, each limb-major over (all terminal, key_main main, alpha aux)
+ * limbs. c0/c1 (may be NULL): adds P*c0 to acc_b and P*c1 to acc_a on the Q
+ * limbs, the CAccum step of Context.cpp:688-711. */
+CFHE_API int cfhe_evk_inner(cfhe_context *ctx, int level, uint32_t *acc_b,
+                            uint32_t *acc_a, const uint32_t *modup,
+                            const uint32_t *c0, const uint32_t *c1,
+                            const uint32_t *const *evk_b,
+                            const uint32_t *const *evk_a, int key_main);
+/* Context::MultKey for a ciphertext without rx (Context.cpp:584-607): the
+ * polynomial d is switched, P*bx is added to the b part, both parts go
+ * through ModDown. Used by HRot / HConj before the permutation. */
+CFHE_API int cfhe_keyswitch(cfhe_context *ctx, int level, uint32_t *out_b,
+                            uint32_t *out_a, const uint32_t *d,
+                            const uint32_t *bx, const uint32_t *const *evk_b,
+                            const uint32_t *const *evk_a, int key_main);
+/* Context::HMult (Context.cpp:862-871): tensor product, relinearisation and,
+ * when rescale != 0, ModDownAndRescale to level-1 (RelinearizeRescale,
+ * :714-737); rescale == 0 keeps the level (Relinearize, :561-565). */
+CFHE_API int cfhe_hmult(cfhe_context *ctx, int level, uint32_t *out_b,
+                        uint32_t *out_a, const uint32_t *b1, const uint32_t *a1,
+                        const uint32_t *b2, const uint32_t *a2,
+                        const uint32_t *const *evk_b,
+                        const uint32_t *const *evk_a, int key_main, int rescale);
 
 #ifdef __cplusplus
 }

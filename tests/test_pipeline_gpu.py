@@ -1,0 +1,154 @@
+"""GPU parity of the element-wise operators, base conversion, ModUp, the
+ModDown family, the evaluation-key inner product, key switching and HMult
+against the CPU golden model, through the C ABI. Every word must match."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def rand_limbs(rng, primes, gidx, n):
+    return np.stack([rng.integers(0, int(primes[g]), n, dtype=np.uint64).astype(np.uint32) for g in gidx])
+
+
+def test_elementwise_matches_oracle(engine40, oracle40):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(21)
+    g = e.level_limbs(28, 12)
+    a, b = rand_limbs(rng, o.primes, g, o.n), rand_limbs(rng, o.primes, g, o.n)
+    for l, gi in enumerate(g):  # edge values
+        q = int(o.primes[gi])
+        a[l, :4] = [0, q - 1, q - 1, 1]
+        b[l, :4] = [0, q - 1, 1, q - 1]
+    assert np.array_equal(e.add(a, b, g), o.add(a, b, g))
+    assert np.array_equal(e.sub(a, b, g), o.sub(a, b, g))
+    assert np.array_equal(e.neg(a, g), o.neg(a, g))
+    assert np.array_equal(e.mul(a, b, g), o.mul(a, b, g))
+    k = np.array([rng.integers(0, int(o.primes[gi])) for gi in g], dtype=np.uint32)
+    for op in range(4):
+        assert np.array_equal(e.const_op(a, k, g, op), o.const_op(a, k, g, op)), op
+    assert np.array_equal(e.const_op(a, k, g, 4, b=b), o.add(o.const_op(a, k, g, 3), b, g))
+    assert np.array_equal(e.mul_imag_unit(a, g), o.mul_imag_unit(a, g))
+
+
+def test_tensor_matches_oracle(engine40, oracle40):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(22)
+    g = e.level_limbs(28)
+    ins = [rand_limbs(rng, o.primes, g, o.n) for _ in range(4)]
+    for x in ins:
+        for l, gi in enumerate(g):
+            x[l, 0] = int(o.primes[gi]) - 1
+    for got, exp in zip(e.tensor(*ins, g), o.tensor(*ins, g)):
+        assert np.array_equal(got, exp)
+
+
+def test_permute_matches_oracle(engine40, oracle40):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(23)
+    g = e.level_limbs(16)
+    a, b = rand_limbs(rng, o.primes, g, o.n), rand_limbs(rng, o.primes, g, o.n)
+    for rot in (1, 1234, 32767, -1):
+        gal = o.galois(rot)
+        assert gal == e.galois(rot)
+        assert np.array_equal(e.permute(a, gal, g), o.permute(a, gal))
+    gal = o.galois(5)
+    assert np.array_equal(e.permute(a, gal, g, add=b), o.add(o.permute(a, gal), b, g))
+
+
+def test_bconv_matches_oracle(engine40, oracle40):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(24)
+    full = list(e.level_limbs(28, 12))
+    for src in (full[12:24], full[0:12], full[36:47], full[47:59] + full[45:47], full[0:2], [full[5]]):
+        dst = [x for x in full if x not in src]
+        y = np.stack([rng.integers(-(int(o.primes[g]) // 2), int(o.primes[g]) // 2 + 1, o.n) for g in src]).astype(np.int32)
+        for k, g in enumerate(src):  # extreme centred values
+            h = int(o.primes[g]) // 2
+            y[k, :2] = [h, -h]
+        assert np.array_equal(e.bconv(y, src, dst), o.bconv(y, src, dst)), len(src)
+
+
+@pytest.mark.parametrize("level", [28, 27, 26, 17, 16, 13, 9, 8, 2, 1, 0])
+def test_modup_matches_oracle(engine40, oracle40, level):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(100 + level)
+    g = e.level_limbs(level)
+    src = rand_limbs(rng, o.primes, g, o.n)
+    assert e.beta(level) == o.beta(level)
+    assert np.array_equal(e.modup(level, src), o.modup(level, src))
+
+
+@pytest.mark.parametrize("level", [28, 27, 26, 17, 16, 15, 14, 13, 12, 3, 2, 1])
+def test_moddown_family_matches_oracle(engine40, oracle40, level):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(200 + level)
+    full = e.level_limbs(level, 12)
+    src = np.stack([rand_limbs(rng, o.primes, full, o.n) for _ in range(2)])
+    nq = len(full) - 12
+    got = e.moddown(level, 0, src)
+    for p in range(2):
+        assert np.array_equal(got[p], o.moddown(level, 0, src[p]))
+    got = e.moddown(level, 2, src)
+    for p in range(2):
+        assert np.array_equal(got[p], o.moddown(level, 2, src[p]))
+    q_only = np.ascontiguousarray(src[0, :nq])
+    assert np.array_equal(e.moddown(level, 1, q_only), o.moddown(level, 1, q_only))
+
+
+def fake_key(rng, e, o, key_main, beta):
+    T = len(e.p["terminal_primes"])
+    L = T + len(e.p["main_primes"])
+    g = list(range(0, T + key_main)) + [L + a for a in range(e.alpha)]
+    kb = [rand_limbs(rng, o.primes, g, o.n) for _ in range(beta)]
+    ka = [rand_limbs(rng, o.primes, g, o.n) for _ in range(beta)]
+    return kb, ka
+
+
+@pytest.mark.parametrize("level,key_main", [(28, 43), (16, 43), (16, 23), (5, 43)])
+def test_inner_product_matches_oracle(engine40, oracle40, level, key_main):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(300 + level)
+    full = e.level_limbs(level, 12)
+    beta = e.beta(level)
+    kb, ka = fake_key(rng, e, o, key_main, beta)
+    mu = np.stack([rand_limbs(rng, o.primes, full, o.n) for _ in range(beta)])
+    ab, aa = e.evk_inner(level, mu, kb, ka, key_main)
+    rb, ra = o.evk_inner(level, mu, kb, ka, key_main)
+    assert np.array_equal(ab, rb) and np.array_equal(aa, ra)
+
+
+@pytest.mark.parametrize("level,rescale", [(28, True), (28, False), (16, True), (8, True), (2, True), (1, True)])
+def test_hmult_matches_oracle(engine40, oracle40, level, rescale):
+    """Config 2 path: tensor, ModUp, inner product with the key, P*(d0,d1),
+    ModDown(AndRescale). Random words stand in for ciphertexts and keys:
+    limb-level parity does not depend on them being valid encryptions."""
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(400 + level)
+    g = e.level_limbs(level)
+    ins = [rand_limbs(rng, o.primes, g, o.n) for _ in range(4)]
+    kb, ka = fake_key(rng, e, o, 43, e.beta(28))
+    got = e.hmult(level, *ins, kb, ka, 43, rescale)
+    exp = o.hmult(level, *ins, kb, ka, 43, rescale)
+    assert np.array_equal(got[0], exp[0]) and np.array_equal(got[1], exp[1])
+
+
+def test_keyswitch_matches_oracle(engine40, oracle40):
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(500)
+    level = 20
+    g = e.level_limbs(level)
+    d, bx = rand_limbs(rng, o.primes, g, o.n), rand_limbs(rng, o.primes, g, o.n)
+    kb, ka = fake_key(rng, e, o, 43, e.beta(28))
+    got = e.keyswitch(level, d, bx, kb, ka, 43)
+    exp = o.keyswitch(level, d, bx, kb, ka, 43)
+    assert np.array_equal(got[0], exp[0]) and np.array_equal(got[1], exp[1])
+
+
+def test_errors_are_reported(engine40, pkg):
+    e = engine40
+    a = e.empty(2, e.n)
+    with pytest.raises(pkg.CfheError):
+        e.moddown_(0, 2, a, a)  # level 0 cannot be rescaled
+    with pytest.raises(pkg.CfheError):
+        e.modup_(99, a, a)
