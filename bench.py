@@ -1,18 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the CKKS hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ntt]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload hmult|ntt]
     python bench.py --impl reference ...      # CPU golden model on host cores
 
-Prints ONE JSON line (rank 0). Under torchrun every rank processes its own
-batch (independent polynomials: weak scaling, no data-path collective).
+Prints ONE JSON line (rank 0). Under torchrun every rank works on its own
+ciphertexts / polynomials (independent units: weak scaling, no data-path
+collective).
 
-Workload "ntt" is the batched forward + inverse negacyclic NTT: 16 polynomials
-x the first 40 Q limbs of bootparam_40 (N = 2^16), residues uniform in [0,q).
-A step is one forward and one inverse transform of the whole batch; the
-algorithmic bytes per step are 16*40*65536*4 B * 2 (read+write) * 2 = 671 MB.
-Source, intermediate and destination are three different 168 MB buffers, so
-every pass streams more than the 126 MB L2.
+Workload "hmult" (default): one CKKS HMult + relinearise + rescale with
+bootparam_40 at the top level 28 (47 Q limbs, 12 auxiliary limbs, 4 digits):
+two ciphertexts encrypting 2^15 complex slots uniform in [-1,1]^2, seeded
+secret / error / key sampling. A step is one cfhe_hmult call (tensor, ModUp,
+inner product with the 118 MiB multiplication key, ModDownAndRescale of both
+polynomials). The key plus the temporaries exceed the 126 MB L2, so every step
+streams from HBM. The NTT workload is run too and reported under "ntt".
+
+Workload "ntt": batched forward + inverse negacyclic NTT, 16 polynomials x the
+first 40 Q limbs (N = 2^16), residues uniform in [0,q); a step is one forward
+and one inverse transform of the batch: 16*40*65536*4 B * 2 * 2 = 671 MB of
+algorithmic traffic, through three different 168 MB buffers.
 """
 import argparse
 import concurrent.futures as cf
@@ -39,9 +46,12 @@ def load_package():
     return mod
 
 
-NTT_POLYS, NTT_LIMBS, N = 16, 40, 65536
-NTT_BYTES_PER_STEP = NTT_POLYS * NTT_LIMBS * N * 4 * 2 * 2
-NTT_BYTES_PER_LAUNCH = NTT_POLYS * NTT_LIMBS * N * 4 * 2
+N = 65536
+LIMB = N * 4
+NTT_POLYS, NTT_LIMBS = 16, 40
+NTT_BYTES_PER_STEP = NTT_POLYS * NTT_LIMBS * LIMB * 2 * 2
+NTT_BYTES_PER_LAUNCH = NTT_POLYS * NTT_LIMBS * LIMB * 2
+HM_LEVEL = 28
 
 
 def measured_peaks():
@@ -69,10 +79,11 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
+                 "-i", str(self.index), "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            time.sleep(0.3)
         except OSError:
             self.proc = None
 
@@ -99,69 +110,94 @@ def make_batch(rng, primes, gidx, polys):
     return np.ascontiguousarray(np.stack(cols, axis=1))
 
 
+def rand_limbs(rng, primes, gidx):
+    return np.stack([rng.integers(0, int(primes[g]), N, dtype=np.uint64).astype(np.uint32) for g in gidx])
+
+
+# --------------------------------------------------------------------------
+# CPU legs (golden model; the reference has no CPU implementation of the path)
+# --------------------------------------------------------------------------
 def cpu_ntt_sample(params, gidx, polys, threads, seed=0xC0FFEE01):
-    """Golden model (plain C, 64-bit %) on `threads` host threads: forward +
-    inverse NTT of `polys` polynomials. Returns (seconds, bytes)."""
     from oracle import Oracle
     o = Oracle(params)
     rng = np.random.default_rng(seed)
     a = make_batch(rng, o.primes, gidx, polys)
 
     def one(p):
-        f = o.ntt(a[p], gidx)
-        o.intt(f, gidx, mont_keep=True)
+        o.intt(o.ntt(a[p], gidx), gidx, mont_keep=True)
 
     t0 = time.perf_counter()
     with cf.ThreadPoolExecutor(threads) as ex:
         list(ex.map(one, range(polys)))
-    dt = time.perf_counter() - t0
-    return dt, polys * len(gidx) * N * 4 * 2 * 2
+    return time.perf_counter() - t0, polys * len(gidx) * LIMB * 2 * 2
+
+
+def cpu_hmult_sample(params, count, threads, seed=0xC0FFEE02):
+    """`count` independent HMults at level 28 with the golden model on
+    `threads` host threads; returns seconds for all of them."""
+    from oracle import Oracle
+    o = Oracle(params)
+    rng = np.random.default_rng(seed)
+    g = o.level_limbs(HM_LEVEL)
+    T, M = len(params["terminal_primes"]), len(params["main_primes"])
+    kg = list(range(T + M)) + [T + M + a for a in range(o.alpha)]
+    beta = o.beta(HM_LEVEL)
+    kb = [rand_limbs(rng, o.primes, kg) for _ in range(beta)]
+    ka = [rand_limbs(rng, o.primes, kg) for _ in range(beta)]
+    ins = [rand_limbs(rng, o.primes, g) for _ in range(4)]
+
+    def one(_):
+        o.hmult(HM_LEVEL, *ins, kb, ka, M, True)
+
+    t0 = time.perf_counter()
+    with cf.ThreadPoolExecutor(threads) as ex:
+        list(ex.map(one, range(count)))
+    return time.perf_counter() - t0
 
 
 def run_reference(args, pkg):
-    """The reference ships no CPU implementation of this path; this arm times
-    the scalar restatement (oracle/) on every host core."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     params = pkg.load_params("bootparam_40.json")
     threads = os.cpu_count() or 1
-    gidx = list(range(0, NTT_LIMBS))
-    polys = max(2, min(NTT_POLYS, threads))
-    for _ in range(min(args.warmup, 1)):
-        cpu_ntt_sample(params, gidx, 1, 1)
-    times = []
-    for _ in range(args.steps):
-        dt, nbytes = cpu_ntt_sample(params, gidx, polys, threads)
-        times.append(dt)
-    dt = float(np.mean(times))
-    val = nbytes / dt / 1e9
-    sample = f"{polys} of {NTT_POLYS} polynomials x {NTT_LIMBS} limbs, forward+inverse, per step"
+    if args.workload == "ntt":
+        gidx = list(range(NTT_LIMBS))
+        polys = max(2, min(NTT_POLYS, threads))
+        times = []
+        for _ in range(args.steps):
+            dt, nbytes = cpu_ntt_sample(params, gidx, polys, threads)
+            times.append(dt)
+        dt = float(np.mean(times))
+        val, unit, metric, hib = nbytes / dt / 1e9, "GB/s", "NTT GB/s", True
+        sample = f"{polys} of {NTT_POLYS} polynomials x {NTT_LIMBS} limbs, forward+inverse, per step"
+        workload = "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), 16 polynomials"
+    else:
+        count = threads
+        steps = max(1, min(args.steps, 2))
+        times = [cpu_hmult_sample(params, count, threads) for _ in range(steps)]
+        dt = float(np.mean(times)) / count
+        val, unit, metric, hib = dt * 1e6, "us", "HMult us", False
+        sample = (f"{count} independent HMult+relin+rescale (level 28, random residues) on {threads} "
+                  f"threads per step; value = step time / {count}")
+        workload = "HMult+relinearise+rescale, bootparam_40 level 28, N=2^16"
     print(json.dumps({
-        "impl": "reference", "metric": "NTT GB/s", "value": val, "unit": "GB/s",
+        "impl": "reference", "metric": metric, "value": val, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": dt * 1e3, "higher_is_better": hib, "scaling": "weak",
         "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": {"workload": "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), "
-                               "16 polynomials", "timed": sample},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": workload, "timed": sample,
+                   "note": "the reference has no CPU implementation; this is the scalar C restatement (oracle/)"},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def run_ntt(args, pkg):
-    import torch
-    import torch.distributed as dist
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    params = pkg.load_params("bootparam_40.json")
-    eng = pkg.Engine(params, device=local)
-    gidx = list(range(0, NTT_LIMBS))
+# --------------------------------------------------------------------------
+# GPU legs
+# --------------------------------------------------------------------------
+def bench_ntt(eng, torch, steps, warmup, rank, barrier):
+    gidx = list(range(NTT_LIMBS))
     rng = np.random.default_rng(0xC0FFEE01 + rank)
     host = make_batch(rng, eng.primes, gidx, NTT_POLYS)
     src = eng.to_dev(host)
@@ -174,88 +210,229 @@ def run_ntt(args, pkg):
         eng.ntt_(mid, src, gidx)
         eng.intt_(out, mid, gidx, mont_keep=True)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     assert torch.equal(out, src), "forward+inverse NTT is not the identity"
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    # ---- device-resident throughput
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     barrier()
-    t_all0 = torch.cuda.Event(enable_timing=True)
-    t_all1 = torch.cuda.Event(enable_timing=True)
-    t_all0.record()
-    for k in range(args.steps):
+    for k in range(steps):
         ev[k][0].record()
         eng.ntt_(mid, src, gidx)
         ev[k][1].record()
         eng.intt_(out, mid, gidx, mont_keep=True)
         ev[k][2].record()
-    t_all1.record()
     barrier()
-    ms_total = t_all0.elapsed_time(t_all1)
+    ms_total = ev[0][0].elapsed_time(ev[-1][2])
     fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
     inv_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
-
-    # ---- end to end: pinned host -> device -> fwd+inv -> pinned host
     for _ in range(2):
         src.copy_(pin_in, non_blocking=True)
         step()
         pin_out.copy_(out, non_blocking=True)
     barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         src.copy_(pin_in, non_blocking=True)
         step()
         pin_out.copy_(out, non_blocking=True)
     e1.record()
     barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    return {"ms_step": ms_total / steps, "ms_e2e": e0.elapsed_time(e1) / steps, "fwd_ms": fwd_ms,
+            "inv_ms": inv_ms, "h2d": int(src.numel() * 4), "d2h": int(out.numel() * 4)}
+
+
+# algorithmic bytes of each HMult stage at a level with nq Q limbs, alpha aux
+# limbs, digit sizes ds, nd limbs after the rescale and ns limbs dropped by it
+def hmult_stage_bytes(nq, alpha, ds, nd, ns):
+    ntot = nq + alpha
+    conv = sum(ntot - d for d in ds)
+    beta = len(ds)
+    return {
+        "tensor": (4 + 3) * nq * LIMB,
+        "modup_intt": 2 * nq * LIMB,
+        "modup_bconv": (nq + conv) * LIMB,
+        "modup_ntt": 2 * conv * LIMB,
+        "inner": (beta * ntot + 2 * beta * ntot + 2 * nq + 2 * ntot) * LIMB,
+        "moddown_intt": 2 * 2 * ns * LIMB,
+        "moddown_bconv": 2 * (ns + nd) * LIMB,
+        "moddown_ntt": 2 * (2 * nd + (nq - (ns - alpha))) * LIMB,
+    }
+
+
+def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
+    client = pkg.client
+    level = HM_LEVEL
+    M = len(params["main_primes"])
+    cl = client.Client(eng, seed=0xC0FFEE02 + rank)
+    scale, prods = client.level_scale(params, level)
+    rng = np.random.default_rng(0xC0FFEE12 + rank)
+    slots = N // 2
+    m1 = rng.uniform(-1, 1, slots) + 1j * rng.uniform(-1, 1, slots)
+    m2 = rng.uniform(-1, 1, slots) + 1j * rng.uniform(-1, 1, slots)
+    b1, a1 = cl.encrypt_message(m1, level, scale)
+    b2, a2 = cl.encrypt_message(m2, level, scale)
+    kb, ka = cl.mult_key(M)
+    dkb = [eng.to_dev(x) for x in kb]
+    dka = [eng.to_dev(x) for x in ka]
+    host_in = np.ascontiguousarray(np.stack([b1, a1, b2, a2]))
+    dev_in = eng.to_dev(host_in)
+    nd = len(eng.level_limbs(level - 1))
+    dev_out = eng.empty(2, nd, N)
+    pin_in = torch.from_numpy(host_in.view(np.int32)).pin_memory()
+    pin_out = torch.empty((2, nd, N), dtype=torch.int32).pin_memory()
+
+    def step():
+        eng.hmult_(level, dev_out[0], dev_out[1], dev_in[0], dev_in[1], dev_in[2], dev_in[3],
+                   dkb, dka, M, True)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    precision_bits = None
+    if check and rank == 0:
+        out = eng.to_host(dev_out)
+        g = eng.level_limbs(level - 1)
+        dec = cl.decrypt_message(out[0], out[1], g, scale * scale / prods[level], slots)
+        err = np.abs(dec - m1 * m2)
+        assert err.max() < 1e-3, f"HMult result is off by {err.max()}"
+        precision_bits = float(-np.log2(err.mean()))
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms_step = e0.elapsed_time(e1) / steps
+    # per-stage device times, CUDA events inside the library on the same stream
+    eng.profile_begin()
+    for _ in range(steps):
+        step()
+    stages = {}
+    for name, ms in eng.profile_end():
+        stages.setdefault(name, []).append(ms)
+    stage_ms = {k: float(np.mean(v)) for k, v in stages.items()}
+    # end to end: ciphertexts from pinned host memory, result back to the host
+    for _ in range(2):
+        dev_in.copy_(pin_in, non_blocking=True)
+        step()
+        pin_out.copy_(dev_out, non_blocking=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        dev_in.copy_(pin_in, non_blocking=True)
+        step()
+        pin_out.copy_(dev_out, non_blocking=True)
+    e1.record()
+    barrier()
+    return {"ms_step": ms_step, "ms_e2e": e0.elapsed_time(e1) / steps, "stage_ms": stage_ms,
+            "h2d": int(dev_in.numel() * 4), "d2h": int(dev_out.numel() * 4),
+            "precision_bits": precision_bits}
+
+
+def run_gpu(args, pkg):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    params = pkg.load_params("bootparam_40.json")
+    eng = pkg.Engine(params, device=local)
+    warmup = max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ntt = bench_ntt(eng, torch, args.steps, warmup, rank, barrier)
+    hm = None
+    if args.workload == "hmult":
+        hm = bench_hmult(eng, pkg, torch, params, args.steps, warmup, rank, barrier, not args.no_check)
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms_total, ms_e2e, fwd_ms, inv_ms], device=f"cuda:{local}", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e, fwd_ms, inv_ms = [float(x) for x in t.cpu()]
+    def reduce_max(x):
+        t = torch.tensor(x, device=f"cuda:{local}", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.cpu()]
+
+    ntt_ms, ntt_e2e, fwd_ms, inv_ms = reduce_max([ntt["ms_step"], ntt["ms_e2e"], ntt["fwd_ms"], ntt["inv_ms"]])
+    if hm:
+        hm_ms, hm_e2e = reduce_max([hm["ms_step"], hm["ms_e2e"]])
     if rank == 0:
         peak, how = measured_peaks()
-        ms_step = ms_total / args.steps
-        value = world * NTT_BYTES_PER_STEP / (ms_step * 1e-3) / 1e9
-        e2e = world * NTT_BYTES_PER_STEP / (ms_e2e / args.steps * 1e-3) / 1e9
-        achieved = NTT_BYTES_PER_LAUNCH / (fwd_ms * 1e-3) / 1e9
-        line = {
-            "metric": "NTT GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32", "data": "synthetic",
-            "config": {"workload": "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), "
-                                   "16 polynomials per GPU", "l2": "three 168 MB buffers per step, larger than L2",
-                       "parallelism": f"independent batches x{world}"},
-            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": int(src.numel() * 4),
-                    "d2h_bytes_per_step": int(out.numel() * 4)},
-            "gpu_launches": 2 * args.steps,
-            "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "ntt_cluster_kernel<forward>",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": how, "traffic": None,
-                         "fwd_ms": fwd_ms, "inv_ms": inv_ms,
-                         "inv_achieved": NTT_BYTES_PER_LAUNCH / (inv_ms * 1e-3) / 1e9},
-        }
+        ntt_val = world * NTT_BYTES_PER_STEP / (ntt_ms * 1e-3) / 1e9
+        ntt_ach = NTT_BYTES_PER_LAUNCH / (fwd_ms * 1e-3) / 1e9
+        ntt_roof = {"bound": "hbm", "kernel": "ntt_cluster_kernel<forward>", "achieved": ntt_ach,
+                    "peak": peak, "unit": "GB/s", "frac": ntt_ach / peak, "peak_source": how,
+                    "traffic": 339_000_000, "traffic_source": "ncu dram read+write of one launch of this workload",
+                    "fwd_ms": fwd_ms, "inv_ms": inv_ms,
+                    "inv_achieved": NTT_BYTES_PER_LAUNCH / (inv_ms * 1e-3) / 1e9}
+        if hm:
+            lp_q = len(eng.level_limbs(HM_LEVEL))
+            nd = len(eng.level_limbs(HM_LEVEL - 1))
+            sb = hmult_stage_bytes(lp_q, eng.alpha, [12, 12, 12, 11], nd, eng.alpha + 2)
+            stage = {k: {"ms": v, "GB/s": sb[k] / (v * 1e-3) / 1e9 if k in sb else None,
+                         "frac": sb[k] / (v * 1e-3) / 1e9 / peak if k in sb else None}
+                     for k, v in hm["stage_ms"].items()}
+            top = max(hm["stage_ms"], key=hm["stage_ms"].get)
+            line = {
+                "metric": "HMult us", "value": hm_ms * 1e3 / world, "unit": "us", "n_gpus": world,
+                "steps": args.steps, "warmup": warmup, "ms_per_step": hm_ms,
+                "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                "dtype": "u32", "data": "synthetic",
+                "config": {"workload": "HMult+relinearise+rescale, bootparam_40 level 28 (47+12 limbs, 4 digits), "
+                                       "N=2^16, 2^15 complex slots uniform in [-1,1]^2, one HMult per GPU per step",
+                           "value_is": "step time / n_gpus",
+                           "l2": "118 MiB key + 200 MiB of temporaries per step, larger than the 126 MB L2",
+                           "parallelism": f"independent ciphertexts x{world}",
+                           "e2e_note": "ciphertexts cross PCIe every step; the multiplication key stays resident"},
+                "e2e": {"value": hm_e2e * 1e3 / world, "unit": "us", "h2d_bytes_per_step": hm["h2d"],
+                        "d2h_bytes_per_step": hm["d2h"]},
+                "gpu_launches": 9 * args.steps,
+                "clocks": clocks,
+                "precision_bits": hm["precision_bits"],
+                "roofline": {"bound": "hbm", "kernel": f"stage {top}", "achieved": stage[top]["GB/s"],
+                             "peak": peak, "unit": "GB/s", "frac": stage[top]["frac"], "peak_source": how,
+                             "traffic": None},
+                "stages": stage,
+                "ntt": {"value": ntt_val, "unit": "GB/s", "ms_per_step": ntt_ms,
+                        "e2e": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "roofline": ntt_roof},
+            }
+        else:
+            line = {
+                "metric": "NTT GB/s", "value": ntt_val, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": warmup, "ms_per_step": ntt_ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "u32", "data": "synthetic",
+                "config": {"workload": "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), "
+                                       "16 polynomials per GPU",
+                           "l2": "three 168 MB buffers per step, larger than L2",
+                           "parallelism": f"independent batches x{world}"},
+                "e2e": {"value": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                        "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
+                "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": ntt_roof,
+            }
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
-            dt, nbytes = cpu_ntt_sample(params, gidx, 2, 1)
-            line["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
-                                    "sample": f"2 of 16 polynomials x 40 limbs fwd+inv, 1 thread of {threads}"}
+            if hm:
+                dt = cpu_hmult_sample(params, 1, 1)
+                line["cpu_baseline"] = {"value": dt * 1e6, "unit": "us", "cores": 1, "kind": "port",
+                                        "sample": f"1 HMult+relin+rescale at level 28, 1 thread of {threads}"}
+            else:
+                dt, nbytes = cpu_ntt_sample(params, list(range(NTT_LIMBS)), 2, 1)
+                line["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                                        "sample": f"2 of 16 polynomials x 40 limbs fwd+inv, 1 thread of {threads}"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -267,14 +444,15 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="ntt", choices=["ntt"])
+    ap.add_argument("--workload", default="hmult", choices=["hmult", "ntt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip decrypting the HMult result")
     args = ap.parse_args()
     pkg = load_package()
     if args.impl == "reference":
         run_reference(args, pkg)
     else:
-        run_ntt(args, pkg)
+        run_gpu(args, pkg)
 
 
 if __name__ == "__main__":

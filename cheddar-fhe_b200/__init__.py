@@ -13,6 +13,8 @@ import subprocess
 
 import numpy as np
 
+from . import client  # noqa: F401  (host-side keygen / encrypt / encode)
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libcheddar_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "cheddar_b200.h")
@@ -175,6 +177,16 @@ class Engine:
         d = self.torch.empty_like(s)
         self.intt_(d, s, gidx, consts, mont_keep, centred)
         return self.to_host(d)
+
+    def profile_begin(self):
+        self._check(self.L.cfhe_profile_begin(self.h))
+
+    def profile_end(self, cap=4096):
+        """[(stage, ms)] of every pipeline stage since profile_begin()."""
+        names = C.create_string_buffer(64 * cap)
+        ms = (C.c_float * cap)()
+        n = self._check(self.L.cfhe_profile_end(self.h, names, C.c_size_t(len(names)), ms, cap))
+        return list(zip(names.value.decode().split(";")[:n], [float(ms[i]) for i in range(n)]))
 
     def beta(self, level):
         return self._check(self.L.cfhe_beta(self.h, level))

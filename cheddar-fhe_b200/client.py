@@ -1,9 +1,12 @@
-"""Small Python CKKS client used by the tests (test infrastructure).
+"""Python mirror of the reference's client side: key generation, encryption,
+decryption (reference src/UserInterface.cu:131-190, :223-276, :366-458) and
+CKKS encoding (reference src/core/Encode.cpp:23-275).
 
-It follows the reference's test client (src/UserInterface.cu:131-190 encrypt /
-decrypt, :223-276 secrets, :366-458 switching keys) on top of any engine that
-offers `ntt`, `intt`, `mul`, `add`, `sub` with the golden model's signatures,
-so the same client drives the CPU model and the CUDA library.
+Like the reference's UserInterface it is host code that samples on the CPU and
+calls the engine for the transforms and the element-wise products. It works on
+any engine object that offers `ntt`, `intt`, `mul`, `add`, `sub`, `const_op`,
+`permute`, `level_limbs` on host arrays, i.e. the CUDA `Engine` of this
+package; the tests also drive the CPU golden model with it.
 """
 import numpy as np
 
@@ -61,6 +64,13 @@ class Client:
         m = self.e.add(b, self.e.mul(a, self.secret(g), g), g)
         c = self.e.intt(m, g)  # leaves M-form: plain residues
         return self.crt(c, g)
+
+    def encrypt_message(self, msg, level, scale):
+        """Encode complex slots at `scale`, then encrypt at `level`."""
+        return self.encrypt(encode_coefs(msg, self.n, scale), level)
+
+    def decrypt_message(self, b, a, gidx, scale, num_slots):
+        return decode_coefs(self.decrypt(b, a, gidx), self.n, scale, num_slots)
 
     def crt(self, res, gidx):
         qs = [int(self.e.primes[g]) for g in gidx]
@@ -157,3 +167,117 @@ def toy_params(logn=5):
                 main_primes=main, terminal_primes=ter, auxiliary_primes=aux,
                 level_config=[[0, 2], [3, 0], [1, 4], [4, 2], [7, 0], [7, 2], [7, 4]],
                 additional_base=[0, 0])
+
+
+# ---------------------------------------------------------------------------
+# CKKS encoding (reference src/core/Encode.cpp:85-248), numpy version
+# ---------------------------------------------------------------------------
+def _bitrev_perm(n):
+    bits = n.bit_length() - 1
+    idx = np.arange(n)
+    out = np.zeros(n, dtype=np.int64)
+    for b in range(bits):
+        out |= ((idx >> b) & 1) << (bits - 1 - b)
+    return out
+
+
+def _galois_pows(count, m):
+    g = np.ones(max(count, 1), dtype=np.int64)
+    for i in range(1, count):
+        g[i] = (g[i - 1] * 5) % m
+    return g
+
+
+def special_ifft(vals, degree):
+    """Encode.cpp:85-109."""
+    d = np.array(vals, dtype=np.complex128)
+    n = len(d)
+    m = 2 * degree
+    tw = np.exp(2j * np.pi * np.arange(m) / m)
+    gal = _galois_pows(n // 2 if n > 1 else 1, m)
+    s = n // 2
+    while s >= 1:
+        st8 = s << 3
+        gap = m // st8
+        idx = (st8 - (gal[:s] % st8)) * gap
+        v = d.reshape(-1, 2, s)
+        x = v[:, 0, :] + v[:, 1, :]
+        y = (v[:, 0, :] - v[:, 1, :]) * tw[idx % m]
+        d = np.stack([x, y], axis=1).reshape(-1)
+        s //= 2
+    return d[_bitrev_perm(n)] / n
+
+
+def special_fft(vals, degree):
+    """Encode.cpp:111-133."""
+    d = np.array(vals, dtype=np.complex128)
+    n = len(d)
+    m = 2 * degree
+    tw = np.exp(2j * np.pi * np.arange(m) / m)
+    gal = _galois_pows(n // 2 if n > 1 else 1, m)
+    d = d[_bitrev_perm(n)]
+    s = 1
+    while s < n:
+        st8 = s << 3
+        gap = m // st8
+        idx = (gal[:s] % st8) * gap
+        v = d.reshape(-1, 2, s)
+        y = v[:, 1, :] * tw[idx]
+        d = np.stack([v[:, 0, :] + y, v[:, 0, :] - y], axis=1).reshape(-1)
+        s *= 2
+    return d
+
+
+def encode_coefs(msg, degree, scale):
+    """Complex slots -> integer coefficients (truncated toward zero, as
+    BigInt(double) does, src/core/BigInt_gmp.cpp:22-25). Real parts at
+    i*gap, imaginary parts at i*gap + N/2 (Encode.cpp:169-182)."""
+    n = len(msg)
+    gap = (degree // 2) // n
+    v = special_ifft(msg, degree) * scale
+    coefs = np.zeros(degree, dtype=object)
+    re = [int(x) for x in np.trunc(v.real)]
+    im = [int(x) for x in np.trunc(v.imag)]
+    for i in range(n):
+        coefs[i * gap] = re[i]
+        coefs[i * gap + degree // 2] = im[i]
+    return coefs
+
+
+def decode_coefs(coefs, degree, scale, num_slots):
+    gap = (degree // 2) // num_slots
+    re = np.array([float(coefs[i * gap]) for i in range(num_slots)])
+    im = np.array([float(coefs[i * gap + degree // 2]) for i in range(num_slots)])
+    return special_fft((re + 1j * im) / scale, degree)
+
+
+def level_scale(params, level):
+    """Scale used by the reference's tests at `level` (unittest/Testbed.h:236-243
+    with the schedule of src/core/Parameter.cu:149-193)."""
+    lc = params["level_config"]
+    main, ter = params["main_primes"], params["terminal_primes"]
+    scale = float(2 ** params["log_default_scale"])
+    prods = [None]
+    for i in range(1, len(lc)):
+        (um, ut), (lm, lt) = lc[i], lc[i - 1]
+        num = den = 1.0
+        if ut >= lt:
+            for j in range(ut - lt):
+                num *= ter[lt + j]
+        else:
+            for j in range(lt - ut):
+                den *= ter[ut + j]
+        if um >= lm:
+            for j in range(um - lm):
+                num *= main[lm + j]
+        else:
+            for j in range(lm - um):
+                den *= main[um + j]
+        prods.append(num / den)
+    scales = [scale]
+    for i in range(1, params["default_encryption_level"] + 1):
+        scale = (scale * prods[i]) ** 0.5
+        scales.append(scale)
+    if level <= params["default_encryption_level"]:
+        return scales[level], prods
+    return prods[level], prods

@@ -497,4 +497,37 @@ int cfhe_hmult(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                        key_main, scratch);
 }
 
+// ---------------------------------------------------------------------------
+// stage timing
+// ---------------------------------------------------------------------------
+int cfhe_profile_begin(cfhe_context *h) {
+  if (!h) return fail("null context");
+  h->c.profiling = true;
+  h->c.prof_used = 0;
+  h->c.mark("begin");
+  return 0;
+}
+
+int cfhe_profile_end(cfhe_context *h, char *names, size_t names_cap, float *ms,
+                     int cap) {
+  if (!h) return fail("null context");
+  Context &c = h->c;
+  c.profiling = false;
+  CFHE_CUDA(cudaStreamSynchronize(c.stream));
+  int n = 0;
+  size_t off = 0;
+  if (names && names_cap) names[0] = 0;
+  for (size_t i = 1; i < c.prof_used && n < cap; i++, n++) {
+    CFHE_CUDA(cudaEventElapsedTime(&ms[n], c.prof_events[i - 1], c.prof_events[i]));
+    const size_t len = strlen(c.prof_names[i]);
+    if (names && off + len + 2 <= names_cap) {
+      memcpy(names + off, c.prof_names[i], len);
+      names[off + len] = ';';
+      names[off + len + 1] = 0;
+      off += len + 1;
+    }
+  }
+  return n;
+}
+
 }  // extern "C"

@@ -92,6 +92,13 @@ struct Context {
   uint32_t *ws = nullptr;
   size_t ws_words = 0;
 
+  // optional stage timing: one CUDA event after each pipeline stage
+  mutable bool profiling = false;
+  mutable std::vector<cudaEvent_t> prof_events;
+  mutable std::vector<const char *> prof_names;
+  mutable size_t prof_used = 0;
+  void mark(const char *stage) const;
+
   const LevelPlan *plan(int level) const {
     if (level < -1 || level + 1 >= (int)levels.size()) return nullptr;
     return &levels[level + 1];

@@ -11,6 +11,20 @@ namespace cg = cooperative_groups;
 namespace cfhe {
 namespace {
 
+// Split cluster barrier: every CTA arrives as soon as it starts and waits only
+// right before its first store into a peer's shared memory, which is all the
+// residency guarantee needs; the second phase orders those stores before the
+// peers read them.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 struct RemoteBuf {
   cg::cluster_group cluster;
   uint32_t *local;
@@ -40,13 +54,14 @@ __device__ __forceinline__ void forward_body(const NttArgs &a, int c, int tid,
     }
   }
   fwd_rows_a<FAST>(v, tid, xbuf, tw, q, q2);
-  // Also guarantees every CTA of the cluster is resident before its shared
-  // memory is written remotely.
-  cluster.sync();
-  fwd_rows_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, tw, q, q2);
-  cluster.sync();
-  fwd_cols_a<FAST>(c, tid, rbuf, xbuf, tw, q, q2);
   __syncthreads();
+  cluster_wait_acquire();  // peers are resident (arrival at kernel entry)
+  fwd_rows_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, tw, q, q2);
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  fwd_cols_a<FAST>(c, tid, rbuf, xbuf, tw, q, q2);
+  // a row's 16 columns groups live in one half-warp: warp-level exchange
+  __syncwarp();
   fwd_cols_b<FAST>(v, c, tid, xbuf, tw, q, q2);
   {
     const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
@@ -117,9 +132,11 @@ __device__ __forceinline__ void inverse_body(const NttArgs &a, int c, int tid,
     }
   }
   inv_cols_a<FAST>(v, c, tid, xbuf, itw, q, q2);
-  cluster.sync();
+  __syncwarp();
+  cluster_wait_acquire();  // peers are resident (arrival at kernel entry)
   inv_cols_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, itw, q, q2);
-  cluster.sync();
+  cluster_arrive_release();
+  cluster_wait_acquire();
   inv_rows_a<FAST>(tid, rbuf, xbuf, itw, q, q2);
   __syncthreads();
   inv_rows_b<FAST>(v, tid, xbuf, itw, a.kc[l], a.centred != 0, q, q2);
@@ -138,6 +155,7 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1)
   extern __shared__ __align__(16) uint32_t smem[];
   uint32_t *xbuf = smem;
   uint32_t *rbuf = smem + kBufWords;
+  cluster_arrive_relaxed();
   const int c = blockIdx.x;  // rank inside the cluster (gridDim.x == 8)
   const int tid = threadIdx.x;
   const int t = blockIdx.y;

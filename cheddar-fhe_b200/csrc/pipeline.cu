@@ -64,6 +64,7 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
       a.kc[k] = inv_const(d.conv.pre[k - d.s0], c.q[g]);
     }
   if (int r = launch_ntt(c, a, true)) return r;
+  c.mark("modup_intt");
   // 2. every digit's base conversion in one launch, written straight to the
   //    limb positions of its (nq + alpha)-limb ModUp buffer
   BconvArgs b;
@@ -78,6 +79,7 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
                    mu + (size_t)d.index * lp.ntot * kN, &d.dst_pos);
   }
   if (int r = launch_bconv(c, b)) return r;
+  c.mark("modup_bconv");
   // 3. forward transforms of all converted limbs of all digits, in place
   memset(&a, 0, sizeof(a));
   a.dst = mu;
@@ -99,6 +101,7 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
     }
   a.n_limbs = n;
   if (int r = launch_ntt(c, a, false)) return r;
+  c.mark("modup_ntt");
   if (copy_own)
     for (const DigitPlan &d : lp.digits)
       CFHE_CUDA(cudaMemcpyAsync(
@@ -140,6 +143,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     a.kc[k] = inv_const(cv.pre[k], c.q[g]);
   }
   if (int r = launch_ntt(c, a, true)) return r;
+  c.mark("moddown_intt");
   // 2. base conversion into the destination buffers
   BconvArgs b;
   memset(&b, 0, sizeof(b));
@@ -148,6 +152,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
                    reinterpret_cast<const int32_t *>(y) + (size_t)p * ns * kN,
                    dst + p * dst_stride, nullptr);
   if (int r = launch_bconv(c, b)) return r;
+  c.mark("moddown_bconv");
   // 3. forward transform in place with the fused (pad*x - t) * P^-1 epilogue
   memset(&a, 0, sizeof(a));
   a.dst = dst;
@@ -169,7 +174,9 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     a.ep_pad[m] = make_tw(cv.ep_pad[m], q);
     a.ep_scale[m] = make_tw(cv.ep_scale[m], q);
   }
-  return launch_ntt(c, a, false);
+  if (int r = launch_ntt(c, a, false)) return r;
+  c.mark("moddown_ntt");
+  return 0;
 }
 
 int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
@@ -212,7 +219,9 @@ int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
     a.own_digit[l] = l < lp.nq ? (uint8_t)lp.own_digit[l] : 255;
     a.pm[l] = l < lp.nq ? lp.p_mont[l] : 0;
   }
-  return launch_inner(c, a);
+  if (int r = launch_inner(c, a)) return r;
+  c.mark("inner");
+  return 0;
 }
 
 int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
@@ -227,7 +236,9 @@ int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
     t.rows[l] = TensorRow{d0 + o, d1 + o, d2 + o, b1 + o, a1 + o,
                           b2 + o, a2 + o, c.q[g], c.nqinv[g]};
   }
-  return launch_tensor(c, t);
+  if (int r = launch_tensor(c, t)) return r;
+  c.mark("tensor");
+  return 0;
 }
 
 int run_keyswitch(Context &c, const LevelPlan &lp, int down_type,

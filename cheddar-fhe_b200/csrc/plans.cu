@@ -163,9 +163,23 @@ void free_plans(Context &c) {
       if (cv.d_table) cudaFree(cv.d_table);
   }
   c.levels.clear();
+  for (cudaEvent_t e : c.prof_events) cudaEventDestroy(e);
+  c.prof_events.clear();
   if (c.ws) cudaFree(c.ws);
   c.ws = nullptr;
   c.ws_words = 0;
+}
+
+void Context::mark(const char *stage) const {
+  if (!profiling) return;
+  if (prof_used == prof_events.size()) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    prof_events.push_back(e);
+    prof_names.push_back(stage);
+  }
+  prof_names[prof_used] = stage;
+  cudaEventRecord(prof_events[prof_used++], stream);
 }
 
 int ensure_workspace(Context &c, size_t words) {

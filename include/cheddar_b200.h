@@ -175,6 +175,15 @@ CFHE_API int cfhe_hmult(cfhe_context *ctx, int level, uint32_t *out_b,
                         const uint32_t *const *evk_b,
                         const uint32_t *const *evk_a, int key_main, int rescale);
 
+/* ---- stage timing (no counterpart in the reference, which only prints
+ * wall-clock time per operator, unittest/Testbed.h:24-47). Between begin and
+ * end every pipeline stage records a CUDA event on the context's stream;
+ * end synchronises and returns the stage count, the milliseconds of each
+ * stage in order and their names joined by ';'. ---- */
+CFHE_API int cfhe_profile_begin(cfhe_context *ctx);
+CFHE_API int cfhe_profile_end(cfhe_context *ctx, char *names, size_t names_cap,
+                              float *ms, int cap);
+
 #ifdef __cplusplus
 }
 #endif

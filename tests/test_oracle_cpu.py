@@ -8,7 +8,10 @@ import subprocess
 import numpy as np
 import pytest
 
-from ckks_client import Client, brev, negacyclic_mul, toy_params
+from conftest import load_package
+
+_client = load_package().client
+Client, brev, negacyclic_mul, toy_params = _client.Client, _client.brev, _client.negacyclic_mul, _client.toy_params
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
