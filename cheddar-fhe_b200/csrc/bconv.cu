@@ -81,11 +81,11 @@ void launch_ns(const Context &ctx, const BconvArgs &a, int max_nd) {
 int launch_bconv(const Context &ctx, const BconvArgs &a) {
   if (a.n_jobs <= 0) return 0;
   // One launch per distinct source length; blocks of other jobs exit at once.
-  bool done[17] = {false};
+  bool done[kMaxBconvSrc + 1] = {false};
   for (int i = 0; i < a.n_jobs; i++) {
     const int ns = a.jobs[i].ns;
-    if (ns < 1 || ns > 16) {
-      set_error("bconv: source length must be 1..16");
+    if (ns < 1 || ns > kMaxBconvSrc) {
+      set_error("bconv: source length must be 1..20");
       return -1;
     }
     if (done[ns]) continue;
@@ -100,6 +100,7 @@ int launch_bconv(const Context &ctx, const BconvArgs &a) {
     break;
       CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
       CASE(9) CASE(10) CASE(11) CASE(12) CASE(13) CASE(14) CASE(15) CASE(16)
+      CASE(17) CASE(18) CASE(19) CASE(20)
 #undef CASE
     }
     CFHE_CUDA(cudaGetLastError());

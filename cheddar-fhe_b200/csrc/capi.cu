@@ -10,9 +10,7 @@
 #include "kernels.h"
 #include "pipeline.h"
 
-struct cfhe_context {
-  cfhe::Context c;
-};
+#include "handle.h"
 
 namespace cfhe {
 static thread_local std::string g_error;
@@ -375,7 +373,7 @@ int cfhe_bconv(cfhe_context *h, uint32_t *dst, const int32_t *y,
                const int *src_gidx, int n_src, const int *dst_gidx, int n_dst) {
   if (!h || !dst || !y || !src_gidx || !dst_gidx) return fail("null argument");
   Context &c = h->c;
-  if (n_src < 1 || n_src > 16 || n_dst < 1 || n_dst > kMaxLimbs)
+  if (n_src < 1 || n_src > kMaxBconvSrc || n_dst < 1 || n_dst > kMaxLimbs)
     return fail("bconv: unsupported shape");
   std::vector<int32_t> t((size_t)n_src * n_dst);
   BconvArgs b;

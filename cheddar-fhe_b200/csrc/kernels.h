@@ -67,6 +67,7 @@ struct BconvJob {
   uint32_t q[kMaxLimbs], qinv[kMaxLimbs];
 };
 constexpr int kMaxBconvJobs = 8;
+constexpr int kMaxBconvSrc = 20;  // source limbs of one conversion
 struct BconvArgs {
   int n_jobs;
   BconvJob jobs[kMaxBconvJobs];

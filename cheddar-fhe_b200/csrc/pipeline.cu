@@ -119,7 +119,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
                 const uint32_t *src, int n_polys, long long dst_stride,
                 long long src_stride, uint32_t *y) {
   const int ns = (int)cv.src_g.size(), nd = (int)cv.dst_g.size();
-  if (ns == 0 || nd == 0 || ns > 16 || n_polys > kMaxBconvJobs) {
+  if (ns == 0 || nd == 0 || ns > kMaxBconvSrc || n_polys > kMaxBconvJobs) {
     set_error("ModDown: unsupported shape");
     return -1;
   }

@@ -1,0 +1,190 @@
+// Thin extern "C" driver over the UNMODIFIED reference library, built by
+// oracle/Makefile into oracle/_ref/libcheddar_ref.so from the sources where
+// they lie (test infrastructure; nothing in the product links it).
+//
+// It lets the GPU tests run the reference's own kernels on the same device
+// buffers as this repository's engine and compare the words, and lets the
+// benchmark time the reference's HMult / NTT on the same B200. Only public
+// members of the reference's classes are used (Context::ntt_handler_,
+// mod_switch_handlers_, the containers' bx_/ax_ vectors).
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <vector>
+
+#include "core/Context.h"
+
+using word = uint32_t;
+using namespace cheddar;
+
+struct RefHandle {
+  std::unique_ptr<Parameter<word>> param;
+  std::shared_ptr<Context<word>> ctx;
+};
+
+namespace {
+void d2d(word *dst, const word *src, size_t words) {
+  cudaMemcpyAsync(dst, src, words * sizeof(word), cudaMemcpyDeviceToDevice, cudaStreamLegacy);
+}
+
+void fill_ct(RefHandle *h, Ciphertext<word> &ct, int level, const word *b, const word *a) {
+  NPInfo np = h->param->LevelToNP(level);
+  ct.ModifyNP(np);
+  size_t words = (size_t)np.GetNumTotal() * h->param->degree_;
+  d2d(ct.bx_.data(), b, words);
+  d2d(ct.ax_.data(), a, words);
+  ct.SetScale(1.0);
+}
+
+void fill_key(RefHandle *h, EvaluationKey<word> &key, int key_main, const word *const *kb,
+              const word *const *ka, int beta) {
+  NPInfo np(key_main, h->param->GetMaxNumTer(), h->param->alpha_);
+  key = EvaluationKey<word>(np, beta);
+  size_t words = (size_t)np.GetNumTotal() * h->param->degree_;
+  for (int j = 0; j < beta; j++) {
+    d2d(key.bx_[j].data(), kb[j], words);
+    d2d(key.ax_[j].data(), ka[j], words);
+  }
+}
+}  // namespace
+
+extern "C" {
+
+RefHandle *ref_create(int log_degree, double base_scale, int default_level, const word *main_p,
+                      int n_main, const word *ter_p, int n_ter, const word *aux_p, int n_aux,
+                      const int *level_config, int n_levels) {
+  auto *h = new RefHandle();
+  std::vector<std::pair<int, int>> lc;
+  for (int i = 0; i < n_levels; i++) lc.emplace_back(level_config[2 * i], level_config[2 * i + 1]);
+  h->param = std::make_unique<Parameter<word>>(
+      log_degree, base_scale, default_level, lc, std::vector<word>(main_p, main_p + n_main),
+      std::vector<word>(aux_p, aux_p + n_aux), std::vector<word>(ter_p, ter_p + n_ter));
+  h->ctx = Context<word>::Create(*h->param);
+  cudaDeviceSynchronize();
+  return h;
+}
+
+void ref_destroy(RefHandle *h) {
+  if (!h) return;
+  h->ctx.reset();
+  h->param.reset();
+  delete h;
+}
+
+// NTTHandler::NTT / INTT on a polynomial with (num_main, num_ter, num_aux) limbs
+int ref_ntt(RefHandle *h, word *dst, const word *src, int num_main, int num_ter, int num_aux,
+            int inverse, int mont_conv) {
+  NPInfo np(num_main, num_ter, num_aux);
+  int n = h->param->degree_;
+  int total = np.GetNumTotal() * n, aux = num_aux * n;
+  DvView<word> d(dst, total, aux);
+  DvConstView<word> s(src, total, aux);
+  if (inverse)
+    h->ctx->ntt_handler_.INTT(d, np, s, mont_conv != 0);
+  else
+    h->ctx->ntt_handler_.NTT(d, np, s, mont_conv != 0);
+  return (int)cudaDeviceSynchronize();
+}
+
+// ModSwitchHandler::ModUp: dst = beta buffers of (nq+alpha) limbs back to back
+int ref_modup(RefHandle *h, int level, word *dst, const word *src) {
+  NPInfo np = h->param->LevelToNP(level);
+  int n = h->param->degree_, alpha = h->param->alpha_;
+  int nq = np.GetNumQ();
+  const auto &ms = h->ctx->mod_switch_handlers_.at(level);
+  int beta = (np.num_main_ + h->param->GetMaxNumTer() + alpha - 1) / alpha;
+  std::vector<DvView<word>> views;
+  for (int i = 0; i < beta; i++)
+    views.emplace_back(dst + (size_t)i * (nq + alpha) * n, (nq + alpha) * n, alpha * n);
+  ms.ModUp(views, DvConstView<word>(src, nq * n, 0));
+  return (int)cudaDeviceSynchronize();
+}
+
+// type 0 ModDown, 1 Rescale, 2 ModDownAndRescale
+int ref_moddown(RefHandle *h, int level, int type, word *dst, const word *src) {
+  int n = h->param->degree_, alpha = h->param->alpha_;
+  NPInfo np = h->param->LevelToNP(level);
+  int nq = np.GetNumQ();
+  int nd = type == 0 ? nq : h->param->LevelToNP(level - 1).GetNumQ();
+  const auto &ms = h->ctx->mod_switch_handlers_.at(level);
+  DvView<word> d(dst, nd * n, 0);
+  if (type == 0)
+    ms.ModDown(d, DvConstView<word>(src, (nq + alpha) * n, alpha * n));
+  else if (type == 1)
+    ms.Rescale(d, DvConstView<word>(src, nq * n, 0));
+  else
+    ms.ModDownAndRescale(d, DvConstView<word>(src, (nq + alpha) * n, alpha * n));
+  return (int)cudaDeviceSynchronize();
+}
+
+// Context::HMult; evaluation key digits given as device pointers laid out over
+// (all terminal, key_main main, alpha aux) limbs. iters > 1 repeats the call
+// for timing and returns the mean device time of one call in microseconds
+// through *usec (CUDA events on the legacy stream, 5 warm-up calls first).
+int ref_hmult(RefHandle *h, int level, word *out_b, word *out_a, const word *b1, const word *a1,
+              const word *b2, const word *a2, const word *const *kb, const word *const *ka,
+              int key_main, int beta, int rescale, int iters, float *usec) {
+  Ciphertext<word> x, y, res;
+  fill_ct(h, x, level, b1, a1);
+  fill_ct(h, y, level, b2, a2);
+  EvaluationKey<word> key;
+  fill_key(h, key, key_main, kb, ka, beta);
+  h->ctx->HMult(res, x, y, key, rescale != 0);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  size_t words = (size_t)res.GetNP().GetNumTotal() * h->param->degree_;
+  d2d(out_b, res.bx_.data(), words);
+  d2d(out_a, res.ax_.data(), words);
+  if (iters > 1 && usec) {
+    for (int i = 0; i < 5; i++) h->ctx->HMult(res, x, y, key, rescale != 0);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, cudaStreamLegacy);
+    for (int i = 0; i < iters; i++) h->ctx->HMult(res, x, y, key, rescale != 0);
+    cudaEventRecord(e1, cudaStreamLegacy);
+    cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    *usec = ms * 1000.0f / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
+  return (int)cudaDeviceSynchronize();
+}
+
+// Forward + inverse NTT of `polys` polynomials (as the reference would run
+// config 1: one call per polynomial); mean device time per fwd+inv pass of
+// the whole batch in microseconds.
+int ref_ntt_batch_time(RefHandle *h, word *buf_a, word *buf_b, int polys, int num_main,
+                       int num_ter, int iters, float *usec) {
+  NPInfo np(num_main, num_ter, 0);
+  int n = h->param->degree_;
+  size_t pw = (size_t)np.GetNumTotal() * n;
+  auto pass = [&]() {
+    for (int p = 0; p < polys; p++) {
+      DvView<word> d(buf_b + p * pw, (int)pw, 0);
+      h->ctx->ntt_handler_.NTT(d, np, DvConstView<word>(buf_a + p * pw, (int)pw, 0), false);
+    }
+    for (int p = 0; p < polys; p++) {
+      DvView<word> d(buf_a + p * pw, (int)pw, 0);
+      h->ctx->ntt_handler_.INTT(d, np, DvConstView<word>(buf_b + p * pw, (int)pw, 0), false);
+    }
+  };
+  for (int i = 0; i < 3; i++) pass();
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  cudaEventRecord(e0, cudaStreamLegacy);
+  for (int i = 0; i < iters; i++) pass();
+  cudaEventRecord(e1, cudaStreamLegacy);
+  cudaEventSynchronize(e1);
+  float ms = 0;
+  cudaEventElapsedTime(&ms, e0, e1);
+  *usec = ms * 1000.0f / iters;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return (int)cudaDeviceSynchronize();
+}
+
+}  // extern "C"
