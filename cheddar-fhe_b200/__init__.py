@@ -235,6 +235,10 @@ class Engine:
         self._check(self.L.cfhe_moddown(self.h, level, kind, self._p(dst), self._p(src), polys,
                                         C.c_longlong(ds), C.c_longlong(ss)))
 
+    def moddown_noalloc_(self, level, kind, dst, src):
+        """One polynomial, [limbs, N]; no device allocation on the call path."""
+        self._check(self.L.cfhe_moddown_noalloc(self.h, level, kind, self._p(dst), self._p(src)))
+
     def evk_inner_(self, level, acc_b, acc_a, modup, c0, c1, evk_b, evk_a, key_main):
         self._check(self.L.cfhe_evk_inner(self.h, level, self._p(acc_b), self._p(acc_a), self._p(modup),
                                           self._p(c0) if c0 is not None else None,

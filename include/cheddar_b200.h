@@ -148,6 +148,23 @@ CFHE_API int cfhe_modup(cfhe_context *ctx, int level, uint32_t *dst,
 CFHE_API int cfhe_moddown(cfhe_context *ctx, int level, int type, uint32_t *dst,
                           const uint32_t *src, int n_polys,
                           long long dst_poly_stride, long long src_poly_stride);
+/* Same result as cfhe_moddown() for ONE polynomial, but the call path never
+ * allocates or frees device memory. This entry point has no counterpart in
+ * the reference (whose every ModDown takes temporaries from its memory pool,
+ * src/core/ModSwitch.cu:589-605). It is for hosts that cannot let a library
+ * call cudaMalloc: processes that gave the whole GPU to their own allocator,
+ * and loops that cannot afford the device-wide synchronisation an allocation
+ * implies. The inverse-transform intermediate lives in a 4 MiB array built
+ * into the library (16 limbs; every GPU that loads the library carries it
+ * until exit); a level/type whose conversion drops more than 16 limbs is
+ * refused with an error. The context's device must be current. The first call
+ * on each device also looks up the array's address, so make that first call
+ * before starting any stream capture. All calls on a device share the array:
+ * two calls running on the GPU at the same time corrupt each other, so keep
+ * them ordered (one stream, or events). Nothing needs clearing between calls:
+ * every word read is written earlier in the same call. */
+CFHE_API int cfhe_moddown_noalloc(cfhe_context *ctx, int level, int type,
+                                  uint32_t *dst, const uint32_t *src);
 /* Evaluation-key inner product, Context::MultKeyNoModDown(accum, a_modup,
  * a_orig, key) (src/core/Context.cpp:609-647) -> ElementWiseHandler::PAccum.
  * modup as produced by cfhe_modup; evk_b/evk_a: HOST arrays of beta device
