@@ -1,0 +1,295 @@
+// gtest-free re-hosting of the reference's basic_test bodies
+// (reference unittest/BasicTest.cpp:10-418, fixture unittest/Testbed.h) on the
+// C++ mirror of its API, which reaches the GPU through the C ABI.
+// Pass criterion as in the reference: |d_re| <= 1e-3 and |d_im| <= 1e-3 per
+// slot (Testbed.h:93); the mean |diff| is printed as precision bits.
+//
+//   basic_test <parameter.json> [--levels 0,1,28 | --all-levels] [--only HMult,HRot]
+#include <chrono>
+#include <cstring>
+#include <functional>
+#include <iomanip>
+#include <set>
+
+#include "cheddar/Cheddar.h"
+
+using namespace cheddar;
+using word = uint32_t;
+
+struct Testbed {
+  ParameterJson json;
+  std::unique_ptr<Parameter<word>> param_;
+  ContextPtr<word> context_;
+  std::unique_ptr<UserInterface<word>> interface_;
+  int log_degree_ = 0, default_encryption_level_ = 0;
+  static constexpr double max_error_ = 1e-3;
+  int failures = 0;
+
+  explicit Testbed(const std::string &path) {
+    json = LoadParameterJson(path);
+    log_degree_ = json.log_degree;
+    default_encryption_level_ = json.default_encryption_level;
+    param_ = MakeParameter<word>(json);
+    context_ = Context<word>::Create(*param_);
+    interface_ = std::make_unique<UserInterface<word>>(context_);
+  }
+  double DetermineScale(int level) const {
+    if (level <= default_encryption_level_) return param_->GetScale(level);
+    return param_->GetRescalePrimeProd(level);  // as Testbed.h:236-243
+  }
+  void GenerateRandomMessage(std::vector<Complex> &res, int num_slots = -1) {
+    if (num_slots == -1) num_slots = (1 << log_degree_) / 2;
+    res.assign(num_slots, Complex(0, 0));
+    Random::SampleUniformComplex(res.data(), num_slots, -1.0, 1.0);
+  }
+  void EncodeConstant(Constant<word> &c, double number, int level) const {
+    context_->encoder().EncodeConstant(c, level, DetermineScale(level), number, 0);
+  }
+  void Encode(Plaintext<word> &res, const std::vector<Complex> &msg, int level) const {
+    context_->encoder().Encode(res, level, DetermineScale(level), msg, 0);
+  }
+  void EncodeAndEncrypt(Ciphertext<word> &res, const std::vector<Complex> &msg, int level) const {
+    Plaintext<word> pt;
+    Encode(pt, msg, level);
+    interface_->Encrypt(res, pt);
+  }
+  void Decode(std::vector<Complex> &res, const Plaintext<word> &pt) const {
+    context_->encoder().Decode(res, pt);
+  }
+  void DecryptAndDecode(std::vector<Complex> &res, const Ciphertext<word> &ct) const {
+    Plaintext<word> pt;
+    interface_->Decrypt(pt, ct);
+    context_->encoder().Decode(res, pt);
+  }
+  void CompareMessages(const std::string &what, int level, const std::vector<Complex> &expected,
+                       const std::vector<Complex> &obtained) {
+    bool equal = expected.size() == obtained.size();
+    double sum = 0, worst = 0;
+    for (size_t i = 0; equal && i < expected.size(); i++) {
+      Complex d = expected[i] - obtained[i];
+      if (std::abs(d.real()) > max_error_ || std::abs(d.imag()) > max_error_) equal = false;
+      sum += std::abs(d);
+      worst = std::max(worst, std::abs(d));
+    }
+    const double mean = sum / expected.size();
+    std::cout << (equal ? "[ OK ] " : "[FAIL] ") << what << " level " << level << "  max|diff| "
+              << std::scientific << std::setprecision(3) << worst << "  precision "
+              << std::fixed << std::setprecision(2) << -std::log2(mean) << " bits" << std::endl;
+    if (!equal) failures++;
+  }
+};
+
+using Msg = std::vector<Complex>;
+using Ct = Ciphertext<word>;
+using Pt = Plaintext<word>;
+
+int main(int argc, char **argv) {
+  if (argc < 2) {
+    std::cerr << "usage: basic_test <parameter.json> [--levels a,b | --all-levels] [--only T1,T2]\n";
+    return 2;
+  }
+  std::vector<int> levels;
+  std::set<std::string> only;
+  bool all_levels = false;
+  for (int i = 2; i < argc; i++) {
+    if (!strcmp(argv[i], "--all-levels")) all_levels = true;
+    if (!strcmp(argv[i], "--levels") && i + 1 < argc) {
+      std::stringstream ss(argv[++i]);
+      std::string t;
+      while (std::getline(ss, t, ',')) levels.push_back(std::stoi(t));
+    }
+    if (!strcmp(argv[i], "--only") && i + 1 < argc) {
+      std::stringstream ss(argv[++i]);
+      std::string t;
+      while (std::getline(ss, t, ',')) only.insert(t);
+    }
+  }
+  Random::Seed(0xC0FFEE03);
+  Testbed tb(argv[1]);
+  const int max_level = tb.param_->max_level_;
+  if (all_levels || levels.empty()) {
+    levels.clear();
+    if (all_levels)
+      for (int l = 0; l <= max_level; l++) levels.push_back(l);
+    else
+      levels = {0, 1, 2, 3, tb.default_encryption_level_, tb.default_encryption_level_ + 1, max_level - 1, max_level};
+  }
+  auto &ctx = *tb.context_;
+  auto run = [&](const std::string &name, int min_level, const std::function<void(int)> &body) {
+    if (!only.empty() && !only.count(name)) return;
+    for (int level : levels)
+      if (level >= min_level && level <= max_level) body(level);
+  };
+  auto binary_msg = [](const Msg &a, const Msg &b, const std::function<Complex(Complex, Complex)> &f) {
+    Msg r;
+    for (size_t i = 0; i < a.size(); i++) r.push_back(f(a[i], b[i]));
+    return r;
+  };
+
+  run("EncodeDecode", 0, [&](int level) {
+    Msg m, res;
+    tb.GenerateRandomMessage(m);
+    Pt pt;
+    tb.Encode(pt, m, level);
+    tb.Decode(res, pt);
+    tb.CompareMessages("EncodeDecode", level, m, res);
+  });
+  run("EncodeEncryptDecryptDecode", 0, [&](int level) {
+    Msg m, res;
+    tb.GenerateRandomMessage(m);
+    Ct ct;
+    tb.EncodeAndEncrypt(ct, m, level);
+    tb.DecryptAndDecode(res, ct);
+    tb.CompareMessages("EncodeEncryptDecryptDecode", level, m, res);
+  });
+  struct CtCt { const char *name; int op; };
+  for (CtCt t : {CtCt{"CtAddCt", 0}, CtCt{"CtSubCt", 1}})
+    run(t.name, 0, [&](int level) {
+      Msg m1, m2, res;
+      tb.GenerateRandomMessage(m1);
+      tb.GenerateRandomMessage(m2);
+      Ct c1, c2, r;
+      tb.EncodeAndEncrypt(c1, m1, level);
+      tb.EncodeAndEncrypt(c2, m2, level);
+      if (t.op == 0) ctx.Add(r, c1, c2); else ctx.Sub(r, c1, c2);
+      tb.DecryptAndDecode(res, r);
+      tb.CompareMessages(t.name, level,
+                         binary_msg(m1, m2, [&](Complex a, Complex b) { return t.op ? a - b : a + b; }), res);
+    });
+  for (CtCt t : {CtCt{"CtAddPt", 0}, CtCt{"CtSubPt", 1}})
+    run(t.name, 0, [&](int level) {
+      Msg m1, m2, res;
+      tb.GenerateRandomMessage(m1);
+      tb.GenerateRandomMessage(m2);
+      Ct c1, r;
+      Pt p2;
+      tb.EncodeAndEncrypt(c1, m1, level);
+      tb.Encode(p2, m2, level);
+      if (t.op == 0) ctx.Add(r, c1, p2); else ctx.Sub(r, c1, p2);
+      tb.DecryptAndDecode(res, r);
+      tb.CompareMessages(t.name, level,
+                         binary_msg(m1, m2, [&](Complex a, Complex b) { return t.op ? a - b : a + b; }), res);
+    });
+  for (CtCt t : {CtCt{"CtAddConst", 0}, CtCt{"CtSubConst", 1}})
+    run(t.name, 0, [&](int level) {
+      Msg m1, m2, res;
+      tb.GenerateRandomMessage(m1);
+      tb.GenerateRandomMessage(m2);
+      const double k = m2[0].real();
+      Ct c1, r;
+      Constant<word> c2;
+      tb.EncodeAndEncrypt(c1, m1, level);
+      tb.EncodeConstant(c2, k, level);
+      if (t.op == 0) ctx.Add(r, c1, c2); else ctx.Sub(r, c1, c2);
+      tb.DecryptAndDecode(res, r);
+      Msg want;
+      for (auto &x : m1) want.push_back(t.op ? x - k : x + k);
+      tb.CompareMessages(t.name, level, want, res);
+    });
+  run("NegCt", 0, [&](int level) {
+    Msg m, res, want;
+    tb.GenerateRandomMessage(m);
+    for (auto &x : m) want.push_back(-x);
+    Ct c, r;
+    tb.EncodeAndEncrypt(c, m, level);
+    ctx.Neg(r, c);
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("NegCt", level, want, res);
+  });
+  run("CtMultPt", 1, [&](int level) {
+    Msg m1, m2, res;
+    tb.GenerateRandomMessage(m1);
+    tb.GenerateRandomMessage(m2);
+    Ct c1, r;
+    Pt p2;
+    tb.EncodeAndEncrypt(c1, m1, level);
+    tb.Encode(p2, m2, level);
+    ctx.Mult(r, c1, p2);
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("CtMultPt", level, binary_msg(m1, m2, [](Complex a, Complex b) { return a * b; }), res);
+  });
+  run("CtMultConst", 1, [&](int level) {
+    Msg m1, m2, res, want;
+    tb.GenerateRandomMessage(m1);
+    tb.GenerateRandomMessage(m2);
+    const double k = m2[0].real();
+    for (auto &x : m1) want.push_back(x * k);
+    Ct c1, r;
+    Constant<word> c2;
+    tb.EncodeAndEncrypt(c1, m1, level);
+    tb.EncodeConstant(c2, k, level);
+    ctx.Mult(r, c1, c2);
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("CtMultConst", level, want, res);
+  });
+  run("CtMultImaginaryUnit", 0, [&](int level) {
+    Msg m, res, want;
+    tb.GenerateRandomMessage(m);
+    for (auto &x : m) want.push_back(Complex(-x.imag(), x.real()));
+    Ct c, r;
+    tb.EncodeAndEncrypt(c, m, level);
+    ctx.MultImaginaryUnit(r, c);
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("CtMultImaginaryUnit", level, want, res);
+  });
+  run("HMult", 1, [&](int level) {
+    Msg m1, m2, res;
+    tb.GenerateRandomMessage(m1);
+    tb.GenerateRandomMessage(m2);
+    Msg want = binary_msg(m1, m2, [](Complex a, Complex b) { return a * b; });
+    Ct c1, c2, r, tmp;
+    tb.EncodeAndEncrypt(c1, m1, level);
+    tb.EncodeAndEncrypt(c2, m2, level);
+    const auto &key = tb.interface_->GetMultiplicationKey();
+    ctx.Synchronize();
+    auto t0 = std::chrono::high_resolution_clock::now();
+    ctx.HMult(r, c1, c2, key, true);
+    ctx.Synchronize();
+    auto t1 = std::chrono::high_resolution_clock::now();
+    std::cout << "       wall clock (+ sync): "
+              << std::chrono::duration_cast<std::chrono::microseconds>(t1 - t0).count() << " us\n";
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("HMult(tensor + merged relin-rescale)", level, want, res);
+    ctx.HMult(tmp, c1, c2, key, false);
+    tb.DecryptAndDecode(res, tmp);
+    tb.CompareMessages("HMult(tensor + relinearize)", level, want, res);
+    ctx.Rescale(r, tmp);
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("Rescale", level, want, res);
+    // the two-step form of the reference: Mult then RelinearizeRescale
+    Ct t3, r3;
+    ctx.Mult(t3, c1, c2);
+    ctx.RelinearizeRescale(r3, t3, key);
+    tb.DecryptAndDecode(res, r3);
+    tb.CompareMessages("Mult + RelinearizeRescale", level, want, res);
+  });
+  if (only.empty() || only.count("HRot")) {
+    const int rot = 1234, num_slots = (1 << tb.log_degree_) / 2;
+    tb.interface_->PrepareRotationKey(rot, max_level);
+    run("HRot", 0, [&](int level) {
+      Msg m, res, want;
+      tb.GenerateRandomMessage(m);
+      for (int i = 0; i < (int)m.size(); i++) want.push_back(m[(i + rot) % num_slots]);
+      Ct c, r;
+      tb.EncodeAndEncrypt(c, m, level);
+      ctx.HRot(r, c, tb.interface_->GetRotationKey(rot), rot);
+      tb.DecryptAndDecode(res, r);
+      tb.CompareMessages("HRot", level, want, res);
+    });
+  }
+  run("HConj", 0, [&](int level) {
+    Msg m, res, want;
+    tb.GenerateRandomMessage(m);
+    for (auto &x : m) want.push_back(std::conj(x));
+    Ct c, r;
+    tb.EncodeAndEncrypt(c, m, level);
+    ctx.HConj(r, c, tb.interface_->GetConjugationKey());
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("HConj", level, want, res);
+  });
+  std::cout << (tb.failures ? "FAILED " : "PASSED ") << "(" << tb.failures << " failures)" << std::endl;
+  tb.interface_.reset();
+  std::cout << "Context use count (should be 1 to prevent memory leak): " << tb.context_.use_count()
+            << std::endl;
+  return tb.failures ? 1 : 0;
+}

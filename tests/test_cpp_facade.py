@@ -1,0 +1,46 @@
+"""The C++ mirror of the reference's operator API: it must compile against the
+C ABI header on any machine (CPU test), and the reference's basic_test bodies,
+re-hosted on it, must pass on the GPU with the reference's 1e-3 criterion."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CPP = os.path.join(ROOT, "tests", "cpp")
+
+
+def build_driver(pkg):
+    if not os.path.exists(pkg.LIB_PATH):
+        pkg.build()
+    subprocess.check_call(["make", "-s", "-C", CPP, "basic_test"])
+    return os.path.join(CPP, "basic_test")
+
+
+def test_facade_compiles_and_links(pkg):
+    exe = build_driver(pkg)
+    assert os.path.exists(exe)
+    # usage error path runs without a GPU
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage" in r.stderr
+
+
+@pytest.mark.gpu
+def test_basic_test_bodies_bootparam_40(pkg):
+    exe = build_driver(pkg)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json")],
+                       capture_output=True, text=True, timeout=1500)
+    print(r.stdout[-6000:])
+    print(r.stderr[-2000:])
+    assert r.returncode == 0, "basic_test reported failures"
+    assert "PASSED" in r.stdout and "[FAIL]" not in r.stdout
+
+
+@pytest.mark.gpu
+def test_wrong_usage_exits_like_the_reference(pkg):
+    """A scale mismatch prints an error and exits non-zero (the reference's
+    AssertTrue -> exit(EXIT_FAILURE), include/common/Assert.h:9-21)."""
+    exe = build_driver(pkg)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "does_not_exist.json")],
+                       capture_output=True, text=True)
+    assert r.returncode != 0 and "ERROR" in r.stderr
