@@ -332,6 +332,45 @@ def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
             "precision_bits": precision_bits}
 
 
+def bench_reference_cuda(eng, torch, params, steps):
+    """The reference's own CUDA library (oracle/_ref, built unmodified from
+    the reference tree) on the same GPU: HMult at level 28 on random residues
+    and the config-1 NTT batch, timed with CUDA events inside its driver.
+    Reported beside the engine's numbers; absent when the library was not
+    built."""
+    try:
+        from oracle import ref_binding
+    except Exception:
+        return None
+    if not ref_binding.available():
+        return None
+    ref = ref_binding.Reference(params)
+    rng = np.random.default_rng(0xC0FFEE22)
+    g = eng.level_limbs(HM_LEVEL)
+    M, T = len(params["main_primes"]), len(params["terminal_primes"])
+    kg = list(range(T + M)) + [T + M + a for a in range(eng.alpha)]
+    beta = eng.beta(HM_LEVEL)
+    ins = [eng.to_dev(rand_limbs(rng, eng.primes, g)) for _ in range(4)]
+    kb = [eng.to_dev(rand_limbs(rng, eng.primes, kg)) for _ in range(beta)]
+    ka = [eng.to_dev(rand_limbs(rng, eng.primes, kg)) for _ in range(beta)]
+    nd = len(eng.level_limbs(HM_LEVEL - 1))
+    ob, oa = eng.empty(nd, N), eng.empty(nd, N)
+    torch.cuda.synchronize()
+    hm_us = ref.hmult(HM_LEVEL, ob, oa, *ins, kb, ka, M, True, iters=max(steps, 2))
+    mine_b, mine_a = eng.empty(nd, N), eng.empty(nd, N)
+    eng.hmult_(HM_LEVEL, mine_b, mine_a, *ins, kb, ka, M, True)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(mine_b, ob) and torch.equal(mine_a, oa))
+    a = eng.to_dev(make_batch(rng, eng.primes, list(range(NTT_LIMBS)), NTT_POLYS))
+    b = torch.empty_like(a)
+    torch.cuda.synchronize()
+    ntt_us = ref.ntt_batch_time(a, b, NTT_POLYS, NTT_LIMBS - T, T, max(steps, 2))
+    ref.close()
+    return {"hmult_us": hm_us, "hmult_words_equal_engine": same,
+            "ntt_fwd_inv_us": ntt_us, "ntt_GBps": NTT_BYTES_PER_STEP / (ntt_us * 1e-6) / 1e9,
+            "how": "unmodified reference sources compiled for sm_100a, legacy stream, CUDA events"}
+
+
 def run_gpu(args, pkg):
     import torch
     import torch.distributed as dist
@@ -359,6 +398,9 @@ def run_gpu(args, pkg):
     if args.workload == "hmult":
         hm = bench_hmult(eng, pkg, torch, params, args.steps, warmup, rank, barrier, not args.no_check)
     clocks = sampler.stop() if rank == 0 else None
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_ref:
+        ref_cuda = bench_reference_cuda(eng, torch, params, args.steps)
 
     def reduce_max(x):
         t = torch.tensor(x, device=f"cuda:{local}", dtype=torch.float64)
@@ -423,6 +465,8 @@ def run_gpu(args, pkg):
                         "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
                 "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": ntt_roof,
             }
+        if ref_cuda:
+            line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             if hm:
@@ -447,6 +491,7 @@ def main():
     ap.add_argument("--workload", default="hmult", choices=["hmult", "ntt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip decrypting the HMult result")
+    ap.add_argument("--no-ref", action="store_true", help="skip timing the reference's CUDA library")
     args = ap.parse_args()
     pkg = load_package()
     if args.impl == "reference":

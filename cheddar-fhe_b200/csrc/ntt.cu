@@ -59,10 +59,10 @@ __device__ __forceinline__ void forward_body(const NttArgs &a, int c, int tid,
   fwd_rows_b<FAST>(c, tid, xbuf, RemoteBuf{cluster, rbuf}, tw, q, q2);
   cluster_arrive_release();
   cluster_wait_acquire();
-  fwd_cols_a<FAST>(c, tid, rbuf, xbuf, tw, q, q2);
-  // a row's 16 columns groups live in one half-warp: warp-level exchange
+  fwd_cols_a<FAST>(c, tid, rbuf, rbuf, tw, q, q2);
+  // a row's 16 column groups live in one half-warp: in-place, warp-level exchange
   __syncwarp();
-  fwd_cols_b<FAST>(v, c, tid, xbuf, tw, q, q2);
+  fwd_cols_b<FAST>(v, c, tid, rbuf, tw, q, q2);
   {
     const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
     const int off = R * kRowWords + 16 * g;
@@ -150,11 +150,13 @@ __device__ __forceinline__ void inverse_body(const NttArgs &a, int c, int tid,
 
 template <bool INV>
 __global__ void __cluster_dims__(kClusterSize, 1, 1)
-    __launch_bounds__(kNttThreads, 2)
+    __launch_bounds__(kNttThreads, 3)
         ntt_cluster_kernel(const __grid_constant__ NttArgs a) {
   extern __shared__ __align__(16) uint32_t smem[];
+  // forward: xbuf strip layout, rbuf in-row layout; inverse: xbuf holds the
+  // in-row layout first and the strip layout later, rbuf the strip layout
   uint32_t *xbuf = smem;
-  uint32_t *rbuf = smem + kBufWords;
+  uint32_t *rbuf = smem + (INV ? kRowBufWords : kStripBufWords);
   cluster_arrive_relaxed();
   const int c = blockIdx.x;  // rank inside the cluster (gridDim.x == 8)
   const int tid = threadIdx.x;

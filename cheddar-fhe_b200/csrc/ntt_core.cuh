@@ -50,8 +50,11 @@ constexpr int kOwnRows = 32;    // rows per CTA in the in-row phases
 // the strided (x0 + 16k) and the contiguous (16g + k) access patterns of a
 // warp touch 32 distinct banks.
 constexpr int kRowStride = 336;
-constexpr int kBufWords = kOwnRows * kRowStride;  // 10752 words = 43008 B
-constexpr int kNttSmemBytes = 2 * kBufWords * 4;
+constexpr int kRowBufWords = kOwnRows * kRowStride;    // in-row layout: 43008 B
+constexpr int kStripBufWords = kRowWords * kStripCols;  // strip layout: 32768 B
+// One strip-layout and one in-row-layout buffer per CTA (75 776 B), so three
+// CTAs fit in the 228 KB of one SM.
+constexpr int kNttSmemBytes = (kRowBufWords + kStripBufWords) * 4;
 
 CFHE_HD uint32_t umulhi32(uint32_t a, uint32_t b) {
 #if defined(__CUDA_ARCH__)
@@ -239,7 +242,8 @@ CFHE_HD void fwd_rows_b(int c, int tid, const uint32_t *xbuf, Remote remote,
   for (int k = 0; k < 16; k++) dst[base + k * kRowStride] = v[k];
 }
 
-// Stages 9-12 inside rows.
+// Stages 9-12 inside rows. rbuf and xbuf may be the same buffer: a row is
+// read and written by one half-warp only.
 template <bool FAST>
 CFHE_HD void fwd_cols_a(int c, int tid, const uint32_t *rbuf, uint32_t *xbuf,
                         const Tw *tw, uint32_t q, uint32_t q2) {

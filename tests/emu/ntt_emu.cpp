@@ -17,10 +17,10 @@ using namespace cfhe;
 namespace {
 struct Cluster {
   std::vector<uint32_t> xbuf[kClusterSize], rbuf[kClusterSize];
-  Cluster() {
+  explicit Cluster(bool inverse) {
     for (int c = 0; c < kClusterSize; c++) {
-      xbuf[c].assign(kBufWords, 0xdeadbeefu);
-      rbuf[c].assign(kBufWords, 0xdeadbeefu);
+      xbuf[c].assign(inverse ? kRowBufWords : kStripBufWords, 0xdeadbeefu);
+      rbuf[c].assign(inverse ? kStripBufWords : kRowBufWords, 0xdeadbeefu);
     }
   }
 };
@@ -28,7 +28,7 @@ struct Cluster {
 template <bool FAST>
 void fwd(const Tw *tw, uint32_t q, const uint32_t *src, uint32_t *dst,
          int premul, Tw kc) {
-  Cluster cl;
+  Cluster cl(false);
   const uint32_t q2 = 2 * q;
   auto remote = [&](int rank) { return cl.rbuf[rank].data(); };
   for (int c = 0; c < kClusterSize; c++)
@@ -46,11 +46,11 @@ void fwd(const Tw *tw, uint32_t q, const uint32_t *src, uint32_t *dst,
       fwd_rows_b<FAST>(c, tid, cl.xbuf[c].data(), remote, tw, q, q2);
   for (int c = 0; c < kClusterSize; c++)
     for (int tid = 0; tid < kNttThreads; tid++)
-      fwd_cols_a<FAST>(c, tid, cl.rbuf[c].data(), cl.xbuf[c].data(), tw, q, q2);
+      fwd_cols_a<FAST>(c, tid, cl.rbuf[c].data(), cl.rbuf[c].data(), tw, q, q2);
   for (int c = 0; c < kClusterSize; c++)
     for (int tid = 0; tid < kNttThreads; tid++) {
       uint32_t v[16];
-      fwd_cols_b<FAST>(v, c, tid, cl.xbuf[c].data(), tw, q, q2);
+      fwd_cols_b<FAST>(v, c, tid, cl.rbuf[c].data(), tw, q, q2);
       const int rho = tid >> 4, g = tid & 15, R = kOwnRows * c + rho;
       for (int k = 0; k < 16; k++) dst[R * kRowWords + 16 * g + k] = v[k];
     }
@@ -59,7 +59,7 @@ void fwd(const Tw *tw, uint32_t q, const uint32_t *src, uint32_t *dst,
 template <bool FAST>
 void inv(const Tw *itw, uint32_t q, const uint32_t *src, uint32_t *dst, Tw kc,
          int centred) {
-  Cluster cl;
+  Cluster cl(true);
   const uint32_t q2 = 2 * q;
   auto remote = [&](int rank) { return cl.rbuf[rank].data(); };
   for (int c = 0; c < kClusterSize; c++)
