@@ -1,0 +1,319 @@
+// Base conversion on the 5th-generation tensor cores (tcgen05, kind::i8),
+// exact, for sm_100a.
+//
+// The conversion  out[m][c] = ( sum_k y_c[k][c] * T[m][k] ) * 2^-32 mod p_m
+// (reference src/core/ModSwitch.cu:23-171) is a dense contraction over the
+// source limbs k. It is evaluated as one unsigned 8-bit GEMM per tile of 128
+// coefficients:
+//
+//   D[c][4m+j] = sum_{k,i} byte_i(y[k][c]) * byte_j( T[m][k] * 2^(8i) mod p_m )
+//
+//   A (128 x K, K = 4*(ns+1) bytes): the canonical residues y[k][c] in [0,s_k)
+//      exactly as they sit in memory (little-endian words are their own byte
+//      planes), plus one pseudo source "number of residues above s_k/2";
+//   B (N x K, N = 4*nd): byte planes of the table entries pre-multiplied by
+//      2^(8i), and for the pseudo source the byte planes of -(prod s)*2^64
+//      mod p_m, which turns the canonical residues back into the centred
+//      ones the reference convention prescribes;
+//   D (int32, in tensor memory): every sum has at most 84 terms of at most
+//      255*255, so it is exact.
+//
+// The epilogue reads a thread's row of D from tensor memory, recombines the
+// four planes V = D0 + D1*2^8 + D2*2^16 + D3*2^24 (V < 2^47, congruent to the
+// centred sum mod p_m) and applies one Montgomery reduction, which returns the
+// same canonical word as the reference's signed reduction of the centred sum.
+//
+// Waits on the MMA completion barrier are bounded; on a timeout the kernel
+// raises a flag in global memory, frees its tensor memory and returns.
+#include <string.h>
+
+#include "context.h"
+#include "host_math.h"
+#include "kernels.h"
+#include "modmath.cuh"
+
+namespace cfhe {
+namespace {
+
+constexpr int kTcThreads = 128;  // one thread per coefficient of the tile
+constexpr int kTcTile = 128;
+constexpr int kTcMaxK = 96;      // bytes of K per tile row: 4 * (20 + 1) padded to 32
+constexpr int kTcSliceN = 64;    // accumulator columns per CTA: 16 destination limbs
+constexpr int kTmemCols = 64;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// K-major, no swizzle: 8-row x 16-byte core matrices; lbo = bytes between the
+// two 16-byte K chunks of one MMA, sbo = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  return d;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kTcThreads)
+    bconv_tc_kernel(const __grid_constant__ BconvTcArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const BconvTcJob &j = a.jobs[a.unit_job[blockIdx.y]];
+  const int slice = a.unit_slice[blockIdx.y];           // 16 destination limbs each
+  uint8_t *sB = smem;                                   // [K/16][8][8][16]
+  uint8_t *sA = smem + kTcMaxK * kTcSliceN;             // [K/16][16][8][16]
+  uint64_t *bar = reinterpret_cast<uint64_t *>(sA + kTcMaxK * kTcTile);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+  // per destination limb of the slice: {q, -q^-1, word offset of the limb, in range}
+  uint4 *s_lim = reinterpret_cast<uint4 *>(sA + kTcMaxK * kTcTile + 64);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int kbytes = j.kpad;
+  constexpr int npad = kTcSliceN;
+  const int m_first = slice * (kTcSliceN / 4);
+  const int m_count = min(j.nd - m_first, kTcSliceN / 4);
+
+  // this slice of the conversion table -> shared memory (operand layout kept)
+  {
+    const uint32_t src_lbo = (uint32_t)(j.npad / 8) * 128;
+    for (int i = tid; i < kbytes / 16 * (kTcSliceN / 8) * 8; i += kTcThreads) {
+      const int t = i / (kTcSliceN / 8 * 8), r = i % (kTcSliceN / 8 * 8);
+      reinterpret_cast<uint4 *>(sB)[i] = *reinterpret_cast<const uint4 *>(
+          j.btile + (size_t)t * src_lbo + (size_t)slice * (kTcSliceN / 8) * 128 + r * 16);
+    }
+  }
+  if (tid < kTcSliceN / 4) {
+    const int m = m_first + tid;
+    const bool in = tid < m_count;
+    s_lim[tid] = in ? make_uint4(j.q[m], j.nqinv[m], (uint32_t)j.dst_limb[m] * kN, 1u)
+                    : make_uint4(3u, 1u, 0u, 0u);
+  }
+  if (tid == 0) mbar_init(smem_u32(bar), 1);
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = npad
+  const uint32_t idesc = (2u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
+  const uint32_t a_lbo = (kTcTile / 8) * 128, b_lbo = (uint32_t)(npad / 8) * 128;
+  uint32_t parity = 0;
+  bool failed = false;
+
+  // residues of one coefficient, and how many lie above half their prime
+  uint32_t y[kMaxBconvSrc + 4];
+  uint32_t nneg = 0;
+  auto load_tile = [&](int tile) {
+    const int col = tile * kTcTile + tid;
+    nneg = 0;
+#pragma unroll
+    for (int k = 0; k < kMaxBconvSrc; k++) {
+      y[k] = 0;
+      if (k < j.ns) {
+        y[k] = __ldg(j.src + (size_t)k * kN + col);
+        nneg += y[k] > j.half[k];
+      }
+    }
+  };
+#pragma unroll
+  for (int k = kMaxBconvSrc; k < kMaxBconvSrc + 4; k++) y[k] = 0;
+  if ((int)blockIdx.x < kN / kTcTile) load_tile(blockIdx.x);
+
+  for (int tile = blockIdx.x; tile < kN / kTcTile && !failed; tile += gridDim.x) {
+    const int col = tile * kTcTile + tid;
+    // 2. operand rows: words y[0..ns), nneg, 0... ; 16-byte chunks t
+#pragma unroll
+    for (int t = 0; t < kTcMaxK / 16; t++) {
+      if (16 * t < kbytes) {
+        uint4 v = make_uint4(y[4 * t], y[4 * t + 1], y[4 * t + 2], y[4 * t + 3]);
+        const int w = j.ns - 4 * t;  // where the pseudo source lands in this chunk
+        if (w == 0) v.x = nneg;
+        if (w == 1) v.y = nneg;
+        if (w == 2) v.z = nneg;
+        if (w == 3) v.w = nneg;
+        *reinterpret_cast<uint4 *>(sA + t * a_lbo + (tid >> 3) * 128 + (tid & 7) * 16) = v;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // 3. one thread issues the MMAs of this tile and commits them to the barrier
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int ks = 0; ks < kbytes / 32; ks++) {
+        const uint64_t da = smem_desc(smem_u32(sA) + ks * 2 * a_lbo, a_lbo, 128);
+        const uint64_t db = smem_desc(smem_u32(sB) + ks * 2 * b_lbo, b_lbo, 128);
+        const uint32_t acc = ks > 0;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+            : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                       smem_u32(bar))
+                   : "memory");
+    }
+    // the next tile's residues travel while the tensor core and the epilogue run
+    if (tile + (int)gridDim.x < kN / kTcTile) load_tile(tile + gridDim.x);
+    // 4. wait for the accumulators (bounded)
+    uint32_t spins = 0;
+    while (!mbar_try_wait(smem_u32(bar), parity)) {
+      if (++spins > kSpinLimit) {
+        failed = true;
+        break;
+      }
+    }
+    parity ^= 1;
+    if (__any_sync(0xffffffffu, failed)) {
+      failed = true;
+      if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // 5. epilogue: 8 destination limbs (32 accumulator columns) per load
+    if (!failed) {
+      const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+      uint32_t *out = j.dst + col;
+#pragma unroll
+      for (int m0 = 0; m0 < kTcSliceN / 4; m0 += 8) {
+        if (m0 < m_count) {
+          uint32_t d[32];
+          tmem_ld32(lane_base + 4 * m0, d);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const uint4 lim = s_lim[m0 + e];
+            // V = d0 + d1*2^8 + d2*2^16 + d3*2^24 as (hi, lo) words; every d < 2^23
+            const uint64_t v = (uint64_t)d[4 * e] + ((uint64_t)d[4 * e + 1] << 8) +
+                               ((uint64_t)d[4 * e + 2] << 16) + ((uint64_t)d[4 * e + 3] << 24);
+            const uint32_t r = mont_reduce(v, lim.x, lim.y);
+            if (lim.w) out[lim.z] = r;
+          }
+        }
+      }
+    }
+    // accumulators and the operand tile are reused by the next tile
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+                 : "memory");
+}
+
+// 6 KB of table slice + 12 KB of operand tile; eight CTAs of 64 tensor-memory
+// columns each can share an SM
+constexpr int kTcSmemBytes = kTcMaxK * kTcSliceN + kTcMaxK * kTcTile + 64 + 16 * (kTcSliceN / 4);
+
+}  // namespace
+
+// Builds the B operand of one conversion in shared-memory operand layout.
+int build_tc_table(const Context &c, ConvPlan &cv) {
+  const int ns = (int)cv.src_g.size(), nd = (int)cv.dst_g.size();
+  if (ns > kMaxBconvSrc) return 0;  // handled by the SIMT kernel only
+  const int kpad = ((4 * (ns + 1) + 31) / 32) * 32;
+  const int npad = ((4 * nd + kTcSliceN - 1) / kTcSliceN) * kTcSliceN;
+  if (kpad > kTcMaxK) return 0;
+  std::vector<uint8_t> tile((size_t)kpad * npad, 0);
+  const uint32_t b_lbo = (uint32_t)(npad / 8) * 128;
+  auto put = [&](int n, int kappa, uint8_t v) {
+    tile[(size_t)(kappa >> 4) * b_lbo + (n >> 3) * 128 + (n & 7) * 16 + (kappa & 15)] = v;
+  };
+  for (int m = 0; m < nd; m++) {
+    const uint32_t p = c.q[cv.dst_g[m]];
+    uint32_t s_all = 1;
+    for (int k = 0; k < ns; k++) s_all = mulmod(s_all, c.q[cv.src_g[k]] % p, p);
+    for (int k = 0; k <= ns; k++) {
+      uint32_t t;
+      if (k < ns) {
+        t = 1;
+        for (int i = 0; i < ns; i++)
+          if (i != k) t = mulmod(t, c.q[cv.src_g[i]] % p, p);
+      } else {
+        t = s_all ? p - s_all : 0;  // -(prod s) mod p for the pseudo source
+      }
+      t = to_mont(to_mont(t, p), p);
+      for (int i = 0; i < (k < ns ? 4 : 1); i++) {
+        const uint32_t ti = mulmod(t, (uint32_t)((1ull << (8 * i)) % p), p);
+        for (int jj = 0; jj < 4; jj++) put(4 * m + jj, 4 * k + i, (uint8_t)(ti >> (8 * jj)));
+      }
+    }
+  }
+  CFHE_CUDA(cudaMalloc(&cv.d_tc_table, tile.size()));
+  CFHE_CUDA(cudaMemcpy(cv.d_tc_table, tile.data(), tile.size(), cudaMemcpyHostToDevice));
+  cv.tc_kpad = kpad;
+  cv.tc_npad = npad;
+  return 0;
+}
+
+int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
+  static bool configured = false;
+  if (!configured) {
+    CFHE_CUDA(cudaFuncSetAttribute(bconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kTcSmemBytes));
+    configured = true;
+  }
+  if (a.n_jobs <= 0) return 0;
+  // work units = (job, slice of 16 destination limbs); about eight CTAs per SM
+  BconvTcArgs b = a;
+  b.n_units = 0;
+  for (int i = 0; i < a.n_jobs; i++)
+    for (int s = 0; s * (kTcSliceN / 4) < a.jobs[i].nd; s++) {
+      if (b.n_units == kMaxTcUnits) {
+        set_error("bconv: too many (job, slice) units");
+        return -1;
+      }
+      b.unit_job[b.n_units] = (uint8_t)i;
+      b.unit_slice[b.n_units++] = (uint8_t)s;
+    }
+  int per_unit = (8 * 148 + b.n_units - 1) / b.n_units;
+  if (per_unit > kN / kTcTile) per_unit = kN / kTcTile;
+  dim3 grid(per_unit, b.n_units);
+  bconv_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, ctx.stream>>>(b);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace cfhe

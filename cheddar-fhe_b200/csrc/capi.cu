@@ -174,6 +174,12 @@ int cfhe_use_own_stream(cfhe_context *h) {
 int cfhe_synchronize(cfhe_context *h) {
   if (!h) return fail("null context");
   CFHE_CUDA(cudaStreamSynchronize(h->c.stream));
+  int flag = 0;
+  CFHE_CUDA(cudaMemcpy(&flag, h->c.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset(h->c.d_error_flag, 0, sizeof(int));
+    return fail("a kernel gave up a bounded wait (tensor-core completion barrier)");
+  }
   return 0;
 }
 

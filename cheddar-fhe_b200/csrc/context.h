@@ -48,6 +48,8 @@ struct ConvPlan {
   std::vector<int> src_pos;         // limb positions of S inside the source
   std::vector<uint32_t> pre;        // per source limb: (S_hat_k * N)^-1 (* restored)
   int32_t *d_table = nullptr;       // [nd][ns] centred, device
+  uint8_t *d_tc_table = nullptr;    // byte planes in tensor-core operand layout, or null
+  int tc_kpad = 0, tc_npad = 0;
   // ModDown-family epilogue, per destination limb
   std::vector<int> ep_pos;          // position of the surviving limb in the source, -1 if restored
   std::vector<uint32_t> ep_pad;     // product of restored primes mod d (plain)
@@ -87,6 +89,8 @@ struct Context {
   bool own_stream = false;
 
   std::vector<uint32_t> nqinv;      // -q^-1 mod 2^32, global order
+  bool use_tc_bconv = true;         // base conversion on tcgen05 (CFHE_BCONV=simt disables)
+  int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out
   std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
   // workspace arena for pipeline temporaries (grown on demand)
   uint32_t *ws = nullptr;

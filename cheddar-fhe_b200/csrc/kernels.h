@@ -58,6 +58,7 @@ struct InnerArgs {
   uint8_t own_digit[kMaxLimbs];  // active-digit index owning limb l, or 255
 };
 
+constexpr int kMaxBconvSrc = 20;  // source limbs of one conversion
 struct BconvJob {
   const int32_t *src;    // [ns][N] centred
   uint32_t *dst;         // limb m stored at dst + dst_limb[m]*N
@@ -67,10 +68,27 @@ struct BconvJob {
   uint32_t q[kMaxLimbs], qinv[kMaxLimbs];
 };
 constexpr int kMaxBconvJobs = 8;
-constexpr int kMaxBconvSrc = 20;  // source limbs of one conversion
 struct BconvArgs {
   int n_jobs;
   BconvJob jobs[kMaxBconvJobs];
+};
+
+// Tensor-core base conversion (bconv_tc.cu): sources are canonical residues.
+struct BconvTcJob {
+  const uint32_t *src;   // [ns][N] canonical residues in [0, s_k)
+  uint32_t *dst;         // limb m stored at dst + dst_limb[m]*N
+  const uint8_t *btile;  // table byte planes in operand layout
+  int ns, nd, kpad, npad;
+  uint32_t half[kMaxBconvSrc];  // s_k >> 1
+  uint8_t dst_limb[kMaxLimbs];
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
+};
+constexpr int kMaxTcUnits = 48;
+struct BconvTcArgs {
+  int n_jobs, n_units;
+  int *error_flag;  // set to 1 when a completion wait timed out
+  uint8_t unit_job[kMaxTcUnits], unit_slice[kMaxTcUnits];  // filled by the launcher
+  BconvTcJob jobs[kMaxBconvJobs];
 };
 
 int launch_ew(const Context &ctx, int op, const EwArgs &args);
@@ -78,5 +96,7 @@ int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
 int launch_inner(const Context &ctx, const InnerArgs &args);
 int launch_bconv(const Context &ctx, const BconvArgs &args);
+int launch_bconv_tc(const Context &ctx, const BconvTcArgs &args);
+int build_tc_table(const Context &ctx, ConvPlan &cv);
 
 }  // namespace cfhe

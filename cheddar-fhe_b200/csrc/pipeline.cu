@@ -36,6 +36,25 @@ void fill_bconv_job(const Context &c, BconvJob &j, const ConvPlan &cv,
   }
 }
 
+void fill_tc_job(const Context &c, BconvTcJob &j, const ConvPlan &cv,
+                 const uint32_t *src, uint32_t *dst,
+                 const std::vector<int> *dst_pos) {
+  j.src = src;
+  j.dst = dst;
+  j.btile = cv.d_tc_table;
+  j.ns = (int)cv.src_g.size();
+  j.nd = (int)cv.dst_g.size();
+  j.kpad = cv.tc_kpad;
+  j.npad = cv.tc_npad;
+  for (int k = 0; k < j.ns; k++) j.half[k] = c.q[cv.src_g[k]] >> 1;
+  for (int m = 0; m < j.nd; m++) {
+    const int g = cv.dst_g[m];
+    j.dst_limb[m] = (uint8_t)(dst_pos ? (*dst_pos)[m] : m);
+    j.q[m] = c.q[g];
+    j.nqinv[m] = c.nqinv[g];
+  }
+}
+
 }  // namespace
 
 size_t modup_scratch_words(const LevelPlan &lp) { return (size_t)lp.nq * kN; }
@@ -52,9 +71,11 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
   a.dst = y;
   a.src = src;
   a.table = c.d_itw;
+  bool tc = c.use_tc_bconv;
+  for (const DigitPlan &d : lp.digits) tc = tc && d.conv.d_tc_table;
   a.n_limbs = lp.nq;
   a.n_polys = 1;
-  a.centred = 1;
+  a.centred = tc ? 0 : 1;  // the tensor-core conversion takes canonical residues
   for (const DigitPlan &d : lp.digits)
     for (int k = d.s0; k < d.s1; k++) {
       const int g = lp.q_g[k];
@@ -67,18 +88,27 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
   c.mark("modup_intt");
   // 2. every digit's base conversion in one launch, written straight to the
   //    limb positions of its (nq + alpha)-limb ModUp buffer
-  BconvArgs b;
-  memset(&b, 0, sizeof(b));
-  for (const DigitPlan &d : lp.digits) {
-    if (b.n_jobs == kMaxBconvJobs) {
-      set_error("ModUp: too many digits");
-      return -1;
-    }
-    fill_bconv_job(c, b.jobs[b.n_jobs++], d.conv,
-                   reinterpret_cast<const int32_t *>(y) + (size_t)d.s0 * kN,
-                   mu + (size_t)d.index * lp.ntot * kN, &d.dst_pos);
+  if ((int)lp.digits.size() > kMaxBconvJobs) {
+    set_error("ModUp: too many digits");
+    return -1;
   }
-  if (int r = launch_bconv(c, b)) return r;
+  if (tc) {
+    BconvTcArgs b;
+    memset(&b, 0, sizeof(b));
+    b.error_flag = c.d_error_flag;
+    for (const DigitPlan &d : lp.digits)
+      fill_tc_job(c, b.jobs[b.n_jobs++], d.conv, y + (size_t)d.s0 * kN,
+                  mu + (size_t)d.index * lp.ntot * kN, &d.dst_pos);
+    if (int r = launch_bconv_tc(c, b)) return r;
+  } else {
+    BconvArgs b;
+    memset(&b, 0, sizeof(b));
+    for (const DigitPlan &d : lp.digits)
+      fill_bconv_job(c, b.jobs[b.n_jobs++], d.conv,
+                     reinterpret_cast<const int32_t *>(y) + (size_t)d.s0 * kN,
+                     mu + (size_t)d.index * lp.ntot * kN, &d.dst_pos);
+    if (int r = launch_bconv(c, b)) return r;
+  }
   c.mark("modup_bconv");
   // 3. forward transforms of all converted limbs of all digits, in place
   memset(&a, 0, sizeof(a));
@@ -123,6 +153,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     set_error("ModDown: unsupported shape");
     return -1;
   }
+  const bool tc = c.use_tc_bconv && cv.d_tc_table;
   // 1. inverse transform of the limbs that disappear
   NttArgs a;
   memset(&a, 0, sizeof(a));
@@ -133,7 +164,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
   a.n_polys = n_polys;
   a.dst_poly_stride = (long long)ns * kN;
   a.src_poly_stride = src_stride;
-  a.centred = 1;
+  a.centred = tc ? 0 : 1;
   for (int k = 0; k < ns; k++) {
     const int g = cv.src_g[k];
     a.g[k] = (uint8_t)g;
@@ -145,13 +176,22 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
   if (int r = launch_ntt(c, a, true)) return r;
   c.mark("moddown_intt");
   // 2. base conversion into the destination buffers
-  BconvArgs b;
-  memset(&b, 0, sizeof(b));
-  for (int p = 0; p < n_polys; p++)
-    fill_bconv_job(c, b.jobs[b.n_jobs++], cv,
-                   reinterpret_cast<const int32_t *>(y) + (size_t)p * ns * kN,
-                   dst + p * dst_stride, nullptr);
-  if (int r = launch_bconv(c, b)) return r;
+  if (tc) {
+    BconvTcArgs b;
+    memset(&b, 0, sizeof(b));
+    b.error_flag = c.d_error_flag;
+    for (int p = 0; p < n_polys; p++)
+      fill_tc_job(c, b.jobs[b.n_jobs++], cv, y + (size_t)p * ns * kN, dst + p * dst_stride, nullptr);
+    if (int r = launch_bconv_tc(c, b)) return r;
+  } else {
+    BconvArgs b;
+    memset(&b, 0, sizeof(b));
+    for (int p = 0; p < n_polys; p++)
+      fill_bconv_job(c, b.jobs[b.n_jobs++], cv,
+                     reinterpret_cast<const int32_t *>(y) + (size_t)p * ns * kN,
+                     dst + p * dst_stride, nullptr);
+    if (int r = launch_bconv(c, b)) return r;
+  }
   c.mark("moddown_bconv");
   // 3. forward transform in place with the fused (pad*x - t) * P^-1 epilogue
   memset(&a, 0, sizeof(a));

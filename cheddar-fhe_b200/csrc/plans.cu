@@ -2,9 +2,12 @@
 // once at context creation (the reference builds one ModSwitchHandler per
 // level, src/core/ModSwitch.cu:175-318, with constants from :320-411).
 #include <algorithm>
+#include <cstdlib>
+#include <string>
 
 #include "context.h"
 #include "host_math.h"
+#include "kernels.h"
 
 namespace cfhe {
 namespace {
@@ -43,7 +46,7 @@ int finish_conv(const Context &c, ConvPlan &cv, const std::vector<int> &restored
   CFHE_CUDA(cudaMalloc(&cv.d_table, t.size() * sizeof(int32_t)));
   CFHE_CUDA(cudaMemcpy(cv.d_table, t.data(), t.size() * sizeof(int32_t),
                        cudaMemcpyHostToDevice));
-  return 0;
+  return build_tc_table(c, cv);
 }
 
 void np_limbs(const Context &c, int nm, int nt, int na, std::vector<int> &g) {
@@ -80,6 +83,10 @@ int build_down(const Context &c, ConvPlan &cv, const std::vector<int> &src,
 }  // namespace
 
 int build_plans(Context &c) {
+  const char *mode = getenv("CFHE_BCONV");
+  c.use_tc_bconv = !(mode && std::string(mode) == "simt");
+  CFHE_CUDA(cudaMalloc(&c.d_error_flag, sizeof(int)));
+  CFHE_CUDA(cudaMemset(c.d_error_flag, 0, sizeof(int)));
   c.nqinv.resize(c.NP);
   for (int g = 0; g < c.NP; g++) {
     uint32_t q = c.q[g], x = q;
@@ -158,9 +165,14 @@ int build_plans(Context &c) {
 void free_plans(Context &c) {
   for (LevelPlan &lp : c.levels) {
     for (DigitPlan &d : lp.digits)
-      if (d.conv.d_table) cudaFree(d.conv.d_table);
-    for (ConvPlan &cv : lp.down)
+      {
+        if (d.conv.d_table) cudaFree(d.conv.d_table);
+        if (d.conv.d_tc_table) cudaFree(d.conv.d_tc_table);
+      }
+    for (ConvPlan &cv : lp.down) {
       if (cv.d_table) cudaFree(cv.d_table);
+      if (cv.d_tc_table) cudaFree(cv.d_tc_table);
+    }
   }
   c.levels.clear();
   for (cudaEvent_t e : c.prof_events) cudaEventDestroy(e);
@@ -168,6 +180,8 @@ void free_plans(Context &c) {
   if (c.ws) cudaFree(c.ws);
   c.ws = nullptr;
   c.ws_words = 0;
+  if (c.d_error_flag) cudaFree(c.d_error_flag);
+  c.d_error_flag = nullptr;
 }
 
 void Context::mark(const char *stage) const {

@@ -152,3 +152,50 @@ def test_errors_are_reported(engine40, pkg):
         e.moddown_(0, 2, a, a)  # level 0 cannot be rescaled
     with pytest.raises(pkg.CfheError):
         e.modup_(99, a, a)
+
+
+@pytest.fixture(scope="module")
+def engine40_simt(pkg, params40):
+    """A second context whose base conversions run on the SIMT kernel instead
+    of the tensor cores (CFHE_BCONV=simt is read at context creation)."""
+    import os
+    os.environ["CFHE_BCONV"] = "simt"
+    try:
+        e = pkg.Engine(params40, device=0)
+    finally:
+        del os.environ["CFHE_BCONV"]
+    yield e
+    e.close()
+
+
+@pytest.mark.parametrize("level", [28, 16, 2, 1])
+def test_simt_and_tensor_core_conversions_agree(engine40, engine40_simt, oracle40, level):
+    rng = np.random.default_rng(900 + level)
+    full = engine40.level_limbs(level, 12)
+    nq = len(full) - 12
+    src = rand_limbs(rng, oracle40.primes, full, oracle40.n)
+    q_only = np.ascontiguousarray(src[:nq])
+    want = oracle40.modup(level, q_only)
+    assert np.array_equal(engine40.modup(level, q_only), want)
+    assert np.array_equal(engine40_simt.modup(level, q_only), want)
+    for kind in (0, 2):
+        want = oracle40.moddown(level, kind, src)
+        assert np.array_equal(engine40.moddown(level, kind, src), want)
+        assert np.array_equal(engine40_simt.moddown(level, kind, src), want)
+
+
+def test_extreme_residues_through_the_tensor_core_conversion(engine40, oracle40):
+    """Residues 0, 1, (q-1)/2, (q+1)/2 and q-1 in every limb: the boundary of
+    the centred representation and the largest byte planes."""
+    level = 28
+    g = engine40.level_limbs(level)
+    src = np.zeros((len(g), oracle40.n), np.uint32)
+    for l, gi in enumerate(g):
+        q = int(oracle40.primes[gi])
+        vals = np.array([0, 1, (q - 1) // 2, (q + 1) // 2, q - 1, q - 2, 255, 256, 65535, 65536], dtype=np.uint32)
+        src[l] = np.resize(np.roll(vals, l), oracle40.n)
+    # feed the values as NTT-domain words: ModUp first inverts the transform,
+    # so also run the conversion on the transform of these coefficient patterns
+    assert np.array_equal(engine40.modup(level, src), oracle40.modup(level, src))
+    coef = oracle40.ntt(src, g)
+    assert np.array_equal(engine40.modup(level, coef), oracle40.modup(level, coef))
