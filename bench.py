@@ -371,6 +371,53 @@ def bench_reference_cuda(eng, torch, params, steps):
             "how": "unmodified reference sources compiled for sm_100a, legacy stream, CUDA events"}
 
 
+def bench_hoisted(eng, torch, params, n_rot, steps):
+    """Config 3: n_rot rotations of one level-28 ciphertext sharing one ModUp
+    (power-of-two distances first, then seeded random ones). Keys hold random
+    residues below every prime: timing does not depend on their values."""
+    rng = np.random.default_rng(0xC0FFEE03)
+    level, M = HM_LEVEL, len(params["main_primes"])
+    g = eng.level_limbs(level)
+    beta = eng.beta(level)
+    nkey = len(params["terminal_primes"]) + M + eng.alpha
+    rots = [1 << i for i in range(min(15, n_rot))]
+    while len(rots) < n_rot:
+        r = int(rng.integers(1, N // 2))
+        if r not in rots:
+            rots.append(r)
+    dev = f"cuda:{eng.device}"
+    keys = torch.randint(0, 1 << 24, (n_rot, 2, beta, nkey, N), dtype=torch.int32, device=dev)
+    kb = [[keys[i, 0, j] for j in range(beta)] for i in range(n_rot)]
+    ka = [[keys[i, 1, j] for j in range(beta)] for i in range(n_rot)]
+    bx = eng.to_dev(rand_limbs(rng, eng.primes, g))
+    ax = eng.to_dev(rand_limbs(rng, eng.primes, g))
+    out = eng.empty(n_rot, 2, len(g), N)
+    for _ in range(2):
+        eng.hoisted_rotations_(level, out, bx, ax, rots, kb, ka, M)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.hoisted_rotations_(level, out, bx, ax, rots, kb, ka, M)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    # unhoisted: one full key switch + permutation per rotation
+    tmp_b, tmp_a = eng.empty(len(g), N), eng.empty(len(g), N)
+    e0.record()
+    for i in range(n_rot):
+        eng.keyswitch_(level, tmp_b, tmp_a, ax, bx, kb[i], ka[i], M)
+        eng.permute_(out[i, 0], tmp_b, None, eng.galois(rots[i]), g)
+        eng.permute_(out[i, 1], tmp_a, None, eng.galois(rots[i]), g)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_plain = e0.elapsed_time(e1)
+    nbytes = (2 * len(g) + n_rot * 2 * beta * (len(g) + eng.alpha) + n_rot * 2 * len(g)) * LIMB
+    return {"rotations": n_rot, "hoisted_ms": ms, "unhoisted_ms": ms_plain,
+            "algorithmic_bytes": nbytes, "GB/s": nbytes / (ms * 1e-3) / 1e9,
+            "key_bytes_resident": int(keys.numel() * 4)}
+
+
 def run_gpu(args, pkg):
     import torch
     import torch.distributed as dist
@@ -398,6 +445,9 @@ def run_gpu(args, pkg):
     if args.workload == "hmult":
         hm = bench_hmult(eng, pkg, torch, params, args.steps, warmup, rank, barrier, not args.no_check)
     clocks = sampler.stop() if rank == 0 else None
+    hoist = None
+    if args.workload == "hmult" and not args.no_hoist:
+        hoist = bench_hoisted(eng, torch, params, 64, max(2, args.steps // 5))
     ref_cuda = None
     if rank == 0 and world == 1 and not args.no_ref:
         ref_cuda = bench_reference_cuda(eng, torch, params, args.steps)
@@ -465,6 +515,10 @@ def run_gpu(args, pkg):
                         "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
                 "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": ntt_roof,
             }
+        if hoist:
+            peak_, _ = measured_peaks()
+            hoist["frac"] = hoist["GB/s"] / peak_
+            line["hoisted_rotations"] = hoist
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:
@@ -491,6 +545,7 @@ def main():
     ap.add_argument("--workload", default="hmult", choices=["hmult", "ntt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip decrypting the HMult result")
+    ap.add_argument("--no-hoist", action="store_true", help="skip the 64-rotation hoisting sweep")
     ap.add_argument("--no-ref", action="store_true", help="skip timing the reference's CUDA library")
     args = ap.parse_args()
     pkg = load_package()

@@ -250,6 +250,15 @@ class Engine:
                                           self._p(bx) if bx is not None else None,
                                           self._ptrs(evk_b), self._ptrs(evk_a), int(key_main)))
 
+    def hoisted_rotations_(self, level, out, bx, ax, rots, evk_b, evk_a, key_main):
+        """out: [n_rot, 2, nq, N]; evk_b/evk_a: per rotation a list of beta digit tensors."""
+        r, rp = _ints(rots)
+        flat_b = [t for key in evk_b for t in key]
+        flat_a = [t for key in evk_a for t in key]
+        self._check(self.L.cfhe_hoisted_rotations(self.h, level, self._p(out), self._p(bx), self._p(ax),
+                                                  len(r), rp, self._ptrs(flat_b), self._ptrs(flat_a),
+                                                  int(key_main)))
+
     def hmult_(self, level, out_b, out_a, b1, a1, b2, a2, evk_b, evk_a, key_main, rescale=True):
         self._check(self.L.cfhe_hmult(self.h, level, self._p(out_b), self._p(out_a),
                                       self._p(b1), self._p(a1), self._p(b2), self._p(a2),

@@ -482,6 +482,24 @@ int cfhe_keyswitch(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                        key_main, h->c.ws);
 }
 
+int cfhe_hoisted_rotations(cfhe_context *h, int level, uint32_t *out,
+                           const uint32_t *bx, const uint32_t *ax, int n_rot,
+                           const int *rot, const uint32_t *const *evk_b,
+                           const uint32_t *const *evk_a, int key_main) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!out || !bx || !ax || !rot || !evk_b || !evk_a) return fail("null argument");
+  if (n_rot < 1) return fail("invalid rotation count");
+  std::vector<uint32_t> galois(n_rot);
+  for (int i = 0; i < n_rot; i++) {
+    if (rot[i] == 0 || rot[i] >= h->c.n / 2) return fail("rotation distance out of range");
+    galois[i] = cfhe_galois_for_rotation(h, rot[i]);
+  }
+  if (int r = ensure_workspace(h->c, hoisted_scratch_words(*lp))) return r;
+  return run_hoisted_rotations(h->c, *lp, out, bx, ax, n_rot, galois.data(), evk_b,
+                               evk_a, key_main, h->c.ws);
+}
+
 int cfhe_hmult(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
                const uint32_t *a2, const uint32_t *const *evk_b,

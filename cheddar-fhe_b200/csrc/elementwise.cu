@@ -153,12 +153,28 @@ __global__ void __launch_bounds__(kEwThreads)
       mac_fold(sa[3], c.w, pm, q32);
     }
   }
-  reinterpret_cast<uint4 *>(a.acc_b + (size_t)l * kN)[v] =
-      make_uint4(mont_reduce(sb[0], q, nq), mont_reduce(sb[1], q, nq),
-                 mont_reduce(sb[2], q, nq), mont_reduce(sb[3], q, nq));
-  reinterpret_cast<uint4 *>(a.acc_a + (size_t)l * kN)[v] =
-      make_uint4(mont_reduce(sa[0], q, nq), mont_reduce(sa[1], q, nq),
-                 mont_reduce(sa[2], q, nq), mont_reduce(sa[3], q, nq));
+  if (a.scatter_galois == 0) {
+    reinterpret_cast<uint4 *>(a.acc_b + (size_t)l * kN)[v] =
+        make_uint4(mont_reduce(sb[0], q, nq), mont_reduce(sb[1], q, nq),
+                   mont_reduce(sb[2], q, nq), mont_reduce(sb[3], q, nq));
+    reinterpret_cast<uint4 *>(a.acc_a + (size_t)l * kN)[v] =
+        make_uint4(mont_reduce(sa[0], q, nq), mont_reduce(sa[1], q, nq),
+                   mont_reduce(sa[2], q, nq), mont_reduce(sa[3], q, nq));
+  } else {
+    // fused automorphism: the key and the ModUp buffers are read in order and
+    // the product lands where the rotation sends it (the reference's fused
+    // baby-step kernel does the same, src/extension/Hoist.cu:20-78); an
+    // aligned block of 128 results stays inside one aligned block of 128
+    uint32_t *ob = a.acc_b + (size_t)l * kN, *oa = a.acc_a + (size_t)l * kN;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const uint32_t i = 4 * v + e;
+      const uint32_t ex = (__brev(i) >> (31 - kLogN)) + 1;
+      const uint32_t d = __brev((ex * a.scatter_galois - 1) << (31 - kLogN)) & (kN - 1);
+      ob[d] = mont_reduce(sb[e], q, nq);
+      oa[d] = mont_reduce(sa[e], q, nq);
+    }
+  }
 }
 
 }  // namespace

@@ -52,6 +52,9 @@ struct InnerArgs {
   const uint32_t *c0, *c1;  // optional P*c0 -> acc_b, P*c1 -> acc_a (Q limbs)
   const uint32_t *kb[kMaxDigits], *ka[kMaxDigits];
   int n_digits, ntot, nq;
+  // 0: results stay in place; otherwise the inverse Galois element g^-1 of an
+  // automorphism applied to the result: word i is stored at pi_{g^-1}(i)
+  uint32_t scatter_galois;
   uint8_t mu_slot[kMaxDigits];
   uint32_t q[kMaxLimbs], nqinv[kMaxLimbs], pm[kMaxLimbs];
   uint8_t kpos[kMaxLimbs];       // limb position inside the key

@@ -219,11 +219,32 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
   return 0;
 }
 
+static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+                          uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+                          const uint32_t *c0, const uint32_t *c1,
+                          const uint32_t *const *kb, const uint32_t *const *ka,
+                          int key_main, uint32_t galois_inv);
+
 int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
               uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
               const uint32_t *c0, const uint32_t *c1,
               const uint32_t *const *kb, const uint32_t *const *ka,
               int key_main) {
+  return run_inner_impl(c, lp, acc_b, acc_a, mu, d, c0, c1, kb, ka, key_main, 0);
+}
+
+int run_inner_rot(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+                  uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+                  const uint32_t *c0, const uint32_t *const *kb,
+                  const uint32_t *const *ka, int key_main, uint32_t galois_inv) {
+  return run_inner_impl(c, lp, acc_b, acc_a, mu, d, c0, nullptr, kb, ka, key_main, galois_inv);
+}
+
+static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+                          uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+                          const uint32_t *c0, const uint32_t *c1,
+                          const uint32_t *const *kb, const uint32_t *const *ka,
+                          int key_main, uint32_t galois_inv) {
   if ((int)lp.digits.size() > kMaxDigits) {
     set_error("inner product: too many digits");
     return -1;
@@ -244,6 +265,7 @@ int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
   a.n_digits = (int)lp.digits.size();
   a.ntot = lp.ntot;
   a.nq = lp.nq;
+  a.scatter_galois = galois_inv;
   for (int i = 0; i < a.n_digits; i++) {
     const int slot = lp.digits[i].index;
     a.kb[i] = kb[slot];
@@ -303,6 +325,53 @@ int run_keyswitch(Context &c, const LevelPlan &lp, int down_type,
   }
   return run_moddown(c, cv, out_b, acc, 2, (long long)(out_a - out_b),
                      (long long)acc_words, y);
+}
+
+constexpr int kHoistChunk = 4;  // rotations whose ModDowns share launches
+
+size_t hoisted_scratch_words(const LevelPlan &lp) {
+  const size_t y_words = std::max(modup_scratch_words(lp),
+                                  moddown_scratch_words(lp.down[0], 2 * kHoistChunk));
+  return y_words + (size_t)(lp.beta + 2 * kHoistChunk) * lp.ntot * kN;
+}
+
+int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
+                          const uint32_t *b, const uint32_t *a, int n_rot,
+                          const uint32_t *galois, const uint32_t *const *kb,
+                          const uint32_t *const *ka, int key_main,
+                          uint32_t *scratch) {
+  const ConvPlan &cv = lp.down[0];
+  const size_t y_words = std::max(modup_scratch_words(lp),
+                                  moddown_scratch_words(cv, 2 * kHoistChunk));
+  uint32_t *y = scratch;
+  uint32_t *mu = y + y_words;
+  uint32_t *acc = mu + (size_t)lp.beta * lp.ntot * kN;
+  const size_t acc_words = (size_t)lp.ntot * kN, out_words = (size_t)lp.nq * kN;
+  const uint32_t m2 = 2u * kN;
+  // the ModUp of a is computed once and shared by every rotation
+  if (int r = run_modup(c, lp, mu, a, false, y)) return r;
+  for (int r0 = 0; r0 < n_rot; r0 += kHoistChunk) {
+    const int cnt = std::min(kHoistChunk, n_rot - r0);
+    for (int i = 0; i < cnt; i++) {
+      const uint32_t g = galois[r0 + i];
+      if ((g & 1u) == 0 || g >= m2) {
+        set_error("hoisted rotations: invalid Galois element");
+        return -1;
+      }
+      // g^-1 mod 2N by exponentiation (the unit group has exponent N/2... use 2N-bit Newton)
+      uint32_t inv = g;
+      for (int it = 0; it < 5; it++) inv = (uint32_t)((uint64_t)inv * (2u - g * inv)) & (m2 - 1);
+      uint32_t *ab = acc + (size_t)(2 * i) * acc_words;
+      if (int rc = run_inner_rot(c, lp, ab, ab + acc_words, mu, a, b,
+                                 kb + (size_t)(r0 + i) * lp.beta,
+                                 ka + (size_t)(r0 + i) * lp.beta, key_main, inv))
+        return rc;
+    }
+    if (int rc = run_moddown(c, cv, out + (size_t)(2 * r0) * out_words, acc, 2 * cnt,
+                             (long long)out_words, (long long)acc_words, y))
+      return rc;
+  }
+  return 0;
 }
 
 size_t keyswitch_scratch_words(const LevelPlan &lp, int down_type) {

@@ -22,6 +22,20 @@ int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
               const uint32_t *c0, const uint32_t *c1,
               const uint32_t *const *kb, const uint32_t *const *ka,
               int key_main);
+// galois_inv != 0: the result is additionally permuted by the automorphism
+// whose inverse Galois element is galois_inv (fused into the store)
+int run_inner_rot(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
+                  uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
+                  const uint32_t *c0, const uint32_t *const *kb,
+                  const uint32_t *const *ka, int key_main, uint32_t galois_inv);
+// Hoisted rotations: one ModUp of `a` shared by n_rot key switches, each fused
+// with its automorphism; out = [n_rot][2][nq][N].
+int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
+                          const uint32_t *b, const uint32_t *a, int n_rot,
+                          const uint32_t *galois, const uint32_t *const *kb,
+                          const uint32_t *const *ka, int key_main,
+                          uint32_t *scratch);
+size_t hoisted_scratch_words(const LevelPlan &lp);
 int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
                uint32_t *d1, uint32_t *d2, const uint32_t *b1,
                const uint32_t *a1, const uint32_t *b2, const uint32_t *a2);

@@ -183,6 +183,20 @@ CFHE_API int cfhe_keyswitch(cfhe_context *ctx, int level, uint32_t *out_b,
                             uint32_t *out_a, const uint32_t *d,
                             const uint32_t *bx, const uint32_t *const *evk_b,
                             const uint32_t *const *evk_a, int key_main);
+/* Hoisted rotations: n_rot homomorphic rotations of one ciphertext (bx, ax)
+ * that share a single ModUp of ax; each rotation is the evaluation-key inner
+ * product fused with its automorphism (the reference's HoistHandler baby step,
+ * src/extension/Hoist.cu:578-691 with kernel :20-78), followed by ModDown.
+ * rot[i] > 0 is the slot distance (negative: conjugation); the keys are laid
+ * out as for Context::HRot (src/core/Context.cpp:776-791): evk_b/evk_a are HOST
+ * arrays of n_rot*beta device pointers, rotation i digit j at [i*beta + j],
+ * beta = cfhe_beta(level). out: [n_rot][2][nq][N] words; every (b, a) pair is
+ * word for word what HRot with the same key returns. */
+CFHE_API int cfhe_hoisted_rotations(cfhe_context *ctx, int level, uint32_t *out,
+                                    const uint32_t *bx, const uint32_t *ax,
+                                    int n_rot, const int *rot,
+                                    const uint32_t *const *evk_b,
+                                    const uint32_t *const *evk_a, int key_main);
 /* Context::HMult (Context.cpp:862-871): tensor product, relinearisation and,
  * when rescale != 0, ModDownAndRescale to level-1 (RelinearizeRescale,
  * :714-737); rescale == 0 keeps the level (Relinearize, :561-565). */

@@ -199,3 +199,26 @@ def test_extreme_residues_through_the_tensor_core_conversion(engine40, oracle40)
     assert np.array_equal(engine40.modup(level, src), oracle40.modup(level, src))
     coef = oracle40.ntt(src, g)
     assert np.array_equal(engine40.modup(level, coef), oracle40.modup(level, coef))
+
+
+@pytest.mark.parametrize("level,rots", [(16, [1, 1234, 32767, -1, 5, 64]), (28, [7, 4096])])
+def test_hoisted_rotations_equal_hrot(engine40, oracle40, level, rots):
+    """Every output of the hoisted path equals MultKey + Permute (the
+    reference's HRot, src/core/Context.cpp:776-791) with the same key."""
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(1000 + level)
+    g = e.level_limbs(level)
+    bx, ax = rand_limbs(rng, o.primes, g, o.n), rand_limbs(rng, o.primes, g, o.n)
+    keys = [fake_key(rng, e, o, 43, e.beta(28)) for _ in rots]
+    dk = [([e.to_dev(x) for x in kb], [e.to_dev(x) for x in ka]) for kb, ka in keys]
+    out = e.empty(len(rots), 2, len(g), e.n)
+    beta = e.beta(level)
+    e.hoisted_rotations_(level, out, e.to_dev(bx), e.to_dev(ax), rots,
+                         [k[0][:beta] for k in dk], [k[1][:beta] for k in dk], 43)
+    got = e.to_host(out)
+    for i, r in enumerate(rots):
+        kb, ka = keys[i]
+        sb, sa = o.keyswitch(level, ax, bx, kb, ka, 43)
+        gal = o.galois(r)
+        assert np.array_equal(got[i, 0], o.permute(sb, gal)), r
+        assert np.array_equal(got[i, 1], o.permute(sa, gal)), r
