@@ -26,9 +26,12 @@ def test_facade_compiles_and_links(pkg):
 
 
 @pytest.mark.gpu
-def test_basic_test_bodies_bootparam_40(pkg):
+@pytest.mark.parametrize("param_set", ["bootparam_40.json", "bootparam_30.json", "bootparam_35.json"])
+def test_basic_test_bodies(pkg, param_set):
+    """The three 32-bit parameter sets the reference instantiates its
+    basic_test with (unittest/BasicTest.cpp:421-429)."""
     exe = build_driver(pkg)
-    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json")],
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, param_set)],
                        capture_output=True, text=True, timeout=1500)
     print(r.stdout[-6000:])
     print(r.stderr[-2000:])
