@@ -372,6 +372,25 @@ int cfhe_mul_imag_unit(cfhe_context *h, uint32_t *dst, const uint32_t *src,
   return launch_ew(c, EW_IMAG, e);
 }
 
+int cfhe_modup_to_max(cfhe_context *h, uint32_t *dst, const uint32_t *src,
+                      const int *src_gidx, int n_src, const int *dst_gidx,
+                      int n_dst) {
+  if (!h || !dst || !src || !src_gidx || !dst_gidx) return fail("null argument");
+  const Context &c = h->c;
+  if (n_src < 1 || n_src > 2) return fail("modup_to_max: one or two source limbs");
+  if (n_dst < 1 || n_dst > kMaxRows) return fail("too many limbs");
+  for (int i = 0; i < n_src; i++)
+    if (src_gidx[i] < 0 || src_gidx[i] >= c.NP) return fail("prime index out of range");
+  EwArgs e;
+  e.n_rows = n_dst;
+  for (int l = 0; l < n_dst; l++) {
+    const int g = dst_gidx[l];
+    if (g < 0 || g >= c.NP) return fail("prime index out of range");
+    e.rows[l] = EwRow{dst + (size_t)l * kN, nullptr, nullptr, c.q[g], c.nqinv[g], 0u, 0u};
+  }
+  return launch_lift(c, e, src, c.q[src_gidx[0]], n_src == 2 ? c.q[src_gidx[1]] : 0u);
+}
+
 // ---------------------------------------------------------------------------
 // mod-switch
 // ---------------------------------------------------------------------------

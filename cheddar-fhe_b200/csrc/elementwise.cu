@@ -177,7 +177,37 @@ __global__ void __launch_bounds__(kEwThreads)
   }
 }
 
+// Exact lift of a value known modulo q0*q1 (two limbs, already multiplied by
+// the inverse of the other prime) to other primes: x = centred(y0*q1 + y1*q0
+// mod q0*q1), out = x mod p (reference kernel ModUpToMax2,
+// src/core/ElementWise.cu:593-623; one-limb case :579-591).
+__global__ void __launch_bounds__(kEwThreads)
+    lift_kernel(const __grid_constant__ EwArgs args, const uint32_t *src, uint32_t q0, uint32_t q1) {
+  const EwRow &r = args.rows[blockIdx.y];
+  const int i = blockIdx.x * kEwThreads + threadIdx.x;  // one word per thread
+  const uint32_t p = r.q;
+  if (q1 == 0) {
+    r.dst[i] = src[i] % p;
+    return;
+  }
+  const int64_t prod = (int64_t)((uint64_t)q0 * q1);
+  int64_t v = (int64_t)((uint64_t)src[i] * q1 + (uint64_t)src[i + kN] * q0);
+  if (v >= prod) v -= prod;
+  if (v > (prod >> 1)) v -= prod;
+  int64_t m = v % (int64_t)p;
+  if (m < 0) m += p;
+  r.dst[i] = (uint32_t)m;
+}
+
 }  // namespace
+
+int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1) {
+  if (args.n_rows <= 0) return 0;
+  dim3 grid(kN / kEwThreads, args.n_rows), block(kEwThreads);
+  lift_kernel<<<grid, block, 0, ctx.stream>>>(args, src, q0, q1);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int launch_ew(const Context &ctx, int op, const EwArgs &args) {
   if (args.n_rows <= 0) return 0;

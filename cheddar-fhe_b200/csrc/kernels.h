@@ -96,6 +96,7 @@ struct BconvTcArgs {
 
 int launch_ew(const Context &ctx, int op, const EwArgs &args);
 int launch_tensor(const Context &ctx, const TensorArgs &args);
+int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
 int launch_inner(const Context &ctx, const InnerArgs &args);
 int launch_bconv(const Context &ctx, const BconvArgs &args);

@@ -1,0 +1,717 @@
+// Bootstrapping on top of the operator API (host-side planning in C++; every
+// GPU step is a C-ABI call made through Context).
+//
+// Class names follow the reference's extension (include/extension/
+// StripedMatrix.h, LinearTransform.h, EvalPoly.h, EvalMod.h, EvalSpecialFFT.h,
+// BootParameter.h, BootContext.h); the pipeline is the same mathematics
+//   scale up -> ModUpToMax (with sparse-secret encapsulation) -> CoeffToSlot
+//   -> EvalMod on the real and imaginary parts -> SlotToCoeff
+// (reference src/extension/BootContext.cpp:299-365) with its own planning:
+//  * linear transforms are diagonal (striped) matrices evaluated by
+//    baby-step/giant-step, the baby rotations sharing one ModUp (hoisting);
+//  * CoeffToSlot and SlotToCoeff are merged groups of radix-2 stages of the
+//    encoder's special (I)FFT (reference src/core/Encode.cpp:85-133), one
+//    group per level the BootParameter grants them;
+//  * polynomials are evaluated in the Chebyshev basis by recursive splitting
+//    p = q * T_m + r (depth ceil(log2(degree + 1))) with exact scale tracking:
+//    every sum is formed at one agreed scale before a single rescale, the
+//    constants carrying whatever factor that takes, so rational rescaling
+//    (levels whose prime products differ) costs no precision and no level;
+//  * EvalMod is an even Chebyshev series of degree 30 for
+//    (1/2pi)^(1/8) cos(2pi(K t - 1/4)/8), evaluated as a degree-15 series in
+//    T_2(t) (five levels), followed by three double-angle steps (reference
+//    src/extension/EvalMod.cpp:8-61 uses the same function with K = 16 and
+//    the same eight levels).
+// Full-slot bootstrapping (2^(logN-1) slots) only.
+#pragma once
+#include <functional>
+#include <set>
+
+#include "cheddar/Cheddar.h"
+
+namespace cheddar {
+
+// ------------------------------------------------------------ StripedMatrix
+// (M v)[p] = sum_k diag[k][p] * v[(p + k) mod n]
+struct StripedMatrix {
+  int n = 0;
+  std::map<int, std::vector<Complex>> diag;
+
+  explicit StripedMatrix(int size = 0) : n(size) {}
+  std::vector<Complex> &At(int k) {
+    k = ((k % n) + n) % n;
+    auto it = diag.find(k);
+    if (it == diag.end()) it = diag.emplace(k, std::vector<Complex>(n, Complex(0, 0))).first;
+    return it->second;
+  }
+  // A * B (B is applied first)
+  static StripedMatrix Mult(const StripedMatrix &A, const StripedMatrix &B) {
+    StripedMatrix C(A.n);
+    for (auto &[k, a] : A.diag)
+      for (auto &[l, b] : B.diag) {
+        auto &c = C.At(k + l);
+        for (int p = 0; p < A.n; p++) c[p] += a[p] * b[(p + k) % A.n];
+      }
+    return C;
+  }
+  void Scale(Complex s) {
+    for (auto &[k, d] : diag)
+      for (auto &x : d) x *= s;
+  }
+  std::vector<Complex> Apply(const std::vector<Complex> &v) const {
+    std::vector<Complex> r(n, Complex(0, 0));
+    for (auto &[k, d] : diag)
+      for (int p = 0; p < n; p++) r[p] += d[p] * v[(p + k) % n];
+    return r;
+  }
+};
+
+// ------------------------------------------------------------ LinearTransform
+// res = Rescale( sum_k diag_k (*) rot_k(in) ) by baby-step/giant-step.
+template <typename word>
+class LinearTransform {
+  using Ct = Ciphertext<word>;
+  using Pt = Plaintext<word>;
+
+ public:
+  // The plaintext diagonals are encoded at `level` with the scale that makes
+  // the output scale scale_out for an input of scale scale_in.
+  LinearTransform(const ConstContextPtr<word> &ctx, const StripedMatrix &m, int level, double scale_in,
+                  double scale_out, int baby_steps = 8)
+      : level_(level), bs_(baby_steps), n_(m.n) {
+    const auto &param = ctx->param_;
+    AssertTrue(level > 0, "LinearTransform needs a level that can be rescaled");
+    pt_scale_ = param.GetRescalePrimeProd(level) * (scale_out / scale_in);
+    // stride g = gcd of the offsets and n; signed multiples t in (-n/2g, n/2g]
+    int g = n_;
+    for (auto &[k, d] : m.diag)
+      if (k) g = std::gcd(g, k);
+    g_ = g;
+    const int period = n_ / g_;
+    int tmin = 0, tmax = 0;
+    std::map<int, const std::vector<Complex> *> by_t;
+    for (auto &[k, d] : m.diag) {
+      int t = k / g_;
+      if (t > period / 2) t -= period;
+      by_t[t] = &d;
+      tmin = std::min(tmin, t);
+      tmax = std::max(tmax, t);
+    }
+    tmin_ = tmin;
+    gs_ = (tmax - tmin) / bs_ + 1;
+    pts_.resize(gs_);
+    for (int j = 0; j < gs_; j++) {
+      const int G = Giant(j);
+      for (int i = 0; i < bs_; i++) {
+        auto it = by_t.find(tmin + i + bs_ * j);
+        if (it == by_t.end()) continue;
+        // the giant rotation is applied after the product: pre-rotate by -G
+        std::vector<Complex> v(n_);
+        for (int p = 0; p < n_; p++) v[p] = (*it->second)[((p - G) % n_ + n_) % n_];
+        Pt pt;
+        ctx->encoder().Encode(pt, level, pt_scale_, v, 0);
+        pts_[j].emplace(i, std::move(pt));
+      }
+    }
+  }
+
+  int Giant(int j) const { return (((long long)g_ * (tmin_ + bs_ * j)) % n_ + n_) % n_; }
+  int Baby(int i) const { return ((long long)g_ * i) % n_; }
+
+  void AddRequiredRotations(std::set<int> &rots) const {
+    for (int i = 1; i < bs_; i++)
+      if (NeedsBaby(i)) rots.insert(Baby(i));
+    for (int j = 0; j < gs_; j++)
+      if (!pts_[j].empty() && Giant(j)) rots.insert(Giant(j));
+  }
+
+  void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &in, const EvkMap<word> &keys) const {
+    AssertTrue(ctx->param_.NPToLevel(in.GetNP()) == level_, "LinearTransform: wrong input level");
+    // baby steps: rotations of the input that share one ModUp
+    std::vector<int> rots;
+    std::vector<const EvaluationKey<word> *> rkeys;
+    std::vector<int> which;
+    for (int i = 1; i < bs_; i++)
+      if (NeedsBaby(i)) {
+        rots.push_back(Baby(i));
+        rkeys.push_back(&keys.GetRotationKey(Baby(i)));
+        which.push_back(i);
+      }
+    std::vector<Ct> rotated;
+    if (!rots.empty()) ctx->HoistedRotate(rotated, in, rots, rkeys);
+    std::map<int, const Ct *> baby;
+    baby[0] = &in;
+    for (size_t k = 0; k < which.size(); k++) baby[which[k]] = &rotated[k];
+    // giant steps
+    Ct total, acc, term, turned;
+    bool have_total = false;
+    for (int j = 0; j < gs_; j++) {
+      if (pts_[j].empty()) continue;
+      bool have_acc = false;
+      for (auto &[i, pt] : pts_[j]) {
+        if (!have_acc) {
+          ctx->Mult(acc, *baby.at(i), pt);
+          have_acc = true;
+        } else {
+          ctx->Mult(term, *baby.at(i), pt);
+          ctx->Add(acc, acc, term);
+        }
+      }
+      const int G = Giant(j);
+      const Ct *part = &acc;
+      if (G) {
+        ctx->HRot(turned, acc, keys.GetRotationKey(G), G);
+        part = &turned;
+      }
+      if (!have_total) {
+        ctx->Copy(total, *part);
+        have_total = true;
+      } else {
+        ctx->Add(total, total, *part);
+      }
+    }
+    ctx->Rescale(res, total);
+  }
+
+  int level() const { return level_; }
+
+ private:
+  bool NeedsBaby(int i) const {
+    for (auto &m : pts_)
+      if (m.count(i)) return true;
+    return false;
+  }
+  int level_, bs_, gs_ = 0, n_, g_ = 1, tmin_ = 0;
+  double pt_scale_ = 1.0;
+  std::vector<std::map<int, Pt>> pts_;  // [giant][baby]
+};
+
+// ------------------------------------------------------------ EvalPoly
+// Chebyshev-basis polynomial evaluation with exact scale tracking.
+template <typename word>
+class EvalPoly {
+  using Ct = Ciphertext<word>;
+  using Evk = EvaluationKey<word>;
+
+ public:
+  // res = 2*A*B - C (C may be null: 2*A*B - c0 with the real constant c0),
+  // one level below min(level A, level B)
+  static void Node(const ConstContextPtr<word> &ctx, Ct &res, const Ct &A, const Ct &B, const Ct *C,
+                   double c0, const Evk &mult_key) {
+    const auto &param = ctx->param_;
+    const int la = param.NPToLevel(A.GetNP()), lb = param.NPToLevel(B.GetNP());
+    const int l = Min(la, lb);
+    Ct a, b, prod, lin;
+    ctx->DropToLevel(a, A, l);
+    if (&A != &B) ctx->DropToLevel(b, B, l);
+    ctx->Mult(prod, a, &A != &B ? b : a);
+    ctx->Relinearize(lin, prod, mult_key);
+    ctx->Add(lin, lin, lin);
+    const double s = lin.GetScale();
+    if (C) {
+      Ct c, cs;
+      ctx->DropToLevel(c, *C, l);
+      Constant<word> one;
+      ctx->encoder().EncodeConstant(one, l, s / c.GetScale(), 1.0, 0);
+      ctx->Mult(cs, c, one);
+      cs.SetScale(s);
+      ctx->Sub(lin, lin, cs);
+    } else if (c0 != 0.0) {
+      Constant<word> k;
+      ctx->encoder().EncodeConstant(k, l, s, c0, 0);
+      ctx->Sub(lin, lin, k);
+    }
+    ctx->Rescale(res, lin);
+  }
+
+  // res = sum_k coeffs[k] T_k(x), x with slot values in [-1, 1]. The result
+  // sits ceil(log2(#coeffs)) levels below x, at scale target_scale.
+  static void EvaluateChebyshev(const ConstContextPtr<word> &ctx, Ct &res, const Ct &x,
+                                const std::vector<double> &coeffs, const Evk &mult_key,
+                                double target_scale) {
+    const auto &param = ctx->param_;
+    std::vector<double> c = coeffs;
+    while (c.size() > 2 && c.back() == 0.0) c.pop_back();
+    int k = 1;
+    while ((size_t(1) << k) < c.size()) k++;
+    // T_1, T_2, T_4, ... each one level below the previous
+    std::map<int, Ct> T;
+    ctx->Copy(T[1], x);
+    for (int j = 1; j < k; j++) Node(ctx, T[1 << j], T.at(1 << (j - 1)), T.at(1 << (j - 1)), nullptr, 1.0, mult_key);
+    const int top = param.NPToLevel(x.GetNP()) - (k - 1);
+    AssertTrue(top > 0, "EvaluateChebyshev: not enough levels");
+    Ct sum;
+    Sum(ctx, sum, c, target_scale * param.GetRescalePrimeProd(top), top, T, mult_key);
+    ctx->Rescale(res, sum);
+  }
+
+ private:
+  // res = sum_k c[k] T_k at level `level`, at scale W, not yet rescaled.
+  // T_{m+j} = 2 T_m T_j - T_{m-j} turns p into q * T_m + r with
+  //   q_0 = c_m, q_j = 2 c_{m+j};  r_0 = c_0, r_k = c_k - c_{2m-k}.
+  static void Sum(const ConstContextPtr<word> &ctx, Ct &res, const std::vector<double> &c, double W,
+                  int level, const std::map<int, Ct> &T, const Evk &mult_key) {
+    const auto &param = ctx->param_;
+    const int len = c.size();
+    auto add_const = [&](Ct &ct, double v) {
+      if (v == 0.0) return;
+      Constant<word> k0;
+      ctx->encoder().EncodeConstant(k0, level, W, v, 0);
+      ctx->Add(ct, ct, k0);
+    };
+    auto scaled = [&](Ct &out, const Ct &basis, double v) {  // v * basis at scale W
+      Ct b;
+      ctx->DropToLevel(b, basis, level);
+      Constant<word> k1;
+      ctx->encoder().EncodeConstant(k1, level, W / b.GetScale(), v, 0);
+      ctx->Mult(out, b, k1);
+      out.SetScale(W);
+    };
+    if (len <= 2) {
+      scaled(res, T.at(1), len == 2 ? c[1] : 0.0);
+      add_const(res, c[0]);
+      return;
+    }
+    int m = 1;
+    while (2 * m < len) m *= 2;
+    std::vector<double> q(len - m), r(m);
+    q[0] = c[m];
+    for (int j = 1; j < len - m; j++) q[j] = 2.0 * c[m + j];
+    for (int i = 0; i < m; i++) r[i] = c[i] - (i > 0 && 2 * m - i < len ? c[2 * m - i] : 0.0);
+    Ct high;
+    if (q.size() == 1) {
+      scaled(high, T.at(m), q[0]);
+    } else {
+      Ct tm, qsum, qv, prod;
+      ctx->DropToLevel(tm, T.at(m), level);
+      Sum(ctx, qsum, q, (W / tm.GetScale()) * param.GetRescalePrimeProd(level + 1), level + 1, T, mult_key);
+      ctx->Rescale(qv, qsum);
+      ctx->Mult(prod, qv, tm);
+      ctx->Relinearize(high, prod, mult_key);
+      high.SetScale(W);
+    }
+    bool r_zero = true;
+    for (double v : r) r_zero = r_zero && v == 0.0;
+    if (r_zero) {
+      res = std::move(high);
+      return;
+    }
+    while (r.size() > 1 && r.back() == 0.0) r.pop_back();
+    if (r.size() == 1) {
+      res = std::move(high);
+      add_const(res, r[0]);
+      return;
+    }
+    Ct low;
+    Sum(ctx, low, r, W, level, T, mult_key);
+    ctx->Add(res, high, low);
+  }
+
+ public:
+  // Chebyshev coefficients of f on [-1,1] (interpolation at `points` nodes)
+  static std::vector<double> ChebyshevCoefficients(const std::function<double(double)> &f, int degree,
+                                                   int points = 256) {
+    std::vector<double> c(degree + 1, 0.0);
+    for (int k = 0; k <= degree; k++) {
+      long double s = 0;
+      for (int j = 0; j < points; j++) {
+        const long double th = M_PIl * (j + 0.5L) / points;
+        s += (long double)f((double)std::cos(th)) * std::cos(k * th);
+      }
+      c[k] = (double)(s * (k == 0 ? 1.0L : 2.0L) / points);
+    }
+    return c;
+  }
+};
+
+// ------------------------------------------------------------ BootParameter
+struct BootParameter {
+  BootParameter(int max_level, int num_cts_levels, int num_stc_levels, int log_message_ratio = 5)
+      : max_level_{max_level},
+        num_cts_levels_{num_cts_levels},
+        num_stc_levels_{num_stc_levels},
+        log_message_ratio_{log_message_ratio} {}
+  const int max_level_, num_cts_levels_, num_stc_levels_, log_message_ratio_;
+  const int num_double_angle_ = 3;
+  const int K_ = 16;           // |u| = |m/q0 + I| stays below K
+  const int poly_degree_ = 30;  // even series in t, degree 15 in T_2(t)
+  // levels: 1 (T_2(t)) + 4 (series of 16 terms in T_2(t)) + double angles
+  int GetNumEvalModLevels() const { return 5 + num_double_angle_; }
+  int GetMaxLevel() const { return max_level_; }
+  int GetStartLevel() const { return max_level_; }
+  int GetCtSStartLevel() const { return max_level_; }
+  int GetEvalModStartLevel() const { return max_level_ - num_cts_levels_; }
+  int GetStCStartLevel() const { return GetEvalModStartLevel() - GetNumEvalModLevels(); }
+  int GetEndLevel() const { return GetStCStartLevel() - num_stc_levels_; }
+};
+
+// ------------------------------------------------------------ EvalMod
+// res ~ (1/2pi) sin(2pi u) for an input holding u/K (real slot values).
+template <typename word>
+class EvalMod {
+  using Ct = Ciphertext<word>;
+
+ public:
+  explicit EvalMod(const BootParameter &bp) : bp_(bp) {
+    const int r = bp.num_double_angle_;
+    const double K = bp.K_, amp = std::pow(0.5 / M_PI, 1.0 / (1 << r)), ang = 2.0 * M_PI * K / (1 << r);
+    auto f = [=](double t) { return amp * std::cos(ang * t); };  // even in t
+    std::vector<double> full = EvalPoly<word>::ChebyshevCoefficients(f, bp.poly_degree_);
+    // T_2k(t) = T_k(T_2(t)): the even coefficients are the series in s = T_2(t)
+    for (int k = 0; 2 * k <= bp.poly_degree_; k++) in_s_.push_back(full[2 * k]);
+  }
+
+  void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &input,
+                const EvaluationKey<word> &mult_key) const {
+    const auto &param = ctx->param_;
+    const int level = param.NPToLevel(input.GetNP());
+    // t = u/K - 1/(4K)
+    Constant<word> shift;
+    ctx->encoder().EncodeConstant(shift, level, input.GetScale(), 0.25 / bp_.K_, 0);
+    Ct t, s, y;
+    ctx->Sub(t, input, shift);
+    EvalPoly<word>::Node(ctx, s, t, t, nullptr, 1.0, mult_key);  // s = 2 t^2 - 1
+    EvalPoly<word>::EvaluateChebyshev(ctx, y, s, in_s_, mult_key, s.GetScale());
+    // y_i = (1/2pi)^(2^i / 2^r) cos(2^i theta): y <- 2 y^2 - (1/2pi)^(2^(i+1) / 2^r)
+    double c = std::pow(0.5 / M_PI, 1.0 / (1 << bp_.num_double_angle_));
+    for (int i = 0; i < bp_.num_double_angle_; i++) {
+      c *= c;
+      Ct next;
+      EvalPoly<word>::Node(ctx, next, y, y, nullptr, c, mult_key);
+      y = std::move(next);
+    }
+    res = std::move(y);
+  }
+
+ private:
+  BootParameter bp_;
+  std::vector<double> in_s_;
+};
+
+// ------------------------------------------------------------ EvalSpecialFFT
+// Stage matrices of the encoder's special FFT / IFFT without the bit-reversal
+// permutation, merged in groups.
+template <typename word>
+class EvalSpecialFFT {
+ public:
+  // one radix-2 stage of SpecialIFFT (reference src/core/Encode.cpp:85-109)
+  static StripedMatrix IfftStage(const Parameter<word> &param, int n, int stride) {
+    StripedMatrix m(n);
+    const int M = 2 * param.degree_, st8 = stride << 3, gap = M / st8;
+    auto &d0 = m.At(0), &dp = m.At(stride), &dm = m.At(-stride);
+    for (int i = 0; i < n; i += 2 * stride)
+      for (int j = 0; j < stride; j++) {
+        const int idx = ((st8 - (param.GetGaloisFactor(j) % st8)) * gap) % M;
+        const Complex tw = std::polar(1.0, 2.0 * M_PI * idx / M);
+        d0[i + j] += 1.0;
+        dp[i + j] += 1.0;
+        d0[i + j + stride] += -tw;
+        dm[i + j + stride] += tw;
+      }
+    return m;
+  }
+  // one radix-2 stage of SpecialFFT (reference src/core/Encode.cpp:111-133)
+  static StripedMatrix FftStage(const Parameter<word> &param, int n, int stride) {
+    StripedMatrix m(n);
+    const int M = 2 * param.degree_, st8 = stride << 3, gap = M / st8;
+    auto &d0 = m.At(0), &dp = m.At(stride), &dm = m.At(-stride);
+    for (int i = 0; i < n; i += 2 * stride)
+      for (int j = 0; j < stride; j++) {
+        const int idx = ((param.GetGaloisFactor(j) % st8) * gap) % M;
+        const Complex tw = std::polar(1.0, 2.0 * M_PI * idx / M);
+        d0[i + j] += 1.0;
+        dp[i + j] += tw;
+        d0[i + j + stride] += -tw;
+        dm[i + j + stride] += 1.0;
+      }
+    return m;
+  }
+  // Groups of merged stages, in application order. CtS: IFFT stages from the
+  // largest stride down; StC: FFT stages from stride 1 up. `total_const` is
+  // spread evenly over the groups.
+  static std::vector<StripedMatrix> Groups(const Parameter<word> &param, int n, bool cts, int groups,
+                                           double total_const) {
+    std::vector<int> strides;
+    if (cts)
+      for (int s = n / 2; s >= 1; s /= 2) strides.push_back(s);
+    else
+      for (int s = 1; s < n; s *= 2) strides.push_back(s);
+    const int per = ((int)strides.size() + groups - 1) / groups;
+    const double each = std::pow(total_const, 1.0 / groups);
+    std::vector<StripedMatrix> out;
+    for (size_t at = 0; at < strides.size(); at += per) {
+      StripedMatrix g = cts ? IfftStage(param, n, strides[at]) : FftStage(param, n, strides[at]);
+      for (size_t k = at + 1; k < std::min(strides.size(), at + per); k++) {
+        StripedMatrix next = cts ? IfftStage(param, n, strides[k]) : FftStage(param, n, strides[k]);
+        g = StripedMatrix::Mult(next, g);
+      }
+      g.Scale(each);
+      out.push_back(std::move(g));
+    }
+    return out;
+  }
+};
+
+// ------------------------------------------------------------ BootContext
+// A Context that can also refresh a ciphertext (reference
+// include/extension/BootContext.h, src/extension/BootContext.cpp).
+template <typename word>
+class BootContext : public Context<word> {
+  using Base = Context<word>;
+  using Ct = Ciphertext<word>;
+  using Evk = EvaluationKey<word>;
+  using Dv = DeviceVector<word>;
+
+ public:
+  static std::shared_ptr<BootContext<word>> Create(const Parameter<word> &param,
+                                                   const BootParameter &boot_param) {
+    return std::shared_ptr<BootContext<word>>(new BootContext<word>(param, boot_param));
+  }
+  ConstContextPtr<word> GetContext() const { return this->shared_from_this(); }
+
+  const BootParameter boot_param_;
+
+  void PrepareEvalMod() {
+    if (eval_mod_) {
+      Warn("EvalMod already prepared");
+      return;
+    }
+    eval_mod_ = std::make_unique<EvalMod<word>>(boot_param_);
+  }
+
+  // Only full-slot bootstrapping: num_slots must be degree / 2.
+  void PrepareEvalSpecialFFT(int num_slots) {
+    const auto &param = this->param_;
+    AssertTrue(num_slots == param.degree_ / 2, "Only full-slot bootstrapping is supported");
+    if (!cts_.empty()) {
+      Warn("EvalSpecialFFT already prepared");
+      return;
+    }
+    const int n = num_slots;
+    // CoeffToSlot: the raised ciphertext holds the integer polynomial q0 * u(X);
+    // read at scale q0 its slots are SpecialFFT(u_j + i u_{j+n}). The groups
+    // apply the inverse transform, its 1/n, and 1/(2K), so that the real and
+    // imaginary parts taken afterwards (each a sum of two terms) are u / K.
+    auto cts = EvalSpecialFFT<word>::Groups(param, n, true, boot_param_.num_cts_levels_,
+                                            1.0 / ((double)n * 2.0 * boot_param_.K_));
+    double s_in = q0_prod_;
+    int level = boot_param_.GetCtSStartLevel();
+    for (auto &g : cts) {
+      cts_.emplace_back(GetContext(), g, level, s_in, eval_mod_scale_, kBabySteps);
+      s_in = eval_mod_scale_;
+      level--;
+    }
+    // SlotToCoeff: the slots hold (p_j + i p_{j+n}) / q0 for the refreshed
+    // plaintext p = scale0' * m; the forward transform and q0 / scale0' give m.
+    // The scale drops from EvalMod's to the end level's in equal steps, which
+    // keeps every diagonal plaintext well above the rounding of its encoding.
+    auto stc = EvalSpecialFFT<word>::Groups(param, n, false, boot_param_.num_stc_levels_,
+                                            q0_prod_ / boot_input_scale_);
+    level = boot_param_.GetStCStartLevel();
+    s_in = eval_mod_end_scale_;
+    const double s_end = param.GetScale(boot_param_.GetEndLevel());
+    const int ng = stc.size();
+    for (int i = 0; i < ng; i++) {
+      const double s_out = i + 1 == ng ? s_end : s_in * std::pow(s_end / s_in, 1.0 / (ng - i));
+      stc_.emplace_back(GetContext(), stc[i], level, s_in, s_out, kBabySteps);
+      s_in = s_out;
+      level--;
+    }
+  }
+
+  bool IsBootPrepared(int num_slots) const {
+    return eval_mod_ && !cts_.empty() && num_slots == this->param_.degree_ / 2;
+  }
+
+  void AddRequiredRotations(EvkRequest &req, int num_slots) const {
+    AssertTrue(IsBootPrepared(num_slots), "Bootstrapping is not prepared for this slot count");
+    std::set<int> rots;
+    for (auto &lt : cts_) lt.AddRequiredRotations(rots);
+    for (auto &lt : stc_) lt.AddRequiredRotations(rots);
+    for (int r : rots) req.AddRequest(r, boot_param_.GetMaxLevel());
+  }
+
+  // Raises a ciphertext on the lowest level's primes to the highest level:
+  // exact centred lift of both parts (reference ModUpToMax,
+  // src/extension/BootContext.cpp:188-277). With sparse-secret encapsulation
+  // the lift is wrapped in a switch to the sparse secret and back; the lifted
+  // a part is produced on the auxiliary primes as well, so that the switch
+  // back is one product with a single-digit key and one ModDown.
+  void ModUpToMax(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
+    const auto &param = this->param_;
+    const int n = param.degree_, L = param.L_, alpha = param.alpha_;
+    NPInfo low = param.LevelToNP(-1), top = param.LevelToNP(param.max_level_);
+    AssertTrue(input.GetNP() == low, "ModUpToMax: input NP mismatch");
+    AssertFalse(input.HasRx(), "ModUpToMax: input has Rx");
+    AssertTrue(top.GetNumQ() == L, "ModUpToMax: the top level must hold every prime");
+    const bool sse = param.IsUsingSparseSecretEncapsulation();
+    Ct switched;
+    const Ct *work = &input;
+    if (sse) {
+      this->MultKey(switched, input, evk_map.GetDenseToSparseKey());
+      work = &switched;
+    }
+    auto g_low = param.GetLimbIndices(low);
+    auto g_top = param.GetLimbIndices(top);
+    auto g_all = param.GetLimbIndices(param.LevelToNP(param.max_level_, alpha));
+    const int nl = g_low.size();
+    AssertTrue(nl <= 2, "ModUpToMax: at most two base primes");
+    // (N * product of the other base primes)^-1 on each base prime
+    std::vector<word> icrt(nl);
+    auto primes = param.GetPrimeVector(low);
+    for (int i = 0; i < nl; i++) {
+      word prod = (word)(n % primes[i]);
+      for (int j = 0; j < nl; j++)
+        if (j != i) prod = detail::MulMod(prod, primes[j] % primes[i], primes[i]);
+      icrt[i] = detail::InvMod(prod, primes[i]);
+    }
+    auto raise = [&](Dv &dst, const Dv &src, const std::vector<int> &g_dst) {
+      Dv coef((size_t)nl * n);
+      CheckAbi(cfhe_intt(this->h_, coef.data(), src.data(), g_low.data(), nl, 1, 0, 0, icrt.data(), 0, 0));
+      dst.resize(g_dst.size() * n);
+      CheckAbi(cfhe_modup_to_max(this->h_, dst.data(), coef.data(), g_low.data(), nl, g_dst.data(),
+                                 g_dst.size()));
+      CheckAbi(cfhe_ntt(this->h_, dst.data(), dst.data(), g_dst.data(), g_dst.size(), 1, 0, 0, 1));
+      this->Synchronize();
+    };
+    Ct out(top);
+    if (!sse) {
+      raise(out.bx_, work->bx_, g_top);
+      raise(out.ax_, work->ax_, g_top);
+    } else {
+      const Evk &key = evk_map.GetSparseToDenseKey();
+      AssertTrue(key.GetNP() == param.LevelToNP(param.max_level_, alpha), "Invalid sparse-to-dense key");
+      Dv b_up, a_up;
+      raise(b_up, work->bx_, g_top);
+      raise(a_up, work->ax_, g_all);
+      const size_t ext = (size_t)(L + alpha) * n;
+      Dv acc(2 * ext);
+      // acc_b = a * key_b + P * b on the Q limbs; acc_a = a * key_a
+      CheckAbi(cfhe_binary(this->h_, 3, acc.data(), a_up.data(), key.bx_[0].data(), g_all.data(), g_all.size()));
+      CheckAbi(cfhe_binary(this->h_, 3, acc.data() + ext, a_up.data(), key.ax_[0].data(), g_all.data(),
+                           g_all.size()));
+      std::vector<word> p_prod(L);
+      for (int i = 0; i < L; i++) {
+        const word q = cfhe_prime(this->h_, g_top[i]);
+        word pp = 1;
+        for (int j = 0; j < alpha; j++) pp = detail::MulMod(pp, param.aux_primes_[j] % q, q);
+        p_prod[i] = detail::ToMontgomery(pp, q);
+      }
+      CheckAbi(cfhe_const_op(this->h_, 4, acc.data(), b_up.data(), acc.data(), p_prod.data(), g_top.data(), L));
+      Dv both((size_t)2 * L * n);
+      CheckAbi(cfhe_moddown(this->h_, param.max_level_, 0, both.data(), acc.data(), 2, (long long)L * n,
+                            (long long)ext));
+      std::vector<word> zero(L, 0);
+      this->ConstKernel(0, out.bx_.data(), both.data(), nullptr, zero, top);
+      this->ConstKernel(0, out.ax_.data(), both.data() + (size_t)L * n, nullptr, zero, top);
+      this->Synchronize();
+    }
+    out.SetScale(input.GetScale());
+    out.SetNumSlots(input.GetNumSlots());
+    res = std::move(out);
+  }
+
+  void CoeffToSlot(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
+    RunGroups(res, input, cts_, evk_map);
+  }
+  void SlotToCoeff(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
+    RunGroups(res, input, stc_, evk_map);
+  }
+  void EvaluateMod(Ct &res, const Ct &input, const Evk &mult_key) const {
+    AssertTrue(eval_mod_ != nullptr, "EvalMod not prepared");
+    this->AssertSameScale(input.GetScale(), eval_mod_scale_);
+    eval_mod_->Evaluate(GetContext(), res, input, mult_key);
+    this->AssertSameScale(res.GetScale(), eval_mod_end_scale_);
+  }
+
+  // Refreshes a level-0 ciphertext with slot values in [-1, 1]^2 to
+  // boot_param_.GetEndLevel() (reference Boot, src/extension/BootContext.cpp:299-365).
+  void Boot(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
+    const auto &param = this->param_;
+    AssertTrue(IsBootPrepared(input.GetNumSlots()), "Boot: not prepared for this slot count");
+    AssertTrue(param.NPToLevel(input.GetNP()) <= 0, "Boot: bring the input to level 0 first");
+    AssertFalse(input.HasRx(), "Boot: relinearize first");
+    this->AssertSameScale(input.GetScale() * (double)(UINT64_C(1) << log_scaleup_), boot_input_scale_);
+    // 0. integer scale-up: the plaintext fills q0 / 2^log_message_ratio
+    Ct main;
+    {
+      NPInfo low = input.GetNP();
+      main.ModifyNP(low);
+      auto primes = param.GetPrimeVector(low);
+      std::vector<word> k(primes.size());
+      for (size_t i = 0; i < primes.size(); i++)
+        k[i] = detail::ToMontgomery((word)((UINT64_C(1) << log_scaleup_) % primes[i]), primes[i]);
+      this->ConstKernel(3, main.bx_.data(), input.bx_.data(), nullptr, k, low);
+      this->ConstKernel(3, main.ax_.data(), input.ax_.data(), nullptr, k, low);
+      main.SetNumSlots(input.GetNumSlots());
+      main.SetScale(boot_input_scale_);
+    }
+    // 1. to the top level
+    Ct raised;
+    ModUpToMax(raised, main, evk_map);
+    raised.SetScale(q0_prod_);
+    // 2. coefficients to slots
+    Ct slots;
+    CoeffToSlot(slots, raised, evk_map);
+    // 3. real and imaginary parts, each through EvalMod
+    Ct conj, re, im;
+    this->HConj(conj, slots, evk_map.GetConjugationKey());
+    this->Add(re, slots, conj);
+    this->Sub(im, conj, slots);
+    this->MultImaginaryUnit(im, im);
+    Ct re_mod, im_mod;
+    EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
+    EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
+    this->MultImaginaryUnit(im_mod, im_mod);
+    this->Add(re_mod, re_mod, im_mod);
+    // 4. slots to coefficients
+    SlotToCoeff(res, re_mod, evk_map);
+    res.SetNumSlots(input.GetNumSlots());
+  }
+
+  int GetLogScaleUp() const { return log_scaleup_; }
+
+ private:
+  static constexpr int kBabySteps = 8;
+
+  BootContext(const Parameter<word> &param, const BootParameter &bp) : Base(param), boot_param_{bp} {
+    AssertTrue(param.max_level_ == bp.max_level_ && param.default_encryption_level_ == bp.GetStCStartLevel(),
+               "Parameter mismatch for BootContext");
+    auto round_log2 = [](double x) { return (int)std::floor(std::log2(x) + 0.5); };
+    q0_prod_ = 1.0;
+    for (word q : param.GetPrimeVector(param.LevelToNP(-1))) q0_prod_ *= (double)q;
+    // level-0 scale times 2^log_scaleup ~ q0 / 2^log_message_ratio
+    // (reference src/extension/BootContext.cpp:47-66)
+    log_scaleup_ = round_log2(q0_prod_) - round_log2(param.base_scale_) - bp.log_message_ratio_;
+    AssertTrue(log_scaleup_ >= 0, "Invalid level zero scaleup");
+    boot_input_scale_ = param.base_scale_ * (double)(UINT64_C(1) << log_scaleup_);
+    const int em = bp.GetEvalModStartLevel();
+    eval_mod_scale_ = std::ldexp(1.0, round_log2(param.GetRescalePrimeProd(em)));
+    // EvalMod: T_2(t) squares the scale once, the series keeps it, every
+    // double-angle step squares it again
+    eval_mod_end_scale_ = eval_mod_scale_ * eval_mod_scale_ / param.GetRescalePrimeProd(em);
+    for (int i = 0; i < bp.num_double_angle_; i++)
+      eval_mod_end_scale_ = eval_mod_end_scale_ * eval_mod_end_scale_ /
+                            param.GetRescalePrimeProd(em - bp.GetNumEvalModLevels() + bp.num_double_angle_ - i);
+  }
+
+  void RunGroups(Ct &res, const Ct &input, const std::vector<LinearTransform<word>> &groups,
+                 const EvkMap<word> &evk_map) const {
+    AssertFalse(groups.empty(), "EvalSpecialFFT not prepared");
+    Ct cur, next;
+    const Ct *in = &input;
+    for (auto &lt : groups) {
+      lt.Evaluate(GetContext(), next, *in, evk_map);
+      cur = std::move(next);
+      in = &cur;
+    }
+    res = std::move(cur);
+  }
+
+  double q0_prod_ = 1.0, boot_input_scale_ = 1.0, eval_mod_scale_ = 1.0, eval_mod_end_scale_ = 1.0;
+  int log_scaleup_ = 0;
+  std::unique_ptr<EvalMod<word>> eval_mod_;
+  std::vector<LinearTransform<word>> cts_, stc_;
+};
+
+}  // namespace cheddar

@@ -577,6 +577,8 @@ template <typename word>
 class Context;
 template <typename word>
 using ContextPtr = std::shared_ptr<Context<word>>;
+template <typename word>
+using ConstContextPtr = std::shared_ptr<const Context<word>>;
 
 // ---------------------------------------------------------------- Encoder
 // CKKS encoding on the host (reference src/core/Encode.cpp); only the final
@@ -725,7 +727,8 @@ class Encoder {
 
 // ---------------------------------------------------------------- Context
 template <typename word>
-class Context {
+class Context : public std::enable_shared_from_this<Context<word>> {
+ protected:
   using Ct = Ciphertext<word>;
   using Pt = Plaintext<word>;
   using Const = Constant<word>;
@@ -755,7 +758,7 @@ class Context {
   }
   Context(const Context &) = delete;
   Context &operator=(const Context &) = delete;
-  ~Context() {
+  virtual ~Context() {
     encoder_.reset();
     if (detail::CurrentHandle() == h_) detail::CurrentHandle() = nullptr;
     cfhe_context_destroy(h_);
@@ -982,12 +985,70 @@ class Context {
     res = std::move(out);
   }
 
+  // Keeps only the limbs of `target_level` (the levels must be nested: every
+  // prime of the target level is present in a). The scale is unchanged. This is
+  // the limb-dropping half of the reference's LevelDown
+  // (src/core/Context.cpp:872-949), without its scale correction.
+  void DropToLevel(Ct &res, const Ct &a, int target_level) const {
+    NPInfo np = a.GetNP(), tnp = param_.LevelToNP(target_level);
+    AssertTrue(tnp.IsSubsetOf(np), "DropToLevel: levels are not nested");
+    if (tnp == np) {
+      Copy(res, a);
+      return;
+    }
+    AssertTrue(&res != &a, "DropToLevel cannot run in place");
+    const size_t off = (size_t)(np.num_ter_ - tnp.num_ter_) * param_.degree_;
+    Ct out(tnp);
+    if (a.HasRx()) out.PrepareRx();
+    std::vector<word> zero(tnp.GetNumTotal(), 0);
+    ConstKernel(0, out.bx_.data(), a.bx_.data() + off, nullptr, zero, tnp);
+    ConstKernel(0, out.ax_.data(), a.ax_.data() + off, nullptr, zero, tnp);
+    if (a.HasRx()) ConstKernel(0, out.rx_.data(), a.rx_.data() + off, nullptr, zero, tnp);
+    out.SetScale(a.GetScale());
+    out.SetNumSlots(a.GetNumSlots());
+    res = std::move(out);
+  }
+
+  // Rotations of one ciphertext by several distances with a single ModUp
+  // (the reference's HoistHandler baby step, src/extension/Hoist.cu:578-691).
+  // keys[i] is the rotation key for rot_dists[i] (distances in (0, num_slots)).
+  void HoistedRotate(std::vector<Ct> &res, const Ct &a, const std::vector<int> &rot_dists,
+                     const std::vector<const Evk *> &keys) const {
+    AssertFalse(a.HasRx(), "HoistedRotate: relinearize first");
+    AssertTrue(rot_dists.size() == keys.size() && !rot_dists.empty(), "HoistedRotate: bad arguments");
+    NPInfo np = a.GetNP();
+    const int level = param_.NPToLevel(np), beta = cfhe_beta(h_, level);
+    const size_t words = (size_t)np.GetNumQ() * param_.degree_;
+    std::vector<const word *> kb, ka;
+    for (const Evk *k : keys) {
+      CheckKey(*k, level);
+      AssertTrue(k->GetNP().num_main_ == keys[0]->GetNP().num_main_, "HoistedRotate: key shapes differ");
+      for (int j = 0; j < beta; j++) {
+        kb.push_back(k->bx_[j].data());
+        ka.push_back(k->ax_[j].data());
+      }
+    }
+    DeviceVector<word> out(2 * words * rot_dists.size());
+    CheckAbi(cfhe_hoisted_rotations(h_, level, out.data(), a.bx_.data(), a.ax_.data(), rot_dists.size(),
+                                    rot_dists.data(), kb.data(), ka.data(), keys[0]->GetNP().num_main_));
+    res.clear();
+    std::vector<word> zero(np.GetNumTotal(), 0);
+    for (size_t i = 0; i < rot_dists.size(); i++) {
+      res.emplace_back(np);
+      ConstKernel(0, res[i].bx_.data(), out.data() + 2 * i * words, nullptr, zero, np);
+      ConstKernel(0, res[i].ax_.data(), out.data() + (2 * i + 1) * words, nullptr, zero, np);
+      res[i].SetScale(a.GetScale());
+      res[i].SetNumSlots(a.GetNumSlots());
+    }
+    Synchronize();
+  }
+
   void AssertSameScale(double s1, double s2) const {
     // relative tolerance of the reference (src/core/Context.cpp:53-60)
     AssertTrue(std::abs(s1 - s2) <= 1e-12 * std::abs(s1), "Scale mismatch");
   }
 
- private:
+ protected:
   template <typename A, typename B>
   void AssertSameNP(const A &a, const B &b) const {
     AssertTrue(a.GetNP() == b.GetNP(), "NP mismatch");
@@ -1122,9 +1183,30 @@ class EvkMap : public std::map<int, EvaluationKey<word>> {
   // indices of the non-rotation keys (reference include/core/EvkMap.h:23-26)
   static constexpr int kMultiplicationKeyIndex = 0;
   static constexpr int kConjugationKeyIndex = -1;
-  const EvaluationKey<word> &GetRotationKey(int r) const { return this->at(r); }
+  static constexpr int kDenseToSparseKeyIndex = -2;
+  static constexpr int kSparseToDenseKeyIndex = -3;
+  const EvaluationKey<word> &GetDenseToSparseKey() const { return this->at(kDenseToSparseKeyIndex); }
+  const EvaluationKey<word> &GetSparseToDenseKey() const { return this->at(kSparseToDenseKeyIndex); }
+  const EvaluationKey<word> &GetRotationKey(int r) const {
+    auto it = this->find(r);
+    AssertTrue(it != this->end(), "Rotation key " + std::to_string(r) + " is not prepared");
+    return it->second;
+  }
   const EvaluationKey<word> &GetMultiplicationKey() const { return this->at(kMultiplicationKeyIndex); }
   const EvaluationKey<word> &GetConjugationKey() const { return this->at(kConjugationKeyIndex); }
+};
+
+// rotation distance -> highest level the key must serve (reference
+// include/core/EvkRequest.h)
+class EvkRequest : public std::map<int, int> {
+ public:
+  void AddRequest(int rot_idx, int level) {
+    auto it = this->find(rot_idx);
+    if (it == this->end())
+      this->emplace(rot_idx, level);
+    else
+      it->second = Max(it->second, level);
+  }
 };
 
 // ---------------------------------------------------------------- UserInterface
@@ -1204,6 +1286,10 @@ class UserInterface {
                           cfhe_galois_for_rotation(context_->h_, half - rot_idx), g.data(), g.size()));
     PrepareEvk(rot_idx, GetNPForEvk(max_level), s_rot, main_secret_);
   }
+  void PrepareRotationKey(const EvkRequest &req) {
+    for (auto &[rot, level] : req)
+      if (evk_map_.find(rot) == evk_map_.end()) PrepareRotationKey(rot, level);
+  }
 
  private:
   static constexpr double kErrorStandardDeviation = 3.2;
@@ -1239,7 +1325,11 @@ class UserInterface {
     CheckAbi(cfhe_ntt(context_->h_, dst.data(), dst.data(), g.data(), nt, 1, 0, 0, 1));
   }
 
-  void PrepareSecrets() { SampleTernary(main_secret_, context_->param_.GetDenseHammingWeight()); }
+  void PrepareSecrets() {
+    const auto &param = context_->param_;
+    SampleTernary(main_secret_, param.GetDenseHammingWeight());
+    if (param.IsUsingSparseSecretEncapsulation()) SampleTernary(sparse_secret_, param.GetSparseHammingWeight());
+  }
 
   void PrepareBasicEvks() {
     const auto &param = context_->param_;
@@ -1252,14 +1342,23 @@ class UserInterface {
     CheckAbi(cfhe_permute(context_->h_, sc.data(), main_secret_.data(), nullptr,
                           cfhe_galois_for_rotation(context_->h_, -1), g.data(), g.size()));
     PrepareEvk(EvkMap<word>::kConjugationKeyIndex, np, sc, main_secret_);
+    if (param.IsUsingSparseSecretEncapsulation()) {
+      // dense -> sparse at the lowest level; sparse -> dense at the highest,
+      // with P * s_sparse on every limb of a single digit (the reference sums
+      // the digits of an ordinary key, src/UserInterface.cu:341-362)
+      PrepareEvk(EvkMap<word>::kDenseToSparseKeyIndex, GetNPForEvk(0), sparse_secret_, main_secret_);
+      PrepareEvk(EvkMap<word>::kSparseToDenseKeyIndex, np, main_secret_, sparse_secret_, true);
+    }
   }
 
   // digit i: b_i = e_i - a_i * s_enc, plus P * s_target on the digit's own limbs
   // (reference src/UserInterface.cu:366-458); both secrets live on every prime.
-  void PrepareEvk(int key_idx, const NPInfo &np, const Dv &enc_secret, const Dv &target_secret) {
+  void PrepareEvk(int key_idx, const NPInfo &np, const Dv &enc_secret, const Dv &target_secret,
+                  bool single_digit = false) {
     const auto &param = context_->param_;
-    const int n = param.degree_, alpha = param.alpha_, L = param.L_;
-    const int num_q = np.GetNumQ(), beta = DivCeil(num_q, np.num_aux_);
+    const int n = param.degree_, L = param.L_;
+    const int num_q = np.GetNumQ(), alpha = single_digit ? num_q : param.alpha_;
+    const int beta = single_digit ? 1 : DivCeil(num_q, np.num_aux_);
     auto g = param.GetLimbIndices(np);
     cfhe_context *h = context_->h_;
     Dv s_enc = SecretLimbs(enc_secret, np), s_tgt = SecretLimbs(target_secret, np);
@@ -1326,6 +1425,7 @@ class UserInterface {
   NPInfo all_np_;
   std::vector<word> all_primes_;  // every prime, global order (index = limb index g)
   Dv main_secret_;                // NTT, M-form, on every prime
+  Dv sparse_secret_;              // same layout; only with sparse-secret encapsulation
   EvkMap<word> evk_map_;
 };
 

@@ -129,6 +129,17 @@ CFHE_API int cfhe_mul_imag_unit(cfhe_context *ctx, uint32_t *dst,
                                 const uint32_t *src, const int *gidx,
                                 int n_limbs);
 
+/* Exact lift of a one- or two-limb value to other primes:
+ * ElementWiseHandler::ModUpToMax (:1646; kernels :579-623), used by
+ * BootContext::ModUpToMax. src holds plain coefficients; in the two-limb case
+ * limb k must already be multiplied by (q_other)^-1 mod q_k (as the
+ * reference's INTTAndMultConst with mod_max_intt_const_ does,
+ * src/extension/BootContext.cpp:93-108). dst: plain coefficients mod each
+ * destination prime, centred lift. */
+CFHE_API int cfhe_modup_to_max(cfhe_context *ctx, uint32_t *dst,
+                               const uint32_t *src, const int *src_gidx,
+                               int n_src, const int *dst_gidx, int n_dst);
+
 /* ---- mod-switch (ModSwitchHandler, src/core/ModSwitch.cu) ---- */
 /* Base conversion of centred, pre-scaled coefficients y[n_src][N] (int32) to
  * M-form coefficients on the destination primes: the kernel

@@ -1,0 +1,203 @@
+// Tests of the bootstrapping building blocks and of full bootstrapping on the
+// C++ mirror of the reference API (the reference's boot_test checks Boot on
+// 2^15 random complex slots in [-1,1]^2, unittest/Bootstrapping.cpp:10-41).
+//
+//   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot]
+#include <chrono>
+#include <cstring>
+#include <iomanip>
+
+#include "cheddar/Boot.h"
+
+using namespace cheddar;
+using word = uint32_t;
+using Ct = Ciphertext<word>;
+using Pt = Plaintext<word>;
+using Msg = std::vector<Complex>;
+
+static int failures = 0;
+
+static void Report(const std::string &what, const Msg &expected, const Msg &got, double tol) {
+  double worst = 0, sum = 0;
+  for (size_t i = 0; i < expected.size(); i++) {
+    const double d = std::abs(expected[i] - got[i]);
+    worst = std::max(worst, d);
+    sum += d;
+  }
+  const bool ok = worst <= tol;
+  std::cout << (ok ? "[ OK ] " : "[FAIL] ") << what << "  max|diff| " << std::scientific
+            << std::setprecision(3) << worst << "  precision " << std::fixed << std::setprecision(2)
+            << -std::log2(sum / expected.size()) << " bits" << std::endl;
+  if (!ok) failures++;
+}
+
+int main(int argc, char **argv) {
+  if (argc < 2) {
+    std::cerr << "usage: boot_test <parameter.json> [--only a,b]\n";
+    return 2;
+  }
+  std::set<std::string> only;
+  for (int i = 2; i < argc; i++)
+    if (!strcmp(argv[i], "--only") && i + 1 < argc) {
+      std::stringstream ss(argv[++i]);
+      std::string t;
+      while (std::getline(ss, t, ',')) only.insert(t);
+    }
+  auto want = [&](const char *n) { return only.empty() || only.count(n); };
+  Random::Seed(0xC0FFEE04);
+  ParameterJson json = LoadParameterJson(argv[1]);
+  auto param = MakeParameter<word>(json);
+  AssertTrue(json.boot, "the parameter file does not enable bootstrapping");
+  BootParameter boot_param(param->max_level_, json.num_cts_levels, json.num_stc_levels);
+  auto boot_ctx = BootContext<word>::Create(*param, boot_param);
+  ContextPtr<word> ctx = boot_ctx;
+  UserInterface<word> ui(ctx);
+  const int n = param->degree_ / 2;
+  auto scale_of = [&](int level) {
+    return level <= param->default_encryption_level_ ? param->GetScale(level)
+                                                     : param->GetRescalePrimeProd(level);
+  };
+  auto encrypt = [&](Ct &ct, const Msg &m, int level, double scale) {
+    Pt pt;
+    ctx->encoder().Encode(pt, level, scale, m, 0);
+    ui.Encrypt(ct, pt);
+  };
+  auto decrypt = [&](Msg &m, const Ct &ct) {
+    Pt pt;
+    ui.Decrypt(pt, ct);
+    ctx->encoder().Decode(m, pt);
+  };
+  auto random_msg = [&](Msg &m, double lo, double hi, bool complex) {
+    m.assign(n, Complex(0, 0));
+    Random::SampleUniformComplex(m.data(), n, lo, hi);
+    if (!complex)
+      for (auto &x : m) x = Complex(x.real(), 0);
+  };
+
+  if (want("linear")) {
+    // striped matrix with offsets that are multiples of 16, t in [-10, 20]
+    const int level = 20;
+    StripedMatrix M(n);
+    for (int t : {-10, -3, -1, 0, 1, 2, 7, 8, 9, 15, 16, 20}) {
+      auto &d = M.At(16 * t);
+      Random::SampleUniformComplex(d.data(), n, -1.0, 1.0);
+    }
+    Msg z, got;
+    random_msg(z, -1, 1, true);
+    Ct ct, out;
+    const double s = scale_of(level);
+    encrypt(ct, z, level, s);
+    LinearTransform<word> lt(ctx, M, level, s, s, 8);
+    std::set<int> rots;
+    lt.AddRequiredRotations(rots);
+    for (int r : rots) ui.PrepareRotationKey(r, param->max_level_);
+    lt.Evaluate(ctx, out, ct, ui.GetEvkMap());
+    decrypt(got, out);
+    Report("LinearTransform (12 diagonals, BSGS 8 x 4, level 20)", M.Apply(z), got, 1e-4);
+    std::cout << "       rotations used: " << rots.size() << std::endl;
+  }
+
+  if (want("poly")) {
+    const int level = 24;
+    std::vector<double> c(16);
+    for (auto &x : c) {
+      Complex t;
+      Random::SampleUniformComplex(&t, 1, -1.0, 1.0);
+      x = t.real();
+    }
+    Msg x, got, expect;
+    random_msg(x, -1, 1, false);
+    for (auto &v : x) {
+      // Clenshaw in double
+      double b1 = 0, b2 = 0, t = v.real();
+      for (int k = 15; k >= 1; k--) {
+        double b0 = c[k] + 2 * t * b1 - b2;
+        b2 = b1;
+        b1 = b0;
+      }
+      expect.push_back(Complex(c[0] + t * b1 - b2, 0));
+    }
+    Ct ct, out;
+    const double s = (double)(UINT64_C(1) << (int)std::lround(std::log2(scale_of(level))));
+    encrypt(ct, x, level, s);
+    EvalPoly<word>::EvaluateChebyshev(ctx, out, ct, c, ui.GetMultiplicationKey(), s);
+    decrypt(got, out);
+    std::cout << "       output level " << param->NPToLevel(out.GetNP()) << std::endl;
+    Report("EvalPoly Chebyshev degree 15 (level 24)", expect, got, 1e-5);
+  }
+
+  if (want("evalmod")) {
+    const BootParameter &bp = boot_param;
+    const int level = bp.GetEvalModStartLevel();
+    EvalMod<word> em(bp);
+    Msg u, got, expect;
+    random_msg(u, -1, 1, false);
+    // u = I + eps with |I| <= 12 and |eps| <= 2^-8
+    for (auto &v : u) {
+      const double I = std::floor(v.real() * 12.0 + 0.5);
+      Complex e;
+      Random::SampleUniformComplex(&e, 1, -1.0, 1.0);
+      const double eps = e.real() / 256.0;
+      expect.push_back(Complex(eps, 0));
+      v = Complex((I + eps) / bp.K_, 0);
+    }
+    Ct ct, out;
+    const double s = (double)(UINT64_C(1) << (int)std::lround(std::log2(scale_of(level))));
+    encrypt(ct, u, level, s);
+    em.Evaluate(ctx, out, ct, ui.GetMultiplicationKey());
+    decrypt(got, out);
+    std::cout << "       levels " << level << " -> " << param->NPToLevel(out.GetNP()) << std::endl;
+    // sin(2 pi eps)/(2 pi) ~ eps up to eps^3
+    Report("EvalMod (K = 16)", expect, got, 2e-6);
+  }
+
+  if (want("fft")) {
+    // host-side consistency of the merged stage matrices: StC o CtS = n * identity
+    auto cts = EvalSpecialFFT<word>::Groups(*param, n, true, boot_param.num_cts_levels_, 1.0);
+    auto stc = EvalSpecialFFT<word>::Groups(*param, n, false, boot_param.num_stc_levels_, 1.0);
+    Msg z;
+    random_msg(z, -1, 1, true);
+    Msg v = z;
+    for (auto &g : cts) v = g.Apply(v);
+    for (auto &g : stc) v = g.Apply(v);
+    for (auto &x : v) x /= n;
+    size_t diags = 0;
+    for (auto &g : cts) diags += g.diag.size();
+    for (auto &g : stc) diags += g.diag.size();
+    std::cout << "       diagonals in the six groups: " << diags << std::endl;
+    Report("special FFT groups: StC(CtS(z)) / n == z (host)", z, v, 1e-9);
+  }
+
+  if (want("boot")) {
+    auto t0 = std::chrono::steady_clock::now();
+    boot_ctx->PrepareEvalMod();
+    boot_ctx->PrepareEvalSpecialFFT(n);
+    EvkRequest req;
+    boot_ctx->AddRequiredRotations(req, n);
+    ui.PrepareRotationKey(req);
+    auto t1 = std::chrono::steady_clock::now();
+    std::cout << "       prepared " << req.size() << " rotation keys and the diagonals in "
+              << std::chrono::duration<double>(t1 - t0).count() << " s" << std::endl;
+    Msg m, got;
+    random_msg(m, -1, 1, true);
+    Ct ct, out;
+    encrypt(ct, m, 0, param->GetScale(0));
+    double best = 1e30;
+    for (int it = 0; it < 4; it++) {
+      ctx->Synchronize();
+      auto a = std::chrono::steady_clock::now();
+      boot_ctx->Boot(out, ct, ui.GetEvkMap());
+      ctx->Synchronize();
+      auto b = std::chrono::steady_clock::now();
+      best = std::min(best, std::chrono::duration<double, std::milli>(b - a).count());
+    }
+    decrypt(got, out);
+    std::cout << "       Boot: level 0 -> " << param->NPToLevel(out.GetNP()) << ", best of 4: " << best << " ms"
+              << std::endl;
+    // the reference's acceptance bound (unittest/Testbed.h:93)
+    Report("Boot, 2^15 complex slots in [-1,1]^2", m, got, 1e-3);
+  }
+
+  std::cout << (failures ? "FAILED " : "PASSED ") << "(" << failures << " failures)" << std::endl;
+  return failures ? 1 : 0;
+}
