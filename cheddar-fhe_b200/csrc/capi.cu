@@ -136,9 +136,14 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
   return 0;
 }
 
+static void pool_release_cached(Context &c);
+
 void cfhe_context_destroy(cfhe_context *h) {
   if (!h) return;
   Context &c = h->c;
+  pool_release_cached(c);
+  for (auto &kv : c.pool_live) cudaFree(kv.first);
+  c.pool_live.clear();
   free_plans(c);
   if (c.d_tw) cudaFree(c.d_tw);
   if (c.d_itw) cudaFree(c.d_itw);
@@ -157,6 +162,7 @@ static void drop_own_stream(Context &c) {
 
 int cfhe_set_stream(cfhe_context *h, void *cuda_stream) {
   if (!h) return fail("null context");
+  pool_release_cached(h->c);
   drop_own_stream(h->c);
   h->c.stream = (cudaStream_t)cuda_stream;
   return 0;
@@ -166,6 +172,7 @@ int cfhe_use_own_stream(cfhe_context *h) {
   if (!h) return fail("null context");
   Context &c = h->c;
   if (c.own_stream) return 0;
+  pool_release_cached(c);
   CFHE_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
   c.own_stream = true;
   return 0;
@@ -197,15 +204,49 @@ int cfhe_level_limbs(const cfhe_context *h, int level, int num_aux, int *gidx) {
   return np_limbs(h->c, nm, nt, num_aux, gidx);
 }
 
+static void pool_release_cached(Context &c) {
+  if (c.pool_free.empty()) return;
+  cudaStreamSynchronize(c.stream);
+  for (auto &kv : c.pool_free) cudaFree(kv.second);
+  c.pool_free.clear();
+  c.pool_cached_bytes = 0;
+}
+
 int cfhe_malloc(cfhe_context *h, void **ptr, size_t bytes) {
   if (!h || !ptr) return fail("null argument");
-  CFHE_CUDA(cudaMalloc(ptr, bytes));
+  Context &c = h->c;
+  // size classes: multiples of 4 KiB below 1 MiB, of 256 KiB (one limb at
+  // N = 2^16) above; a cached block is reused only for its exact class
+  const size_t unit = bytes < (1u << 20) ? 4096 : (256u << 10);
+  const size_t rounded = bytes ? (bytes + unit - 1) / unit * unit : unit;
+  auto it = c.pool_free.find(rounded);
+  if (it != c.pool_free.end()) {
+    *ptr = it->second;
+    c.pool_free.erase(it);
+    c.pool_cached_bytes -= rounded;
+    c.pool_live[*ptr] = rounded;
+    return 0;
+  }
+  cudaError_t e = cudaMalloc(ptr, rounded);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    pool_release_cached(c);
+    e = cudaMalloc(ptr, rounded);
+  }
+  if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+  c.pool_live[*ptr] = rounded;
   return 0;
 }
 
 int cfhe_free(cfhe_context *h, void *ptr) {
   if (!h) return fail("null context");
-  CFHE_CUDA(cudaFree(ptr));
+  if (!ptr) return 0;
+  Context &c = h->c;
+  auto it = c.pool_live.find(ptr);
+  if (it == c.pool_live.end()) return fail("cfhe_free: pointer was not returned by cfhe_malloc");
+  c.pool_free.emplace(it->second, ptr);
+  c.pool_cached_bytes += it->second;
+  c.pool_live.erase(it);
   return 0;
 }
 

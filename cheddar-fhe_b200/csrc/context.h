@@ -5,6 +5,8 @@
 
 #include <string>
 #include <utility>
+#include <map>
+#include <unordered_map>
 #include <vector>
 
 #include "ntt_core.cuh"
@@ -95,6 +97,15 @@ struct Context {
   // workspace arena for pipeline temporaries (grown on demand)
   uint32_t *ws = nullptr;
   size_t ws_words = 0;
+
+  // Caching device allocator behind cfhe_malloc / cfhe_free. A freed block is
+  // kept and handed to a later request of the same rounded size; since every
+  // kernel of this context runs on one stream, the next user's work is ordered
+  // after the previous user's without a synchronisation. Blocks go back to
+  // the driver when an allocation fails, on a stream change and on destroy.
+  std::multimap<size_t, void *> pool_free;
+  std::unordered_map<void *, size_t> pool_live;
+  size_t pool_cached_bytes = 0;
 
   // optional stage timing: one CUDA event after each pipeline stage
   mutable bool profiling = false;

@@ -24,6 +24,7 @@
 //    the same eight levels).
 // Full-slot bootstrapping (2^(logN-1) slots) only.
 #pragma once
+#include <chrono>
 #include <functional>
 #include <set>
 
@@ -333,7 +334,8 @@ struct BootParameter {
         log_message_ratio_{log_message_ratio} {}
   const int max_level_, num_cts_levels_, num_stc_levels_, log_message_ratio_;
   const int num_double_angle_ = 3;
-  const int K_ = 16;           // |u| = |m/q0 + I| stays below K
+  const int K_ = 16;           // u = m/q0 + I is divided by K before EvalMod
+  const int max_integer_part_ = 12;  // |I| the sine approximation is fitted for (7 sigma at h = 32)
   const int poly_degree_ = 30;  // even series in t, degree 15 in T_2(t)
   // levels: 1 (T_2(t)) + 4 (series of 16 terms in T_2(t)) + double angles
   int GetNumEvalModLevels() const { return 5 + num_double_angle_; }
@@ -352,13 +354,68 @@ class EvalMod {
   using Ct = Ciphertext<word>;
 
  public:
-  explicit EvalMod(const BootParameter &bp) : bp_(bp) {
-    const int r = bp.num_double_angle_;
-    const double K = bp.K_, amp = std::pow(0.5 / M_PI, 1.0 / (1 << r)), ang = 2.0 * M_PI * K / (1 << r);
-    auto f = [=](double t) { return amp * std::cos(ang * t); };  // even in t
-    std::vector<double> full = EvalPoly<word>::ChebyshevCoefficients(f, bp.poly_degree_);
-    // T_2k(t) = T_k(T_2(t)): the even coefficients are the series in s = T_2(t)
-    for (int k = 0; 2 * k <= bp.poly_degree_; k++) in_s_.push_back(full[2 * k]);
+  explicit EvalMod(const BootParameter &bp) : bp_(bp) { in_s_ = FitNearIntegers(bp); }
+
+  // Coefficients c_k of sum_k c_k T_k(s), s = T_2(t), for
+  //   f(t) = (1/2pi)^(1/2^r) cos(2 pi K t / 2^r),  t = (u - 1/4) / K,
+  // fitted by least squares only where it is evaluated: u within
+  // 2^-log_message_ratio of an integer of magnitude <= max_integer_part_.
+  // Restricting the fit to those intervals buys several digits over the
+  // Chebyshev series on all of [-1, 1] at the same degree. Householder QR in
+  // long double; the sample points are Chebyshev nodes of each interval.
+  static std::vector<double> FitNearIntegers(const BootParameter &bp) {
+    using ld = long double;
+    const int deg = bp.poly_degree_ / 2, per = 33, I_max = bp.max_integer_part_;
+    const ld K = bp.K_, radius = std::ldexp(1.0L, -bp.log_message_ratio_);
+    const ld amp = std::pow((ld)0.5 / M_PIl, (ld)1 / (1 << bp.num_double_angle_));
+    const ld ang = 2 * M_PIl * K / (1 << bp.num_double_angle_);
+    const int rows = (2 * I_max + 1) * per, cols = deg + 1;
+    std::vector<ld> A((size_t)rows * cols), b(rows);
+    int row = 0;
+    for (int I = -I_max; I <= I_max; I++)
+      for (int k = 0; k < per; k++, row++) {
+        const ld u = I + radius * std::cos(M_PIl * (k + 0.5L) / per);
+        const ld t = (u - 0.25L) / K, x = 2 * t * t - 1;
+        b[row] = amp * std::cos(ang * t);
+        ld t0 = 1, t1 = x;
+        A[(size_t)row * cols] = 1;
+        if (cols > 1) A[(size_t)row * cols + 1] = x;
+        for (int j = 2; j < cols; j++) {
+          const ld t2 = 2 * x * t1 - t0;
+          A[(size_t)row * cols + j] = t2;
+          t0 = t1;
+          t1 = t2;
+        }
+      }
+    for (int j = 0; j < cols; j++) {  // Householder reflections, applied to A and b
+      ld norm = 0;
+      for (int i = j; i < rows; i++) norm += A[(size_t)i * cols + j] * A[(size_t)i * cols + j];
+      norm = std::sqrt(norm);
+      if (A[(size_t)j * cols + j] > 0) norm = -norm;
+      std::vector<ld> v(rows - j);
+      for (int i = j; i < rows; i++) v[i - j] = A[(size_t)i * cols + j];
+      v[0] -= norm;
+      ld vv = 0;
+      for (ld x : v) vv += x * x;
+      if (vv == 0) continue;
+      for (int c = j; c < cols; c++) {
+        ld dot = 0;
+        for (int i = j; i < rows; i++) dot += v[i - j] * A[(size_t)i * cols + c];
+        dot *= 2 / vv;
+        for (int i = j; i < rows; i++) A[(size_t)i * cols + c] -= dot * v[i - j];
+      }
+      ld dot = 0;
+      for (int i = j; i < rows; i++) dot += v[i - j] * b[i];
+      dot *= 2 / vv;
+      for (int i = j; i < rows; i++) b[i] -= dot * v[i - j];
+    }
+    std::vector<ld> c(cols);
+    for (int j = cols - 1; j >= 0; j--) {
+      ld acc = b[j];
+      for (int k = j + 1; k < cols; k++) acc -= A[(size_t)j * cols + k] * c[k];
+      c[j] = acc / A[(size_t)j * cols + j];
+    }
+    return std::vector<double>(c.begin(), c.end());
   }
 
   void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &input,
@@ -572,7 +629,6 @@ class BootContext : public Context<word> {
       CheckAbi(cfhe_modup_to_max(this->h_, dst.data(), coef.data(), g_low.data(), nl, g_dst.data(),
                                  g_dst.size()));
       CheckAbi(cfhe_ntt(this->h_, dst.data(), dst.data(), g_dst.data(), g_dst.size(), 1, 0, 0, 1));
-      this->Synchronize();
     };
     Ct out(top);
     if (!sse) {
@@ -604,7 +660,6 @@ class BootContext : public Context<word> {
       std::vector<word> zero(L, 0);
       this->ConstKernel(0, out.bx_.data(), both.data(), nullptr, zero, top);
       this->ConstKernel(0, out.ax_.data(), both.data() + (size_t)L * n, nullptr, zero, top);
-      this->Synchronize();
     }
     out.SetScale(input.GetScale());
     out.SetNumSlots(input.GetNumSlots());
@@ -626,8 +681,19 @@ class BootContext : public Context<word> {
 
   // Refreshes a level-0 ciphertext with slot values in [-1, 1]^2 to
   // boot_param_.GetEndLevel() (reference Boot, src/extension/BootContext.cpp:299-365).
-  void Boot(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
+  // phase_ms (optional): the host synchronises after every phase and appends
+  // its name and wall-clock milliseconds.
+  void Boot(Ct &res, const Ct &input, const EvkMap<word> &evk_map,
+            std::vector<std::pair<std::string, double>> *phase_ms = nullptr) const {
     const auto &param = this->param_;
+    auto last = std::chrono::steady_clock::now();
+    auto phase = [&](const char *name) {
+      if (!phase_ms) return;
+      this->Synchronize();
+      auto now = std::chrono::steady_clock::now();
+      phase_ms->emplace_back(name, std::chrono::duration<double, std::milli>(now - last).count());
+      last = now;
+    };
     AssertTrue(IsBootPrepared(input.GetNumSlots()), "Boot: not prepared for this slot count");
     AssertTrue(param.NPToLevel(input.GetNP()) <= 0, "Boot: bring the input to level 0 first");
     AssertFalse(input.HasRx(), "Boot: relinearize first");
@@ -650,23 +716,28 @@ class BootContext : public Context<word> {
     Ct raised;
     ModUpToMax(raised, main, evk_map);
     raised.SetScale(q0_prod_);
+    phase("ModUpToMax");
     // 2. coefficients to slots
     Ct slots;
     CoeffToSlot(slots, raised, evk_map);
+    phase("CoeffToSlot");
     // 3. real and imaginary parts, each through EvalMod
     Ct conj, re, im;
     this->HConj(conj, slots, evk_map.GetConjugationKey());
     this->Add(re, slots, conj);
     this->Sub(im, conj, slots);
     this->MultImaginaryUnit(im, im);
+    phase("conjugate split");
     Ct re_mod, im_mod;
     EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
     EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
     this->MultImaginaryUnit(im_mod, im_mod);
     this->Add(re_mod, re_mod, im_mod);
+    phase("EvalMod x2");
     // 4. slots to coefficients
     SlotToCoeff(res, re_mod, evk_map);
     res.SetNumSlots(input.GetNumSlots());
+    phase("SlotToCoeff");
   }
 
   int GetLogScaleUp() const { return log_scaleup_; }

@@ -1040,7 +1040,6 @@ class Context : public std::enable_shared_from_this<Context<word>> {
       res[i].SetScale(a.GetScale());
       res[i].SetNumSlots(a.GetNumSlots());
     }
-    Synchronize();
   }
 
   void AssertSameScale(double s1, double s2) const {
@@ -1171,8 +1170,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     if (rescale) scale /= param_.GetRescalePrimeProd(level);
     out.SetScale(scale);
     out.SetNumSlots(a.GetNumSlots());
-    Synchronize();  // temporaries are released when this scope ends
-    res = std::move(out);
+    res = std::move(out);  // temporaries go back to the allocator's cache, reused in stream order
   }
 };
 

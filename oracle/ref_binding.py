@@ -68,3 +68,24 @@ class Reference:
                                        iters, C.byref(usec))
         assert rc == 0, rc
         return usec.value
+
+
+def boot(p, iters=3, min_ks=False):
+    """Runs the reference's own bootstrapping (BootContext::Boot) on random
+    slots and returns its latency and error; see ref_boot in ref_driver.cu."""
+    L = C.CDLL(REF_LIB)
+    u = lambda a: np.ascontiguousarray(a, dtype=np.uint32)
+    main, ter, aux = u(p["main_primes"]), u(p["terminal_primes"] or [0]), u(p["auxiliary_primes"])
+    lc = np.ascontiguousarray(np.array(p["level_config"], dtype=np.int32).reshape(-1))
+    out = (C.c_double * 6)()
+    rc = L.ref_boot(
+        p["log_degree"], C.c_double(float(2 ** p["log_default_scale"])), p["default_encryption_level"],
+        main.ctypes.data_as(C.c_void_p), len(p["main_primes"]),
+        ter.ctypes.data_as(C.c_void_p), len(p["terminal_primes"]),
+        aux.ctypes.data_as(C.c_void_p), len(p["auxiliary_primes"]),
+        lc.ctypes.data_as(C.c_void_p), len(p["level_config"]),
+        int(p.get("dense_hamming_weight", 0)), int(p.get("sparse_hamming_weight", 0)),
+        int(p["num_cts_levels"]), int(p["num_stc_levels"]), int(min_ks), iters, out)
+    assert rc == 0, rc
+    return {"ms": out[0], "max_err": out[1], "mean_err": out[2], "prepare_s": out[3],
+            "rotation_keys": int(out[4]), "end_level": int(out[5])}

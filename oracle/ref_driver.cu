@@ -12,7 +12,14 @@
 #include <memory>
 #include <vector>
 
+#include <chrono>
+#include <cmath>
+#include <complex>
+
+#include "Random.h"
+#include "UserInterface.h"
 #include "core/Context.h"
+#include "extension/BootContext.h"
 
 using word = uint32_t;
 using namespace cheddar;
@@ -184,6 +191,74 @@ int ref_ntt_batch_time(RefHandle *h, word *buf_a, word *buf_b, int polys, int nu
   *usec = ms * 1000.0f / iters;
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
+  return (int)cudaDeviceSynchronize();
+}
+
+// The reference's bootstrapping test (unittest/Bootstrapping.cpp:10-41) without
+// gtest: BootContext + UserInterface on the given parameter set, Boot of a
+// level-0 encryption of 2^(logN-1) random complex slots in [-1,1]^2, five
+// warm-up calls, then `iters` timed calls (host clock around a device
+// synchronisation, as the reference's profiling macro measures).
+// out[0] = mean ms per Boot, out[1] = max |diff| per component, out[2] = mean
+// |diff|, out[3] = seconds spent preparing keys and plaintexts, out[4] =
+// number of rotation keys, out[5] = output level. min_ks selects the
+// reference's minimum-key-switching variant.
+int ref_boot(int log_degree, double base_scale, int default_level, const word *main_p, int n_main,
+             const word *ter_p, int n_ter, const word *aux_p, int n_aux, const int *level_config,
+             int n_levels, int dense_h, int sparse_h, int num_cts, int num_stc, int min_ks, int iters,
+             double *out) {
+  std::vector<std::pair<int, int>> lc;
+  for (int i = 0; i < n_levels; i++) lc.emplace_back(level_config[2 * i], level_config[2 * i + 1]);
+  Parameter<word> param(log_degree, base_scale, default_level, lc,
+                        std::vector<word>(main_p, main_p + n_main),
+                        std::vector<word>(aux_p, aux_p + n_aux),
+                        std::vector<word>(ter_p, ter_p + n_ter));
+  if (dense_h > 0) param.SetDenseHammingWeight(dense_h);
+  if (sparse_h > 0) param.SetSparseHammingWeight(sparse_h);
+  const int num_slots = param.degree_ / 2;
+  auto t0 = std::chrono::steady_clock::now();
+  std::shared_ptr<BootContext<word>> boot =
+      BootContext<word>::Create(param, BootParameter(param.max_level_, num_cts, num_stc));
+  {
+    UserInterface<word> ui(boot);
+    boot->PrepareEvalMod();
+    boot->PrepareEvalSpecialFFT(num_slots);
+    EvkRequest req;
+    boot->AddRequiredRotations(req, num_slots, min_ks != 0);
+    ui.PrepareRotationKey(req);
+    cudaDeviceSynchronize();
+    auto t1 = std::chrono::steady_clock::now();
+    out[3] = std::chrono::duration<double>(t1 - t0).count();
+    out[4] = (double)req.size();
+
+    std::vector<Complex> msg(num_slots), got;
+    Random::SampleUniformComplex(msg.data(), num_slots, -1.0, 1.0);
+    Plaintext<word> pt;
+    Ciphertext<word> ct, res;
+    boot->encoder_.Encode(pt, 0, param.GetScale(0), msg);
+    ui.Encrypt(ct, pt);
+    for (int i = 0; i < 5; i++) boot->Boot(res, ct, ui.GetEvkMap(), min_ks != 0);
+    cudaDeviceSynchronize();
+    auto a = std::chrono::steady_clock::now();
+    for (int i = 0; i < iters; i++) boot->Boot(res, ct, ui.GetEvkMap(), min_ks != 0);
+    cudaError_t e = cudaDeviceSynchronize();
+    auto b = std::chrono::steady_clock::now();
+    if (e != cudaSuccess) return (int)e;
+    out[0] = std::chrono::duration<double, std::milli>(b - a).count() / iters;
+    Plaintext<word> dec;
+    ui.Decrypt(dec, res);
+    boot->encoder_.Decode(got, dec);
+    double worst = 0, sum = 0;
+    for (int i = 0; i < num_slots; i++) {
+      worst = std::max(worst, std::max(std::abs(msg[i].real() - got[i].real()),
+                                       std::abs(msg[i].imag() - got[i].imag())));
+      sum += std::abs(msg[i] - got[i]);
+    }
+    out[1] = worst;
+    out[2] = sum / num_slots;
+    out[5] = (double)param.NPToLevel(res.GetNP());
+  }
+  boot.reset();
   return (int)cudaDeviceSynchronize();
 }
 

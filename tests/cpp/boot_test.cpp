@@ -3,6 +3,7 @@
 // 2^15 random complex slots in [-1,1]^2, unittest/Bootstrapping.cpp:10-41).
 //
 //   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot]
+#include <algorithm>
 #include <chrono>
 #include <cstring>
 #include <iomanip>
@@ -138,7 +139,7 @@ int main(int argc, char **argv) {
       Complex e;
       Random::SampleUniformComplex(&e, 1, -1.0, 1.0);
       const double eps = e.real() / 256.0;
-      expect.push_back(Complex(eps, 0));
+      expect.push_back(Complex(std::sin(2 * M_PI * eps) / (2 * M_PI), 0));
       v = Complex((I + eps) / bp.K_, 0);
     }
     Ct ct, out;
@@ -147,8 +148,7 @@ int main(int argc, char **argv) {
     em.Evaluate(ctx, out, ct, ui.GetMultiplicationKey());
     decrypt(got, out);
     std::cout << "       levels " << level << " -> " << param->NPToLevel(out.GetNP()) << std::endl;
-    // sin(2 pi eps)/(2 pi) ~ eps up to eps^3
-    Report("EvalMod (K = 16)", expect, got, 2e-6);
+    Report("EvalMod (K = 16) against sin(2 pi u) / 2 pi", expect, got, 1e-10);
   }
 
   if (want("fft")) {
@@ -191,11 +191,99 @@ int main(int argc, char **argv) {
       auto b = std::chrono::steady_clock::now();
       best = std::min(best, std::chrono::duration<double, std::milli>(b - a).count());
     }
+    std::vector<std::pair<std::string, double>> phases;
+    boot_ctx->Boot(out, ct, ui.GetEvkMap(), &phases);
+    std::cout << "       phases (ms, host-synchronised):";
+    for (auto &[name, ms] : phases) std::cout << "  " << name << " " << std::fixed << std::setprecision(2) << ms;
+    std::cout << std::endl;
     decrypt(got, out);
     std::cout << "       Boot: level 0 -> " << param->NPToLevel(out.GetNP()) << ", best of 4: " << best << " ms"
               << std::endl;
     // the reference's acceptance bound (unittest/Testbed.h:93)
     Report("Boot, 2^15 complex slots in [-1,1]^2", m, got, 1e-3);
+  }
+
+  if (only.count("stages")) {
+    // error introduced by each stage of Boot, against the same stage computed
+    // in double precision from the decrypted input of that stage
+    boot_ctx->PrepareEvalMod();
+    boot_ctx->PrepareEvalSpecialFFT(n);
+    EvkRequest req;
+    boot_ctx->AddRequiredRotations(req, n);
+    ui.PrepareRotationKey(req);
+    const auto &evk = ui.GetEvkMap();
+    Msg m;
+    random_msg(m, -1, 1, true);
+    Ct ct, up, raised, slots, conj, re, im, re_mod, im_mod, sum, out;
+    encrypt(ct, m, 0, param->GetScale(0));
+    const int lsu = boot_ctx->GetLogScaleUp();
+    {
+      Constant<word> k;
+      ctx->encoder().EncodeConstant(k, 0, 1.0, (double)(1 << lsu), 0);
+      ctx->Mult(up, ct, k);
+      up.SetScale(ct.GetScale() * (1 << lsu));
+    }
+    boot_ctx->ModUpToMax(raised, up, evk);
+    double q0 = 1;
+    for (word q : param->GetPrimeVector(param->LevelToNP(-1))) q0 *= q;
+    raised.SetScale(q0);
+    Msg z0, z1, got;
+    decrypt(z0, raised);
+    {
+      double big = 0;
+      for (auto &x : z0) big = std::max(big, std::abs(x));
+      std::cout << "       raised: max |slot| at scale q0 = " << big << std::endl;
+    }
+    auto cts = EvalSpecialFFT<word>::Groups(*param, n, true, boot_param.num_cts_levels_,
+                                            1.0 / ((double)n * 2.0 * boot_param.K_));
+    z1 = z0;
+    for (auto &g : cts) z1 = g.Apply(z1);
+    {
+      double big = 0;
+      for (auto &x : z1) big = std::max(big, std::max(std::abs(x.real()), std::abs(x.imag())));
+      std::cout << "       after CtS: max |u|/(2K) = " << big << "  (max |u| = " << big * 2 * boot_param.K_ << ")" << std::endl;
+    }
+    boot_ctx->CoeffToSlot(slots, raised, evk);
+    decrypt(got, slots);
+    Report("stage CoeffToSlot", z1, got, 1e-9);
+    ctx->HConj(conj, slots, evk.GetConjugationKey());
+    ctx->Add(re, slots, conj);
+    ctx->Sub(im, conj, slots);
+    ctx->MultImaginaryUnit(im, im);
+    Msg re_in, im_in, expect;
+    decrypt(re_in, re);
+    decrypt(im_in, im);
+    boot_ctx->EvaluateMod(re_mod, re, evk.GetMultiplicationKey());
+    boot_ctx->EvaluateMod(im_mod, im, evk.GetMultiplicationKey());
+    auto sine = [&](const Msg &in) {
+      Msg o;
+      for (auto &x : in) o.push_back(Complex(std::sin(2 * M_PI * boot_param.K_ * x.real()) / (2 * M_PI), 0));
+      return o;
+    };
+    decrypt(got, re_mod);
+    Report("stage EvalMod (real part)", sine(re_in), got, 1e-8);
+    Msg re_out = got;
+    decrypt(got, im_mod);
+    Report("stage EvalMod (imaginary part)", sine(im_in), got, 1e-8);
+    ctx->MultImaginaryUnit(im_mod, im_mod);
+    ctx->Add(sum, re_mod, im_mod);
+    Msg z2;
+    decrypt(z2, sum);
+    auto stc = EvalSpecialFFT<word>::Groups(*param, n, false, boot_param.num_stc_levels_,
+                                            q0 / (param->GetScale(0) * (1 << lsu)));
+    Msg z3 = z2;
+    for (auto &g : stc) z3 = g.Apply(z3);
+    boot_ctx->SlotToCoeff(out, sum, evk);
+    decrypt(got, out);
+    Report("stage SlotToCoeff", z3, got, 1e-5);
+    Report("whole Boot", m, got, 1e-3);
+    // where the largest errors sit
+    std::vector<std::pair<double, int>> worst;
+    for (int i = 0; i < n; i++) worst.emplace_back(std::abs(m[i] - got[i]), i);
+    std::sort(worst.rbegin(), worst.rend());
+    std::cout << "       largest errors (slot: error):";
+    for (int i = 0; i < 8; i++) std::cout << "  " << worst[i].second << ": " << std::scientific << worst[i].first;
+    std::cout << std::endl;
   }
 
   std::cout << (failures ? "FAILED " : "PASSED ") << "(" << failures << " failures)" << std::endl;
