@@ -560,6 +560,44 @@ int cfhe_hoisted_rotations(cfhe_context *h, int level, uint32_t *out,
                                evk_a, key_main, h->c.ws);
 }
 
+int cfhe_linear_transform(cfhe_context *h, int level, int rescale, uint32_t *out_b,
+                          uint32_t *out_a, const uint32_t *in_b, const uint32_t *in_a,
+                          int n_baby, const int *baby_rot,
+                          const uint32_t *const *baby_evk_b, const uint32_t *const *baby_evk_a,
+                          int n_giant, const int *giant_rot,
+                          const uint32_t *const *giant_evk_b, const uint32_t *const *giant_evk_a,
+                          const uint32_t *const *pt, int key_main) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!out_b || !out_a || !in_b || !in_a || !baby_rot || !giant_rot || !pt)
+    return fail("null argument");
+  if (n_baby < 1 || n_baby > kMaxBaby || n_giant < 1 || n_giant > kMaxGiant)
+    return fail("linear transform: at most 16 baby and 16 giant steps");
+  if (baby_rot[0] != 0) return fail("linear transform: the first baby step must be the identity");
+  const int half = h->c.n / 2;
+  std::vector<uint32_t> bg(n_baby), gg(n_giant);
+  bool need_baby_keys = false, need_giant_keys = false;
+  for (int i = 0; i < n_baby; i++) {
+    if (baby_rot[i] < 0 || baby_rot[i] >= half || (i > 0 && baby_rot[i] == 0))
+      return fail("rotation distance out of range");
+    bg[i] = baby_rot[i] ? cfhe_galois_for_rotation(h, baby_rot[i]) : 1u;
+    need_baby_keys = need_baby_keys || baby_rot[i] != 0;
+  }
+  for (int j = 0; j < n_giant; j++) {
+    if (giant_rot[j] < 0 || giant_rot[j] >= half) return fail("rotation distance out of range");
+    gg[j] = giant_rot[j] ? cfhe_galois_for_rotation(h, giant_rot[j]) : 1u;
+    need_giant_keys = need_giant_keys || giant_rot[j] != 0;
+  }
+  if ((need_baby_keys && (!baby_evk_b || !baby_evk_a)) ||
+      (need_giant_keys && (!giant_evk_b || !giant_evk_a)))
+    return fail("null argument");
+  if (int r = ensure_workspace(h->c, linear_transform_scratch_words(*lp, n_baby, n_giant, rescale != 0)))
+    return r;
+  return run_linear_transform(h->c, *lp, rescale != 0, out_b, out_a, in_b, in_a, n_baby, bg.data(),
+                              baby_evk_b, baby_evk_a, n_giant, gg.data(), giant_evk_b,
+                              giant_evk_a, pt, key_main, h->c.ws);
+}
+
 int cfhe_hmult(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
                const uint32_t *a2, const uint32_t *const *evk_b,

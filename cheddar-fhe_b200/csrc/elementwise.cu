@@ -154,12 +154,21 @@ __global__ void __launch_bounds__(kEwThreads)
     }
   }
   if (a.scatter_galois == 0) {
-    reinterpret_cast<uint4 *>(a.acc_b + (size_t)l * kN)[v] =
-        make_uint4(mont_reduce(sb[0], q, nq), mont_reduce(sb[1], q, nq),
-                   mont_reduce(sb[2], q, nq), mont_reduce(sb[3], q, nq));
-    reinterpret_cast<uint4 *>(a.acc_a + (size_t)l * kN)[v] =
-        make_uint4(mont_reduce(sa[0], q, nq), mont_reduce(sa[1], q, nq),
-                   mont_reduce(sa[2], q, nq), mont_reduce(sa[3], q, nq));
+    uint4 rb = make_uint4(mont_reduce(sb[0], q, nq), mont_reduce(sb[1], q, nq),
+                          mont_reduce(sb[2], q, nq), mont_reduce(sb[3], q, nq));
+    uint4 ra = make_uint4(mont_reduce(sa[0], q, nq), mont_reduce(sa[1], q, nq),
+                          mont_reduce(sa[2], q, nq), mont_reduce(sa[3], q, nq));
+    uint4 *pb = reinterpret_cast<uint4 *>(a.acc_b + (size_t)l * kN) + v;
+    uint4 *pa = reinterpret_cast<uint4 *>(a.acc_a + (size_t)l * kN) + v;
+    if (a.accumulate) {
+      const uint4 ob = *pb, oa = *pa;
+      rb = make_uint4(add_mod(rb.x, ob.x, q), add_mod(rb.y, ob.y, q), add_mod(rb.z, ob.z, q),
+                      add_mod(rb.w, ob.w, q));
+      ra = make_uint4(add_mod(ra.x, oa.x, q), add_mod(ra.y, oa.y, q), add_mod(ra.z, oa.z, q),
+                      add_mod(ra.w, oa.w, q));
+    }
+    *pb = rb;
+    *pa = ra;
   } else {
     // fused automorphism: the key and the ModUp buffers are read in order and
     // the product lands where the rotation sends it (the reference's fused
@@ -171,9 +180,57 @@ __global__ void __launch_bounds__(kEwThreads)
       const uint32_t i = 4 * v + e;
       const uint32_t ex = (__brev(i) >> (31 - kLogN)) + 1;
       const uint32_t d = __brev((ex * a.scatter_galois - 1) << (31 - kLogN)) & (kN - 1);
-      ob[d] = mont_reduce(sb[e], q, nq);
-      oa[d] = mont_reduce(sa[e], q, nq);
+      uint32_t rb = mont_reduce(sb[e], q, nq), ra = mont_reduce(sa[e], q, nq);
+      if (a.accumulate) {  // every destination word belongs to exactly one thread
+        rb = add_mod(rb, ob[d], q);
+        ra = add_mod(ra, oa[d], q);
+      }
+      ob[d] = rb;
+      oa[d] = ra;
     }
+  }
+}
+
+// acc_j = sum_i pt[j][i] (*) rot_i on one limb, two coefficients per thread.
+// The rotations are held in registers across the giant steps, so every
+// plaintext word and every rotation word is read once (the reference's
+// GSFusedPAccum kernel keeps the same operands in registers,
+// src/extension/Hoist.cu:80-120). Products are summed before one Montgomery
+// reduction per output.
+constexpr int kPtThreads = 256;
+__global__ void __launch_bounds__(kPtThreads)
+    pt_accum_kernel(const __grid_constant__ PtAccumArgs a) {
+  const int l = blockIdx.y;
+  const int v = blockIdx.x * kPtThreads + threadIdx.x;  // pair index inside the limb
+  const uint32_t q = a.q[l], nq = a.nqinv[l];
+  const uint64_t q32 = (uint64_t)q << 32;
+  const size_t limb = (size_t)l * kN, poly = (size_t)a.ntot * kN;
+  uint2 rb[kMaxBaby], ra[kMaxBaby];
+#pragma unroll
+  for (int i = 0; i < kMaxBaby; i++)
+    if (i < a.n_baby) {
+      rb[i] = reinterpret_cast<const uint2 *>(a.rot + (size_t)(2 * i) * poly + limb)[v];
+      ra[i] = reinterpret_cast<const uint2 *>(a.rot + (size_t)(2 * i + 1) * poly + limb)[v];
+    }
+#pragma unroll 1
+  for (int j = 0; j < a.n_giant; j++) {
+    uint64_t sb0 = 0, sb1 = 0, sa0 = 0, sa1 = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxBaby; i++)
+      if (i < a.n_baby) {
+        const uint32_t *p = a.pt[j * kMaxBaby + i];
+        if (p) {
+          const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(p + limb) + v);
+          mac_fold(sb0, rb[i].x, w.x, q32);
+          mac_fold(sb1, rb[i].y, w.y, q32);
+          mac_fold(sa0, ra[i].x, w.x, q32);
+          mac_fold(sa1, ra[i].y, w.y, q32);
+        }
+      }
+    reinterpret_cast<uint2 *>(a.acc + (size_t)(2 * j) * poly + limb)[v] =
+        make_uint2(mont_reduce(sb0, q, nq), mont_reduce(sb1, q, nq));
+    reinterpret_cast<uint2 *>(a.acc + (size_t)(2 * j + 1) * poly + limb)[v] =
+        make_uint2(mont_reduce(sa0, q, nq), mont_reduce(sa1, q, nq));
   }
 }
 
@@ -249,6 +306,13 @@ int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois) {
   if (args.n_rows <= 0) return 0;
   dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
   permute_kernel<<<grid, block, 0, ctx.stream>>>(args, galois);
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_pt_accum(const Context &ctx, const PtAccumArgs &args) {
+  dim3 grid(kN / 2 / kPtThreads, args.ntot), block(kPtThreads);
+  pt_accum_kernel<<<grid, block, 0, ctx.stream>>>(args);
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -55,6 +55,7 @@ struct InnerArgs {
   // 0: results stay in place; otherwise the inverse Galois element g^-1 of an
   // automorphism applied to the result: word i is stored at pi_{g^-1}(i)
   uint32_t scatter_galois;
+  int accumulate;  // != 0: the result is added to what acc_b / acc_a hold
   uint8_t mu_slot[kMaxDigits];
   uint32_t q[kMaxLimbs], nqinv[kMaxLimbs], pm[kMaxLimbs];
   uint8_t kpos[kMaxLimbs];       // limb position inside the key
@@ -94,7 +95,19 @@ struct BconvTcArgs {
   BconvTcJob jobs[kMaxBconvJobs];
 };
 
+// Plaintext accumulation of a baby-step/giant-step linear transform on the
+// extended basis: acc_j = sum_i pt[j][i] (*) rot_i for both polynomials.
+constexpr int kMaxBaby = 16, kMaxGiant = 16;
+struct PtAccumArgs {
+  const uint32_t *rot;  // [n_baby][2][ntot][N]: (b, a) of every baby rotation
+  uint32_t *acc;        // [n_giant][2][ntot][N]
+  const uint32_t *pt[kMaxGiant * kMaxBaby];  // [giant * kMaxBaby + baby], [ntot][N] each; null = absent
+  int n_baby, n_giant, ntot;
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
+};
+
 int launch_ew(const Context &ctx, int op, const EwArgs &args);
+int launch_pt_accum(const Context &ctx, const PtAccumArgs &args);
 int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);

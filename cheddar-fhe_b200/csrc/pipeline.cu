@@ -223,7 +223,7 @@ static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b
                           uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
                           const uint32_t *c0, const uint32_t *c1,
                           const uint32_t *const *kb, const uint32_t *const *ka,
-                          int key_main, uint32_t galois_inv);
+                          int key_main, uint32_t galois_inv, bool accumulate = false);
 
 int run_inner(const Context &c, const LevelPlan &lp, uint32_t *acc_b,
               uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
@@ -244,7 +244,7 @@ static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b
                           uint32_t *acc_a, const uint32_t *mu, const uint32_t *d,
                           const uint32_t *c0, const uint32_t *c1,
                           const uint32_t *const *kb, const uint32_t *const *ka,
-                          int key_main, uint32_t galois_inv) {
+                          int key_main, uint32_t galois_inv, bool accumulate) {
   if ((int)lp.digits.size() > kMaxDigits) {
     set_error("inner product: too many digits");
     return -1;
@@ -266,6 +266,7 @@ static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b
   a.ntot = lp.ntot;
   a.nq = lp.nq;
   a.scatter_galois = galois_inv;
+  a.accumulate = accumulate ? 1 : 0;
   for (int i = 0; i < a.n_digits; i++) {
     const int slot = lp.digits[i].index;
     a.kb[i] = kb[slot];
@@ -327,6 +328,14 @@ int run_keyswitch(Context &c, const LevelPlan &lp, int down_type,
                      (long long)acc_words, y);
 }
 
+// g^-1 modulo 2N by Newton iteration on the 2-adic inverse (g odd)
+static uint32_t galois_inverse(uint32_t g) {
+  const uint32_t m2 = 2u * kN;
+  uint32_t inv = g;
+  for (int it = 0; it < 5; it++) inv = (uint32_t)((uint64_t)inv * (2u - g * inv)) & (m2 - 1);
+  return inv;
+}
+
 constexpr int kHoistChunk = 4;  // rotations whose ModDowns share launches
 
 size_t hoisted_scratch_words(const LevelPlan &lp) {
@@ -358,9 +367,7 @@ int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
         set_error("hoisted rotations: invalid Galois element");
         return -1;
       }
-      // g^-1 mod 2N by exponentiation (the unit group has exponent N/2... use 2N-bit Newton)
-      uint32_t inv = g;
-      for (int it = 0; it < 5; it++) inv = (uint32_t)((uint64_t)inv * (2u - g * inv)) & (m2 - 1);
+      const uint32_t inv = galois_inverse(g);
       uint32_t *ab = acc + (size_t)(2 * i) * acc_words;
       if (int rc = run_inner_rot(c, lp, ab, ab + acc_words, mu, a, b,
                                  kb + (size_t)(r0 + i) * lp.beta,
@@ -372,6 +379,159 @@ int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
       return rc;
   }
   return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Baby-step/giant-step linear transform with both hoistings:
+//   out = Down( sum_j rot_Gj( Down( sum_i pt[j][i] (*) rot_bi(in) ) ) )
+// * the baby rotations share one ModUp and stay on the extended basis (no
+//   ModDown per rotation); the unrotated input joins them as P * in;
+// * the plaintexts, given on the extended basis, are accumulated per giant
+//   step by one kernel; the giant sums go through ModDown together;
+// * every giant rotation is a key switch whose extended-basis result is
+//   added into one accumulator, so a single (rescaling) ModDown ends the call.
+// ---------------------------------------------------------------------------
+static size_t lt_y_words(const LevelPlan &lp, int n_giant, bool rescale) {
+  size_t y = modup_scratch_words(lp);
+  y = std::max(y, moddown_scratch_words(lp.down[0], std::min(2 * n_giant, kMaxBconvJobs)));
+  y = std::max(y, moddown_scratch_words(lp.down[rescale ? 2 : 0], 2));
+  return y;
+}
+
+size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale) {
+  return lt_y_words(lp, n_giant, rescale) +
+         ((size_t)(lp.beta + 2 * n_baby + 2 * n_giant + 2) * lp.ntot + (size_t)2 * n_giant * lp.nq) * kN;
+}
+
+// dst = (P * src on the Q limbs, 0 on the auxiliary limbs) for `n_polys`
+// polynomials; src polynomials are nq limbs apart, dst ntot limbs apart.
+static int lift_to_extended(const Context &c, const LevelPlan &lp, uint32_t *dst,
+                            const uint32_t *const *src, int n_polys) {
+  EwArgs e;
+  e.n_rows = 0;
+  for (int p = 0; p < n_polys; p++) {
+    uint32_t *d = dst + (size_t)p * lp.ntot * kN;
+    for (int l = 0; l < lp.nq; l++) {
+      const int g = lp.q_g[l];
+      e.rows[e.n_rows++] = EwRow{d + (size_t)l * kN, src[p] + (size_t)l * kN, nullptr,
+                                 c.q[g], c.nqinv[g], lp.p_mont[l], 0u};
+    }
+    CFHE_CUDA(cudaMemsetAsync(d + (size_t)lp.nq * kN, 0, (size_t)(lp.ntot - lp.nq) * kN * sizeof(uint32_t),
+                              c.stream));
+  }
+  return launch_ew(c, EW_MULC, e);
+}
+
+int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t *out_b,
+                         uint32_t *out_a, const uint32_t *in_b, const uint32_t *in_a,
+                         int n_baby, const uint32_t *baby_galois,
+                         const uint32_t *const *baby_kb, const uint32_t *const *baby_ka,
+                         int n_giant, const uint32_t *giant_galois,
+                         const uint32_t *const *giant_kb, const uint32_t *const *giant_ka,
+                         const uint32_t *const *pt, int key_main, uint32_t *scratch) {
+  if (n_baby < 1 || n_baby > kMaxBaby || n_giant < 1 || n_giant > kMaxGiant) {
+    set_error("linear transform: at most 16 baby and 16 giant steps");
+    return -1;
+  }
+  if (baby_galois[0] != 1u) {
+    set_error("linear transform: the first baby step must be the identity");
+    return -1;
+  }
+  if (rescale && !lp.has_rescale) {
+    set_error("linear transform: this level cannot be rescaled");
+    return -1;
+  }
+  if (2 * lp.ntot > kMaxRows) {
+    set_error("linear transform: too many limbs");
+    return -1;
+  }
+  const uint32_t m2 = 2u * kN;
+  const size_t ext = (size_t)lp.ntot * kN, qw = (size_t)lp.nq * kN;
+  uint32_t *y = scratch;
+  uint32_t *mu = y + lt_y_words(lp, n_giant, rescale);
+  uint32_t *rot = mu + (size_t)lp.beta * ext;       // [n_baby][2][ntot][N]
+  uint32_t *acc = rot + (size_t)2 * n_baby * ext;   // [n_giant][2][ntot][N]
+  uint32_t *total = acc + (size_t)2 * n_giant * ext;  // [2][ntot][N]
+  uint32_t *cj = total + 2 * ext;                   // [n_giant][2][nq][N]
+  // 1. baby steps on the extended basis
+  if (n_baby > 1)
+    if (int r = run_modup(c, lp, mu, in_a, false, y)) return r;
+  {
+    const uint32_t *src[2] = {in_b, in_a};
+    if (int r = lift_to_extended(c, lp, rot, src, 2)) return r;
+  }
+  for (int i = 1; i < n_baby; i++) {
+    const uint32_t g = baby_galois[i];
+    if ((g & 1u) == 0 || g >= m2 || g == 1u) {
+      set_error("linear transform: invalid baby-step Galois element");
+      return -1;
+    }
+    uint32_t *rb = rot + (size_t)(2 * i) * ext;
+    if (int r = run_inner_impl(c, lp, rb, rb + ext, mu, in_a, in_b, nullptr,
+                               baby_kb + (size_t)i * lp.beta, baby_ka + (size_t)i * lp.beta,
+                               key_main, galois_inverse(g)))
+      return r;
+  }
+  // 2. plaintext accumulation per giant step
+  PtAccumArgs pa;
+  memset(&pa, 0, sizeof(pa));
+  pa.rot = rot;
+  pa.acc = acc;
+  pa.n_baby = n_baby;
+  pa.n_giant = n_giant;
+  pa.ntot = lp.ntot;
+  for (int j = 0; j < n_giant; j++)
+    for (int i = 0; i < n_baby; i++) pa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
+  for (int l = 0; l < lp.ntot; l++) {
+    pa.q[l] = c.q[lp.full_g[l]];
+    pa.nqinv[l] = c.nqinv[lp.full_g[l]];
+  }
+  if (int r = launch_pt_accum(c, pa)) return r;
+  c.mark("pt_accum");
+  // 3. the giant sums leave the extended basis together
+  for (int p0 = 0; p0 < 2 * n_giant; p0 += kMaxBconvJobs) {
+    const int cnt = std::min(kMaxBconvJobs, 2 * n_giant - p0);
+    if (int r = run_moddown(c, lp.down[0], cj + (size_t)p0 * qw, acc + (size_t)p0 * ext, cnt,
+                            (long long)qw, (long long)ext, y))
+      return r;
+  }
+  // 4. giant rotations accumulate on the extended basis
+  int plain = -1;
+  for (int j = 0; j < n_giant; j++)
+    if (giant_galois[j] == 1u) {
+      if (plain >= 0) {
+        set_error("linear transform: more than one unrotated giant step");
+        return -1;
+      }
+      plain = j;
+    }
+  if (plain >= 0) {
+    const uint32_t *src[2] = {cj + (size_t)(2 * plain) * qw, cj + (size_t)(2 * plain + 1) * qw};
+    if (int r = lift_to_extended(c, lp, total, src, 2)) return r;
+  } else {
+    CFHE_CUDA(cudaMemsetAsync(total, 0, 2 * ext * sizeof(uint32_t), c.stream));
+  }
+  for (int j = 0; j < n_giant; j++) {
+    if (j == plain) continue;
+    const uint32_t g = giant_galois[j];
+    if ((g & 1u) == 0 || g >= m2) {
+      set_error("linear transform: invalid giant-step Galois element");
+      return -1;
+    }
+    const uint32_t *cb = cj + (size_t)(2 * j) * qw, *ca = cb + qw;
+    if (int r = run_modup(c, lp, mu, ca, false, y)) return r;
+    if (int r = run_inner_impl(c, lp, total, total + ext, mu, ca, cb, nullptr,
+                               giant_kb + (size_t)j * lp.beta, giant_ka + (size_t)j * lp.beta,
+                               key_main, galois_inverse(g), true))
+      return r;
+  }
+  // 5. one ModDown (with the rescale) for the whole transform
+  if (out_a - out_b == 0) {
+    set_error("linear transform: output polynomials alias");
+    return -1;
+  }
+  return run_moddown(c, lp.down[rescale ? 2 : 0], out_b, total, 2, (long long)(out_a - out_b),
+                     (long long)ext, y);
 }
 
 size_t keyswitch_scratch_words(const LevelPlan &lp, int down_type) {

@@ -36,6 +36,17 @@ int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
                           const uint32_t *const *ka, int key_main,
                           uint32_t *scratch);
 size_t hoisted_scratch_words(const LevelPlan &lp);
+// Baby-step/giant-step linear transform with both hoistings (see pipeline.cu).
+// baby_galois[0] must be 1; key arrays hold beta pointers per step (entries of
+// unrotated steps are not read); pt[j*n_baby+i] on the extended basis or null.
+int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t *out_b,
+                         uint32_t *out_a, const uint32_t *in_b, const uint32_t *in_a,
+                         int n_baby, const uint32_t *baby_galois,
+                         const uint32_t *const *baby_kb, const uint32_t *const *baby_ka,
+                         int n_giant, const uint32_t *giant_galois,
+                         const uint32_t *const *giant_kb, const uint32_t *const *giant_ka,
+                         const uint32_t *const *pt, int key_main, uint32_t *scratch);
+size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale);
 int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
                uint32_t *d1, uint32_t *d2, const uint32_t *b1,
                const uint32_t *a1, const uint32_t *b2, const uint32_t *a2);

@@ -68,123 +68,132 @@ struct StripedMatrix {
 };
 
 // ------------------------------------------------------------ LinearTransform
-// res = Rescale( sum_k diag_k (*) rot_k(in) ) by baby-step/giant-step.
+// res = Rescale( sum_k diag_k (*) rot_k(in) ) by baby-step/giant-step, run by
+// one engine call (cfhe_linear_transform) that hoists both the baby and the
+// giant steps.
 template <typename word>
 class LinearTransform {
   using Ct = Ciphertext<word>;
   using Pt = Plaintext<word>;
 
  public:
-  // The plaintext diagonals are encoded at `level` with the scale that makes
-  // the output scale scale_out for an input of scale scale_in.
+  // The plaintext diagonals are encoded at `level`, on the auxiliary primes as
+  // well, with the scale that makes the output scale scale_out for an input of
+  // scale scale_in. baby_steps <= 16.
   LinearTransform(const ConstContextPtr<word> &ctx, const StripedMatrix &m, int level, double scale_in,
-                  double scale_out, int baby_steps = 8)
-      : level_(level), bs_(baby_steps), n_(m.n) {
+                  double scale_out, int baby_steps = 16)
+      : level_(level), bs_(baby_steps), n_(m.n), scale_out_(scale_out) {
     const auto &param = ctx->param_;
     AssertTrue(level > 0, "LinearTransform needs a level that can be rescaled");
-    pt_scale_ = param.GetRescalePrimeProd(level) * (scale_out / scale_in);
+    AssertTrue(bs_ >= 1 && bs_ <= 16, "LinearTransform: 1 to 16 baby steps");
+    const double pt_scale = param.GetRescalePrimeProd(level) * (scale_out / scale_in);
     // stride g = gcd of the offsets and n; signed multiples t in (-n/2g, n/2g]
     int g = n_;
     for (auto &[k, d] : m.diag)
       if (k) g = std::gcd(g, k);
-    g_ = g;
-    const int period = n_ / g_;
+    const int period = n_ / g;
     int tmin = 0, tmax = 0;
     std::map<int, const std::vector<Complex> *> by_t;
     for (auto &[k, d] : m.diag) {
-      int t = k / g_;
+      int t = k / g;
       if (t > period / 2) t -= period;
       by_t[t] = &d;
       tmin = std::min(tmin, t);
       tmax = std::max(tmax, t);
     }
-    tmin_ = tmin;
-    gs_ = (tmax - tmin) / bs_ + 1;
-    pts_.resize(gs_);
-    for (int j = 0; j < gs_; j++) {
-      const int G = Giant(j);
-      for (int i = 0; i < bs_; i++) {
-        auto it = by_t.find(tmin + i + bs_ * j);
-        if (it == by_t.end()) continue;
-        // the giant rotation is applied after the product: pre-rotate by -G
-        std::vector<Complex> v(n_);
-        for (int p = 0; p < n_; p++) v[p] = (*it->second)[((p - G) % n_ + n_) % n_];
-        Pt pt;
-        ctx->encoder().Encode(pt, level, pt_scale_, v, 0);
-        pts_[j].emplace(i, std::move(pt));
+    // giant offsets are multiples of bs, so one of them is zero whenever the
+    // range of t includes it (one key switch fewer)
+    const int t0 = (int)std::floor((double)tmin / bs_) * bs_;
+    // keyed by the giant rotation itself: offsets wrap modulo n, so different
+    // multiples can be the same rotation
+    std::map<int, std::map<int, Pt>> pts;  // [giant rotation][baby index]
+    std::set<int> babies{0};
+    for (auto &[t, d] : by_t) {
+      const int j = (t - t0) / bs_, i = (t - t0) % bs_;
+      const int G = Mod((long long)g * (t0 + bs_ * j));
+      // the giant rotation is applied after the product: pre-rotate by -G
+      std::vector<Complex> v(n_);
+      for (int p = 0; p < n_; p++) v[p] = (*d)[Mod((long long)p - G)];
+      AssertTrue(!pts[G].count(i), "LinearTransform: two diagonals share a slot");
+      ctx->encoder().Encode(pts[G][i], level, pt_scale, v, param.alpha_);
+      babies.insert(i);
+    }
+    std::map<int, int> baby_slot;
+    for (int i : babies) {
+      baby_slot[i] = baby_rot_.size();
+      baby_rot_.push_back(Mod((long long)g * i));
+    }
+    for (auto &[G, row] : pts) {
+      giant_rot_.push_back(G);
+      std::vector<Pt> dense(baby_rot_.size());
+      std::vector<bool> have(baby_rot_.size(), false);
+      for (auto &[i, pt] : row) {
+        dense[baby_slot.at(i)] = std::move(pt);
+        have[baby_slot.at(i)] = true;
+      }
+      for (size_t k = 0; k < dense.size(); k++) {
+        pts_.push_back(std::move(dense[k]));
+        present_.push_back(have[k]);
       }
     }
+    AssertTrue(giant_rot_.size() <= 16, "LinearTransform: more than 16 giant steps");
   }
 
-  int Giant(int j) const { return (((long long)g_ * (tmin_ + bs_ * j)) % n_ + n_) % n_; }
-  int Baby(int i) const { return ((long long)g_ * i) % n_; }
-
   void AddRequiredRotations(std::set<int> &rots) const {
-    for (int i = 1; i < bs_; i++)
-      if (NeedsBaby(i)) rots.insert(Baby(i));
-    for (int j = 0; j < gs_; j++)
-      if (!pts_[j].empty() && Giant(j)) rots.insert(Giant(j));
+    for (int r : baby_rot_)
+      if (r) rots.insert(r);
+    for (int r : giant_rot_)
+      if (r) rots.insert(r);
   }
 
   void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &in, const EvkMap<word> &keys) const {
-    AssertTrue(ctx->param_.NPToLevel(in.GetNP()) == level_, "LinearTransform: wrong input level");
-    // baby steps: rotations of the input that share one ModUp
-    std::vector<int> rots;
-    std::vector<const EvaluationKey<word> *> rkeys;
-    std::vector<int> which;
-    for (int i = 1; i < bs_; i++)
-      if (NeedsBaby(i)) {
-        rots.push_back(Baby(i));
-        rkeys.push_back(&keys.GetRotationKey(Baby(i)));
-        which.push_back(i);
-      }
-    std::vector<Ct> rotated;
-    if (!rots.empty()) ctx->HoistedRotate(rotated, in, rots, rkeys);
-    std::map<int, const Ct *> baby;
-    baby[0] = &in;
-    for (size_t k = 0; k < which.size(); k++) baby[which[k]] = &rotated[k];
-    // giant steps
-    Ct total, acc, term, turned;
-    bool have_total = false;
-    for (int j = 0; j < gs_; j++) {
-      if (pts_[j].empty()) continue;
-      bool have_acc = false;
-      for (auto &[i, pt] : pts_[j]) {
-        if (!have_acc) {
-          ctx->Mult(acc, *baby.at(i), pt);
-          have_acc = true;
-        } else {
-          ctx->Mult(term, *baby.at(i), pt);
-          ctx->Add(acc, acc, term);
+    const auto &param = ctx->param_;
+    AssertTrue(param.NPToLevel(in.GetNP()) == level_, "LinearTransform: wrong input level");
+    AssertFalse(in.HasRx(), "LinearTransform: relinearize first");
+    const int beta = cfhe_beta(ctx->h_, level_);
+    int key_main = -1;
+    auto gather = [&](const std::vector<int> &rots, std::vector<const word *> &kb,
+                      std::vector<const word *> &ka) {
+      for (int r : rots)
+        for (int d = 0; d < beta; d++) {
+          if (!r) {
+            kb.push_back(nullptr);
+            ka.push_back(nullptr);
+            continue;
+          }
+          const auto &key = keys.GetRotationKey(r);
+          AssertTrue(key.GetBeta() >= beta, "Beta mismatch");
+          AssertTrue(key_main < 0 || key_main == key.GetNP().num_main_, "LinearTransform: key shapes differ");
+          key_main = key.GetNP().num_main_;
+          kb.push_back(key.bx_[d].data());
+          ka.push_back(key.ax_[d].data());
         }
-      }
-      const int G = Giant(j);
-      const Ct *part = &acc;
-      if (G) {
-        ctx->HRot(turned, acc, keys.GetRotationKey(G), G);
-        part = &turned;
-      }
-      if (!have_total) {
-        ctx->Copy(total, *part);
-        have_total = true;
-      } else {
-        ctx->Add(total, total, *part);
-      }
-    }
-    ctx->Rescale(res, total);
+    };
+    std::vector<const word *> bkb, bka, gkb, gka, pt;
+    gather(baby_rot_, bkb, bka);
+    gather(giant_rot_, gkb, gka);
+    for (size_t k = 0; k < pts_.size(); k++) pt.push_back(present_[k] ? pts_[k].mx_.data() : nullptr);
+    Ct out(param.LevelToNP(level_ - 1));
+    CheckAbi(cfhe_linear_transform(ctx->h_, level_, 1, out.bx_.data(), out.ax_.data(), in.bx_.data(),
+                                   in.ax_.data(), baby_rot_.size(), baby_rot_.data(), bkb.data(), bka.data(),
+                                   giant_rot_.size(), giant_rot_.data(), gkb.data(), gka.data(), pt.data(),
+                                   Max(key_main, 0)));
+    out.SetScale(scale_out_);
+    out.SetNumSlots(in.GetNumSlots());
+    res = std::move(out);
   }
 
   int level() const { return level_; }
+  int NumBabySteps() const { return baby_rot_.size(); }
+  int NumGiantSteps() const { return giant_rot_.size(); }
 
  private:
-  bool NeedsBaby(int i) const {
-    for (auto &m : pts_)
-      if (m.count(i)) return true;
-    return false;
-  }
-  int level_, bs_, gs_ = 0, n_, g_ = 1, tmin_ = 0;
-  double pt_scale_ = 1.0;
-  std::vector<std::map<int, Pt>> pts_;  // [giant][baby]
+  int Mod(long long x) const { return (int)(((x % n_) + n_) % n_); }
+  int level_, bs_, n_;
+  double scale_out_;
+  std::vector<int> baby_rot_, giant_rot_;  // slot distances; baby_rot_[0] == 0
+  std::vector<Pt> pts_;                    // [giant][baby], dense
+  std::vector<bool> present_;
 };
 
 // ------------------------------------------------------------ EvalPoly
@@ -196,19 +205,19 @@ class EvalPoly {
 
  public:
   // res = 2*A*B - C (C may be null: 2*A*B - c0 with the real constant c0),
-  // one level below min(level A, level B)
+  // one level below min(level A, level B). Everything is subtracted from the
+  // unrelinearised product, so the node costs one RelinearizeRescale.
   static void Node(const ConstContextPtr<word> &ctx, Ct &res, const Ct &A, const Ct &B, const Ct *C,
                    double c0, const Evk &mult_key) {
     const auto &param = ctx->param_;
     const int la = param.NPToLevel(A.GetNP()), lb = param.NPToLevel(B.GetNP());
     const int l = Min(la, lb);
-    Ct a, b, prod, lin;
+    Ct a, b, prod;
     ctx->DropToLevel(a, A, l);
     if (&A != &B) ctx->DropToLevel(b, B, l);
     ctx->Mult(prod, a, &A != &B ? b : a);
-    ctx->Relinearize(lin, prod, mult_key);
-    ctx->Add(lin, lin, lin);
-    const double s = lin.GetScale();
+    ctx->Add(prod, prod, prod);
+    const double s = prod.GetScale();
     if (C) {
       Ct c, cs;
       ctx->DropToLevel(c, *C, l);
@@ -216,13 +225,21 @@ class EvalPoly {
       ctx->encoder().EncodeConstant(one, l, s / c.GetScale(), 1.0, 0);
       ctx->Mult(cs, c, one);
       cs.SetScale(s);
-      ctx->Sub(lin, lin, cs);
+      ctx->Sub(prod, prod, cs);
     } else if (c0 != 0.0) {
       Constant<word> k;
       ctx->encoder().EncodeConstant(k, l, s, c0, 0);
-      ctx->Sub(lin, lin, k);
+      ctx->Sub(prod, prod, k);
     }
-    ctx->Rescale(res, lin);
+    ctx->RelinearizeRescale(res, prod, mult_key);
+  }
+
+  // Rescale of a sum that may still carry unrelinearised products
+  static void Finish(const ConstContextPtr<word> &ctx, Ct &res, const Ct &sum, const Evk &mult_key) {
+    if (sum.HasRx())
+      ctx->RelinearizeRescale(res, sum, mult_key);
+    else
+      ctx->Rescale(res, sum);
   }
 
   // res = sum_k coeffs[k] T_k(x), x with slot values in [-1, 1]. The result
@@ -243,11 +260,13 @@ class EvalPoly {
     AssertTrue(top > 0, "EvaluateChebyshev: not enough levels");
     Ct sum;
     Sum(ctx, sum, c, target_scale * param.GetRescalePrimeProd(top), top, T, mult_key);
-    ctx->Rescale(res, sum);
+    Finish(ctx, res, sum, mult_key);
   }
 
  private:
-  // res = sum_k c[k] T_k at level `level`, at scale W, not yet rescaled.
+  // res = sum_k c[k] T_k at level `level`, at scale W, not yet rescaled and
+  // with its products not yet relinearised (all products formed at one level
+  // share the relinearisation that Finish performs).
   // T_{m+j} = 2 T_m T_j - T_{m-j} turns p into q * T_m + r with
   //   q_0 = c_m, q_j = 2 c_{m+j};  r_0 = c_0, r_k = c_k - c_{2m-k}.
   static void Sum(const ConstContextPtr<word> &ctx, Ct &res, const std::vector<double> &c, double W,
@@ -283,12 +302,11 @@ class EvalPoly {
     if (q.size() == 1) {
       scaled(high, T.at(m), q[0]);
     } else {
-      Ct tm, qsum, qv, prod;
+      Ct tm, qsum, qv;
       ctx->DropToLevel(tm, T.at(m), level);
       Sum(ctx, qsum, q, (W / tm.GetScale()) * param.GetRescalePrimeProd(level + 1), level + 1, T, mult_key);
-      ctx->Rescale(qv, qsum);
-      ctx->Mult(prod, qv, tm);
-      ctx->Relinearize(high, prod, mult_key);
+      Finish(ctx, qv, qsum, mult_key);
+      ctx->Mult(high, qv, tm);
       high.SetScale(W);
     }
     bool r_zero = true;
@@ -743,7 +761,7 @@ class BootContext : public Context<word> {
   int GetLogScaleUp() const { return log_scaleup_; }
 
  private:
-  static constexpr int kBabySteps = 8;
+  static constexpr int kBabySteps = 16;
 
   BootContext(const Parameter<word> &param, const BootParameter &bp) : Base(param), boot_param_{bp} {
     AssertTrue(param.max_level_ == bp.max_level_ && param.default_encryption_level_ == bp.GetStCStartLevel(),

@@ -1078,11 +1078,33 @@ class Context : public std::enable_shared_from_this<Context<word>> {
   void AddSub(Ct &res, const Ct &a, const Ct &b, int op) const {
     AssertSameNP(a, b);
     AssertSameScale(a.GetScale(), b.GetScale());
-    AssertTrue(a.HasRx() == b.HasRx(), "Add/Sub: operands must both carry rx or both not");
+    NPInfo np = a.GetNP();
+    if (a.HasRx() != b.HasRx()) {
+      // an unrelinearised product plus an ordinary ciphertext: the third
+      // polynomial passes through (negated when it is subtracted). The
+      // reference requires relinearisation first; this saves one key switch
+      // when several products at one level are summed.
+      const Ct &x = a.HasRx() ? a : b;
+      if (&res != &x) {
+        res.ModifyNP(np);
+        res.PrepareRx();
+      }
+      res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
+      res.SetScale(a.GetScale());
+      Binary(op, res.bx_.data(), a.bx_.data(), b.bx_.data(), np);
+      Binary(op, res.ax_.data(), a.ax_.data(), b.ax_.data(), np);
+      if (a.HasRx()) {
+        if (&res != &a) D2D(res.rx_, a.rx_, np);
+      } else if (op == 0) {
+        if (&res != &b) D2D(res.rx_, b.rx_, np);
+      } else {
+        Binary(2, res.rx_.data(), b.rx_.data(), nullptr, np);
+      }
+      return;
+    }
     MatchResultWith(res, a);
     res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
     res.SetScale(a.GetScale());
-    NPInfo np = res.GetNP();
     Binary(op, res.bx_.data(), a.bx_.data(), b.bx_.data(), np);
     Binary(op, res.ax_.data(), a.ax_.data(), b.ax_.data(), np);
     if (a.HasRx()) Binary(op, res.rx_.data(), a.rx_.data(), b.rx_.data(), np);

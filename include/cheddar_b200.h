@@ -208,6 +208,32 @@ CFHE_API int cfhe_hoisted_rotations(cfhe_context *ctx, int level, uint32_t *out,
                                     int n_rot, const int *rot,
                                     const uint32_t *const *evk_b,
                                     const uint32_t *const *evk_a, int key_main);
+/* Baby-step/giant-step linear transform of one ciphertext (the reference's
+ * HoistHandler: BSFusedKeyMult and GSFusedPAccum, src/extension/Hoist.cu:20-120,
+ * 208-360, driven by LinearTransform::Evaluate,
+ * src/extension/LinearTransform.cpp:118-124):
+ *   out = Down( sum_j rot_{giant_rot[j]}( Down( sum_i pt[j][i] (*) rot_{baby_rot[i]}(in) ) ) )
+ * The baby rotations share one ModUp and stay on the extended basis; the
+ * plaintexts are multiplied there; every giant rotation is a key switch added
+ * into one extended-basis accumulator, so one ModDown ends the call, fused
+ * with the rescale to level-1 when rescale != 0.
+ * baby_rot[0] must be 0 (the input itself); the other baby_rot[i] and the
+ * non-zero giant_rot[j] are slot distances in (0, N/2); at most one giant_rot
+ * may be 0; n_baby, n_giant <= 16. Keys as for cfhe_hoisted_rotations: HOST
+ * arrays of n*beta device pointers, step s digit d at [s*beta + d] (entries of
+ * unrotated steps are not read). pt: HOST array of n_giant*n_baby device
+ * pointers, pt[j*n_baby + i] = NTT, M-form plaintext on the level's limbs
+ * followed by the alpha auxiliary limbs ((nq+alpha)*N words), or NULL. */
+CFHE_API int cfhe_linear_transform(cfhe_context *ctx, int level, int rescale,
+                                   uint32_t *out_b, uint32_t *out_a,
+                                   const uint32_t *in_b, const uint32_t *in_a,
+                                   int n_baby, const int *baby_rot,
+                                   const uint32_t *const *baby_evk_b,
+                                   const uint32_t *const *baby_evk_a,
+                                   int n_giant, const int *giant_rot,
+                                   const uint32_t *const *giant_evk_b,
+                                   const uint32_t *const *giant_evk_a,
+                                   const uint32_t *const *pt, int key_main);
 /* Context::HMult (Context.cpp:862-871): tensor product, relinearisation and,
  * when rescale != 0, ModDownAndRescale to level-1 (RelinearizeRescale,
  * :714-737); rescale == 0 keeps the level (Relinearize, :561-565). */

@@ -94,7 +94,7 @@ int main(int argc, char **argv) {
     for (int r : rots) ui.PrepareRotationKey(r, param->max_level_);
     lt.Evaluate(ctx, out, ct, ui.GetEvkMap());
     decrypt(got, out);
-    Report("LinearTransform (12 diagonals, BSGS 8 x 4, level 20)", M.Apply(z), got, 1e-4);
+    Report("LinearTransform (12 diagonals, baby steps of 8, level 20)", M.Apply(z), got, 1e-4);
     std::cout << "       rotations used: " << rots.size() << std::endl;
   }
 
@@ -148,7 +148,7 @@ int main(int argc, char **argv) {
     em.Evaluate(ctx, out, ct, ui.GetMultiplicationKey());
     decrypt(got, out);
     std::cout << "       levels " << level << " -> " << param->NPToLevel(out.GetNP()) << std::endl;
-    Report("EvalMod (K = 16) against sin(2 pi u) / 2 pi", expect, got, 1e-10);
+    Report("EvalMod (K = 16) against sin(2 pi u) / 2 pi", expect, got, 1e-9);
   }
 
   if (want("fft")) {
