@@ -281,7 +281,7 @@ int cfhe_ntt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
   a.premul = mont_conv != 0;
   if (a.premul)
     for (int l = 0; l < n_limbs; l++) a.kc[l] = make_tw(r_mod(a.q[l]), a.q[l]);
-  return launch_ntt(c, a, false);
+  { int r_ = launch_ntt(c, a, false); c.mark("ntt"); return r_; }
 }
 
 int cfhe_intt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
@@ -311,7 +311,7 @@ int cfhe_intt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
     }
     a.kc[l] = make_tw(k, q);
   }
-  return launch_ntt(c, a, true);
+  { int r_ = launch_ntt(c, a, true); c.mark("intt"); return r_; }
 }
 
 // ---------------------------------------------------------------------------
@@ -341,7 +341,7 @@ int cfhe_binary(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
   if (op != 2 && !b) return fail("null argument");
   EwArgs e;
   if (int r = fill_rows(h->c, e, dst, a, b, nullptr, gidx, n_limbs)) return r;
-  return launch_ew(h->c, map[op], e);
+  { int r_ = launch_ew(h->c, map[op], e); h->c.mark("elementwise"); return r_; }
 }
 
 int cfhe_const_op(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
@@ -353,7 +353,7 @@ int cfhe_const_op(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
   if (op == 4 && !b) return fail("null argument");
   EwArgs e;
   if (int r = fill_rows(h->c, e, dst, a, b, consts, gidx, n_limbs)) return r;
-  return launch_ew(h->c, map[op], e);
+  { int r_ = launch_ew(h->c, map[op], e); h->c.mark("elementwise"); return r_; }
 }
 
 int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
@@ -372,7 +372,7 @@ int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
     t.rows[l] = TensorRow{d0 + o, d1 + o, d2 + o, b1 + o, a1 + o,
                           b2 + o, a2 + o, c.q[g], c.nqinv[g]};
   }
-  return launch_tensor(c, t);
+  { int r_ = launch_tensor(c, t); c.mark("tensor"); return r_; }
 }
 
 int cfhe_permute(cfhe_context *h, uint32_t *dst, const uint32_t *src,
@@ -383,7 +383,7 @@ int cfhe_permute(cfhe_context *h, uint32_t *dst, const uint32_t *src,
   if ((galois & 1u) == 0 || galois >= 2u * kN) return fail("invalid Galois element");
   EwArgs e;
   if (int r = fill_rows(h->c, e, dst, src, add, nullptr, gidx, n_limbs)) return r;
-  return launch_permute(h->c, e, galois);
+  { int r_ = launch_permute(h->c, e, galois); h->c.mark("permute"); return r_; }
 }
 
 uint32_t cfhe_galois_for_rotation(const cfhe_context *h, int rot) {
@@ -410,7 +410,7 @@ int cfhe_mul_imag_unit(cfhe_context *h, uint32_t *dst, const uint32_t *src,
   }
   EwArgs e;
   if (int r = fill_rows(c, e, dst, src, nullptr, u.data(), gidx, n_limbs)) return r;
-  return launch_ew(c, EW_IMAG, e);
+  { int r_ = launch_ew(c, EW_IMAG, e); c.mark("elementwise"); return r_; }
 }
 
 int cfhe_modup_to_max(cfhe_context *h, uint32_t *dst, const uint32_t *src,
@@ -429,7 +429,7 @@ int cfhe_modup_to_max(cfhe_context *h, uint32_t *dst, const uint32_t *src,
     if (g < 0 || g >= c.NP) return fail("prime index out of range");
     e.rows[l] = EwRow{dst + (size_t)l * kN, nullptr, nullptr, c.q[g], c.nqinv[g], 0u, 0u};
   }
-  return launch_lift(c, e, src, c.q[src_gidx[0]], n_src == 2 ? c.q[src_gidx[1]] : 0u);
+  { int r_ = launch_lift(c, e, src, c.q[src_gidx[0]], n_src == 2 ? c.q[src_gidx[1]] : 0u); c.mark("lift"); return r_; }
 }
 
 // ---------------------------------------------------------------------------

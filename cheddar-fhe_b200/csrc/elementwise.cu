@@ -191,46 +191,47 @@ __global__ void __launch_bounds__(kEwThreads)
   }
 }
 
-// acc_j = sum_i pt[j][i] (*) rot_i on one limb, two coefficients per thread.
+// acc_j = sum_i pt[j][i] (*) rot_i on one limb, one coefficient per thread.
 // The rotations are held in registers across the giant steps, so every
 // plaintext word and every rotation word is read once (the reference's
 // GSFusedPAccum kernel keeps the same operands in registers,
-// src/extension/Hoist.cu:80-120). Products are summed before one Montgomery
-// reduction per output.
+// src/extension/Hoist.cu:80-120). Products are summed in 64 bits, folded below
+// q*2^32 after every second one (2 q^2 <= q*2^32 for q < 2^31), with one
+// Montgomery reduction per output. About 100 registers per thread keep two
+// blocks of 256 threads on an SM.
 constexpr int kPtThreads = 256;
-__global__ void __launch_bounds__(kPtThreads)
+__global__ void __launch_bounds__(kPtThreads, 2)
     pt_accum_kernel(const __grid_constant__ PtAccumArgs a) {
   const int l = blockIdx.y;
-  const int v = blockIdx.x * kPtThreads + threadIdx.x;  // pair index inside the limb
+  const int v = blockIdx.x * kPtThreads + threadIdx.x;
   const uint32_t q = a.q[l], nq = a.nqinv[l];
   const uint64_t q32 = (uint64_t)q << 32;
-  const size_t limb = (size_t)l * kN, poly = (size_t)a.ntot * kN;
-  uint2 rb[kMaxBaby], ra[kMaxBaby];
+  const size_t limb = (size_t)l * kN + v, poly = (size_t)a.ntot * kN;
+  uint32_t rb[kMaxBaby], ra[kMaxBaby];
 #pragma unroll
   for (int i = 0; i < kMaxBaby; i++)
     if (i < a.n_baby) {
-      rb[i] = reinterpret_cast<const uint2 *>(a.rot + (size_t)(2 * i) * poly + limb)[v];
-      ra[i] = reinterpret_cast<const uint2 *>(a.rot + (size_t)(2 * i + 1) * poly + limb)[v];
+      rb[i] = a.rot[(size_t)(2 * i) * poly + limb];
+      ra[i] = a.rot[(size_t)(2 * i + 1) * poly + limb];
     }
 #pragma unroll 1
   for (int j = 0; j < a.n_giant; j++) {
-    uint64_t sb0 = 0, sb1 = 0, sa0 = 0, sa1 = 0;
+    uint32_t w[kMaxBaby];
 #pragma unroll
-    for (int i = 0; i < kMaxBaby; i++)
-      if (i < a.n_baby) {
-        const uint32_t *p = a.pt[j * kMaxBaby + i];
-        if (p) {
-          const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(p + limb) + v);
-          mac_fold(sb0, rb[i].x, w.x, q32);
-          mac_fold(sb1, rb[i].y, w.y, q32);
-          mac_fold(sa0, ra[i].x, w.x, q32);
-          mac_fold(sa1, ra[i].y, w.y, q32);
-        }
-      }
-    reinterpret_cast<uint2 *>(a.acc + (size_t)(2 * j) * poly + limb)[v] =
-        make_uint2(mont_reduce(sb0, q, nq), mont_reduce(sb1, q, nq));
-    reinterpret_cast<uint2 *>(a.acc + (size_t)(2 * j + 1) * poly + limb)[v] =
-        make_uint2(mont_reduce(sa0, q, nq), mont_reduce(sa1, q, nq));
+    for (int i = 0; i < kMaxBaby; i++) {
+      const uint32_t *p = i < a.n_baby ? a.pt[j * kMaxBaby + i] : nullptr;
+      w[i] = p ? __ldcs(p + limb) : 0u;
+    }
+    uint64_t sb = 0, sa = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxBaby; i += 2) {
+      sb += (uint64_t)rb[i] * w[i] + (uint64_t)rb[i + 1] * w[i + 1];
+      sa += (uint64_t)ra[i] * w[i] + (uint64_t)ra[i + 1] * w[i + 1];
+      if (sb >= q32) sb -= q32;
+      if (sa >= q32) sa -= q32;
+    }
+    a.acc[(size_t)(2 * j) * poly + limb] = mont_reduce(sb, q, nq);
+    a.acc[(size_t)(2 * j + 1) * poly + limb] = mont_reduce(sa, q, nq);
   }
 }
 
@@ -311,7 +312,7 @@ int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois) {
 }
 
 int launch_pt_accum(const Context &ctx, const PtAccumArgs &args) {
-  dim3 grid(kN / 2 / kPtThreads, args.ntot), block(kPtThreads);
+  dim3 grid(kN / kPtThreads, args.ntot), block(kPtThreads);
   pt_accum_kernel<<<grid, block, 0, ctx.stream>>>(args);
   CFHE_CUDA(cudaGetLastError());
   return 0;

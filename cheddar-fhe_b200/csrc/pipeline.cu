@@ -419,7 +419,9 @@ static int lift_to_extended(const Context &c, const LevelPlan &lp, uint32_t *dst
     CFHE_CUDA(cudaMemsetAsync(d + (size_t)lp.nq * kN, 0, (size_t)(lp.ntot - lp.nq) * kN * sizeof(uint32_t),
                               c.stream));
   }
-  return launch_ew(c, EW_MULC, e);
+  if (int r = launch_ew(c, EW_MULC, e)) return r;
+  c.mark("lift");
+  return 0;
 }
 
 int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t *out_b,

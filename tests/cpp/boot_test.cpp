@@ -196,6 +196,27 @@ int main(int argc, char **argv) {
     std::cout << "       phases (ms, host-synchronised):";
     for (auto &[name, ms] : phases) std::cout << "  " << name << " " << std::fixed << std::setprecision(2) << ms;
     std::cout << std::endl;
+    if (only.count("profile")) {
+      // device time per pipeline stage (CUDA events after every stage), summed by name
+      CheckAbi(cfhe_profile_begin(ctx->h_));
+      boot_ctx->Boot(out, ct, ui.GetEvkMap());
+      std::vector<char> names(1 << 20);
+      std::vector<float> ms(1 << 16);
+      const int cnt = cfhe_profile_end(ctx->h_, names.data(), names.size(), ms.data(), ms.size());
+      std::map<std::string, std::pair<double, int>> by_name;
+      std::stringstream ss(names.data());
+      std::string nm;
+      double total = 0;
+      for (int i = 0; i < cnt && std::getline(ss, nm, ';'); i++) {
+        by_name[nm].first += ms[i];
+        by_name[nm].second++;
+        total += ms[i];
+      }
+      std::cout << "       device time by stage (" << cnt << " stages, " << total << " ms):" << std::endl;
+      for (auto &[k, v] : by_name)
+        std::cout << "         " << std::setw(16) << k << "  " << std::setw(5) << v.second << " x  " << std::fixed
+                  << std::setprecision(3) << v.first << " ms" << std::endl;
+    }
     decrypt(got, out);
     std::cout << "       Boot: level 0 -> " << param->NPToLevel(out.GetNP()) << ", best of 4: " << best << " ms"
               << std::endl;
