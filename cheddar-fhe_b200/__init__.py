@@ -259,6 +259,40 @@ class Engine:
                                                   len(r), rp, self._ptrs(flat_b), self._ptrs(flat_a),
                                                   int(key_main)))
 
+    def linear_transform_(self, level, out_b, out_a, in_b, in_a, baby_rots, baby_keys, giant_rots,
+                          giant_keys, pts, key_main, rescale=True):
+        """Baby-step/giant-step linear transform (cfhe_linear_transform).
+        baby_rots[0] must be 0. baby_keys / giant_keys: per step a pair
+        (digits_b, digits_a) of lists of beta device tensors, or None for an
+        unrotated step. pts[j][i]: device tensor [(nq+alpha), N] or None."""
+        beta = self.beta(level)
+
+        def flat(keys, part):
+            out = []
+            for k in keys:
+                out += [None] * beta if k is None else list(k[part][:beta])
+            return (C.c_void_p * len(out))(*[t.data_ptr() if t is not None else None for t in out])
+
+        br, brp = _ints(baby_rots)
+        gr, grp = _ints(giant_rots)
+        ptl = [pts[j][i] for j in range(len(gr)) for i in range(len(br))]
+        pta = (C.c_void_p * len(ptl))(*[t.data_ptr() if t is not None else None for t in ptl])
+        self._check(self.L.cfhe_linear_transform(
+            self.h, level, int(rescale), self._p(out_b), self._p(out_a), self._p(in_b), self._p(in_a),
+            len(br), brp, flat(baby_keys, 0), flat(baby_keys, 1),
+            len(gr), grp, flat(giant_keys, 0), flat(giant_keys, 1), pta, int(key_main)))
+
+    def modup_to_max_(self, dst, src, src_gidx, dst_gidx):
+        """Exact centred lift of a one- or two-limb value (cfhe_modup_to_max)."""
+        sg, sgp = _ints(src_gidx)
+        dg, dgp = _ints(dst_gidx)
+        self._check(self.L.cfhe_modup_to_max(self.h, self._p(dst), self._p(src), sgp, len(sg), dgp, len(dg)))
+
+    def modup_to_max(self, src, src_gidx, dst_gidx):
+        d = self.empty(len(dst_gidx), self.n)
+        self.modup_to_max_(d, self.to_dev(src), src_gidx, dst_gidx)
+        return self.to_host(d)
+
     def hmult_(self, level, out_b, out_a, b1, a1, b2, a2, evk_b, evk_a, key_main, rescale=True):
         self._check(self.L.cfhe_hmult(self.h, level, self._p(out_b), self._p(out_a),
                                       self._p(b1), self._p(a1), self._p(b2), self._p(a2),

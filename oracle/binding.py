@@ -250,6 +250,24 @@ class Oracle:
         self._call("orc_add_p_times", level, acc, _u32(x))
         return acc
 
+    def modup_to_max(self, src, src_gidx, dst_gidx):
+        """Exact centred lift of a value known modulo one or two primes to
+        other primes (reference kernels ModUpToMax1 / ModUpToMax2,
+        src/core/ElementWise.cu:579-623). src: plain coefficients; in the
+        two-limb case limb k is already multiplied by (q_other)^-1 mod q_k."""
+        src = np.asarray(src, dtype=np.uint32).astype(np.int64)
+        q = [int(self.primes[g]) for g in src_gidx]
+        out = np.empty((len(dst_gidx), self.n), dtype=np.uint32)
+        if len(q) == 1:
+            x = src[0]
+        else:
+            prod = q[0] * q[1]
+            x = (src[0] * q[1] + src[1] * q[0]) % prod
+            x = np.where(x > prod // 2, x - prod, x)
+        for m, g in enumerate(dst_gidx):
+            out[m] = (x % int(self.primes[g])).astype(np.uint32)
+        return out
+
     def hmult(self, level, b1, a1, b2, a2, evk_b, evk_a, key_main, rescale=True):
         b1, a1, b2, a2 = map(_u32, (b1, a1, b2, a2))
         evk_b = [_u32(x) for x in evk_b]

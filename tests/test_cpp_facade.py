@@ -25,6 +25,16 @@ def test_facade_compiles_and_links(pkg):
     assert r.returncode == 2 and "usage" in r.stderr
 
 
+def test_bootstrapping_facade_compiles_and_links(pkg):
+    """Boot.h (linear transforms, Chebyshev evaluation, EvalMod, BootContext)
+    builds against the C ABI header; the usage path runs without a GPU."""
+    if not os.path.exists(pkg.LIB_PATH):
+        pkg.build()
+    subprocess.check_call(["make", "-s", "-C", CPP, "boot_test"])
+    r = subprocess.run([os.path.join(CPP, "boot_test")], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage" in r.stderr
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("param_set", ["bootparam_40.json", "bootparam_30.json", "bootparam_35.json"])
 def test_basic_test_bodies(pkg, param_set):

@@ -201,3 +201,25 @@ def test_library_exports_every_declared_symbol(pkg):
     lib = C.CDLL(pkg.LIB_PATH)
     for n in sorted(names):
         assert hasattr(lib, n), n
+
+
+def test_modup_to_max_is_the_centred_lift(oracle40):
+    """Golden model of the bootstrapping lift (reference ModUpToMax1/2,
+    src/core/ElementWise.cu:579-623) against Python integers."""
+    o = oracle40
+    rng = np.random.default_rng(9)
+    base = [2, 3]
+    q0, q1 = int(o.primes[2]), int(o.primes[3])
+    xs = [0, 1, -1, (q0 * q1 - 1) // 2, -((q0 * q1 - 1) // 2)] + [int(v) for v in rng.integers(-2**48, 2**48, 11)]
+    src = np.zeros((2, o.n), dtype=np.uint32)
+    for i, x in enumerate(xs):
+        src[0, i] = (x * pow(q1, -1, q0)) % q0
+        src[1, i] = (x * pow(q0, -1, q1)) % q1
+    dst = [0, 4, 30, 47, 58]
+    out = o.modup_to_max(src, base, dst)
+    for i, x in enumerate(xs):
+        for m, g in enumerate(dst):
+            assert int(out[m, i]) == x % int(o.primes[g])
+    one = o.modup_to_max(src[:1], base[:1], dst)
+    for m, g in enumerate(dst):
+        assert int(one[m, 3]) == int(src[0, 3]) % int(o.primes[g])
