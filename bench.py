@@ -25,6 +25,7 @@ import argparse
 import concurrent.futures as cf
 import importlib.util
 import json
+import math
 import os
 import subprocess
 import sys
@@ -332,7 +333,7 @@ def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
             "precision_bits": precision_bits}
 
 
-def bench_reference_cuda(eng, torch, params, steps):
+def bench_reference_cuda(eng, torch, params, steps, with_boot=True):
     """The reference's own CUDA library (oracle/_ref, built unmodified from
     the reference tree) on the same GPU: HMult at level 28 on random residues
     and the config-1 NTT batch, timed with CUDA events inside its driver.
@@ -366,9 +367,33 @@ def bench_reference_cuda(eng, torch, params, steps):
     torch.cuda.synchronize()
     ntt_us = ref.ntt_batch_time(a, b, NTT_POLYS, NTT_LIMBS - T, T, max(steps, 2))
     ref.close()
-    return {"hmult_us": hm_us, "hmult_words_equal_engine": same,
+    boot = None
+    if with_boot:
+        torch.cuda.empty_cache()
+        boot = ref_binding.boot(params, iters=min(max(steps, 2), 10))
+    return {"bootstrap": boot, "hmult_us": hm_us, "hmult_words_equal_engine": same,
             "ntt_fwd_inv_us": ntt_us, "ntt_GBps": NTT_BYTES_PER_STEP / (ntt_us * 1e-6) / 1e9,
             "how": "unmodified reference sources compiled for sm_100a, legacy stream, CUDA events"}
+
+
+def bench_bootstrap(pkg, local, iters, warmup):
+    """Config 4: full bootstrapping of a level-0 ciphertext with 2^15 random
+    complex slots (bootparam_40, BootParameter(28, 4, 3)) through the C++
+    mirror of the reference API, one bootstrap per GPU per step. The host
+    program lib/boot_bench builds the keys and plaintext diagonals (tens of
+    seconds, untimed) and times Boot with the host clock around a device
+    synchronisation, as the reference's test does."""
+    exe = os.path.join(os.path.dirname(pkg.LIB_PATH), "boot_bench")
+    if not os.path.exists(exe):
+        raise RuntimeError("lib/boot_bench is missing: run the package build")
+    env = dict(os.environ)
+    visible = env.get("CUDA_VISIBLE_DEVICES")
+    env["CUDA_VISIBLE_DEVICES"] = visible.split(",")[local] if visible else str(local)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--iters", str(iters),
+                        "--warmup", str(warmup)], capture_output=True, text=True, env=env, timeout=900)
+    if r.returncode != 0:
+        raise RuntimeError("boot_bench failed: " + r.stderr[-500:])
+    return json.loads(r.stdout.strip().splitlines()[-1])
 
 
 def bench_hoisted(eng, torch, params, n_rot, steps):
@@ -450,7 +475,11 @@ def run_gpu(args, pkg):
         hoist = bench_hoisted(eng, torch, params, 64, max(2, args.steps // 5))
     ref_cuda = None
     if rank == 0 and world == 1 and not args.no_ref:
-        ref_cuda = bench_reference_cuda(eng, torch, params, args.steps)
+        ref_cuda = bench_reference_cuda(eng, torch, params, args.steps, not args.no_boot)
+    boot = None
+    if args.workload == "hmult" and not args.no_boot:
+        barrier()
+        boot = bench_bootstrap(pkg, local, min(max(args.steps, 2), 10), 3)
 
     def reduce_max(x):
         t = torch.tensor(x, device=f"cuda:{local}", dtype=torch.float64)
@@ -461,6 +490,8 @@ def run_gpu(args, pkg):
     ntt_ms, ntt_e2e, fwd_ms, inv_ms = reduce_max([ntt["ms_step"], ntt["ms_e2e"], ntt["fwd_ms"], ntt["inv_ms"]])
     if hm:
         hm_ms, hm_e2e = reduce_max([hm["ms_step"], hm["ms_e2e"]])
+    if boot:
+        boot_ms, boot_err = reduce_max([boot["boot_ms"], boot["mean_err"]])
     if rank == 0:
         peak, how = measured_peaks()
         ntt_val = world * NTT_BYTES_PER_STEP / (ntt_ms * 1e-3) / 1e9
@@ -519,6 +550,12 @@ def run_gpu(args, pkg):
             peak_, _ = measured_peaks()
             hoist["frac"] = hoist["GB/s"] / peak_
             line["hoisted_rotations"] = hoist
+        if boot:
+            line["bootstrap"] = {"ms": boot_ms, "unit": "ms per bootstrap (max over ranks)",
+                                 "bootstraps_per_s": world / (boot_ms * 1e-3),
+                                 "precision_bits": -math.log2(boot_err), "rank0": boot,
+                                 "workload": "bootparam_40, BootParameter(28,4,3), level 0 -> 13, 2^15 complex "
+                                             "slots uniform in [-1,1]^2, one ciphertext per GPU"}
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:
@@ -547,6 +584,7 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip decrypting the HMult result")
     ap.add_argument("--no-hoist", action="store_true", help="skip the 64-rotation hoisting sweep")
     ap.add_argument("--no-ref", action="store_true", help="skip timing the reference's CUDA library")
+    ap.add_argument("--no-boot", action="store_true", help="skip the bootstrapping workload")
     args = ap.parse_args()
     pkg = load_package()
     if args.impl == "reference":
