@@ -92,6 +92,7 @@ struct Context {
 
   std::vector<uint32_t> nqinv;      // -q^-1 mod 2^32, global order
   bool use_tc_bconv = true;         // base conversion on tcgen05 (CFHE_BCONV=simt disables)
+  bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
   int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out
   std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
   // workspace arena for pipeline temporaries (grown on demand)
@@ -137,5 +138,6 @@ const std::string &get_error();
   } while (0)
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse);
+int launch_ntt_twopass(const Context &ctx, const NttArgs &args, bool inverse);
 
 }  // namespace cfhe

@@ -185,6 +185,7 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1)
 }  // namespace
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse) {
+  if (ctx.use_twopass_ntt) return launch_ntt_twopass(ctx, args, inverse);
   static bool configured = false;
   if (!configured) {
     CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<false>,
