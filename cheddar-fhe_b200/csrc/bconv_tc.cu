@@ -8,9 +8,11 @@
 //
 //   D[c][4m+j] = sum_{k,i} byte_i(y[k][c]) * byte_j( T[m][k] * 2^(8i) mod p_m )
 //
-//   A (128 x K, K = 4*(ns+1) bytes): the canonical residues y[k][c] in [0,s_k)
+//   A (128 x K, K = 4*(ns+1) bytes): one pseudo source "number of residues
+//      above s_k/2" in word 0, then the canonical residues y[k][c] in [0,s_k)
 //      exactly as they sit in memory (little-endian words are their own byte
-//      planes), plus one pseudo source "number of residues above s_k/2";
+//      planes). Words past the last source hold repeats of it; their table
+//      rows are zero;
 //   B (N x K, N = 4*nd): byte planes of the table entries pre-multiplied by
 //      2^(8i), and for the pseudo source the byte planes of -(prod s)*2^64
 //      mod p_m, which turns the canonical residues back into the centred
@@ -87,6 +89,118 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
       : "memory");
 }
 
+// KCH = 16-byte chunks of K per operand row (K = 16 * KCH bytes, 4 * KCH words:
+// the pseudo source and up to 4 * KCH - 1 residues).
+template <int KCH>
+__device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob &j, uint8_t *sA,
+                                         uint8_t *sB, uint64_t *bar, const uint4 *s_lim,
+                                         uint32_t tmem, int m_count) {
+  constexpr int kWords = 4 * KCH;
+  constexpr int npad = kTcSliceN;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = npad
+  const uint32_t idesc = (2u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
+  constexpr uint32_t a_lbo = (kTcTile / 8) * 128, b_lbo = (uint32_t)(npad / 8) * 128;
+  uint32_t parity = 0;
+  bool failed = false;
+
+  // Residues of one coefficient. The loads of the next tile are issued before
+  // the wait on the tensor core and the epilogue of the current one and are
+  // not touched until the next iteration, so their latency hides behind that
+  // work. Source k >= ns re-reads the last source (its table rows are zero).
+  uint32_t yn[kWords - 1];
+  const uint32_t *src = j.src + tid;
+  auto load_tile = [&](int tile) {
+#pragma unroll
+    for (int k = 0; k < kWords - 1; k++)
+      yn[k] = __ldg(src + (size_t)min(k, j.ns - 1) * kN + tile * kTcTile);
+  };
+  if ((int)blockIdx.x < kN / kTcTile) load_tile(blockIdx.x);
+
+  for (int tile = blockIdx.x; tile < kN / kTcTile && !failed; tile += gridDim.x) {
+    const int col = tile * kTcTile + tid;
+    // 1. operand row: [count of residues above half their prime, residues...]
+    uint32_t w[kWords];
+    uint32_t nneg = 0;
+#pragma unroll
+    for (int k = 0; k < kWords - 1; k++) {
+      w[k + 1] = yn[k];
+      nneg += yn[k] > j.half[k];  // half[k >= ns] = 2^32 - 1
+    }
+    w[0] = nneg;
+#pragma unroll
+    for (int t = 0; t < KCH; t++)
+      *reinterpret_cast<uint4 *>(sA + t * a_lbo + (tid >> 3) * 128 + (tid & 7) * 16) =
+          make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // 2. one thread issues the MMAs of this tile and commits them to the barrier
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int ks = 0; ks < KCH / 2; ks++) {
+        const uint64_t da = smem_desc(smem_u32(sA) + ks * 2 * a_lbo, a_lbo, 128);
+        const uint64_t db = smem_desc(smem_u32(sB) + ks * 2 * b_lbo, b_lbo, 128);
+        const uint32_t acc = ks > 0;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+            : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                       smem_u32(bar))
+                   : "memory");
+    }
+    // the next tile's residues travel while the tensor core and the epilogue run
+    if (tile + (int)gridDim.x < kN / kTcTile) load_tile(tile + gridDim.x);
+    // 3. wait for the accumulators (bounded)
+    uint32_t spins = 0;
+    while (!mbar_try_wait(smem_u32(bar), parity)) {
+      if (++spins > kSpinLimit) {
+        failed = true;
+        break;
+      }
+    }
+    parity ^= 1;
+    if (__any_sync(0xffffffffu, failed)) {
+      failed = true;
+      if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // 4. epilogue: 8 destination limbs (32 accumulator columns) per load
+    if (!failed) {
+      const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+      uint32_t *out = j.dst + col;
+#pragma unroll
+      for (int m0 = 0; m0 < kTcSliceN / 4; m0 += 8) {
+        if (m0 < m_count) {
+          uint32_t d[32];
+          tmem_ld32(lane_base + 4 * m0, d);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const uint4 lim = s_lim[m0 + e];
+            // V = d0 + d1*2^8 + d2*2^16 + d3*2^24; every d < 2^23, so the two
+            // 16-bit-apart halves fit 32 bits and one wide multiply-add joins them
+            const uint32_t lo = d[4 * e + 1] * 256u + d[4 * e];
+            const uint32_t hi = d[4 * e + 3] * 256u + d[4 * e + 2];
+            const uint64_t v = (uint64_t)hi * 65536u + lo;
+            const uint32_t r = mont_reduce(v, lim.x, lim.y);
+            if (lim.w) out[lim.z] = r;
+          }
+        }
+      }
+    }
+    // accumulators and the operand tile are reused by the next tile
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+}
+
 __global__ void __launch_bounds__(kTcThreads)
     bconv_tc_kernel(const __grid_constant__ BconvTcArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -100,7 +214,6 @@ __global__ void __launch_bounds__(kTcThreads)
   uint4 *s_lim = reinterpret_cast<uint4 *>(sA + kTcMaxK * kTcTile + 64);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int kbytes = j.kpad;
-  constexpr int npad = kTcSliceN;
   const int m_first = slice * (kTcSliceN / 4);
   const int m_count = min(j.nd - m_first, kTcSliceN / 4);
 
@@ -133,110 +246,13 @@ __global__ void __launch_bounds__(kTcThreads)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
-  // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = npad
-  const uint32_t idesc = (2u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
-  const uint32_t a_lbo = (kTcTile / 8) * 128, b_lbo = (uint32_t)(npad / 8) * 128;
-  uint32_t parity = 0;
-  bool failed = false;
+  if (kbytes == 32)
+    tc_tiles<2>(a, j, sA, sB, bar, s_lim, tmem, m_count);
+  else if (kbytes == 64)
+    tc_tiles<4>(a, j, sA, sB, bar, s_lim, tmem, m_count);
+  else
+    tc_tiles<6>(a, j, sA, sB, bar, s_lim, tmem, m_count);
 
-  // residues of one coefficient, and how many lie above half their prime
-  uint32_t y[kMaxBconvSrc + 4];
-  uint32_t nneg = 0;
-  auto load_tile = [&](int tile) {
-    const int col = tile * kTcTile + tid;
-    nneg = 0;
-#pragma unroll
-    for (int k = 0; k < kMaxBconvSrc; k++) {
-      y[k] = 0;
-      if (k < j.ns) {
-        y[k] = __ldg(j.src + (size_t)k * kN + col);
-        nneg += y[k] > j.half[k];
-      }
-    }
-  };
-#pragma unroll
-  for (int k = kMaxBconvSrc; k < kMaxBconvSrc + 4; k++) y[k] = 0;
-  if ((int)blockIdx.x < kN / kTcTile) load_tile(blockIdx.x);
-
-  for (int tile = blockIdx.x; tile < kN / kTcTile && !failed; tile += gridDim.x) {
-    const int col = tile * kTcTile + tid;
-    // 2. operand rows: words y[0..ns), nneg, 0... ; 16-byte chunks t
-#pragma unroll
-    for (int t = 0; t < kTcMaxK / 16; t++) {
-      if (16 * t < kbytes) {
-        uint4 v = make_uint4(y[4 * t], y[4 * t + 1], y[4 * t + 2], y[4 * t + 3]);
-        const int w = j.ns - 4 * t;  // where the pseudo source lands in this chunk
-        if (w == 0) v.x = nneg;
-        if (w == 1) v.y = nneg;
-        if (w == 2) v.z = nneg;
-        if (w == 3) v.w = nneg;
-        *reinterpret_cast<uint4 *>(sA + t * a_lbo + (tid >> 3) * 128 + (tid & 7) * 16) = v;
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    // 3. one thread issues the MMAs of this tile and commits them to the barrier
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      for (int ks = 0; ks < kbytes / 32; ks++) {
-        const uint64_t da = smem_desc(smem_u32(sA) + ks * 2 * a_lbo, a_lbo, 128);
-        const uint64_t db = smem_desc(smem_u32(sB) + ks * 2 * b_lbo, b_lbo, 128);
-        const uint32_t acc = ks > 0;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-            : "memory");
-      }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                       smem_u32(bar))
-                   : "memory");
-    }
-    // the next tile's residues travel while the tensor core and the epilogue run
-    if (tile + (int)gridDim.x < kN / kTcTile) load_tile(tile + gridDim.x);
-    // 4. wait for the accumulators (bounded)
-    uint32_t spins = 0;
-    while (!mbar_try_wait(smem_u32(bar), parity)) {
-      if (++spins > kSpinLimit) {
-        failed = true;
-        break;
-      }
-    }
-    parity ^= 1;
-    if (__any_sync(0xffffffffu, failed)) {
-      failed = true;
-      if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // 5. epilogue: 8 destination limbs (32 accumulator columns) per load
-    if (!failed) {
-      const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-      uint32_t *out = j.dst + col;
-#pragma unroll
-      for (int m0 = 0; m0 < kTcSliceN / 4; m0 += 8) {
-        if (m0 < m_count) {
-          uint32_t d[32];
-          tmem_ld32(lane_base + 4 * m0, d);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int e = 0; e < 8; e++) {
-            const uint4 lim = s_lim[m0 + e];
-            // V = d0 + d1*2^8 + d2*2^16 + d3*2^24 as (hi, lo) words; every d < 2^23
-            const uint64_t v = (uint64_t)d[4 * e] + ((uint64_t)d[4 * e + 1] << 8) +
-                               ((uint64_t)d[4 * e + 2] << 16) + ((uint64_t)d[4 * e + 3] << 24);
-            const uint32_t r = mont_reduce(v, lim.x, lim.y);
-            if (lim.w) out[lim.z] = r;
-          }
-        }
-      }
-    }
-    // accumulators and the operand tile are reused by the next tile
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  }
   __syncthreads();
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
@@ -275,9 +291,11 @@ int build_tc_table(const Context &c, ConvPlan &cv) {
         t = s_all ? p - s_all : 0;  // -(prod s) mod p for the pseudo source
       }
       t = to_mont(to_mont(t, p), p);
+      // K layout: word 0 = pseudo source, word k + 1 = source k
+      const int word = k < ns ? k + 1 : 0;
       for (int i = 0; i < (k < ns ? 4 : 1); i++) {
         const uint32_t ti = mulmod(t, (uint32_t)((1ull << (8 * i)) % p), p);
-        for (int jj = 0; jj < 4; jj++) put(4 * m + jj, 4 * k + i, (uint8_t)(ti >> (8 * jj)));
+        for (int jj = 0; jj < 4; jj++) put(4 * m + jj, 4 * word + i, (uint8_t)(ti >> (8 * jj)));
       }
     }
   }

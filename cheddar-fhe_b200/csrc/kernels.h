@@ -83,7 +83,7 @@ struct BconvTcJob {
   uint32_t *dst;         // limb m stored at dst + dst_limb[m]*N
   const uint8_t *btile;  // table byte planes in operand layout
   int ns, nd, kpad, npad;
-  uint32_t half[kMaxBconvSrc];  // s_k >> 1
+  uint32_t half[kMaxBconvSrc + 3];  // s_k >> 1; 2^32 - 1 past the last source
   uint8_t dst_limb[kMaxLimbs];
   uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
 };

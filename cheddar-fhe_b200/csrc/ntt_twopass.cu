@@ -25,7 +25,7 @@ namespace {
 constexpr int kTpThreads = 256;
 constexpr int kColTile = 16;   // columns per CTA in the column pass
 constexpr int kRowTile = 16;   // rows per CTA in the row pass
-constexpr int kChunkJobs = 128;
+constexpr int kChunkJobs = 192;
 // column-pass buffer: word (r, x) at r*16 + x + 16*(r >> 4): both the
 // (r0 + 16k) and the (16g + k) access of a warp touch 32 distinct banks
 constexpr int kColBufWords = 256 * kColTile + 256;

@@ -46,7 +46,8 @@ void fill_tc_job(const Context &c, BconvTcJob &j, const ConvPlan &cv,
   j.nd = (int)cv.dst_g.size();
   j.kpad = cv.tc_kpad;
   j.npad = cv.tc_npad;
-  for (int k = 0; k < j.ns; k++) j.half[k] = c.q[cv.src_g[k]] >> 1;
+  for (int k = 0; k < kMaxBconvSrc + 3; k++)
+    j.half[k] = k < j.ns ? c.q[cv.src_g[k]] >> 1 : 0xffffffffu;  // repeats past the last source never count
   for (int m = 0; m < j.nd; m++) {
     const int g = cv.dst_g[m];
     j.dst_limb[m] = (uint8_t)(dst_pos ? (*dst_pos)[m] : m);
