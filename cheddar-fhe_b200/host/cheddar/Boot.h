@@ -212,18 +212,15 @@ class EvalPoly {
     const auto &param = ctx->param_;
     const int la = param.NPToLevel(A.GetNP()), lb = param.NPToLevel(B.GetNP());
     const int l = Min(la, lb);
-    Ct a, b, prod;
-    ctx->DropToLevel(a, A, l);
-    if (&A != &B) ctx->DropToLevel(b, B, l);
-    ctx->Mult(prod, a, &A != &B ? b : a);
+    Ct prod;
+    ctx->MultUnsafe(prod, A, B, l);  // operands of a higher level are read in place
     ctx->Add(prod, prod, prod);
     const double s = prod.GetScale();
     if (C) {
-      Ct c, cs;
-      ctx->DropToLevel(c, *C, l);
+      Ct cs;
       Constant<word> one;
-      ctx->encoder().EncodeConstant(one, l, s / c.GetScale(), 1.0, 0);
-      ctx->Mult(cs, c, one);
+      ctx->encoder().EncodeConstant(one, l, s / C->GetScale(), 1.0, 0);
+      ctx->MultUnsafe(cs, *C, one, l);
       cs.SetScale(s);
       ctx->Sub(prod, prod, cs);
     } else if (c0 != 0.0) {
@@ -280,11 +277,9 @@ class EvalPoly {
       ctx->Add(ct, ct, k0);
     };
     auto scaled = [&](Ct &out, const Ct &basis, double v) {  // v * basis at scale W
-      Ct b;
-      ctx->DropToLevel(b, basis, level);
       Constant<word> k1;
-      ctx->encoder().EncodeConstant(k1, level, W / b.GetScale(), v, 0);
-      ctx->Mult(out, b, k1);
+      ctx->encoder().EncodeConstant(k1, level, W / basis.GetScale(), v, 0);
+      ctx->MultUnsafe(out, basis, k1, level);
       out.SetScale(W);
     };
     if (len <= 2) {
@@ -302,11 +297,11 @@ class EvalPoly {
     if (q.size() == 1) {
       scaled(high, T.at(m), q[0]);
     } else {
-      Ct tm, qsum, qv;
-      ctx->DropToLevel(tm, T.at(m), level);
+      Ct qsum, qv;
+      const Ct &tm = T.at(m);
       Sum(ctx, qsum, q, (W / tm.GetScale()) * param.GetRescalePrimeProd(level + 1), level + 1, T, mult_key);
       Finish(ctx, qv, qsum, mult_key);
-      ctx->Mult(high, qv, tm);
+      ctx->MultUnsafe(high, qv, tm, level);
       high.SetScale(W);
     }
     bool r_zero = true;
@@ -713,8 +708,13 @@ class BootContext : public Context<word> {
       last = now;
     };
     AssertTrue(IsBootPrepared(input.GetNumSlots()), "Boot: not prepared for this slot count");
-    AssertTrue(param.NPToLevel(input.GetNP()) <= 0, "Boot: bring the input to level 0 first");
     AssertFalse(input.HasRx(), "Boot: relinearize first");
+    if (param.NPToLevel(input.GetNP()) > 0) {
+      Ct low;
+      this->LevelDown(low, input, 0);
+      Boot(res, low, evk_map, phase_ms);
+      return;
+    }
     this->AssertSameScale(input.GetScale() * (double)(UINT64_C(1) << log_scaleup_), boot_input_scale_);
     // 0. integer scale-up: the plaintext fills q0 / 2^log_message_ratio
     Ct main;

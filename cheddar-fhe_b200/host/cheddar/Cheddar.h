@@ -853,6 +853,116 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     if (a.HasRx()) ConstKernel(3, res.rx_.data(), a.rx_.data(), nullptr, b.cx_, np);
   }
 
+  // ---- products whose operands may sit at a higher level than the result:
+  // the limbs of `level` are read in place out of the larger operand
+  // (reference MultUnsafe / MadUnsafe, src/core/Context.cpp:357-489, 872-913).
+  bool IsMultUnsafeCompatible(int level1, int level2) const {
+    if (level1 == level2) return true;
+    return param_.LevelToNP(Min(level1, level2)).IsSubsetOf(param_.LevelToNP(Max(level1, level2)));
+  }
+  void MultUnsafe(Ct &res, const Ct &a, const Ct &b, int level = -1) const {
+    AssertFalse(a.HasRx() || b.HasRx(), "Relinearization required before MultUnsafe Ct x Ct");
+    const NPInfo a_np = a.GetNP(), b_np = b.GetNP();
+    AssertTrue(a_np.num_aux_ == 0 && b_np.num_aux_ == 0,
+               "MultUnsafe Ct x Ct should be only used for ciphertexts without aux primes");
+    if (level == -1) level = Min(param_.NPToLevel(a_np), param_.NPToLevel(b_np));
+    if (&res == &a || &res == &b) {
+      Ct tmp;
+      MultUnsafe(tmp, a, b, level);
+      res = std::move(tmp);
+      return;
+    }
+    const NPInfo np = param_.LevelToNP(level, 0);
+    AssertTrue(np.IsSubsetOf(a_np) && np.IsSubsetOf(b_np), "Incompatible levels for MultUnsafe Ct x Ct");
+    res.ModifyNP(np);
+    res.PrepareRx();
+    res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
+    res.SetScale(a.GetScale() * b.GetScale());
+    const size_t ao = FrontIgnore(a_np, np), bo = FrontIgnore(b_np, np);
+    auto g = param_.GetLimbIndices(np);
+    CheckAbi(cfhe_tensor(h_, res.bx_.data(), res.ax_.data(), res.rx_.data(), a.bx_.data() + ao,
+                         a.ax_.data() + ao, b.bx_.data() + bo, b.ax_.data() + bo, g.data(), g.size()));
+  }
+  void MultUnsafe(Ct &res, const Ct &a, const Pt &b, int level = -1) const {
+    const NPInfo a_np = a.GetNP(), b_np = b.GetNP();
+    if (level == -1) level = Min(param_.NPToLevel(a_np), param_.NPToLevel(b_np));
+    if (&res == &a && param_.NPToLevel(a_np) != level) {
+      Ct tmp;
+      MultUnsafe(tmp, a, b, level);
+      res = std::move(tmp);
+      return;
+    }
+    const NPInfo np = param_.LevelToNP(level, Min(a_np.num_aux_, b_np.num_aux_));
+    AssertTrue(np.IsSubsetOf(a_np) && np.IsSubsetOf(b_np), "Incompatible levels for MultUnsafe Ct x Pt");
+    AssertTrue(np.num_aux_ == 0 || (a_np.num_main_ == np.num_main_ && b_np.num_main_ == np.num_main_),
+               "MultUnsafe with aux primes needs operands with the result's main primes");
+    PrepareResult(res, np, a.HasRx());
+    res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
+    res.SetScale(a.GetScale() * b.GetScale());
+    const size_t ao = FrontIgnore(a_np, np), bo = FrontIgnore(b_np, np);
+    Binary(3, res.bx_.data(), a.bx_.data() + ao, b.mx_.data() + bo, np);
+    Binary(3, res.ax_.data(), a.ax_.data() + ao, b.mx_.data() + bo, np);
+    if (a.HasRx()) Binary(3, res.rx_.data(), a.rx_.data() + ao, b.mx_.data() + bo, np);
+  }
+  void MultUnsafe(Ct &res, const Ct &a, const Const &b, int level = -1) const {
+    const NPInfo a_np = a.GetNP(), b_np = b.GetNP();
+    if (level == -1) level = Min(param_.NPToLevel(a_np), param_.NPToLevel(b_np));
+    if (&res == &a && param_.NPToLevel(a_np) != level) {
+      Ct tmp;
+      MultUnsafe(tmp, a, b, level);
+      res = std::move(tmp);
+      return;
+    }
+    const NPInfo np = param_.LevelToNP(level, Min(a_np.num_aux_, b_np.num_aux_));
+    AssertTrue(np.IsSubsetOf(a_np) && np.IsSubsetOf(b_np), "Incompatible levels for MultUnsafe Ct x Const");
+    AssertTrue(np.num_aux_ == 0 || a_np.num_main_ == np.num_main_,
+               "MultUnsafe with aux primes needs operands with the result's main primes");
+    PrepareResult(res, np, a.HasRx());
+    res.SetNumSlots(a.GetNumSlots());
+    res.SetScale(a.GetScale() * b.GetScale());
+    const size_t ao = FrontIgnore(a_np, np);
+    const std::vector<word> k = ConstLimbs(b, np);
+    ConstKernel(3, res.bx_.data(), a.bx_.data() + ao, nullptr, k, np);
+    ConstKernel(3, res.ax_.data(), a.ax_.data() + ao, nullptr, k, np);
+    if (a.HasRx()) ConstKernel(3, res.rx_.data(), a.rx_.data() + ao, nullptr, k, np);
+  }
+  // res += a * b on the limbs of res
+  void MadUnsafe(Ct &res, const Ct &a, const Const &b) const {
+    const NPInfo a_np = a.GetNP(), b_np = b.GetNP(), np = res.GetNP();
+    AssertTrue(np.IsSubsetOf(a_np) && np.IsSubsetOf(b_np), "Incompatible levels for MultUnsafe Ct x Const");
+    AssertTrue(np.num_aux_ == 0 && a_np.num_aux_ == 0, "MadUnsafe should be only used for q primes");
+    AssertTrue(res.GetNumSlots() == a.GetNumSlots(), "MadUnsafe should be only used for the same number of slots");
+    AssertSameScale(res.GetScale(), a.GetScale() * b.GetScale());
+    if (a.HasRx() && !res.HasRx()) {
+      res.PrepareRx();
+      CheckAbi(cfhe_binary(h_, 1, res.rx_.data(), res.bx_.data(), res.bx_.data(),
+                           param_.GetLimbIndices(np).data(), np.GetNumTotal()));  // zero
+    }
+    const size_t ao = FrontIgnore(a_np, np);
+    const std::vector<word> k = ConstLimbs(b, np);
+    ConstKernel(4, res.bx_.data(), a.bx_.data() + ao, res.bx_.data(), k, np);
+    ConstKernel(4, res.ax_.data(), a.ax_.data() + ao, res.ax_.data(), k, np);
+    if (a.HasRx()) ConstKernel(4, res.rx_.data(), a.rx_.data() + ao, res.rx_.data(), k, np);
+  }
+  // Brings a ciphertext down to target_level one level at a time: multiply by
+  // the constant 1 encoded at the level's scale, then rescale (reference
+  // LevelDown, src/core/Context.cpp:915-928, which calls itself unoptimised).
+  void LevelDown(Ct &res, const Ct &a, int target_level) const {
+    Ct mult_temp, next;
+    const int level = param_.NPToLevel(a.GetNP());
+    AssertTrue(level >= target_level, "Invalid target level for LevelDown");
+    AssertTrue(level <= param_.default_encryption_level_, "LevelDown starts at or below the default encryption level");
+    const Ct *prev = &a;
+    for (int i = level; i > target_level; i--) {
+      Const one;
+      encoder_->EncodeConstant(one, i, param_.GetScale(i), 1.0, 0);
+      Mult(mult_temp, *prev, one);
+      Rescale(next, mult_temp);
+      prev = &next;
+    }
+    Copy(res, *prev);
+  }
+
   void Permute(Ct &res, const Ct &a, int rot_dist) const {
     const int num_slots = a.GetNumSlots();
     int rot_idx = rot_dist % num_slots;
@@ -1060,6 +1170,27 @@ class Context : public std::enable_shared_from_this<Context<word>> {
       res.RemoveRx();
       res.ModifyNP(a.GetNP());
     }
+  }
+  // words to skip at the front of a polynomial of `big` to reach the limbs of `small`
+  size_t FrontIgnore(const NPInfo &big, const NPInfo &small) const {
+    return (size_t)(big.num_ter_ - small.num_ter_) * param_.degree_;
+  }
+  void PrepareResult(Ct &res, const NPInfo &np, bool rx) const {
+    if (rx) {
+      res.ModifyNP(np);
+      res.PrepareRx();
+    } else {
+      res.RemoveRx();
+      res.ModifyNP(np);
+    }
+  }
+  // per-limb words of a constant restricted to the limbs of np
+  std::vector<word> ConstLimbs(const Const &b, const NPInfo &np) const {
+    const NPInfo b_np = b.GetNP();
+    const int skip = b_np.num_ter_ - np.num_ter_;
+    std::vector<word> k(b.cx_.begin() + skip, b.cx_.begin() + skip + np.GetNumQ());
+    for (int a = 0; a < np.num_aux_; a++) k.push_back(b.cx_[b_np.GetNumQ() + a]);
+    return k;
   }
   void D2D(DeviceVector<word> &dst, const DeviceVector<word> &src, const NPInfo &np) const {
     std::vector<word> zero(np.GetNumTotal(), 0);

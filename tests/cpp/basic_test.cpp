@@ -287,6 +287,72 @@ int main(int argc, char **argv) {
     tb.DecryptAndDecode(res, r);
     tb.CompareMessages("HConj", level, want, res);
   });
+  // ---- operators the reference's basic_test does not cover but its Context offers
+  // (src/core/Context.cpp:357-489, 872-928); the lower level must be nested in the higher one
+  auto nested_below = [&](int level) {
+    for (int lo = level - 1; lo >= 0; lo--)
+      if (ctx.IsMultUnsafeCompatible(level, lo)) return lo;
+    return -1;
+  };
+  run("MultUnsafe", 1, [&](int level) {
+    const int lo = nested_below(level);
+    if (lo < 1) return;  // the product is rescaled below
+    Msg m1, m2, res;
+    tb.GenerateRandomMessage(m1);
+    tb.GenerateRandomMessage(m2);
+    Ct c1, c2, prod, lin, r;
+    tb.EncodeAndEncrypt(c1, m1, level);
+    tb.EncodeAndEncrypt(c2, m2, lo);
+    ctx.MultUnsafe(prod, c1, c2);  // level lo, read in place out of c1
+    ctx.RelinearizeRescale(r, prod, tb.interface_->GetMultiplicationKey());
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("MultUnsafe ct x ct (" + std::to_string(level) + " x " + std::to_string(lo) + ")", lo - 1,
+                       binary_msg(m1, m2, [](Complex a, Complex b) { return a * b; }), res);
+    // ct x const and the multiply-add form
+    const double k = m2[0].real();
+    Constant<word> kc;
+    tb.EncodeConstant(kc, k, lo);
+    Ct scaled, acc;
+    ctx.MultUnsafe(scaled, c1, kc);
+    ctx.MultUnsafe(acc, c1, kc);
+    ctx.MadUnsafe(acc, c1, kc);
+    Ct r1, r2;
+    ctx.Rescale(r1, scaled);
+    ctx.Rescale(r2, acc);
+    Msg want1, want2;
+    for (auto &x : m1) {
+      want1.push_back(x * k);
+      want2.push_back(2.0 * k * x);
+    }
+    tb.DecryptAndDecode(res, r1);
+    tb.CompareMessages("MultUnsafe ct x const", lo - 1, want1, res);
+    tb.DecryptAndDecode(res, r2);
+    tb.CompareMessages("MadUnsafe", lo - 1, want2, res);
+    Pt p2;
+    tb.Encode(p2, m2, lo);
+    Ct cp, r3;
+    ctx.MultUnsafe(cp, c1, p2);
+    ctx.Rescale(r3, cp);
+    tb.DecryptAndDecode(res, r3);
+    tb.CompareMessages("MultUnsafe ct x pt", lo - 1, binary_msg(m1, m2, [](Complex a, Complex b) { return a * b; }),
+                       res);
+  });
+  run("LevelDown", 1, [&](int level) {
+    if (level > tb.default_encryption_level_) return;
+    Msg m, res;
+    tb.GenerateRandomMessage(m);
+    Ct c, r;
+    tb.EncodeAndEncrypt(c, m, level);
+    const int target = level >= 2 ? level - 2 : 0;
+    ctx.LevelDown(r, c, target);
+    if (tb.param_->NPToLevel(r.GetNP()) != target) {
+      std::cout << "[FAIL] LevelDown level " << level << ": wrong output level" << std::endl;
+      tb.failures++;
+    }
+    ctx.AssertSameScale(r.GetScale(), tb.param_->GetScale(target));
+    tb.DecryptAndDecode(res, r);
+    tb.CompareMessages("LevelDown to " + std::to_string(target), level, m, res);
+  });
   std::cout << (tb.failures ? "FAILED " : "PASSED ") << "(" << tb.failures << " failures)" << std::endl;
   tb.interface_.reset();
   std::cout << "Context use count (should be 1 to prevent memory leak): " << tb.context_.use_count()

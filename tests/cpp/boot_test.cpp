@@ -222,6 +222,12 @@ int main(int argc, char **argv) {
               << std::endl;
     // the reference's acceptance bound (unittest/Testbed.h:93)
     Report("Boot, 2^15 complex slots in [-1,1]^2", m, got, 1e-3);
+    // an input above level 0 is first brought down (reference BootContext.cpp:308-313)
+    Ct high;
+    encrypt(high, m, 3, param->GetScale(3));
+    boot_ctx->Boot(out, high, ui.GetEvkMap());
+    decrypt(got, out);
+    Report("Boot of a level-3 input", m, got, 1e-3);
   }
 
   if (only.count("stages")) {
