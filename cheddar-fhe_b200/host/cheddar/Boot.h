@@ -506,9 +506,9 @@ class EvalSpecialFFT {
       for (int s = n / 2; s >= 1; s /= 2) strides.push_back(s);
     else
       for (int s = 1; s < n; s *= 2) strides.push_back(s);
-    const int per = ((int)strides.size() + groups - 1) / groups;
     const double each = std::pow(total_const, 1.0 / groups);
     std::vector<StripedMatrix> out;
+    const int per = strides.empty() ? 1 : ((int)strides.size() + groups - 1) / groups;
     for (size_t at = 0; at < strides.size(); at += per) {
       StripedMatrix g = cts ? IfftStage(param, n, strides[at]) : FftStage(param, n, strides[at]);
       for (size_t k = at + 1; k < std::min(strides.size(), at + per); k++) {
@@ -517,6 +517,13 @@ class EvalSpecialFFT {
       }
       g.Scale(each);
       out.push_back(std::move(g));
+    }
+    // fewer stages than levels (few slots): the remaining levels carry the constant only
+    while ((int)out.size() < groups) {
+      StripedMatrix id(n);
+      auto &d = id.At(0);
+      for (auto &x : d) x = each;
+      out.push_back(std::move(id));
     }
     return out;
   }
@@ -549,25 +556,33 @@ class BootContext : public Context<word> {
     eval_mod_ = std::make_unique<EvalMod<word>>(boot_param_);
   }
 
-  // Only full-slot bootstrapping: num_slots must be degree / 2.
+  // Linear transforms for ciphertexts with num_slots slots (a power of two up to
+  // degree / 2). Fewer slots mean a plaintext in the subring of X^(degree/2/num_slots):
+  // the transforms have num_slots-periodic diagonals, and Boot projects the
+  // raised ciphertext onto the subring first (Trace).
   void PrepareEvalSpecialFFT(int num_slots) {
     const auto &param = this->param_;
-    AssertTrue(num_slots == param.degree_ / 2, "Only full-slot bootstrapping is supported");
-    if (!cts_.empty()) {
+    const int half = param.degree_ / 2;
+    AssertTrue(num_slots >= 2 && num_slots <= half && (num_slots & (num_slots - 1)) == 0,
+               "Only power-of-two slots are supported");
+    if (eval_fft_.count(num_slots)) {
       Warn("EvalSpecialFFT already prepared");
       return;
     }
+    FftPlan &plan = eval_fft_[num_slots];
     const int n = num_slots;
-    // CoeffToSlot: the raised ciphertext holds the integer polynomial q0 * u(X);
-    // read at scale q0 its slots are SpecialFFT(u_j + i u_{j+n}). The groups
-    // apply the inverse transform, its 1/n, and 1/(2K), so that the real and
-    // imaginary parts taken afterwards (each a sum of two terms) are u / K.
+    // CoeffToSlot: the raised (and traced) ciphertext holds (half / n) * q0 * u(Y),
+    // Y = X^(half/n); read at scale q0 its n distinct slots are
+    // (half/n) * SpecialFFT_n(u_j + i u_{j+n}). The groups apply the inverse
+    // transform, its 1/n, the 1/(half/n) of the trace and 1/(2K), so that the
+    // real and imaginary parts taken afterwards (each a sum of two terms) are
+    // u / K: the constant is 1 / (half * 2K) whatever n is.
     auto cts = EvalSpecialFFT<word>::Groups(param, n, true, boot_param_.num_cts_levels_,
-                                            1.0 / ((double)n * 2.0 * boot_param_.K_));
+                                            1.0 / ((double)half * 2.0 * boot_param_.K_));
     double s_in = q0_prod_;
     int level = boot_param_.GetCtSStartLevel();
     for (auto &g : cts) {
-      cts_.emplace_back(GetContext(), g, level, s_in, eval_mod_scale_, kBabySteps);
+      plan.cts.emplace_back(GetContext(), g, level, s_in, eval_mod_scale_, kBabySteps);
       s_in = eval_mod_scale_;
       level--;
     }
@@ -583,22 +598,47 @@ class BootContext : public Context<word> {
     const int ng = stc.size();
     for (int i = 0; i < ng; i++) {
       const double s_out = i + 1 == ng ? s_end : s_in * std::pow(s_end / s_in, 1.0 / (ng - i));
-      stc_.emplace_back(GetContext(), stc[i], level, s_in, s_out, kBabySteps);
+      plan.stc.emplace_back(GetContext(), stc[i], level, s_in, s_out, kBabySteps);
       s_in = s_out;
       level--;
     }
   }
 
-  bool IsBootPrepared(int num_slots) const {
-    return eval_mod_ && !cts_.empty() && num_slots == this->param_.degree_ / 2;
-  }
+  bool IsBootPrepared(int num_slots) const { return eval_mod_ && eval_fft_.count(num_slots); }
 
+  // Rotation keys Boot needs for this slot count: those of the linear
+  // transforms and the trace's num_slots * 2^i (reference AddRequiredRotations,
+  // src/extension/BootContext.cpp:174-184).
   void AddRequiredRotations(EvkRequest &req, int num_slots) const {
     AssertTrue(IsBootPrepared(num_slots), "Bootstrapping is not prepared for this slot count");
+    const FftPlan &plan = eval_fft_.at(num_slots);
     std::set<int> rots;
-    for (auto &lt : cts_) lt.AddRequiredRotations(rots);
-    for (auto &lt : stc_) lt.AddRequiredRotations(rots);
+    for (auto &lt : plan.cts) lt.AddRequiredRotations(rots);
+    for (auto &lt : plan.stc) lt.AddRequiredRotations(rots);
+    for (int ns = num_slots; ns < this->param_.degree_ / 2; ns *= 2) rots.insert(ns);
     for (int r : rots) req.AddRequest(r, boot_param_.GetMaxLevel());
+  }
+
+  // res = sum_{j < num_accum} rot_{j * start_rot_dist}(input), num_accum a
+  // power of two (reference Trace, src/extension/BootContext.cpp:367-402).
+  void Trace(Ct &res, int start_rot_dist, int num_accum, const Ct &input, const EvkMap<word> &evk_map) const {
+    AssertTrue(num_accum >= 1 && (num_accum & (num_accum - 1)) == 0, "Num accum must be power of 2");
+    AssertTrue(input.GetNP().num_aux_ == 0, "Trace: Aux primes are not allowed");
+    if (num_accum == 1) {
+      this->Copy(res, input);
+      return;
+    }
+    const int num_slots = input.GetNumSlots();
+    Ct acc, next;
+    const Ct *cur = &input;
+    for (int step = 1; step < num_accum; step *= 2) {
+      int rot = (int)(((long long)start_rot_dist * step) % num_slots);
+      if (rot < 0) rot += num_slots;
+      this->HRotAdd(next, *cur, *cur, evk_map.GetRotationKey(rot), rot);
+      acc = std::move(next);
+      cur = &acc;
+    }
+    res = std::move(acc);
   }
 
   // Raises a ciphertext on the lowest level's primes to the highest level:
@@ -680,10 +720,10 @@ class BootContext : public Context<word> {
   }
 
   void CoeffToSlot(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
-    RunGroups(res, input, cts_, evk_map);
+    RunGroups(res, input, PlanFor(input.GetNumSlots()).cts, evk_map);
   }
   void SlotToCoeff(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
-    RunGroups(res, input, stc_, evk_map);
+    RunGroups(res, input, PlanFor(input.GetNumSlots()).stc, evk_map);
   }
   void EvaluateMod(Ct &res, const Ct &input, const Evk &mult_key) const {
     AssertTrue(eval_mod_ != nullptr, "EvalMod not prepared");
@@ -734,6 +774,15 @@ class BootContext : public Context<word> {
     Ct raised;
     ModUpToMax(raised, main, evk_map);
     raised.SetScale(q0_prod_);
+    const int half = param.degree_ / 2, num_slots = input.GetNumSlots();
+    if (num_slots < half) {
+      // fewer slots: keep only the subring part of the raised polynomial
+      Ct traced;
+      raised.SetNumSlots(half);
+      Trace(traced, num_slots, half / num_slots, raised, evk_map);
+      raised = std::move(traced);
+      raised.SetNumSlots(num_slots);
+    }
     phase("ModUpToMax");
     // 2. coefficients to slots
     Ct slots;
@@ -800,7 +849,15 @@ class BootContext : public Context<word> {
   double q0_prod_ = 1.0, boot_input_scale_ = 1.0, eval_mod_scale_ = 1.0, eval_mod_end_scale_ = 1.0;
   int log_scaleup_ = 0;
   std::unique_ptr<EvalMod<word>> eval_mod_;
-  std::vector<LinearTransform<word>> cts_, stc_;
+  struct FftPlan {
+    std::vector<LinearTransform<word>> cts, stc;
+  };
+  const FftPlan &PlanFor(int num_slots) const {
+    auto it = eval_fft_.find(num_slots);
+    AssertTrue(it != eval_fft_.end(), "BootContext not prepared for num slots: " + std::to_string(num_slots));
+    return it->second;
+  }
+  std::map<int, FftPlan> eval_fft_;
 };
 
 }  // namespace cheddar

@@ -2,7 +2,7 @@
 // C++ mirror of the reference API (the reference's boot_test checks Boot on
 // 2^15 random complex slots in [-1,1]^2, unittest/Bootstrapping.cpp:10-41).
 //
-//   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot]
+//   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot,sparse]
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -228,6 +228,37 @@ int main(int argc, char **argv) {
     boot_ctx->Boot(out, high, ui.GetEvkMap());
     decrypt(got, out);
     Report("Boot of a level-3 input", m, got, 1e-3);
+  }
+
+  if (want("sparse")) {
+    // fewer slots than degree / 2: subring plaintexts, Trace after the lift
+    boot_ctx->PrepareEvalMod();
+    for (int ns : {1 << 10, 1 << 3}) {
+      boot_ctx->PrepareEvalSpecialFFT(ns);
+      EvkRequest req;
+      boot_ctx->AddRequiredRotations(req, ns);
+      ui.PrepareRotationKey(req);
+      Msg m(ns), got;
+      Random::SampleUniformComplex(m.data(), ns, -1.0, 1.0);
+      Pt pt;
+      Ct ct, out;
+      ctx->encoder().Encode(pt, 0, param->GetScale(0), m, 0);
+      ui.Encrypt(ct, pt);
+      ctx->Synchronize();
+      auto a = std::chrono::steady_clock::now();
+      boot_ctx->Boot(out, ct, ui.GetEvkMap());
+      ctx->Synchronize();
+      const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count();
+      Pt dec;
+      ui.Decrypt(dec, out);
+      ctx->encoder().Decode(got, dec);
+      std::cout << "       " << ns << " slots: " << req.size() << " rotation keys requested, first Boot " << ms
+                << " ms, level " << param->NPToLevel(out.GetNP()) << std::endl;
+      // With few slots the plaintext coefficients are large (about 1/sqrt(slots)),
+      // and the cubic term of sin(2 pi x)/2 pi, 6.6 * (coefficient / 35)^3 * 35 per
+      // coefficient at this message ratio, is no longer below 1e-3 on the slots.
+      Report("Boot with " + std::to_string(ns) + " slots", m, got, ns >= 64 ? 1e-3 : 5e-3);
+    }
   }
 
   if (only.count("stages")) {
