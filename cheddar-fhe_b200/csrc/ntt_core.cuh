@@ -207,6 +207,48 @@ CFHE_HD void gs_radix16(uint32_t *v, const Tw *tw, int i0, uint32_t q,
   }
 }
 
+// The same four stages with all 15 twiddles fetched up front, so that their
+// load latency overlaps whatever the caller does between the fetch and the
+// butterflies. t: [0] stage 0, [1..2] stage 1, [3..6] stage 2, [7..14] stage 3.
+CFHE_HD void ld_tw16(const Tw *tw, int i0, Tw *t) {
+  t[0] = ld_tw(tw + i0);
+  ld_tws<2>(tw + (i0 << 1), t + 1);
+  ld_tws<4>(tw + (i0 << 2), t + 3);
+  ld_tws<8>(tw + (i0 << 3), t + 7);
+}
+
+template <bool FAST>
+CFHE_HD void ct_radix16_pre(uint32_t *v, const Tw *t, uint32_t q, uint32_t q2) {
+#pragma unroll
+  for (int e = 0; e < 8; e++) ct_bfly<FAST>(v[e], v[e + 8], t[0], q, q2);
+#pragma unroll
+  for (int j = 0; j < 2; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) ct_bfly<FAST>(v[8 * j + e], v[8 * j + e + 4], t[1 + j], q, q2);
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+#pragma unroll
+    for (int e = 0; e < 2; e++) ct_bfly<FAST>(v[4 * j + e], v[4 * j + e + 2], t[3 + j], q, q2);
+#pragma unroll
+  for (int j = 0; j < 8; j++) ct_bfly<FAST>(v[2 * j], v[2 * j + 1], t[7 + j], q, q2);
+}
+
+template <bool FAST>
+CFHE_HD void gs_radix16_pre(uint32_t *v, const Tw *t, uint32_t q, uint32_t q2) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) gs_bfly<FAST>(v[2 * j], v[2 * j + 1], t[7 + j], q, q2);
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+#pragma unroll
+    for (int e = 0; e < 2; e++) gs_bfly<FAST>(v[4 * j + e], v[4 * j + e + 2], t[3 + j], q, q2);
+#pragma unroll
+  for (int j = 0; j < 2; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) gs_bfly<FAST>(v[8 * j + e], v[8 * j + e + 4], t[1 + j], q, q2);
+#pragma unroll
+  for (int e = 0; e < 8; e++) gs_bfly<FAST>(v[e], v[e + 8], t[0], q, q2);
+}
+
 // word offset of column x inside a padded in-row buffer row
 CFHE_HD int pad_col(int x) { return x + 4 * (x >> 4); }
 

@@ -59,22 +59,25 @@ __device__ __forceinline__ void fwd_cols(const NttArgs &a, const Job &j, int til
   const uint32_t q = j.q, q2 = 2 * q;
   const int x = tid & 15, r0 = tid >> 4;
   uint32_t v[16];
+  Tw t[15];
   const uint32_t *s = j.src + r0 * kRowWords + kColTile * tile + x;
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = s[k * 16 * kRowWords];
+  ld_tw16(j.tw, 1, t);
   if (a.premul) {
     const Tw kc = a.kc[j.l];
 #pragma unroll
     for (int k = 0; k < 16; k++) v[k] = shoup_mul(v[k], kc, q);
   }
-  ct_radix16<FAST>(v, j.tw, 1, q, q2);
+  ct_radix16_pre<FAST>(v, t, q, q2);
+  const int g = r0;
+  ld_tw16(j.tw, 16 + g, t);  // in flight across the transposition
 #pragma unroll
   for (int k = 0; k < 16; k++) xbuf[col_word(r0 + 16 * k, x)] = v[k];
   __syncthreads();
-  const int g = r0;
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = xbuf[col_word(16 * g + k, x)];
-  ct_radix16<FAST>(v, j.tw, 16 + g, q, q2);
+  ct_radix16_pre<FAST>(v, t, q, q2);
   uint32_t *o = j.dst + (16 * g) * kRowWords + kColTile * tile + x;
 #pragma unroll
   for (int k = 0; k < 16; k++) o[k * kRowWords] = v[k];
@@ -88,10 +91,13 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
   const int rho = tid >> 4, x0 = tid & 15, g = x0;
   const int R = kRowTile * blk + rho;
   uint32_t v[16];
+  Tw t[15];
   const uint32_t *s = j.dst + R * kRowWords + x0;
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = s[16 * k];
-  ct_radix16<FAST>(v, j.tw, 256 + R, q, q2);
+  ld_tw16(j.tw, 256 + R, t);
+  ct_radix16_pre<FAST>(v, t, q, q2);
+  ld_tw16(j.tw, 4096 + 16 * R + g, t);  // in flight across the exchange
   uint32_t *row = xbuf + rho * kRowStride;
 #pragma unroll
   for (int k = 0; k < 16; k++) row[x0 + 20 * k] = v[k];
@@ -104,12 +110,12 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
     v[4 * i + 2] = t.z;
     v[4 * i + 3] = t.w;
   }
-  ct_radix16<FAST>(v, j.tw, 4096 + 16 * R + g, q, q2);
+  ct_radix16_pre<FAST>(v, t, q, q2);
 #pragma unroll
   for (int k = 0; k < 16; k++) {
-    uint32_t t = v[k];
-    if constexpr (FAST) t = umin32(t, t - q2);
-    v[k] = umin32(t, t - q);
+    uint32_t u = v[k];
+    if constexpr (FAST) u = umin32(u, u - q2);
+    v[k] = umin32(u, u - q);
   }
   const int off = R * kRowWords + 16 * g;
   if (a.ep_mode) {
@@ -171,7 +177,10 @@ __device__ __forceinline__ void inv_rows(const NttArgs &, const Job &j, int blk,
     v[4 * i + 2] = t.z;
     v[4 * i + 3] = t.w;
   }
-  gs_radix16<FAST>(v, j.tw, 4096 + 16 * R + g, q, q2);
+  Tw t[15];
+  ld_tw16(j.tw, 4096 + 16 * R + g, t);
+  gs_radix16_pre<FAST>(v, t, q, q2);
+  ld_tw16(j.tw, 256 + R, t);  // in flight across the exchange
   uint32_t *row = xbuf + rho * kRowStride;
 #pragma unroll
   for (int i = 0; i < 4; i++)
@@ -180,7 +189,7 @@ __device__ __forceinline__ void inv_rows(const NttArgs &, const Job &j, int blk,
   __syncwarp();
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = row[x0 + 20 * k];
-  gs_radix16<FAST>(v, j.tw, 256 + R, q, q2);
+  gs_radix16_pre<FAST>(v, t, q, q2);
   uint32_t *o = j.dst + R * kRowWords + x0;
 #pragma unroll
   for (int k = 0; k < 16; k++) o[16 * k] = v[k];
@@ -196,14 +205,17 @@ __device__ __forceinline__ void inv_cols(const NttArgs &a, const Job &j, int til
   uint32_t *base = j.dst + kColTile * tile + x;
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = base[(16 * g + k) * kRowWords];
-  gs_radix16<FAST>(v, j.tw, 16 + g, q, q2);
+  Tw t[15];
+  ld_tw16(j.tw, 16 + g, t);
+  gs_radix16_pre<FAST>(v, t, q, q2);
+  ld_tw16(j.tw, 1, t);  // in flight across the transposition
 #pragma unroll
   for (int k = 0; k < 16; k++) xbuf[col_word(16 * g + k, x)] = v[k];
   __syncthreads();
   const int r0 = g;
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = xbuf[col_word(r0 + 16 * k, x)];
-  gs_radix16<FAST>(v, j.tw, 1, q, q2);
+  gs_radix16_pre<FAST>(v, t, q, q2);
   const Tw kc = a.kc[j.l];
   const uint32_t half = q >> 1;
   const bool centred = a.centred != 0;

@@ -60,7 +60,7 @@ int main(int argc, char **argv) {
     best = std::min(best, ms);
   }
   std::vector<std::pair<std::string, double>> phases;
-  ctx->Boot(out, ct, ui.GetEvkMap(), &phases);
+  ctx->Boot(out, ct, ui.GetEvkMap(), false, &phases);
   ui.Decrypt(dec, out);
   ctx->encoder().Decode(got, dec);
   double worst = 0, sum = 0;

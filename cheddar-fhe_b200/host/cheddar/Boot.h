@@ -104,13 +104,19 @@ class LinearTransform {
     // giant offsets are multiples of bs, so one of them is zero whenever the
     // range of t includes it (one key switch fewer)
     const int t0 = (int)std::floor((double)tmin / bs_) * bs_;
-    // keyed by the giant rotation itself: offsets wrap modulo n, so different
-    // multiples can be the same rotation
+    g_ = g % n_;
+    giant_stride_ = Mod((long long)g * bs_);
+    giant_first_ = Mod((long long)g * t0);
+    // giant steps form the progression giant_first_ + jj * giant_stride_ (mod n);
+    // offsets wrap modulo n, so different multiples can be the same rotation
+    const int wrap = giant_stride_ ? n_ / std::gcd(giant_stride_, n_) : 1;
+    std::map<int, int> jj_of;              // giant rotation -> position in the progression
     std::map<int, std::map<int, Pt>> pts;  // [giant rotation][baby index]
     std::set<int> babies{0};
     for (auto &[t, d] : by_t) {
       const int j = (t - t0) / bs_, i = (t - t0) % bs_;
       const int G = Mod((long long)g * (t0 + bs_ * j));
+      jj_of[G] = j % wrap;
       // the giant rotation is applied after the product: pre-rotate by -G
       std::vector<Complex> v(n_);
       for (int p = 0; p < n_; p++) v[p] = (*d)[Mod((long long)p - G)];
@@ -122,9 +128,11 @@ class LinearTransform {
     for (int i : babies) {
       baby_slot[i] = baby_rot_.size();
       baby_rot_.push_back(Mod((long long)g * i));
+      baby_idx_.push_back(i);
     }
     for (auto &[G, row] : pts) {
       giant_rot_.push_back(G);
+      giant_jj_.push_back(jj_of.at(G));
       std::vector<Pt> dense(baby_rot_.size());
       std::vector<bool> have(baby_rot_.size(), false);
       for (auto &[i, pt] : row) {
@@ -139,14 +147,31 @@ class LinearTransform {
     AssertTrue(giant_rot_.size() <= 16, "LinearTransform: more than 16 giant steps");
   }
 
-  void AddRequiredRotations(std::set<int> &rots) const {
+  // min_ks: the plan that needs at most three keys per transform (the baby
+  // stride, the giant stride and the first giant offset), at the price of
+  // sequential, unhoisted rotations (the reference's minimum key-switching
+  // mode, src/extension/Hoist.cu:979-985).
+  void AddRequiredRotations(std::set<int> &rots, bool min_ks = false) const {
+    if (min_ks) {
+      if (baby_idx_.back() > 0) rots.insert(g_);
+      int jmax = 0;
+      for (int jj : giant_jj_) jmax = Max(jmax, jj);
+      if (jmax > 0 && giant_stride_) rots.insert(giant_stride_);
+      if (giant_first_) rots.insert(giant_first_);
+      return;
+    }
     for (int r : baby_rot_)
       if (r) rots.insert(r);
     for (int r : giant_rot_)
       if (r) rots.insert(r);
   }
 
-  void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &in, const EvkMap<word> &keys) const {
+  void Evaluate(const ConstContextPtr<word> &ctx, Ct &res, const Ct &in, const EvkMap<word> &keys,
+                bool min_ks = false) const {
+    if (min_ks) {
+      EvaluateMinKS(ctx, res, in, keys);
+      return;
+    }
     const auto &param = ctx->param_;
     AssertTrue(param.NPToLevel(in.GetNP()) == level_, "LinearTransform: wrong input level");
     AssertFalse(in.HasRx(), "LinearTransform: relinearize first");
@@ -183,6 +208,68 @@ class LinearTransform {
     res = std::move(out);
   }
 
+  // Baby rotations one after the other with the key of the baby stride, the
+  // giant sums folded Horner-wise with the key of the giant stride:
+  //   out = rot_first( acc_0 + rot_S( acc_1 + rot_S( acc_2 + ... ) ) )
+  void EvaluateMinKS(const ConstContextPtr<word> &ctx, Ct &res, const Ct &in, const EvkMap<word> &keys) const {
+    const auto &param = ctx->param_;
+    AssertTrue(param.NPToLevel(in.GetNP()) == level_, "LinearTransform: wrong input level");
+    AssertFalse(in.HasRx(), "LinearTransform: relinearize first");
+    const int nb = baby_rot_.size(), top = baby_idx_.back();
+    std::vector<Ct> store(top + 1);
+    std::vector<const Ct *> rot(top + 1, nullptr);
+    rot[0] = &in;
+    for (int i = 1; i <= top; i++) {
+      ctx->HRot(store[i], *rot[i - 1], keys.GetRotationKey(g_), g_);
+      rot[i] = &store[i];
+    }
+    int jmax = 0;
+    for (int jj : giant_jj_) jmax = Max(jmax, jj);
+    std::vector<Ct> acc(jmax + 1);
+    std::vector<bool> have(jmax + 1, false);
+    Ct term;
+    for (size_t gi = 0; gi < giant_rot_.size(); gi++) {
+      const int jj = giant_jj_[gi];
+      for (int k = 0; k < nb; k++) {
+        if (!present_[gi * nb + k]) continue;
+        const Ct &r = *rot[baby_idx_[k]];
+        if (!have[jj]) {
+          ctx->MultUnsafe(acc[jj], r, pts_[gi * nb + k], level_);  // the Q limbs of the extended plaintext
+          have[jj] = true;
+        } else {
+          ctx->MultUnsafe(term, r, pts_[gi * nb + k], level_);
+          ctx->Add(acc[jj], acc[jj], term);
+        }
+      }
+    }
+    Ct sum, turned;
+    bool started = false;
+    for (int jj = jmax; jj >= 0; jj--) {
+      if (started && giant_stride_) {
+        if (have[jj]) {
+          ctx->HRotAdd(turned, sum, acc[jj], keys.GetRotationKey(giant_stride_), giant_stride_);
+        } else {
+          ctx->HRot(turned, sum, keys.GetRotationKey(giant_stride_), giant_stride_);
+        }
+        sum = std::move(turned);
+      } else if (have[jj]) {
+        if (started) {
+          ctx->Add(sum, sum, acc[jj]);
+        } else {
+          sum = std::move(acc[jj]);
+          started = true;
+        }
+      }
+    }
+    AssertTrue(started, "LinearTransform: empty matrix");
+    if (giant_first_) {
+      ctx->HRot(turned, sum, keys.GetRotationKey(giant_first_), giant_first_);
+      sum = std::move(turned);
+    }
+    ctx->Rescale(res, sum);
+    res.SetScale(scale_out_);
+  }
+
   int level() const { return level_; }
   int NumBabySteps() const { return baby_rot_.size(); }
   int NumGiantSteps() const { return giant_rot_.size(); }
@@ -191,6 +278,8 @@ class LinearTransform {
   int Mod(long long x) const { return (int)(((x % n_) + n_) % n_); }
   int level_, bs_, n_;
   double scale_out_;
+  int g_ = 0, giant_stride_ = 0, giant_first_ = 0;  // slot distances of the min_ks plan
+  std::vector<int> baby_idx_, giant_jj_;            // baby multiple / giant position per entry
   std::vector<int> baby_rot_, giant_rot_;  // slot distances; baby_rot_[0] == 0
   std::vector<Pt> pts_;                    // [giant][baby], dense
   std::vector<bool> present_;
@@ -609,12 +698,12 @@ class BootContext : public Context<word> {
   // Rotation keys Boot needs for this slot count: those of the linear
   // transforms and the trace's num_slots * 2^i (reference AddRequiredRotations,
   // src/extension/BootContext.cpp:174-184).
-  void AddRequiredRotations(EvkRequest &req, int num_slots) const {
+  void AddRequiredRotations(EvkRequest &req, int num_slots, bool min_ks = false) const {
     AssertTrue(IsBootPrepared(num_slots), "Bootstrapping is not prepared for this slot count");
     const FftPlan &plan = eval_fft_.at(num_slots);
     std::set<int> rots;
-    for (auto &lt : plan.cts) lt.AddRequiredRotations(rots);
-    for (auto &lt : plan.stc) lt.AddRequiredRotations(rots);
+    for (auto &lt : plan.cts) lt.AddRequiredRotations(rots, min_ks);
+    for (auto &lt : plan.stc) lt.AddRequiredRotations(rots, min_ks);
     for (int ns = num_slots; ns < this->param_.degree_ / 2; ns *= 2) rots.insert(ns);
     for (int r : rots) req.AddRequest(r, boot_param_.GetMaxLevel());
   }
@@ -719,11 +808,11 @@ class BootContext : public Context<word> {
     res = std::move(out);
   }
 
-  void CoeffToSlot(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
-    RunGroups(res, input, PlanFor(input.GetNumSlots()).cts, evk_map);
+  void CoeffToSlot(Ct &res, const Ct &input, const EvkMap<word> &evk_map, bool min_ks = false) const {
+    RunGroups(res, input, PlanFor(input.GetNumSlots()).cts, evk_map, min_ks);
   }
-  void SlotToCoeff(Ct &res, const Ct &input, const EvkMap<word> &evk_map) const {
-    RunGroups(res, input, PlanFor(input.GetNumSlots()).stc, evk_map);
+  void SlotToCoeff(Ct &res, const Ct &input, const EvkMap<word> &evk_map, bool min_ks = false) const {
+    RunGroups(res, input, PlanFor(input.GetNumSlots()).stc, evk_map, min_ks);
   }
   void EvaluateMod(Ct &res, const Ct &input, const Evk &mult_key) const {
     AssertTrue(eval_mod_ != nullptr, "EvalMod not prepared");
@@ -736,7 +825,8 @@ class BootContext : public Context<word> {
   // boot_param_.GetEndLevel() (reference Boot, src/extension/BootContext.cpp:299-365).
   // phase_ms (optional): the host synchronises after every phase and appends
   // its name and wall-clock milliseconds.
-  void Boot(Ct &res, const Ct &input, const EvkMap<word> &evk_map,
+  // min_ks: linear transforms with at most three rotation keys each.
+  void Boot(Ct &res, const Ct &input, const EvkMap<word> &evk_map, bool min_ks = false,
             std::vector<std::pair<std::string, double>> *phase_ms = nullptr) const {
     const auto &param = this->param_;
     auto last = std::chrono::steady_clock::now();
@@ -752,7 +842,7 @@ class BootContext : public Context<word> {
     if (param.NPToLevel(input.GetNP()) > 0) {
       Ct low;
       this->LevelDown(low, input, 0);
-      Boot(res, low, evk_map, phase_ms);
+      Boot(res, low, evk_map, min_ks, phase_ms);
       return;
     }
     this->AssertSameScale(input.GetScale() * (double)(UINT64_C(1) << log_scaleup_), boot_input_scale_);
@@ -786,7 +876,7 @@ class BootContext : public Context<word> {
     phase("ModUpToMax");
     // 2. coefficients to slots
     Ct slots;
-    CoeffToSlot(slots, raised, evk_map);
+    CoeffToSlot(slots, raised, evk_map, min_ks);
     phase("CoeffToSlot");
     // 3. real and imaginary parts, each through EvalMod
     Ct conj, re, im;
@@ -802,7 +892,7 @@ class BootContext : public Context<word> {
     this->Add(re_mod, re_mod, im_mod);
     phase("EvalMod x2");
     // 4. slots to coefficients
-    SlotToCoeff(res, re_mod, evk_map);
+    SlotToCoeff(res, re_mod, evk_map, min_ks);
     res.SetNumSlots(input.GetNumSlots());
     phase("SlotToCoeff");
   }
@@ -834,12 +924,12 @@ class BootContext : public Context<word> {
   }
 
   void RunGroups(Ct &res, const Ct &input, const std::vector<LinearTransform<word>> &groups,
-                 const EvkMap<word> &evk_map) const {
+                 const EvkMap<word> &evk_map, bool min_ks) const {
     AssertFalse(groups.empty(), "EvalSpecialFFT not prepared");
     Ct cur, next;
     const Ct *in = &input;
     for (auto &lt : groups) {
-      lt.Evaluate(GetContext(), next, *in, evk_map);
+      lt.Evaluate(GetContext(), next, *in, evk_map, min_ks);
       cur = std::move(next);
       in = &cur;
     }

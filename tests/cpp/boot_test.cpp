@@ -2,7 +2,7 @@
 // C++ mirror of the reference API (the reference's boot_test checks Boot on
 // 2^15 random complex slots in [-1,1]^2, unittest/Bootstrapping.cpp:10-41).
 //
-//   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot,sparse]
+//   boot_test <parameter.json> [--only linear,poly,evalmod,fft,boot,minks,sparse]
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -192,7 +192,7 @@ int main(int argc, char **argv) {
       best = std::min(best, std::chrono::duration<double, std::milli>(b - a).count());
     }
     std::vector<std::pair<std::string, double>> phases;
-    boot_ctx->Boot(out, ct, ui.GetEvkMap(), &phases);
+    boot_ctx->Boot(out, ct, ui.GetEvkMap(), false, &phases);
     std::cout << "       phases (ms, host-synchronised):";
     for (auto &[name, ms] : phases) std::cout << "  " << name << " " << std::fixed << std::setprecision(2) << ms;
     std::cout << std::endl;
@@ -228,6 +228,31 @@ int main(int argc, char **argv) {
     boot_ctx->Boot(out, high, ui.GetEvkMap());
     decrypt(got, out);
     Report("Boot of a level-3 input", m, got, 1e-3);
+  }
+
+  if (want("minks")) {
+    // the plan with at most three rotation keys per linear transform
+    // (the reference's Boot(..., min_ks = true), unittest/Bootstrapping.cpp:34-40)
+    boot_ctx->PrepareEvalMod();
+    boot_ctx->PrepareEvalSpecialFFT(n);
+    EvkRequest req;
+    boot_ctx->AddRequiredRotations(req, n, true);
+    ui.PrepareRotationKey(req);
+    Msg m, got;
+    random_msg(m, -1, 1, true);
+    Ct ct, out;
+    encrypt(ct, m, 0, param->GetScale(0));
+    double best = 1e30;
+    for (int it = 0; it < 3; it++) {
+      ctx->Synchronize();
+      auto a = std::chrono::steady_clock::now();
+      boot_ctx->Boot(out, ct, ui.GetEvkMap(), true);
+      ctx->Synchronize();
+      best = std::min(best, std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count());
+    }
+    decrypt(got, out);
+    std::cout << "       min_ks: " << req.size() << " rotation keys, best of 3: " << best << " ms" << std::endl;
+    Report("Boot with minimum key switching", m, got, 1e-3);
   }
 
   if (want("sparse")) {
