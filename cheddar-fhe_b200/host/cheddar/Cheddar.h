@@ -475,6 +475,25 @@ class Random {
     std::uniform_int_distribution<word> d(lo, hi);
     std::generate(p, p + n, [&]() { return d(gen_); });
   }
+  // Uniform residues in [0, q): both 32-bit halves of every generator output
+  // are used, each mapped to the range by the multiply-and-reject method
+  // (exactly uniform), several times faster than a distribution object per word.
+  static void SampleUniformBelow(uint32_t *p, size_t n, uint32_t q) {
+    const uint32_t reject_below = (uint32_t)(0u - q) % q;  // 2^32 mod q
+    uint64_t pool = 0;
+    int have = 0;
+    for (size_t i = 0; i < n;) {
+      if (!have) {
+        pool = gen_();
+        have = 2;
+      }
+      const uint32_t r = (uint32_t)pool;
+      pool >>= 32;
+      have--;
+      const uint64_t m = (uint64_t)r * q;
+      if ((uint32_t)m >= reject_below) p[i++] = (uint32_t)(m >> 32);
+    }
+  }
   static void SampleWithoutReplacement(int *p, int n, int lo, int hi) {
     AssertTrue(hi - lo + 1 >= n, "Invalid length");
     std::vector<int> v(hi - lo + 1);
@@ -606,7 +625,18 @@ class Encoder {
     std::vector<word> mx((size_t)nt * degree, 0);
     for (int i = 0; i < num_slots; i++) {
       // truncation toward zero, as the reference's BigInt(double)
-      const __int128 re = (__int128)(data[i].real() * scale), im = (__int128)(data[i].imag() * scale);
+      const double fr = data[i].real() * scale, fi = data[i].imag() * scale;
+      if (std::abs(fr) < 0x1p62 && std::abs(fi) < 0x1p62) {  // 64-bit remainders are much cheaper
+        const int64_t re = (int64_t)fr, im = (int64_t)fi;
+        for (int j = 0; j < nt; j++) {
+          const int64_t q = primes[j];
+          int64_t a = re % q, b = im % q;
+          mx[(size_t)j * degree + i * gap] = (word)(a < 0 ? a + q : a);
+          mx[(size_t)j * degree + i * gap + half] = (word)(b < 0 ? b + q : b);
+        }
+        continue;
+      }
+      const __int128 re = (__int128)fr, im = (__int128)fi;
       for (int j = 0; j < nt; j++) {
         mx[(size_t)j * degree + i * gap] = detail::ModI128(re, primes[j]);
         mx[(size_t)j * degree + i * gap + half] = detail::ModI128(im, primes[j]);
@@ -1543,8 +1573,7 @@ class UserInterface {
     const int n = param.degree_;
     auto g = param.GetLimbIndices(np);
     std::vector<word> host(g.size() * n);
-    for (size_t i = 0; i < g.size(); i++)
-      Random::SampleUniformWord<word>(host.data() + i * n, n, 0, all_primes_[g[i]] - 1);
+    for (size_t i = 0; i < g.size(); i++) Random::SampleUniformBelow(host.data() + i * n, n, all_primes_[g[i]]);
     CopyHostToDevice(poly, host);
   }
 
