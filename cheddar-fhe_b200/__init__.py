@@ -214,6 +214,17 @@ class Engine:
         self._check(self.L.cfhe_const_op(self.h, op, self._p(dst), self._p(a),
                                          self._p(b) if b is not None else None, kp, gp, len(g)))
 
+    def elementwise_multi_(self, with_const, op, dsts, a_list, b_list, consts, gidx):
+        """One launch for several polynomials (cfhe_elementwise_multi)."""
+        g, gp = _ints(gidx)
+        n = len(dsts)
+        arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in ts])
+        kp = None
+        if consts is not None:
+            k, kp = _u32s(consts)
+        self._check(self.L.cfhe_elementwise_multi(self.h, int(with_const), int(op), n, arr(dsts), arr(a_list),
+                                                  arr(b_list) if b_list is not None else None, kp, gp, len(g)))
+
     def tensor_(self, d0, d1, d2, b1, a1, b2, a2, gidx):
         g, gp = _ints(gidx)
         self._check(self.L.cfhe_tensor(self.h, *[self._p(t) for t in (d0, d1, d2, b1, a1, b2, a2)], gp, len(g)))

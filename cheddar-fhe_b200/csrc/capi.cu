@@ -356,6 +356,33 @@ int cfhe_const_op(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
   { int r_ = launch_ew(h->c, map[op], e); h->c.mark("elementwise"); return r_; }
 }
 
+int cfhe_elementwise_multi(cfhe_context *h, int with_const, int op, int n_polys,
+                           uint32_t *const *dst, const uint32_t *const *a,
+                           const uint32_t *const *b, const uint32_t *consts,
+                           const int *gidx, int n_limbs) {
+  if (!h || !dst || !a || !gidx) return fail("null argument");
+  static const int bin[4] = {EW_ADD, EW_SUB, EW_NEG, EW_MUL};
+  static const int con[5] = {EW_ADDC, EW_SUBC, EW_RSUBC, EW_MULC, EW_MULC_ADD};
+  if (op < 0 || op > (with_const ? 4 : 3)) return fail("unknown element-wise op");
+  if (with_const && !consts) return fail("null argument");
+  const bool needs_b = with_const ? op == 4 : op != 2;
+  if (n_polys < 1 || n_limbs < 0 || n_polys * n_limbs > kMaxRows) return fail("too many limbs");
+  const Context &c = h->c;
+  EwArgs e;
+  e.n_rows = 0;
+  for (int p = 0; p < n_polys; p++) {
+    if (!dst[p] || !a[p] || (needs_b && (!b || !b[p]))) return fail("null argument");
+    for (int l = 0; l < n_limbs; l++) {
+      const int g = gidx[l];
+      if (g < 0 || g >= c.NP) return fail("prime index out of range");
+      const size_t o = (size_t)l * kN;
+      e.rows[e.n_rows++] = EwRow{dst[p] + o, a[p] + o, (b && b[p]) ? b[p] + o : nullptr, c.q[g],
+                                 c.nqinv[g], with_const ? consts[l] % c.q[g] : 0u, 0u};
+    }
+  }
+  { int r_ = launch_ew(c, with_const ? con[op] : bin[op], e); c.mark("elementwise"); return r_; }
+}
+
 int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
                 const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
                 const uint32_t *a2, const int *gidx, int n_limbs) {

@@ -50,10 +50,11 @@ int main(int argc, char **argv) {
   ui.Encrypt(ct, pt);
   for (int i = 0; i < warmup; i++) ctx->Boot(out, ct, ui.GetEvkMap());
   ctx->Synchronize();
-  double total = 0, best = 1e30;
+  double total = 0, best = 1e30, enqueue = 0;
   for (int i = 0; i < iters; i++) {
     auto a = std::chrono::steady_clock::now();
     ctx->Boot(out, ct, ui.GetEvkMap());
+    enqueue += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count();
     ctx->Synchronize();
     const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count();
     total += ms;
@@ -69,7 +70,7 @@ int main(int argc, char **argv) {
     sum += std::abs(msg[i] - got[i]);
   }
   std::cout << std::setprecision(6) << "{\"boot_ms\": " << total / iters << ", \"boot_ms_best\": " << best
-            << ", \"iters\": " << iters << ", \"warmup\": " << warmup << ", \"slots\": " << n
+            << ", \"host_enqueue_ms\": " << enqueue / iters << ", \"iters\": " << iters << ", \"warmup\": " << warmup << ", \"slots\": " << n
             << ", \"end_level\": " << param->NPToLevel(out.GetNP()) << ", \"max_err\": " << worst
             << ", \"mean_err\": " << sum / n << ", \"precision_bits\": " << -std::log2(sum / n)
             << ", \"prepare_s\": " << prepare_s << ", \"rotation_keys\": " << req.size() << ", \"phases_ms\": {";

@@ -807,9 +807,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetNumSlots(a.GetNumSlots());
     res.SetScale(a.GetScale());
     NPInfo np = a.GetNP();
-    D2D(res.bx_, a.bx_, np);
-    D2D(res.ax_, a.ax_, np);
-    if (a.HasRx()) D2D(res.rx_, a.rx_, np);
+    ConstCt(0, res, {a.bx_.data(), a.ax_.data(), a.rx_.data()}, {nullptr, nullptr, nullptr},
+            std::vector<word>(np.GetNumTotal(), 0), np, a.HasRx());  // a + 0: device copy on the stream
   }
 
   void Add(Ct &res, const Ct &a, const Ct &b) const { AddSub(res, a, b, 0); }
@@ -845,9 +844,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetNumSlots(a.GetNumSlots());
     res.SetScale(a.GetScale());
     NPInfo np = res.GetNP();
-    Binary(2, res.bx_.data(), a.bx_.data(), nullptr, np);
-    Binary(2, res.ax_.data(), a.ax_.data(), nullptr, np);
-    if (a.HasRx()) Binary(2, res.rx_.data(), a.rx_.data(), nullptr, np);
+    BinaryCt(2, res, {a.bx_.data(), a.ax_.data(), a.rx_.data()}, {nullptr, nullptr, nullptr}, np, a.HasRx());
   }
 
   void Mult(Ct &res, const Ct &a, const Ct &b) const {
@@ -868,9 +865,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
     res.SetScale(a.GetScale() * b.GetScale());
     NPInfo np = res.GetNP();
-    Binary(3, res.bx_.data(), a.bx_.data(), b.mx_.data(), np);
-    Binary(3, res.ax_.data(), a.ax_.data(), b.mx_.data(), np);
-    if (a.HasRx()) Binary(3, res.rx_.data(), a.rx_.data(), b.mx_.data(), np);
+    BinaryCt(3, res, {a.bx_.data(), a.ax_.data(), a.rx_.data()}, {b.mx_.data(), b.mx_.data(), b.mx_.data()}, np,
+             a.HasRx());
   }
   void Mult(Ct &res, const Ct &a, const Const &b) const {
     AssertSameNP(a, b);
@@ -878,9 +874,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetNumSlots(a.GetNumSlots());
     res.SetScale(a.GetScale() * b.GetScale());
     NPInfo np = res.GetNP();
-    ConstKernel(3, res.bx_.data(), a.bx_.data(), nullptr, b.cx_, np);
-    ConstKernel(3, res.ax_.data(), a.ax_.data(), nullptr, b.cx_, np);
-    if (a.HasRx()) ConstKernel(3, res.rx_.data(), a.rx_.data(), nullptr, b.cx_, np);
+    ConstCt(3, res, {a.bx_.data(), a.ax_.data(), a.rx_.data()}, {nullptr, nullptr, nullptr}, b.cx_, np, a.HasRx());
   }
 
   // ---- products whose operands may sit at a higher level than the result:
@@ -930,9 +924,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
     res.SetScale(a.GetScale() * b.GetScale());
     const size_t ao = FrontIgnore(a_np, np), bo = FrontIgnore(b_np, np);
-    Binary(3, res.bx_.data(), a.bx_.data() + ao, b.mx_.data() + bo, np);
-    Binary(3, res.ax_.data(), a.ax_.data() + ao, b.mx_.data() + bo, np);
-    if (a.HasRx()) Binary(3, res.rx_.data(), a.rx_.data() + ao, b.mx_.data() + bo, np);
+    BinaryCt(3, res, {a.bx_.data() + ao, a.ax_.data() + ao, a.HasRx() ? a.rx_.data() + ao : nullptr},
+             {b.mx_.data() + bo, b.mx_.data() + bo, b.mx_.data() + bo}, np, a.HasRx());
   }
   void MultUnsafe(Ct &res, const Ct &a, const Const &b, int level = -1) const {
     const NPInfo a_np = a.GetNP(), b_np = b.GetNP();
@@ -952,9 +945,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     res.SetScale(a.GetScale() * b.GetScale());
     const size_t ao = FrontIgnore(a_np, np);
     const std::vector<word> k = ConstLimbs(b, np);
-    ConstKernel(3, res.bx_.data(), a.bx_.data() + ao, nullptr, k, np);
-    ConstKernel(3, res.ax_.data(), a.ax_.data() + ao, nullptr, k, np);
-    if (a.HasRx()) ConstKernel(3, res.rx_.data(), a.rx_.data() + ao, nullptr, k, np);
+    ConstCt(3, res, {a.bx_.data() + ao, a.ax_.data() + ao, a.HasRx() ? a.rx_.data() + ao : nullptr},
+            {nullptr, nullptr, nullptr}, k, np, a.HasRx());
   }
   // res += a * b on the limbs of res
   void MadUnsafe(Ct &res, const Ct &a, const Const &b) const {
@@ -970,9 +962,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     }
     const size_t ao = FrontIgnore(a_np, np);
     const std::vector<word> k = ConstLimbs(b, np);
-    ConstKernel(4, res.bx_.data(), a.bx_.data() + ao, res.bx_.data(), k, np);
-    ConstKernel(4, res.ax_.data(), a.ax_.data() + ao, res.ax_.data(), k, np);
-    if (a.HasRx()) ConstKernel(4, res.rx_.data(), a.rx_.data() + ao, res.rx_.data(), k, np);
+    ConstCt(4, res, {a.bx_.data() + ao, a.ax_.data() + ao, a.HasRx() ? a.rx_.data() + ao : nullptr},
+            {res.bx_.data(), res.ax_.data(), res.rx_.data()}, k, np, a.HasRx());
   }
   // Brings a ciphertext down to target_level one level at a time: multiply by
   // the constant 1 encoded at the level's scale, then rescale (reference
@@ -1226,6 +1217,20 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     std::vector<word> zero(np.GetNumTotal(), 0);
     ConstKernel(0, dst.data(), src.data(), nullptr, zero, np);  // a + 0: device copy on the stream
   }
+  // one launch for the two or three polynomials of a ciphertext
+  void BinaryCt(int op, Ct &res, const word *const (&a)[3], const word *const (&b)[3], const NPInfo &np,
+                bool rx) const {
+    auto g = param_.GetLimbIndices(np);
+    word *dst[3] = {res.bx_.data(), res.ax_.data(), rx ? res.rx_.data() : nullptr};
+    CheckAbi(cfhe_elementwise_multi(h_, 0, op, rx ? 3 : 2, dst, a, b, nullptr, g.data(), g.size()));
+  }
+  void ConstCt(int op, Ct &res, const word *const (&a)[3], const word *const (&b)[3],
+               const std::vector<word> &k, const NPInfo &np, bool rx) const {
+    auto g = param_.GetLimbIndices(np);
+    AssertTrue(k.size() == g.size(), "Constant has a different number of limbs");
+    word *dst[3] = {res.bx_.data(), res.ax_.data(), rx ? res.rx_.data() : nullptr};
+    CheckAbi(cfhe_elementwise_multi(h_, 1, op, rx ? 3 : 2, dst, a, b, k.data(), g.data(), g.size()));
+  }
   void Binary(int op, word *dst, const word *a, const word *b, const NPInfo &np) const {
     auto g = param_.GetLimbIndices(np);
     CheckAbi(cfhe_binary(h_, op, dst, a, b, g.data(), g.size()));
@@ -1266,9 +1271,8 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     MatchResultWith(res, a);
     res.SetNumSlots(Max(a.GetNumSlots(), b.GetNumSlots()));
     res.SetScale(a.GetScale());
-    Binary(op, res.bx_.data(), a.bx_.data(), b.bx_.data(), np);
-    Binary(op, res.ax_.data(), a.ax_.data(), b.ax_.data(), np);
-    if (a.HasRx()) Binary(op, res.rx_.data(), a.rx_.data(), b.rx_.data(), np);
+    BinaryCt(op, res, {a.bx_.data(), a.ax_.data(), a.rx_.data()}, {b.bx_.data(), b.ax_.data(), b.rx_.data()}, np,
+             a.HasRx());
   }
   void PtOp(Ct &res, const Ct &a, const Pt &b, int op) const {
     AssertSameNP(a, b);

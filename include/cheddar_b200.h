@@ -111,6 +111,19 @@ CFHE_API int cfhe_binary(cfhe_context *ctx, int op, uint32_t *dst,
 CFHE_API int cfhe_const_op(cfhe_context *ctx, int op, uint32_t *dst,
                            const uint32_t *a, const uint32_t *b,
                            const uint32_t *consts, const int *gidx, int n_limbs);
+/* The operators of cfhe_binary (with_const == 0, op 0..3) or cfhe_const_op
+ * (with_const != 0, op 0..4) applied to n_polys polynomials in one launch, as
+ * the reference's element-wise kernels do for the two or three polynomials of
+ * a ciphertext (template parameter num_poly, ElementWise.cu:32-60). dst, a, b:
+ * HOST arrays of n_polys device pointers (b may be NULL where the op has no
+ * second operand); consts and gidx are shared by all polynomials;
+ * n_polys * n_limbs <= 192. */
+CFHE_API int cfhe_elementwise_multi(cfhe_context *ctx, int with_const, int op,
+                                    int n_polys, uint32_t *const *dst,
+                                    const uint32_t *const *a,
+                                    const uint32_t *const *b,
+                                    const uint32_t *consts, const int *gidx,
+                                    int n_limbs);
 /* (d0,d1,d2) = (b1*b2, b1*a2 + a1*b2, a1*a2): ElementWiseHandler::Tensor
  * (:922, kernel :504-546). */
 CFHE_API int cfhe_tensor(cfhe_context *ctx, uint32_t *d0, uint32_t *d1,

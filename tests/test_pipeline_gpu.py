@@ -31,6 +31,33 @@ def test_elementwise_matches_oracle(engine40, oracle40):
     assert np.array_equal(e.mul_imag_unit(a, g), o.mul_imag_unit(a, g))
 
 
+def test_elementwise_multi_equals_single_calls(engine40, oracle40):
+    """Two and three polynomials in one launch give the words of one launch per
+    polynomial, for every binary and constant operator."""
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(23)
+    g = e.level_limbs(20)
+    polys = [[e.to_dev(rand_limbs(rng, o.primes, g, o.n)) for _ in range(3)] for _ in range(2)]
+    k = np.array([rng.integers(0, int(o.primes[gi])) for gi in g], dtype=np.uint32)
+    t = e.torch
+    for n in (2, 3):
+        a, b = polys[0][:n], polys[1][:n]
+        for op in range(4):
+            multi = [t.empty_like(x) for x in a]
+            e.elementwise_multi_(0, op, multi, a, b if op != 2 else None, None, g)
+            for i in range(n):
+                single = t.empty_like(a[i])
+                e.binary_(op, single, a[i], b[i] if op != 2 else None, g)
+                assert t.equal(multi[i], single), (n, op, i)
+        for op in range(5):
+            multi = [t.empty_like(x) for x in a]
+            e.elementwise_multi_(1, op, multi, a, b if op == 4 else None, k, g)
+            for i in range(n):
+                single = t.empty_like(a[i])
+                e.const_op_(op, single, a[i], b[i] if op == 4 else None, k, g)
+                assert t.equal(multi[i], single), (n, op, i)
+
+
 def test_tensor_matches_oracle(engine40, oracle40):
     e, o = engine40, oracle40
     rng = np.random.default_rng(22)
