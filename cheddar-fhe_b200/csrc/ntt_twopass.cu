@@ -9,8 +9,8 @@
 // cluster, no cross-CTA wait, at least four CTAs per SM.
 //
 // What makes two passes cost one trip to HBM: the host launches them over
-// chunks of at most kChunkJobs limbs (32 MiB), the second pass works in place
-// on what the first just wrote, and a chunk is a quarter of the 126 MB L2. The
+// chunks of at most kChunkJobs limbs (48 MiB), the second pass works in place
+// on what the first just wrote, and a chunk is well below the 126 MB L2. The
 // first pass reads HBM and writes L2; the second reads and rewrites the same
 // lines in L2; they reach HBM once, when they are evicted.
 //
