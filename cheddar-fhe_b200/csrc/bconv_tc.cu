@@ -110,6 +110,9 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
   // work. Source k >= ns re-reads the last source (its table rows are zero).
   uint32_t yn[kWords - 1];
   const uint32_t *src = j.src + tid;
+  // everything above (table slice, constants, tensor memory) did not depend on
+  // earlier kernels; the residues do
+  pdl_wait();
   auto load_tile = [&](int tile) {
 #pragma unroll
     for (int k = 0; k < kWords - 1; k++)
@@ -204,6 +207,7 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
 __global__ void __launch_bounds__(kTcThreads)
     bconv_tc_kernel(const __grid_constant__ BconvTcArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
   const BconvTcJob &j = a.jobs[a.unit_job[blockIdx.y]];
   const int slice = a.unit_slice[blockIdx.y];           // 16 destination limbs each
   uint8_t *sB = smem;                                   // [K/16][8][8][16]
@@ -329,7 +333,7 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
   int per_unit = (8 * 148 + b.n_units - 1) / b.n_units;
   if (per_unit > kN / kTcTile) per_unit = kN / kTcTile;
   dim3 grid(per_unit, b.n_units);
-  bconv_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, ctx.stream>>>(b);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, bconv_tc_kernel, grid, dim3(kTcThreads), kTcSmemBytes, ctx.stream, b));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -92,6 +92,7 @@ struct Context {
 
   std::vector<uint32_t> nqinv;      // -q^-1 mod 2^32, global order
   bool use_tc_bconv = true;         // base conversion on tcgen05 (CFHE_BCONV=simt disables)
+  bool use_pdl = true;              // programmatic dependent launch between the kernels of a stream (CFHE_PDL=0 disables)
   bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
   int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out
   std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
@@ -136,6 +137,38 @@ const std::string &get_error();
       return -2;                                                             \
     }                                                                        \
   } while (0)
+
+
+// ---- programmatic dependent launch ------------------------------------------
+// Kernels of one stream are launched with the programmatic-serialisation
+// attribute: a kernel may be scheduled while the previous one drains, runs
+// whatever does not depend on earlier kernels (parameter decoding, table
+// loads, tensor-memory allocation) and calls pdl_wait() before it reads or
+// writes anything an earlier kernel touches. pdl_launch_dependents() at the
+// top of a kernel lets its own successor in as soon as all of its CTAs have
+// started. Both are no-ops in a kernel launched the ordinary way.
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse);
 int launch_ntt_twopass(const Context &ctx, const NttArgs &args, bool inverse);

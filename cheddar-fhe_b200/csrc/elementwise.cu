@@ -21,6 +21,8 @@ __device__ __forceinline__ uint4 map4(uint4 a, uint4 b, F f) {
 template <int OP>
 __global__ void __launch_bounds__(kEwThreads)
     ew_kernel(const __grid_constant__ EwArgs args) {
+  pdl_launch_dependents();
+  pdl_wait();
   const EwRow &r = args.rows[blockIdx.y];
   const int v = blockIdx.x * kEwThreads + threadIdx.x;
   const uint32_t q = r.q, nq = r.nqinv, k = r.k;
@@ -61,6 +63,8 @@ __global__ void __launch_bounds__(kEwThreads)
 
 __global__ void __launch_bounds__(kEwThreads)
     tensor_kernel(const __grid_constant__ TensorArgs args) {
+  pdl_launch_dependents();
+  pdl_wait();
   const TensorRow &r = args.rows[blockIdx.y];
   const int v = blockIdx.x * kEwThreads + threadIdx.x;
   const uint32_t q = r.q, nq = r.nqinv;
@@ -88,6 +92,8 @@ __global__ void __launch_bounds__(kEwThreads)
 // loads stay inside one 512-byte block.
 __global__ void __launch_bounds__(kEwThreads)
     permute_kernel(const __grid_constant__ EwArgs args, uint32_t galois) {
+  pdl_launch_dependents();
+  pdl_wait();
   const EwRow &r = args.rows[blockIdx.y];
   const int v = blockIdx.x * kEwThreads + threadIdx.x;
   const uint32_t q = r.q;
@@ -113,6 +119,8 @@ __global__ void __launch_bounds__(kEwThreads)
 // to digit i, else the ModUp output. One Montgomery reduction per output.
 __global__ void __launch_bounds__(kEwThreads)
     inner_kernel(const __grid_constant__ InnerArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int l = blockIdx.y;
   const int v = blockIdx.x * kEwThreads + threadIdx.x;
   const uint32_t q = a.q[l], nq = a.nqinv[l];
@@ -202,6 +210,8 @@ __global__ void __launch_bounds__(kEwThreads)
 constexpr int kPtThreads = 256;
 __global__ void __launch_bounds__(kPtThreads, 2)
     pt_accum_kernel(const __grid_constant__ PtAccumArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int l = blockIdx.y;
   const int v = blockIdx.x * kPtThreads + threadIdx.x;
   const uint32_t q = a.q[l], nq = a.nqinv[l];
@@ -241,6 +251,8 @@ __global__ void __launch_bounds__(kPtThreads, 2)
 // src/core/ElementWise.cu:593-623; one-limb case :579-591).
 __global__ void __launch_bounds__(kEwThreads)
     lift_kernel(const __grid_constant__ EwArgs args, const uint32_t *src, uint32_t q0, uint32_t q1) {
+  pdl_launch_dependents();
+  pdl_wait();
   const EwRow &r = args.rows[blockIdx.y];
   const int i = blockIdx.x * kEwThreads + threadIdx.x;  // one word per thread
   const uint32_t p = r.q;
@@ -262,7 +274,7 @@ __global__ void __launch_bounds__(kEwThreads)
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1) {
   if (args.n_rows <= 0) return 0;
   dim3 grid(kN / kEwThreads, args.n_rows), block(kEwThreads);
-  lift_kernel<<<grid, block, 0, ctx.stream>>>(args, src, q0, q1);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, lift_kernel, grid, block, 0, ctx.stream, args, src, q0, q1));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }
@@ -273,7 +285,7 @@ int launch_ew(const Context &ctx, int op, const EwArgs &args) {
   switch (op) {
 #define CASE(OP)                                            \
   case OP:                                                  \
-    ew_kernel<OP><<<grid, block, 0, ctx.stream>>>(args);    \
+    CFHE_CUDA(launch_kernel(ctx.use_pdl, ew_kernel<OP>, grid, block, 0, ctx.stream, args)); \
     break;
     CASE(EW_ADD)
     CASE(EW_SUB)
@@ -298,7 +310,7 @@ int launch_ew(const Context &ctx, int op, const EwArgs &args) {
 int launch_tensor(const Context &ctx, const TensorArgs &args) {
   if (args.n_rows <= 0) return 0;
   dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
-  tensor_kernel<<<grid, block, 0, ctx.stream>>>(args);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, tensor_kernel, grid, block, 0, ctx.stream, args));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }
@@ -306,21 +318,21 @@ int launch_tensor(const Context &ctx, const TensorArgs &args) {
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois) {
   if (args.n_rows <= 0) return 0;
   dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
-  permute_kernel<<<grid, block, 0, ctx.stream>>>(args, galois);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, permute_kernel, grid, block, 0, ctx.stream, args, galois));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }
 
 int launch_pt_accum(const Context &ctx, const PtAccumArgs &args) {
   dim3 grid(kN / kPtThreads, args.ntot), block(kPtThreads);
-  pt_accum_kernel<<<grid, block, 0, ctx.stream>>>(args);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, pt_accum_kernel, grid, block, 0, ctx.stream, args));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }
 
 int launch_inner(const Context &ctx, const InnerArgs &args) {
   dim3 grid(kEwBlocksX, args.ntot), block(kEwThreads);
-  inner_kernel<<<grid, block, 0, ctx.stream>>>(args);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, inner_kernel, grid, block, 0, ctx.stream, args));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -61,9 +61,10 @@ __device__ __forceinline__ void fwd_cols(const NttArgs &a, const Job &j, int til
   uint32_t v[16];
   Tw t[15];
   const uint32_t *s = j.src + r0 * kRowWords + kColTile * tile + x;
+  ld_tw16(j.tw, 1, t);  // the tables are never written by a kernel: fetched before the wait
+  pdl_wait();
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = s[k * 16 * kRowWords];
-  ld_tw16(j.tw, 1, t);
   if (a.premul) {
     const Tw kc = a.kc[j.l];
 #pragma unroll
@@ -93,9 +94,10 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
   uint32_t v[16];
   Tw t[15];
   const uint32_t *s = j.dst + R * kRowWords + x0;
+  ld_tw16(j.tw, 256 + R, t);
+  pdl_wait();
 #pragma unroll
   for (int k = 0; k < 16; k++) v[k] = s[16 * k];
-  ld_tw16(j.tw, 256 + R, t);
   ct_radix16_pre<FAST>(v, t, q, q2);
   ld_tw16(j.tw, 4096 + 16 * R + g, t);  // in flight across the exchange
   uint32_t *row = xbuf + rho * kRowStride;
@@ -168,17 +170,18 @@ __device__ __forceinline__ void inv_rows(const NttArgs &, const Job &j, int blk,
   const int rho = tid >> 4, g = tid & 15, x0 = g;
   const int R = kRowTile * blk + rho;
   uint32_t v[16];
+  Tw t[15];
+  ld_tw16(j.tw, 4096 + 16 * R + g, t);
+  pdl_wait();
   const uint4 *s = reinterpret_cast<const uint4 *>(j.src + R * kRowWords + 16 * g);
 #pragma unroll
   for (int i = 0; i < 4; i++) {
-    const uint4 t = s[i];
-    v[4 * i] = t.x;
-    v[4 * i + 1] = t.y;
-    v[4 * i + 2] = t.z;
-    v[4 * i + 3] = t.w;
+    const uint4 u = s[i];
+    v[4 * i] = u.x;
+    v[4 * i + 1] = u.y;
+    v[4 * i + 2] = u.z;
+    v[4 * i + 3] = u.w;
   }
-  Tw t[15];
-  ld_tw16(j.tw, 4096 + 16 * R + g, t);
   gs_radix16_pre<FAST>(v, t, q, q2);
   ld_tw16(j.tw, 256 + R, t);  // in flight across the exchange
   uint32_t *row = xbuf + rho * kRowStride;
@@ -203,10 +206,11 @@ __device__ __forceinline__ void inv_cols(const NttArgs &a, const Job &j, int til
   const int x = tid & 15, g = tid >> 4;
   uint32_t v[16];
   uint32_t *base = j.dst + kColTile * tile + x;
-#pragma unroll
-  for (int k = 0; k < 16; k++) v[k] = base[(16 * g + k) * kRowWords];
   Tw t[15];
   ld_tw16(j.tw, 16 + g, t);
+  pdl_wait();
+#pragma unroll
+  for (int k = 0; k < 16; k++) v[k] = base[(16 * g + k) * kRowWords];
   gs_radix16_pre<FAST>(v, t, q, q2);
   ld_tw16(j.tw, 1, t);  // in flight across the transposition
 #pragma unroll
@@ -233,7 +237,8 @@ template <bool INV, int PASS>
 __global__ void __launch_bounds__(kTpThreads, 4)
     ntt_twopass_kernel(const __grid_constant__ NttArgs a, int job0) {
   __shared__ __align__(16) uint32_t xbuf[PASS == 0 ? kColBufWords : kRowBufTileWords];
-  const Job j = get_job(a, job0 + blockIdx.y);
+  pdl_launch_dependents();
+  const Job j = get_job(a, job0 + blockIdx.y);  // each pass calls pdl_wait() after its first twiddle fetch
   const int tid = threadIdx.x, part = blockIdx.x;
   const bool fast = j.q < (1u << 30);
   if constexpr (!INV && PASS == 0) {
@@ -257,11 +262,11 @@ int launch_ntt_twopass(const Context &ctx, const NttArgs &args, bool inverse) {
     const int cnt = total - job0 < kChunkJobs ? total - job0 : kChunkJobs;
     const dim3 cols(kRowWords / kColTile, cnt), rows(kRowWords / kRowTile, cnt);
     if (inverse) {
-      ntt_twopass_kernel<true, 1><<<rows, block, 0, ctx.stream>>>(args, job0);
-      ntt_twopass_kernel<true, 0><<<cols, block, 0, ctx.stream>>>(args, job0);
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, ntt_twopass_kernel<true, 1>, rows, block, 0, ctx.stream, args, job0));
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, ntt_twopass_kernel<true, 0>, cols, block, 0, ctx.stream, args, job0));
     } else {
-      ntt_twopass_kernel<false, 0><<<cols, block, 0, ctx.stream>>>(args, job0);
-      ntt_twopass_kernel<false, 1><<<rows, block, 0, ctx.stream>>>(args, job0);
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, ntt_twopass_kernel<false, 0>, cols, block, 0, ctx.stream, args, job0));
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, ntt_twopass_kernel<false, 1>, rows, block, 0, ctx.stream, args, job0));
     }
   }
   CFHE_CUDA(cudaGetLastError());
