@@ -668,10 +668,34 @@ class BootContext : public Context<word> {
     // u / K: the constant is 1 / (half * 2K) whatever n is.
     auto cts = EvalSpecialFFT<word>::Groups(param, n, true, boot_param_.num_cts_levels_,
                                             1.0 / ((double)half * 2.0 * boot_param_.K_));
+    // With fewer than degree / 2 slots there is room for the real and the
+    // imaginary parts side by side: the last CoeffToSlot group M is replaced by
+    //   U = A x + B conj(x),  A = diag(D1) M,  B = diag(D2) conj(M)
+    // on 2n slots, D1 = (1 | -i), D2 = (1 | i) on the two halves, so that
+    // U = (2 Re(M x) | 2 Im(M x)) and a single EvalMod serves both parts; the
+    // first SlotToCoeff group S absorbs the way back, S (V + i rot_n(V)).
+    plan.merged = n < half;
+    const Complex I(0, 1);
     double s_in = q0_prod_;
     int level = boot_param_.GetCtSStartLevel();
-    for (auto &g : cts) {
-      plan.cts.emplace_back(GetContext(), g, level, s_in, eval_mod_scale_, kBabySteps);
+    for (size_t gi = 0; gi < cts.size(); gi++) {
+      const StripedMatrix &g = cts[gi];
+      if (plan.merged && gi + 1 == cts.size()) {
+        StripedMatrix A(2 * n), B(2 * n);
+        for (auto &[k, d] : g.diag) {
+          const int ks = k > n / 2 ? k - n : k;  // the same rotation of an n-periodic vector, nearer zero
+          auto &da = A.At(ks), &db = B.At(ks);
+          for (int p = 0; p < 2 * n; p++) {
+            const Complex m = d[p % n];
+            da[p] = (p < n ? Complex(1, 0) : -I) * m;
+            db[p] = (p < n ? Complex(1, 0) : I) * std::conj(m);
+          }
+        }
+        plan.cts_last.emplace_back(GetContext(), A, level, s_in, eval_mod_scale_, kBabySteps);
+        plan.cts_last.emplace_back(GetContext(), B, level, s_in, eval_mod_scale_, kBabySteps);
+      } else {
+        plan.cts.emplace_back(GetContext(), g, level, s_in, eval_mod_scale_, kBabySteps);
+      }
       s_in = eval_mod_scale_;
       level--;
     }
@@ -681,6 +705,19 @@ class BootContext : public Context<word> {
     // keeps every diagonal plaintext well above the rounding of its encoding.
     auto stc = EvalSpecialFFT<word>::Groups(param, n, false, boot_param_.num_stc_levels_,
                                             q0_prod_ / boot_input_scale_);
+    if (plan.merged) {
+      StripedMatrix tiled(2 * n), back(2 * n);
+      for (auto &[k, d] : stc[0].diag) {
+        auto &t = tiled.At(k > n / 2 ? k - n : k);
+        for (int p = 0; p < 2 * n; p++) t[p] = d[p % n];
+      }
+      auto &c0 = back.At(0), &c1 = back.At(n);
+      for (int p = 0; p < 2 * n; p++) {
+        c0[p] = p < n ? Complex(1, 0) : I;
+        c1[p] = p < n ? I : Complex(1, 0);
+      }
+      stc[0] = StripedMatrix::Mult(tiled, back);
+    }
     level = boot_param_.GetStCStartLevel();
     s_in = eval_mod_end_scale_;
     const double s_end = param.GetScale(boot_param_.GetEndLevel());
@@ -703,6 +740,7 @@ class BootContext : public Context<word> {
     const FftPlan &plan = eval_fft_.at(num_slots);
     std::set<int> rots;
     for (auto &lt : plan.cts) lt.AddRequiredRotations(rots, min_ks);
+    for (auto &lt : plan.cts_last) lt.AddRequiredRotations(rots, min_ks);
     for (auto &lt : plan.stc) lt.AddRequiredRotations(rots, min_ks);
     for (int ns = num_slots; ns < this->param_.degree_ / 2; ns *= 2) rots.insert(ns);
     for (int r : rots) req.AddRequest(r, boot_param_.GetMaxLevel());
@@ -808,11 +846,36 @@ class BootContext : public Context<word> {
     res = std::move(out);
   }
 
+  // With fewer than degree / 2 slots the result has twice the input's slots:
+  // real parts of the coefficients' slots in the first half, imaginary parts
+  // in the second (see PrepareEvalSpecialFFT); SlotToCoeff takes that form back.
   void CoeffToSlot(Ct &res, const Ct &input, const EvkMap<word> &evk_map, bool min_ks = false) const {
-    RunGroups(res, input, PlanFor(input.GetNumSlots()).cts, evk_map, min_ks);
+    const FftPlan &plan = PlanFor(input.GetNumSlots());
+    if (!plan.merged) {
+      RunGroups(res, input, plan.cts, evk_map, min_ks);
+      return;
+    }
+    Ct x, xc, ua, ub;
+    const Ct *in = &input;
+    if (!plan.cts.empty()) {
+      RunGroups(x, input, plan.cts, evk_map, min_ks);
+      in = &x;
+    }
+    this->HConj(xc, *in, evk_map.GetConjugationKey());
+    plan.cts_last[0].Evaluate(GetContext(), ua, *in, evk_map, min_ks);
+    plan.cts_last[1].Evaluate(GetContext(), ub, xc, evk_map, min_ks);
+    this->Add(res, ua, ub);
+    res.SetNumSlots(2 * input.GetNumSlots());
   }
   void SlotToCoeff(Ct &res, const Ct &input, const EvkMap<word> &evk_map, bool min_ks = false) const {
-    RunGroups(res, input, PlanFor(input.GetNumSlots()).stc, evk_map, min_ks);
+    const int half = this->param_.degree_ / 2;
+    // a merged input carries twice the plan's slot count
+    auto it = eval_fft_.find(input.GetNumSlots());
+    const bool direct = it != eval_fft_.end() && !it->second.merged;
+    const int num_slots = direct ? input.GetNumSlots() : input.GetNumSlots() / 2;
+    AssertTrue(num_slots <= half, "SlotToCoeff: too many slots");
+    RunGroups(res, input, PlanFor(num_slots).stc, evk_map, min_ks);
+    res.SetNumSlots(num_slots);
   }
   void EvaluateMod(Ct &res, const Ct &input, const Evk &mult_key) const {
     AssertTrue(eval_mod_ != nullptr, "EvalMod not prepared");
@@ -878,19 +941,25 @@ class BootContext : public Context<word> {
     Ct slots;
     CoeffToSlot(slots, raised, evk_map, min_ks);
     phase("CoeffToSlot");
-    // 3. real and imaginary parts, each through EvalMod
-    Ct conj, re, im;
-    this->HConj(conj, slots, evk_map.GetConjugationKey());
-    this->Add(re, slots, conj);
-    this->Sub(im, conj, slots);
-    this->MultImaginaryUnit(im, im);
-    phase("conjugate split");
-    Ct re_mod, im_mod;
-    EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
-    EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
-    this->MultImaginaryUnit(im_mod, im_mod);
-    this->Add(re_mod, re_mod, im_mod);
-    phase("EvalMod x2");
+    // 3. real and imaginary parts through EvalMod: side by side in one
+    // ciphertext when there is room, else one after the other
+    Ct re_mod;
+    if (PlanFor(num_slots).merged) {
+      EvaluateMod(re_mod, slots, evk_map.GetMultiplicationKey());
+      phase("EvalMod");
+    } else {
+      Ct conj, re, im, im_mod;
+      this->HConj(conj, slots, evk_map.GetConjugationKey());
+      this->Add(re, slots, conj);
+      this->Sub(im, conj, slots);
+      this->MultImaginaryUnit(im, im);
+      phase("conjugate split");
+      EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
+      EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
+      this->MultImaginaryUnit(im_mod, im_mod);
+      this->Add(re_mod, re_mod, im_mod);
+      phase("EvalMod x2");
+    }
     // 4. slots to coefficients
     SlotToCoeff(res, re_mod, evk_map, min_ks);
     res.SetNumSlots(input.GetNumSlots());
@@ -940,7 +1009,8 @@ class BootContext : public Context<word> {
   int log_scaleup_ = 0;
   std::unique_ptr<EvalMod<word>> eval_mod_;
   struct FftPlan {
-    std::vector<LinearTransform<word>> cts, stc;
+    bool merged = false;  // fewer than degree / 2 slots: one EvalMod for both parts
+    std::vector<LinearTransform<word>> cts, cts_last, stc;
   };
   const FftPlan &PlanFor(int num_slots) const {
     auto it = eval_fft_.find(num_slots);

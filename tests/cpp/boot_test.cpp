@@ -269,15 +269,18 @@ int main(int argc, char **argv) {
       Ct ct, out;
       ctx->encoder().Encode(pt, 0, param->GetScale(0), m, 0);
       ui.Encrypt(ct, pt);
-      ctx->Synchronize();
-      auto a = std::chrono::steady_clock::now();
-      boot_ctx->Boot(out, ct, ui.GetEvkMap());
-      ctx->Synchronize();
-      const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count();
+      double ms = 1e30;
+      for (int it = 0; it < 3; it++) {  // the first call also grows the workspace
+        ctx->Synchronize();
+        auto a = std::chrono::steady_clock::now();
+        boot_ctx->Boot(out, ct, ui.GetEvkMap());
+        ctx->Synchronize();
+        ms = std::min(ms, std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - a).count());
+      }
       Pt dec;
       ui.Decrypt(dec, out);
       ctx->encoder().Decode(got, dec);
-      std::cout << "       " << ns << " slots: " << req.size() << " rotation keys requested, first Boot " << ms
+      std::cout << "       " << ns << " slots: " << req.size() << " rotation keys requested, best of 3: " << ms
                 << " ms, level " << param->NPToLevel(out.GetNP()) << std::endl;
       // With few slots the plaintext coefficients are large (about 1/sqrt(slots)),
       // and the cubic term of sin(2 pi x)/2 pi, 6.6 * (coefficient / 35)^3 * 35 per
