@@ -618,6 +618,13 @@ class EvalSpecialFFT {
   }
 };
 
+// How Boot finishes (reference include/extension/BootContext.h:16-20).
+enum class BootVariant {
+  kNormal,             // complex bootstrapping
+  kImaginaryRemoving,  // SlotToCoeff carries a factor 1/2 and Boot ends with res + conj(res)
+  kMergeTwoReal        // SlotToCoeff carries the factor 1/2; the caller combines two results
+};
+
 // ------------------------------------------------------------ BootContext
 // A Context that can also refresh a ciphertext (reference
 // include/extension/BootContext.h, src/extension/BootContext.cpp).
@@ -649,7 +656,7 @@ class BootContext : public Context<word> {
   // degree / 2). Fewer slots mean a plaintext in the subring of X^(degree/2/num_slots):
   // the transforms have num_slots-periodic diagonals, and Boot projects the
   // raised ciphertext onto the subring first (Trace).
-  void PrepareEvalSpecialFFT(int num_slots) {
+  void PrepareEvalSpecialFFT(int num_slots, BootVariant variant = BootVariant::kNormal) {
     const auto &param = this->param_;
     const int half = param.degree_ / 2;
     AssertTrue(num_slots >= 2 && num_slots <= half && (num_slots & (num_slots - 1)) == 0,
@@ -659,6 +666,7 @@ class BootContext : public Context<word> {
       return;
     }
     FftPlan &plan = eval_fft_[num_slots];
+    plan.variant = variant;
     const int n = num_slots;
     // CoeffToSlot: the raised (and traced) ciphertext holds (half / n) * q0 * u(Y),
     // Y = X^(half/n); read at scale q0 its n distinct slots are
@@ -703,8 +711,9 @@ class BootContext : public Context<word> {
     // plaintext p = scale0' * m; the forward transform and q0 / scale0' give m.
     // The scale drops from EvalMod's to the end level's in equal steps, which
     // keeps every diagonal plaintext well above the rounding of its encoding.
-    auto stc = EvalSpecialFFT<word>::Groups(param, n, false, boot_param_.num_stc_levels_,
-                                            q0_prod_ / boot_input_scale_);
+    auto stc = EvalSpecialFFT<word>::Groups(
+        param, n, false, boot_param_.num_stc_levels_,
+        (q0_prod_ / boot_input_scale_) * (variant == BootVariant::kNormal ? 1.0 : 0.5));
     if (plan.merged) {
       StripedMatrix tiled(2 * n), back(2 * n);
       for (auto &[k, d] : stc[0].diag) {
@@ -962,6 +971,8 @@ class BootContext : public Context<word> {
     }
     // 4. slots to coefficients
     SlotToCoeff(res, re_mod, evk_map, min_ks);
+    if (PlanFor(num_slots).variant == BootVariant::kImaginaryRemoving)
+      this->HConjAdd(res, res, res, evk_map.GetConjugationKey());  // res + conj(res): the real part, twice the half
     res.SetNumSlots(input.GetNumSlots());
     phase("SlotToCoeff");
   }
@@ -1010,6 +1021,7 @@ class BootContext : public Context<word> {
   std::unique_ptr<EvalMod<word>> eval_mod_;
   struct FftPlan {
     bool merged = false;  // fewer than degree / 2 slots: one EvalMod for both parts
+    BootVariant variant = BootVariant::kNormal;
     std::vector<LinearTransform<word>> cts, cts_last, stc;
   };
   const FftPlan &PlanFor(int num_slots) const {

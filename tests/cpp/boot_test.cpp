@@ -287,6 +287,25 @@ int main(int argc, char **argv) {
       // coefficient at this message ratio, is no longer below 1e-3 on the slots.
       Report("Boot with " + std::to_string(ns) + " slots", m, got, ns >= 64 ? 1e-3 : 5e-3);
     }
+    {
+      // imaginary-removing variant on a real message (256 slots)
+      const int ns = 1 << 8;
+      boot_ctx->PrepareEvalSpecialFFT(ns, BootVariant::kImaginaryRemoving);
+      EvkRequest req;
+      boot_ctx->AddRequiredRotations(req, ns);
+      ui.PrepareRotationKey(req);
+      Msg m(ns), got;
+      Random::SampleUniformComplex(m.data(), ns, -1.0, 1.0);
+      for (auto &x : m) x = Complex(x.real(), 0);
+      Pt pt, dec;
+      Ct ct, out;
+      ctx->encoder().Encode(pt, 0, param->GetScale(0), m, 0);
+      ui.Encrypt(ct, pt);
+      boot_ctx->Boot(out, ct, ui.GetEvkMap());
+      ui.Decrypt(dec, out);
+      ctx->encoder().Decode(got, dec);
+      Report("Boot, imaginary-removing variant, 256 real slots", m, got, 1e-3);
+    }
   }
 
   if (only.count("stages")) {
