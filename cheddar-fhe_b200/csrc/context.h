@@ -92,6 +92,7 @@ struct Context {
 
   std::vector<uint32_t> nqinv;      // -q^-1 mod 2^32, global order
   bool use_tc_bconv = true;         // base conversion on tcgen05 (CFHE_BCONV=simt disables)
+  bool use_fused_lt = true;         // baby steps and plaintext accumulation in one kernel (CFHE_LT=unfused disables)
   bool use_pdl = true;              // programmatic dependent launch between the kernels of a stream (CFHE_PDL=0 disables)
   bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
   int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out

@@ -106,8 +106,26 @@ struct PtAccumArgs {
   uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
 };
 
+// Fused baby steps of a linear transform: for every output word, every baby
+// rotation's key inner product is formed at the source index of the
+// automorphism and multiplied straight into the giant-step sums, so the
+// rotated ciphertexts are never stored.
+struct LtBabyArgs {
+  uint32_t *acc;                // [n_giant][2][ntot][N]
+  const uint32_t *mu;           // ModUp buffers of the input's a part, slot s at mu + s*ntot*N
+  const uint32_t *in_b, *in_a;  // input ciphertext on the Q limbs
+  const uint32_t *kb[kMaxBaby * kMaxDigits], *ka[kMaxBaby * kMaxDigits];  // [baby][active digit]
+  const uint32_t *pt[kMaxGiant * kMaxBaby];  // [giant][baby], null = absent
+  uint32_t galois[kMaxBaby];    // Galois element of each baby rotation (1 = identity)
+  int n_baby, n_giant, n_digits, ntot, nq;
+  uint8_t mu_slot[kMaxDigits];
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs], pm[kMaxLimbs];
+  uint8_t kpos[kMaxLimbs], own_digit[kMaxLimbs];
+};
+
 int launch_ew(const Context &ctx, int op, const EwArgs &args);
 int launch_pt_accum(const Context &ctx, const PtAccumArgs &args);
+int launch_lt_baby(const Context &ctx, const LtBabyArgs &args);
 int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);

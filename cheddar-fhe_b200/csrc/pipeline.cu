@@ -456,41 +456,89 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
   uint32_t *acc = rot + (size_t)2 * n_baby * ext;   // [n_giant][2][ntot][N]
   uint32_t *total = acc + (size_t)2 * n_giant * ext;  // [2][ntot][N]
   uint32_t *cj = total + 2 * ext;                   // [n_giant][2][nq][N]
-  // 1. baby steps on the extended basis
+  // 1 + 2. baby steps and plaintext accumulation
   if (n_baby > 1)
     if (int r = run_modup(c, lp, mu, in_a, false, y)) return r;
-  {
-    const uint32_t *src[2] = {in_b, in_a};
-    if (int r = lift_to_extended(c, lp, rot, src, 2)) return r;
-  }
   for (int i = 1; i < n_baby; i++) {
     const uint32_t g = baby_galois[i];
     if ((g & 1u) == 0 || g >= m2 || g == 1u) {
       set_error("linear transform: invalid baby-step Galois element");
       return -1;
     }
-    uint32_t *rb = rot + (size_t)(2 * i) * ext;
-    if (int r = run_inner_impl(c, lp, rb, rb + ext, mu, in_a, in_b, nullptr,
-                               baby_kb + (size_t)i * lp.beta, baby_ka + (size_t)i * lp.beta,
-                               key_main, galois_inverse(g)))
-      return r;
   }
-  // 2. plaintext accumulation per giant step
-  PtAccumArgs pa;
-  memset(&pa, 0, sizeof(pa));
-  pa.rot = rot;
-  pa.acc = acc;
-  pa.n_baby = n_baby;
-  pa.n_giant = n_giant;
-  pa.ntot = lp.ntot;
-  for (int j = 0; j < n_giant; j++)
-    for (int i = 0; i < n_baby; i++) pa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
-  for (int l = 0; l < lp.ntot; l++) {
-    pa.q[l] = c.q[lp.full_g[l]];
-    pa.nqinv[l] = c.nqinv[lp.full_g[l]];
+  if (c.use_fused_lt) {
+    // one kernel: every baby rotation is formed at the automorphism's source
+    // index and multiplied straight into the giant-step sums
+    if ((int)lp.digits.size() > kMaxDigits) {
+      set_error("linear transform: too many digits");
+      return -1;
+    }
+    if (key_main < lp.num_main || key_main > c.M) {
+      set_error("evaluation key holds fewer main limbs than the level needs");
+      return -1;
+    }
+    LtBabyArgs fa;
+    memset(&fa, 0, sizeof(fa));
+    fa.acc = acc;
+    fa.mu = mu;
+    fa.in_b = in_b;
+    fa.in_a = in_a;
+    fa.n_baby = n_baby;
+    fa.n_giant = n_giant;
+    fa.n_digits = (int)lp.digits.size();
+    fa.ntot = lp.ntot;
+    fa.nq = lp.nq;
+    for (int i = 0; i < n_baby; i++) {
+      fa.galois[i] = baby_galois[i];
+      if (i == 0) continue;
+      for (int d = 0; d < fa.n_digits; d++) {
+        const int slot = lp.digits[d].index;
+        fa.kb[i * kMaxDigits + d] = baby_kb[(size_t)i * lp.beta + slot];
+        fa.ka[i * kMaxDigits + d] = baby_ka[(size_t)i * lp.beta + slot];
+      }
+    }
+    for (int d = 0; d < fa.n_digits; d++) fa.mu_slot[d] = (uint8_t)lp.digits[d].index;
+    for (int j = 0; j < n_giant; j++)
+      for (int i = 0; i < n_baby; i++) fa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
+    const int key_ter = lp.level == -1 ? lp.num_ter : c.T;
+    for (int l = 0; l < lp.ntot; l++) {
+      const int g = lp.full_g[l];
+      fa.q[l] = c.q[g];
+      fa.nqinv[l] = c.nqinv[g];
+      fa.kpos[l] = (uint8_t)(g < c.L ? g - (c.T - key_ter) : key_ter + key_main + (g - c.L));
+      fa.own_digit[l] = l < lp.nq ? (uint8_t)lp.own_digit[l] : 255;
+      fa.pm[l] = l < lp.nq ? lp.p_mont[l] : 0;
+    }
+    if (int r = launch_lt_baby(c, fa)) return r;
+    c.mark("lt_baby");
+  } else {
+    {
+      const uint32_t *src[2] = {in_b, in_a};
+      if (int r = lift_to_extended(c, lp, rot, src, 2)) return r;
+    }
+    for (int i = 1; i < n_baby; i++) {
+      uint32_t *rb = rot + (size_t)(2 * i) * ext;
+      if (int r = run_inner_impl(c, lp, rb, rb + ext, mu, in_a, in_b, nullptr,
+                                 baby_kb + (size_t)i * lp.beta, baby_ka + (size_t)i * lp.beta,
+                                 key_main, galois_inverse(baby_galois[i])))
+        return r;
+    }
+    PtAccumArgs pa;
+    memset(&pa, 0, sizeof(pa));
+    pa.rot = rot;
+    pa.acc = acc;
+    pa.n_baby = n_baby;
+    pa.n_giant = n_giant;
+    pa.ntot = lp.ntot;
+    for (int j = 0; j < n_giant; j++)
+      for (int i = 0; i < n_baby; i++) pa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
+    for (int l = 0; l < lp.ntot; l++) {
+      pa.q[l] = c.q[lp.full_g[l]];
+      pa.nqinv[l] = c.nqinv[lp.full_g[l]];
+    }
+    if (int r = launch_pt_accum(c, pa)) return r;
+    c.mark("pt_accum");
   }
-  if (int r = launch_pt_accum(c, pa)) return r;
-  c.mark("pt_accum");
   // 3. the giant sums leave the extended basis together
   for (int p0 = 0; p0 < 2 * n_giant; p0 += kMaxBconvJobs) {
     const int cnt = std::min(kMaxBconvJobs, 2 * n_giant - p0);

@@ -85,6 +85,8 @@ int build_down(const Context &c, ConvPlan &cv, const std::vector<int> &src,
 int build_plans(Context &c) {
   const char *mode = getenv("CFHE_BCONV");
   c.use_tc_bconv = !(mode && std::string(mode) == "simt");
+  const char *lt = getenv("CFHE_LT");
+  c.use_fused_lt = !(lt && std::string(lt) == "unfused");
   const char *pdl = getenv("CFHE_PDL");
   c.use_pdl = !(pdl && std::string(pdl) == "0");
   const char *ntt_mode = getenv("CFHE_NTT");
