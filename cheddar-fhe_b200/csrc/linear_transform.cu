@@ -49,6 +49,11 @@ __global__ void __launch_bounds__(kLtThreads)
   uint64_t sb[G], sa[G];
 #pragma unroll
   for (int j = 0; j < G; j++) sb[j] = sa[j] = 0;
+  // ModUp (or own-limb) rows of this limb, one per active digit
+  const uint32_t *xrow[kMaxDigits];
+#pragma unroll
+  for (int d = 0; d < kMaxDigits; d++)
+    xrow[d] = a.own_digit[l] == d ? a.in_a + limb : a.mu + ((size_t)a.mu_slot[d] * a.ntot + l) * kN;
 #pragma unroll 1
   for (int i = 0; i < a.n_baby; i++) {
     uint32_t rb = 0, ra = 0;
@@ -61,16 +66,21 @@ __global__ void __launch_bounds__(kLtThreads)
     } else {
       const uint32_t x = source_index(y, a.galois[i]);
       uint64_t tb = 0, ta = 0;
-#pragma unroll 4
-      for (int d = 0; d < a.n_digits; d++) {
-        const uint32_t *xp = a.own_digit[l] == d ? a.in_a + limb
-                                                 : a.mu + ((size_t)a.mu_slot[d] * a.ntot + l) * kN;
-        const uint32_t xv = xp[x];
-        const uint32_t kbv = __ldcs(a.kb[i * kMaxDigits + d] + koff + x);
-        const uint32_t kav = __ldcs(a.ka[i * kMaxDigits + d] + koff + x);
-        mac_fold(tb, xv, kbv, q32);
-        mac_fold(ta, xv, kav, q32);
-      }
+      // two products per fold: 2 q^2 <= q * 2^32 for q < 2^31
+#pragma unroll
+      for (int d = 0; d < kMaxDigits; d += 2)
+        if (d < a.n_digits) {
+          const bool two = d + 1 < a.n_digits;
+          const uint32_t x0 = xrow[d][x], x1 = two ? xrow[d + 1][x] : 0u;
+          const uint32_t b0 = __ldcs(a.kb[i * kMaxDigits + d] + koff + x);
+          const uint32_t a0 = __ldcs(a.ka[i * kMaxDigits + d] + koff + x);
+          const uint32_t b1 = two ? __ldcs(a.kb[i * kMaxDigits + d + 1] + koff + x) : 0u;
+          const uint32_t a1 = two ? __ldcs(a.ka[i * kMaxDigits + d + 1] + koff + x) : 0u;
+          tb += (uint64_t)x0 * b0 + (uint64_t)x1 * b1;
+          ta += (uint64_t)x0 * a0 + (uint64_t)x1 * a1;
+          if (tb >= q32) tb -= q32;
+          if (ta >= q32) ta -= q32;
+        }
       if (on_q) mac_fold(tb, a.in_b[limb + x], pm, q32);
       rb = mont_reduce(tb, q, nq);
       ra = mont_reduce(ta, q, nq);
