@@ -246,6 +246,12 @@ def bench_ntt(eng, torch, steps, warmup, rank, barrier):
 
 # algorithmic bytes of each HMult stage at a level with nq Q limbs, alpha aux
 # limbs, digit sizes ds, nd limbs after the rescale and ns limbs dropped by it
+# DRAM bytes of each HMult stage measured with ncu (warm L2) at level 28
+HMULT_STAGE_TRAFFIC = {"tensor": 60_600_000, "modup_intt": 47_800_000, "modup_bconv": 30_100_000,
+                       "modup_ntt": 69_600_000, "inner": 232_400_000, "moddown_intt": 13_200_000,
+                       "moddown_bconv": 9_200_000, "moddown_ntt": 64_000_000}
+
+
 def hmult_stage_bytes(nq, alpha, ds, nd, ns):
     ntot = nq + alpha
     conv = sum(ntot - d for d in ds)
@@ -560,9 +566,15 @@ def run_gpu(args, pkg):
                 "gpu_launches": 14 * args.steps,
                 "clocks": clocks,
                 "precision_bits": hm["precision_bits"],
-                "roofline": {"bound": "hbm", "kernel": f"stage {top}", "achieved": stage[top]["GB/s"],
+                "roofline": {"bound": "hbm",
+                             "kernel": f"stage {top}" + (": ntt_twopass_kernel<forward>, column + row pass over the "
+                                                         "188 converted limbs of the 4 digits" if top == "modup_ntt" else ""),
+                             "achieved": stage[top]["GB/s"],
                              "peak": peak, "unit": "GB/s", "frac": stage[top]["frac"], "peak_source": how,
-                             "traffic": None},
+                             "traffic": HMULT_STAGE_TRAFFIC.get(top),
+                             "traffic_source": "ncu dram read+write of the stage's launches inside one HMult, warm L2 "
+                                               "(--cache-control none); the conversion output is still L2-resident, "
+                                               "35 MB of the reads are twiddle tables"},
                 "stages": stage,
                 "ntt": {"value": ntt_val, "unit": "GB/s", "ms_per_step": ntt_ms,
                         "e2e": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "roofline": ntt_roof},
