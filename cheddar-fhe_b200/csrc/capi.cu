@@ -618,7 +618,8 @@ int cfhe_linear_transform(cfhe_context *h, int level, int rescale, uint32_t *out
   if ((need_baby_keys && (!baby_evk_b || !baby_evk_a)) ||
       (need_giant_keys && (!giant_evk_b || !giant_evk_a)))
     return fail("null argument");
-  if (int r = ensure_workspace(h->c, linear_transform_scratch_words(*lp, n_baby, n_giant, rescale != 0)))
+  if (int r = ensure_workspace(h->c, linear_transform_scratch_words(*lp, n_baby, n_giant, rescale != 0,
+                                                              !h->c.use_fused_lt)))
     return r;
   return run_linear_transform(h->c, *lp, rescale != 0, out_b, out_a, in_b, in_a, n_baby, bg.data(),
                               baby_evk_b, baby_evk_a, n_giant, gg.data(), giant_evk_b,

@@ -399,9 +399,13 @@ static size_t lt_y_words(const LevelPlan &lp, int n_giant, bool rescale) {
   return y;
 }
 
-size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale) {
+// stored_rotations: the two-kernel form keeps every baby rotation (2 * n_baby
+// extended polynomials); the fused kernel keeps none
+size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale,
+                                      bool stored_rotations) {
+  const int rot_polys = stored_rotations ? 2 * n_baby : 0;
   return lt_y_words(lp, n_giant, rescale) +
-         ((size_t)(lp.beta + 2 * n_baby + 2 * n_giant + 2) * lp.ntot + (size_t)2 * n_giant * lp.nq) * kN;
+         ((size_t)(lp.beta + rot_polys + 2 * n_giant + 2) * lp.ntot + (size_t)2 * n_giant * lp.nq) * kN;
 }
 
 // dst = (P * src on the Q limbs, 0 on the auxiliary limbs) for `n_polys`
@@ -452,8 +456,8 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
   const size_t ext = (size_t)lp.ntot * kN, qw = (size_t)lp.nq * kN;
   uint32_t *y = scratch;
   uint32_t *mu = y + lt_y_words(lp, n_giant, rescale);
-  uint32_t *rot = mu + (size_t)lp.beta * ext;       // [n_baby][2][ntot][N]
-  uint32_t *acc = rot + (size_t)2 * n_baby * ext;   // [n_giant][2][ntot][N]
+  uint32_t *rot = mu + (size_t)lp.beta * ext;       // [n_baby][2][ntot][N], two-kernel form only
+  uint32_t *acc = rot + (c.use_fused_lt ? 0 : (size_t)2 * n_baby * ext);  // [n_giant][2][ntot][N]
   uint32_t *total = acc + (size_t)2 * n_giant * ext;  // [2][ntot][N]
   uint32_t *cj = total + 2 * ext;                   // [n_giant][2][nq][N]
   // 1 + 2. baby steps and plaintext accumulation

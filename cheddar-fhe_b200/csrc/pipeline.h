@@ -46,7 +46,8 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
                          int n_giant, const uint32_t *giant_galois,
                          const uint32_t *const *giant_kb, const uint32_t *const *giant_ka,
                          const uint32_t *const *pt, int key_main, uint32_t *scratch);
-size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale);
+size_t linear_transform_scratch_words(const LevelPlan &lp, int n_baby, int n_giant, bool rescale,
+                                      bool stored_rotations);
 int run_tensor(const Context &c, const LevelPlan &lp, uint32_t *d0,
                uint32_t *d1, uint32_t *d2, const uint32_t *b1,
                const uint32_t *a1, const uint32_t *b2, const uint32_t *a2);
