@@ -477,7 +477,7 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
       set_error("linear transform: too many digits");
       return -1;
     }
-    if (key_main < lp.num_main || key_main > c.M) {
+    if (n_baby > 1 && (key_main < lp.num_main || key_main > c.M)) {
       set_error("evaluation key holds fewer main limbs than the level needs");
       return -1;
     }
@@ -509,7 +509,7 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
       const int g = lp.full_g[l];
       fa.q[l] = c.q[g];
       fa.nqinv[l] = c.nqinv[g];
-      fa.kpos[l] = (uint8_t)(g < c.L ? g - (c.T - key_ter) : key_ter + key_main + (g - c.L));
+      fa.kpos[l] = (uint8_t)(g < c.L ? g - (c.T - key_ter) : key_ter + (n_baby > 1 ? key_main : 0) + (g - c.L));
       fa.own_digit[l] = l < lp.nq ? (uint8_t)lp.own_digit[l] : 255;
       fa.pm[l] = l < lp.nq ? lp.p_mont[l] : 0;
     }
