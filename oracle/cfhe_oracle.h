@@ -10,10 +10,13 @@
  * Cheddar reference (file:line cited at each function, relative to the
  * reference project root). The reference ships no golden vectors or known-
  * answer tests for this path (its tests are randomised round trips with a
- * 1e-3 tolerance, unittest/Testbed.h:93), so limb-level parity of this model
- * with the reference is pinned only by algebraic identities and by the
- * reference's own CUDA build when that is run on the same buffers; see the
- * tests for what is checked.
+ * 1e-3 tolerance, unittest/Testbed.h:93). Limb-level parity of this model
+ * with the reference is pinned by the reference itself: its CUDA sources are
+ * compiled unmodified into oracle/_ref/libcheddar_ref.so (Makefile target
+ * `ref`), and tests/test_reference_gpu.py feeds the same device buffers to
+ * that library, to the engine and to this model and compares every word
+ * (NTT, INTT, ModUp, the three ModDown forms, HMult). Algebraic identities on
+ * a toy ring (tests/test_oracle_cpu.py) pin it where no GPU is present.
  *
  * Conventions (reference include/core/Parameter.h:199-206,
  * src/core/Parameter.cu:104-105):
