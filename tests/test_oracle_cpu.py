@@ -223,3 +223,70 @@ def test_modup_to_max_is_the_centred_lift(oracle40):
     one = o.modup_to_max(src[:1], base[:1], dst)
     for m, g in enumerate(dst):
         assert int(one[m, 3]) == int(src[0, 3]) % int(o.primes[g])
+
+
+# ---------------------------------------------------------------------------
+# Golden vectors produced by the reference's own CUDA library
+# ---------------------------------------------------------------------------
+def _golden():
+    import importlib.util
+    import json
+    import os
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with open(os.path.join(here, "reference_digests.json")) as f:
+        return mod, json.load(f)["cases"]
+
+
+def _matches(case, arr):
+    import hashlib
+    a = np.ascontiguousarray(arr, dtype=np.uint32)
+    assert list(a.shape) == case["shape"]
+    assert a.reshape(-1, a.shape[-1])[:, :len(case["head"][0])].tolist() == case["head"]
+    assert hashlib.sha256(a.tobytes()).hexdigest() == case["sha256"]
+
+
+def test_oracle_ntt_equals_reference_golden(oracle40):
+    """NTT / INTT words of the golden model against digests of the reference's
+    own kernels (tests/golden/make_golden.py generated them on a B200)."""
+    g_mod, cases = _golden()
+    o = oracle40
+    for case in g_mod.NTT_CASES:
+        g = g_mod.ntt_limbs(case)
+        a = g_mod.rand_limbs(np.random.default_rng(9000 + sum(case)), o.primes, g)
+        for mont in (False, True):
+            _matches(cases[f"ntt{case}_inv0_mont{int(mont)}"], o.ntt(a, g, mont))
+            # the reference's INTT with montgomery conversion leaves M-form
+            _matches(cases[f"ntt{case}_inv1_mont{int(mont)}"], o.intt(a, g, mont_keep=not mont))
+
+
+def test_oracle_modswitch_equals_reference_golden(oracle40):
+    g_mod, cases = _golden()
+    o = oracle40
+    for level in g_mod.MODUP_LEVELS:
+        a = g_mod.rand_limbs(np.random.default_rng(9100 + level), o.primes, o.level_limbs(level))
+        _matches(cases[f"modup_level{level}"], o.modup(level, a))
+    for level in g_mod.MODDOWN_LEVELS:
+        full = o.level_limbs(level, 12)
+        a = g_mod.rand_limbs(np.random.default_rng(9200 + level), o.primes, full)
+        nq = len(full) - 12
+        for kind in (0, 1, 2):
+            x = a if kind != 1 else np.ascontiguousarray(a[:nq])
+            _matches(cases[f"moddown_level{level}_kind{kind}"], o.moddown(level, kind, x))
+
+
+def test_oracle_hmult_equals_reference_golden(oracle40):
+    g_mod, cases = _golden()
+    o = oracle40
+    kg = list(range(47)) + [47 + a for a in range(12)]
+    for level, rescale in g_mod.HMULT_CASES:
+        rng = np.random.default_rng(9300 + level)
+        g = o.level_limbs(level)
+        ins = [g_mod.rand_limbs(rng, o.primes, g) for _ in range(4)]
+        beta = o.beta(28)
+        kb = [g_mod.rand_limbs(rng, o.primes, kg) for _ in range(beta)]
+        ka = [g_mod.rand_limbs(rng, o.primes, kg) for _ in range(beta)]
+        b, a = o.hmult(level, *ins, kb, ka, 43, rescale)
+        _matches(cases[f"hmult_level{level}_rescale{int(rescale)}"], np.stack([b, a]))
