@@ -532,12 +532,13 @@ def run_gpu(args, pkg):
         peak, how = measured_peaks()
         ntt_val = world * NTT_BYTES_PER_STEP / (ntt_ms * 1e-3) / 1e9
         ntt_ach = NTT_BYTES_PER_LAUNCH / (fwd_ms * 1e-3) / 1e9
-        ntt_roof = {"bound": "hbm", "kernel": "ntt_twopass_kernel<forward> (5 chunks x 2 passes = one batch)",
+        ntt_roof = {"bound": "hbm", "kernel": "ntt_twopass_kernel<forward> (4 chunks x 2 passes = one batch)",
                     "achieved": ntt_ach,
                     "peak": peak, "unit": "GB/s", "frac": ntt_ach / peak, "peak_source": how,
-                    "traffic": 437_000_000,
-                    "traffic_source": "ncu dram read+write summed over the 10 launches of one forward batch, "
-                                      "warm L2 (269 MB read incl. twiddle tables once per chunk, 168 MB written)",
+                    "traffic": 558_000_000,
+                    "traffic_source": "ncu dram read+write summed over the 8 launches of one forward batch, warm L2 "
+                                      "(297 MB read incl. twiddle tables once per chunk, 261 MB written; 48 MiB "
+                                      "chunks keep about 60 % of a chunk in L2 between its two passes)",
                     "fwd_ms": fwd_ms, "inv_ms": inv_ms,
                     "inv_achieved": NTT_BYTES_PER_LAUNCH / (inv_ms * 1e-3) / 1e9}
         if hm:
@@ -591,7 +592,7 @@ def run_gpu(args, pkg):
                            "parallelism": f"independent batches x{world}"},
                 "e2e": {"value": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "unit": "GB/s",
                         "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
-                "gpu_launches": 20 * args.steps, "clocks": clocks, "roofline": ntt_roof,
+                "gpu_launches": 16 * args.steps, "clocks": clocks, "roofline": ntt_roof,
             }
         if hoist:
             peak_, _ = measured_peaks()
