@@ -385,6 +385,7 @@ int run_hoisted_rotations(Context &c, const LevelPlan &lp, uint32_t *out,
 // ---------------------------------------------------------------------------
 // Baby-step/giant-step linear transform with both hoistings:
 //   out = Down( sum_j rot_Gj( Down( sum_i pt[j][i] (*) rot_bi(in) ) ) )
+// (the unrotated giant step skips its inner Down)
 // * the baby rotations share one ModUp and stay on the extended basis (no
 //   ModDown per rotation); the unrotated input joins them as P * in;
 // * the plaintexts, given on the extended basis, are accumulated per giant
@@ -460,6 +461,25 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
   uint32_t *acc = rot + (c.use_fused_lt ? 0 : (size_t)2 * n_baby * ext);  // [n_giant][2][ntot][N]
   uint32_t *total = acc + (size_t)2 * n_giant * ext;  // [2][ntot][N]
   uint32_t *cj = total + 2 * ext;                   // [n_giant][2][nq][N]
+  // giant steps in working order: the rotating ones first, the unrotated one
+  // (if any) last, so that its extended-basis sum doubles as the accumulator
+  int order[kMaxGiant], n_rot = 0, plain = -1;
+  for (int j = 0; j < n_giant; j++) {
+    const uint32_t g = giant_galois[j];
+    if (g == 1u) {
+      if (plain >= 0) {
+        set_error("linear transform: more than one unrotated giant step");
+        return -1;
+      }
+      plain = j;
+    } else if ((g & 1u) == 0 || g >= m2) {
+      set_error("linear transform: invalid giant-step Galois element");
+      return -1;
+    } else {
+      order[n_rot++] = j;
+    }
+  }
+  if (plain >= 0) order[n_rot] = plain;
   // 1 + 2. baby steps and plaintext accumulation
   if (n_baby > 1)
     if (int r = run_modup(c, lp, mu, in_a, false, y)) return r;
@@ -503,7 +523,7 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
     }
     for (int d = 0; d < fa.n_digits; d++) fa.mu_slot[d] = (uint8_t)lp.digits[d].index;
     for (int j = 0; j < n_giant; j++)
-      for (int i = 0; i < n_baby; i++) fa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
+      for (int i = 0; i < n_baby; i++) fa.pt[j * kMaxBaby + i] = pt[(size_t)order[j] * n_baby + i];
     const int key_ter = lp.level == -1 ? lp.num_ter : c.T;
     for (int l = 0; l < lp.ntot; l++) {
       const int g = lp.full_g[l];
@@ -535,7 +555,7 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
     pa.n_giant = n_giant;
     pa.ntot = lp.ntot;
     for (int j = 0; j < n_giant; j++)
-      for (int i = 0; i < n_baby; i++) pa.pt[j * kMaxBaby + i] = pt[(size_t)j * n_baby + i];
+      for (int i = 0; i < n_baby; i++) pa.pt[j * kMaxBaby + i] = pt[(size_t)order[j] * n_baby + i];
     for (int l = 0; l < lp.ntot; l++) {
       pa.q[l] = c.q[lp.full_g[l]];
       pa.nqinv[l] = c.nqinv[lp.full_g[l]];
@@ -543,41 +563,26 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
     if (int r = launch_pt_accum(c, pa)) return r;
     c.mark("pt_accum");
   }
-  // 3. the giant sums leave the extended basis together
-  for (int p0 = 0; p0 < 2 * n_giant; p0 += kMaxBconvJobs) {
-    const int cnt = std::min(kMaxBconvJobs, 2 * n_giant - p0);
+  // 3. the sums of the rotating giant steps leave the extended basis together;
+  // the unrotated one stays: it is already what the accumulator must start from
+  for (int p0 = 0; p0 < 2 * n_rot; p0 += kMaxBconvJobs) {
+    const int cnt = std::min(kMaxBconvJobs, 2 * n_rot - p0);
     if (int r = run_moddown(c, lp.down[0], cj + (size_t)p0 * qw, acc + (size_t)p0 * ext, cnt,
                             (long long)qw, (long long)ext, y))
       return r;
   }
   // 4. giant rotations accumulate on the extended basis
-  int plain = -1;
-  for (int j = 0; j < n_giant; j++)
-    if (giant_galois[j] == 1u) {
-      if (plain >= 0) {
-        set_error("linear transform: more than one unrotated giant step");
-        return -1;
-      }
-      plain = j;
-    }
-  if (plain >= 0) {
-    const uint32_t *src[2] = {cj + (size_t)(2 * plain) * qw, cj + (size_t)(2 * plain + 1) * qw};
-    if (int r = lift_to_extended(c, lp, total, src, 2)) return r;
-  } else {
+  if (plain >= 0)
+    total = acc + (size_t)2 * n_rot * ext;
+  else
     CFHE_CUDA(cudaMemsetAsync(total, 0, 2 * ext * sizeof(uint32_t), c.stream));
-  }
-  for (int j = 0; j < n_giant; j++) {
-    if (j == plain) continue;
-    const uint32_t g = giant_galois[j];
-    if ((g & 1u) == 0 || g >= m2) {
-      set_error("linear transform: invalid giant-step Galois element");
-      return -1;
-    }
-    const uint32_t *cb = cj + (size_t)(2 * j) * qw, *ca = cb + qw;
+  for (int jj = 0; jj < n_rot; jj++) {
+    const int j = order[jj];
+    const uint32_t *cb = cj + (size_t)(2 * jj) * qw, *ca = cb + qw;
     if (int r = run_modup(c, lp, mu, ca, false, y)) return r;
     if (int r = run_inner_impl(c, lp, total, total + ext, mu, ca, cb, nullptr,
                                giant_kb + (size_t)j * lp.beta, giant_ka + (size_t)j * lp.beta,
-                               key_main, galois_inverse(g), true))
+                               key_main, galois_inverse(giant_galois[j]), true))
       return r;
   }
   // 5. one ModDown (with the rescale) for the whole transform

@@ -229,7 +229,9 @@ CFHE_API int cfhe_hoisted_rotations(cfhe_context *ctx, int level, uint32_t *out,
  * The baby rotations share one ModUp and stay on the extended basis; the
  * plaintexts are multiplied there; every giant rotation is a key switch added
  * into one extended-basis accumulator, so one ModDown ends the call, fused
- * with the rescale to level-1 when rescale != 0.
+ * with the rescale to level-1 when rescale != 0. The sum of the unrotated
+ * giant step (giant_rot == 0) skips its inner Down: it starts the accumulator
+ * as it is.
  * baby_rot[0] must be 0 (the input itself); the other baby_rot[i] and the
  * non-zero giant_rot[j] are slot distances in (0, N/2); at most one giant_rot
  * may be 0; n_baby, n_giant <= 16. Keys as for cfhe_hoisted_rotations: HOST

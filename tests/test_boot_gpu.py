@@ -109,10 +109,13 @@ def test_linear_transform_equals_composition(engine40, oracle40, level, baby_rot
             for k in range(2):
                 e.binary_(3, tmp, rots[i][k], pts[j][i], full)
                 e.binary_(0, acc[k], acc[k], tmp, full)
-        cj = [e.empty(nq, n), e.empty(nq, n)]
-        for k in range(2):
-            e.moddown_(level, 0, cj[k], acc[k])
-        part = lift(*cj) if G == 0 else switched(cj[0], cj[1], giant_keys[j], G)
+        if G == 0:
+            part = acc  # the unrotated sum stays on the extended basis
+        else:
+            cj = [e.empty(nq, n), e.empty(nq, n)]
+            for k in range(2):
+                e.moddown_(level, 0, cj[k], acc[k])
+            part = switched(cj[0], cj[1], giant_keys[j], G)
         for k in range(2):
             e.binary_(0, total[k], total[k], part[k], full)
     ref_b, ref_a = t.empty_like(out_b), t.empty_like(out_a)
