@@ -563,12 +563,14 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
     if (int r = launch_pt_accum(c, pa)) return r;
     c.mark("pt_accum");
   }
-  // 3. the sums of the rotating giant steps leave the extended basis together;
-  // the unrotated one stays: it is already what the accumulator must start from
-  for (int p0 = 0; p0 < 2 * n_rot; p0 += kMaxBconvJobs) {
-    const int cnt = std::min(kMaxBconvJobs, 2 * n_rot - p0);
-    if (int r = run_moddown(c, lp.down[0], cj + (size_t)p0 * qw, acc + (size_t)p0 * ext, cnt,
-                            (long long)qw, (long long)ext, y))
+  // 3. Of the rotating giant steps only the a parts leave the extended basis
+  // (they are what gets decomposed and switched); the b parts are rotated where
+  // they are and added to the accumulator. The unrotated step stays entirely:
+  // it is already what the accumulator must start from.
+  for (int p0 = 0; p0 < n_rot; p0 += kMaxBconvJobs) {
+    const int cnt = std::min(kMaxBconvJobs, n_rot - p0);
+    if (int r = run_moddown(c, lp.down[0], cj + (size_t)p0 * qw, acc + (size_t)(2 * p0 + 1) * ext, cnt,
+                            (long long)qw, (long long)(2 * ext), y))
       return r;
   }
   // 4. giant rotations accumulate on the extended basis
@@ -578,11 +580,24 @@ int run_linear_transform(Context &c, const LevelPlan &lp, bool rescale, uint32_t
     CFHE_CUDA(cudaMemsetAsync(total, 0, 2 * ext * sizeof(uint32_t), c.stream));
   for (int jj = 0; jj < n_rot; jj++) {
     const int j = order[jj];
-    const uint32_t *cb = cj + (size_t)(2 * jj) * qw, *ca = cb + qw;
+    const uint32_t g = giant_galois[j];
+    {
+      EwArgs e;
+      e.n_rows = lp.ntot;
+      const uint32_t *sb = acc + (size_t)(2 * jj) * ext;
+      for (int l = 0; l < lp.ntot; l++) {
+        const int gi = lp.full_g[l];
+        const size_t o = (size_t)l * kN;
+        e.rows[l] = EwRow{total + o, sb + o, total + o, c.q[gi], c.nqinv[gi], 0u, 0u};
+      }
+      if (int r = launch_permute(c, e, g)) return r;
+      c.mark("permute");
+    }
+    const uint32_t *ca = cj + (size_t)jj * qw;
     if (int r = run_modup(c, lp, mu, ca, false, y)) return r;
-    if (int r = run_inner_impl(c, lp, total, total + ext, mu, ca, cb, nullptr,
+    if (int r = run_inner_impl(c, lp, total, total + ext, mu, ca, nullptr, nullptr,
                                giant_kb + (size_t)j * lp.beta, giant_ka + (size_t)j * lp.beta,
-                               key_main, galois_inverse(giant_galois[j]), true))
+                               key_main, galois_inverse(g), true))
       return r;
   }
   // 5. one ModDown (with the rescale) for the whole transform

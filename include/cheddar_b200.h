@@ -231,7 +231,8 @@ CFHE_API int cfhe_hoisted_rotations(cfhe_context *ctx, int level, uint32_t *out,
  * into one extended-basis accumulator, so one ModDown ends the call, fused
  * with the rescale to level-1 when rescale != 0. The sum of the unrotated
  * giant step (giant_rot == 0) skips its inner Down: it starts the accumulator
- * as it is.
+ * as it is; of a rotating giant step only the a part goes through Down and the
+ * key switch, its b part is rotated on the extended basis.
  * baby_rot[0] must be 0 (the input itself); the other baby_rot[i] and the
  * non-zero giant_rot[j] are slot distances in (0, N/2); at most one giant_rot
  * may be 0; n_baby, n_giant <= 16. Keys as for cfhe_hoisted_rotations: HOST

@@ -112,10 +112,14 @@ def test_linear_transform_equals_composition(engine40, oracle40, level, baby_rot
         if G == 0:
             part = acc  # the unrotated sum stays on the extended basis
         else:
-            cj = [e.empty(nq, n), e.empty(nq, n)]
-            for k in range(2):
-                e.moddown_(level, 0, cj[k], acc[k])
-            part = switched(cj[0], cj[1], giant_keys[j], G)
+            # only the a part leaves the extended basis and is switched; the b
+            # part is rotated where it is
+            ca = e.empty(nq, n)
+            e.moddown_(level, 0, ca, acc[1])
+            part = switched(None, ca, giant_keys[j], G)
+            pb = e.empty(ntot, n)
+            e.permute_(pb, acc[0], None, e.galois(G), full)
+            e.binary_(0, part[0], part[0], pb, full)
         for k in range(2):
             e.binary_(0, total[k], total[k], part[k], full)
     ref_b, ref_a = t.empty_like(out_b), t.empty_like(out_a)
