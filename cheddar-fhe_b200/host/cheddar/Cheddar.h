@@ -1027,8 +1027,11 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     }
     res.SetNumSlots(a.GetNumSlots());
     res.SetScale(a.GetScale() / param_.GetRescalePrimeProd(level));
-    CheckAbi(cfhe_moddown(h_, level, 1, res.bx_.data(), a.bx_.data(), 1, 0, 0));
-    CheckAbi(cfhe_moddown(h_, level, 1, res.ax_.data(), a.ax_.data(), 1, 0, 0));
+    // b and a in one call (the polynomials of a container are separate
+    // allocations, so the strides are their distances)
+    CheckAbi(cfhe_moddown(h_, level, 1, res.bx_.data(), a.bx_.data(), 2,
+                          (long long)(res.ax_.data() - res.bx_.data()),
+                          (long long)(a.ax_.data() - a.bx_.data())));
     if (a.HasRx()) CheckAbi(cfhe_moddown(h_, level, 1, res.rx_.data(), a.rx_.data(), 1, 0, 0));
   }
 
@@ -1346,13 +1349,9 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     CheckAbi(cfhe_evk_inner(h_, level, acc.data(), acc.data() + (size_t)ntot * n, mu.data(),
                             a.bx_.data(), a.ax_.data(), kb.data(), ka.data(), key.GetNP().num_main_));
     Ct out(param_.LevelToNP(rescale ? level - 1 : level));
-    const int nd = out.GetNP().GetNumQ();
-    DeviceVector<word> both((size_t)2 * nd * n);
-    CheckAbi(cfhe_moddown(h_, level, rescale ? 2 : 0, both.data(), acc.data(), 2, (long long)nd * n,
-                          (long long)ntot * n));
-    std::vector<word> zero(nd, 0);
-    ConstKernel(0, out.bx_.data(), both.data(), nullptr, zero, out.GetNP());
-    ConstKernel(0, out.ax_.data(), both.data() + (size_t)nd * n, nullptr, zero, out.GetNP());
+    // both polynomials in one call, written straight into the result's buffers
+    CheckAbi(cfhe_moddown(h_, level, rescale ? 2 : 0, out.bx_.data(), acc.data(), 2,
+                          (long long)(out.ax_.data() - out.bx_.data()), (long long)ntot * n));
     double scale = a.GetScale();
     if (rescale) scale /= param_.GetRescalePrimeProd(level);
     out.SetScale(scale);
