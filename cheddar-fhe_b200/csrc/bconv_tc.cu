@@ -263,8 +263,8 @@ __global__ void __launch_bounds__(kTcThreads)
                  : "memory");
 }
 
-// 6 KB of table slice + 12 KB of operand tile; eight CTAs of 64 tensor-memory
-// columns each can share an SM
+// 6 KB of table slice + 12 KB of operand tile; tensor memory (64 columns per
+// CTA) allows eight CTAs per SM, the 72 registers per thread allow seven
 constexpr int kTcSmemBytes = kTcMaxK * kTcSliceN + kTcMaxK * kTcTile + 64 + 16 * (kTcSliceN / 4);
 
 }  // namespace
@@ -318,7 +318,7 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
     configured = true;
   }
   if (a.n_jobs <= 0) return 0;
-  // work units = (job, slice of 16 destination limbs); about eight CTAs per SM
+  // work units = (job, slice of 16 destination limbs); the grid holds about eight CTAs per SM
   BconvTcArgs b = a;
   b.n_units = 0;
   for (int i = 0; i < a.n_jobs; i++)

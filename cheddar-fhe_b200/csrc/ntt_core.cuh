@@ -1,6 +1,9 @@
-// Single-pass negacyclic NTT / INTT for N = 2^16, written as per-thread phase
-// functions so that the same index and arithmetic code runs inside the CUDA
-// kernels (ntt.cu) and inside a host emulation used by the CPU tests.
+// Negacyclic NTT / INTT for N = 2^16: the arithmetic (Shoup twiddles, lazy
+// butterflies, radix-16 register phases) shared by the two-pass kernels
+// (ntt_twopass.cu, the default) and the single-launch cluster kernels (ntt.cu),
+// and the per-thread phase functions of the latter, written so that the same
+// index and arithmetic code also runs inside a host emulation used by the CPU
+// tests. The decomposition described next is the cluster kernels'.
 //
 // Decomposition: a limb is a 256 x 256 matrix (row-major, row = index >> 8).
 // A thread-block cluster of 8 CTAs owns one limb of one polynomial.
