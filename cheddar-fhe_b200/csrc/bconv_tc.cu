@@ -27,6 +27,7 @@
 //
 // Waits on the MMA completion barrier are bounded; on a timeout the kernel
 // raises a flag in global memory, frees its tensor memory and returns.
+#include <stdlib.h>
 #include <string.h>
 
 #include "context.h"
@@ -38,10 +39,18 @@ namespace cfhe {
 namespace {
 
 constexpr int kTcThreads = 128;  // one thread per coefficient of the tile
+// A CTA is kTcGroups independent groups of 128 threads, one CTA per SM: each
+// group owns an operand tile, a table slice, a completion barrier and 64
+// columns of the CTA's tensor memory and walks its own tiles. (Measured: an SM
+// admits a new CTA of the one-group form of this kernel only about every 2 us,
+// so a grid of a thousand small CTAs spent two thirds of its time ramping up.)
+constexpr int kTcGroups = 7;
+constexpr int kTcCtaThreads = kTcThreads * kTcGroups;
 constexpr int kTcTile = 128;
 constexpr int kTcMaxK = 96;      // bytes of K per tile row: 4 * (20 + 1) padded to 32
 constexpr int kTcSliceN = 64;    // accumulator columns per CTA: 16 destination limbs
-constexpr int kTmemCols = 64;
+constexpr int kTmemCols = 64;        // per group
+constexpr int kTmemAlloc = 512;      // per CTA: power of two >= kTcGroups * kTmemCols
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -57,6 +66,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
   d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
   d |= (uint64_t)1 << 46;  // descriptor version of this architecture
   return d;
+}
+
+// barrier among the 128 threads of one group (id 0 is __syncthreads)
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kTcThreads) : "memory");
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -94,10 +108,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
 template <int KCH>
 __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob &j, uint8_t *sA,
                                          uint8_t *sB, uint64_t *bar, const uint4 *s_lim,
-                                         uint32_t tmem, int m_count) {
+                                         uint32_t tmem, int m_count, int group, int first_tile,
+                                         int tile_step) {
   constexpr int kWords = 4 * KCH;
   constexpr int npad = kTcSliceN;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x & (kTcThreads - 1), warp = tid >> 5;
   // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = npad
   const uint32_t idesc = (2u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
   constexpr uint32_t a_lbo = (kTcTile / 8) * 128, b_lbo = (uint32_t)(npad / 8) * 128;
@@ -118,9 +133,9 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
     for (int k = 0; k < kWords - 1; k++)
       yn[k] = __ldg(src + (size_t)min(k, j.ns - 1) * kN + tile * kTcTile);
   };
-  if ((int)blockIdx.x < kN / kTcTile) load_tile(blockIdx.x);
+  if (first_tile < kN / kTcTile) load_tile(first_tile);
 
-  for (int tile = blockIdx.x; tile < kN / kTcTile && !failed; tile += gridDim.x) {
+  for (int tile = first_tile; tile < kN / kTcTile && !failed; tile += tile_step) {
     const int col = tile * kTcTile + tid;
     // 1. operand row: [count of residues above half their prime, residues...]
     uint32_t w[kWords];
@@ -137,7 +152,7 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
           make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    group_sync(group);
     // 2. one thread issues the MMAs of this tile and commits them to the barrier
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -158,7 +173,7 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
                    : "memory");
     }
     // the next tile's residues travel while the tensor core and the epilogue run
-    if (tile + (int)gridDim.x < kN / kTcTile) load_tile(tile + gridDim.x);
+    if (tile + tile_step < kN / kTcTile) load_tile(tile + tile_step);
     // 3. wait for the accumulators (bounded)
     uint32_t spins = 0;
     while (!mbar_try_wait(smem_u32(bar), parity)) {
@@ -199,48 +214,63 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
     }
     // accumulators and the operand tile are reused by the next tile
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    group_sync(group);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
 }
 
-__global__ void __launch_bounds__(kTcThreads)
+// shared memory of one group: table slice (6 KB), operand tile (12 KB), the
+// completion barrier and the per-limb constants, padded to a multiple of 128
+constexpr int kTcGroupSmem =
+    (kTcMaxK * kTcSliceN + kTcMaxK * kTcTile + 64 + 16 * (kTcSliceN / 4) + 127) / 128 * 128;
+// More than half of an SM's shared memory, so two of these CTAs never share an
+// SM and the tensor-memory allocation below cannot wait on another CTA.
+constexpr int kTcSmemBytes = kTcGroups * kTcGroupSmem + 16;
+static_assert(kTcSmemBytes > 116 * 1024, "one CTA per SM is what keeps the allocation from blocking");
+static_assert(kTcGroups * kTmemCols <= kTmemAlloc, "tensor memory columns");
+
+__global__ void __launch_bounds__(kTcCtaThreads, 1)
     bconv_tc_kernel(const __grid_constant__ BconvTcArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
-  const BconvTcJob &j = a.jobs[a.unit_job[blockIdx.y]];
-  const int slice = a.unit_slice[blockIdx.y];           // 16 destination limbs each
-  uint8_t *sB = smem;                                   // [K/16][8][8][16]
-  uint8_t *sA = smem + kTcMaxK * kTcSliceN;             // [K/16][16][8][16]
+  const int group = threadIdx.x / kTcThreads, tid = threadIdx.x & (kTcThreads - 1);
+  // virtual grid: per_unit groups share the tiles of one (job, slice) unit
+  const int vid = blockIdx.x * kTcGroups + group;
+  const int unit = vid / a.per_unit, first_tile = vid - unit * a.per_unit;
+  const bool active = unit < a.n_units;
+  uint8_t *gs = smem + group * kTcGroupSmem;
+  uint8_t *sB = gs;                                     // [K/16][8][8][16]
+  uint8_t *sA = gs + kTcMaxK * kTcSliceN;               // [K/16][16][8][16]
   uint64_t *bar = reinterpret_cast<uint64_t *>(sA + kTcMaxK * kTcTile);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
   // per destination limb of the slice: {q, -q^-1, word offset of the limb, in range}
   uint4 *s_lim = reinterpret_cast<uint4 *>(sA + kTcMaxK * kTcTile + 64);
-  const int tid = threadIdx.x, warp = tid >> 5;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kTcGroups * kTcGroupSmem);
+  const BconvTcJob &j = a.jobs[a.unit_job[active ? unit : 0]];
+  const int slice = a.unit_slice[active ? unit : 0];    // 16 destination limbs each
   const int kbytes = j.kpad;
   const int m_first = slice * (kTcSliceN / 4);
   const int m_count = min(j.nd - m_first, kTcSliceN / 4);
 
-  // this slice of the conversion table -> shared memory (operand layout kept)
-  {
+  if (active) {
+    // this slice of the conversion table -> shared memory (operand layout kept)
     const uint32_t src_lbo = (uint32_t)(j.npad / 8) * 128;
     for (int i = tid; i < kbytes / 16 * (kTcSliceN / 8) * 8; i += kTcThreads) {
       const int t = i / (kTcSliceN / 8 * 8), r = i % (kTcSliceN / 8 * 8);
       reinterpret_cast<uint4 *>(sB)[i] = *reinterpret_cast<const uint4 *>(
           j.btile + (size_t)t * src_lbo + (size_t)slice * (kTcSliceN / 8) * 128 + r * 16);
     }
+    if (tid < kTcSliceN / 4) {
+      const int m = m_first + tid;
+      const bool in = tid < m_count;
+      s_lim[tid] = in ? make_uint4(j.q[m], j.nqinv[m], (uint32_t)j.dst_limb[m] * kN, 1u)
+                      : make_uint4(3u, 1u, 0u, 0u);
+    }
+    if (tid == 0) mbar_init(smem_u32(bar), 1);
   }
-  if (tid < kTcSliceN / 4) {
-    const int m = m_first + tid;
-    const bool in = tid < m_count;
-    s_lim[tid] = in ? make_uint4(j.q[m], j.nqinv[m], (uint32_t)j.dst_limb[m] * kN, 1u)
-                    : make_uint4(3u, 1u, 0u, 0u);
-  }
-  if (tid == 0) mbar_init(smem_u32(bar), 1);
-  if (warp == 0) {
+  if (threadIdx.x < 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(kTmemCols)
+                 "r"(kTmemAlloc)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -248,24 +278,25 @@ __global__ void __launch_bounds__(kTcThreads)
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_cta = *tmem_slot;
+  const uint32_t tmem = tmem_cta + (uint32_t)(group * kTmemCols);
 
-  if (kbytes == 32)
-    tc_tiles<2>(a, j, sA, sB, bar, s_lim, tmem, m_count);
-  else if (kbytes == 64)
-    tc_tiles<4>(a, j, sA, sB, bar, s_lim, tmem, m_count);
-  else
-    tc_tiles<6>(a, j, sA, sB, bar, s_lim, tmem, m_count);
+  if (active) {
+    if (kbytes == 32)
+      tc_tiles<2>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
+    else if (kbytes == 64)
+      tc_tiles<4>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
+    else
+      tc_tiles<6>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
+  }
 
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+  if (threadIdx.x < 32)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_cta),
+                 "r"(kTmemAlloc)
                  : "memory");
 }
-
-// 6 KB of table slice + 12 KB of operand tile; tensor memory (64 columns per
-// CTA) allows eight CTAs per SM, the 72 registers per thread allow seven
-constexpr int kTcSmemBytes = kTcMaxK * kTcSliceN + kTcMaxK * kTcTile + 64 + 16 * (kTcSliceN / 4);
 
 }  // namespace
 
@@ -310,6 +341,7 @@ int build_tc_table(const Context &c, ConvPlan &cv) {
   return 0;
 }
 
+
 int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
   static bool configured = false;
   if (!configured) {
@@ -318,7 +350,7 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
     configured = true;
   }
   if (a.n_jobs <= 0) return 0;
-  // work units = (job, slice of 16 destination limbs); the grid holds about eight CTAs per SM
+  // work units = (job, slice of 16 destination limbs)
   BconvTcArgs b = a;
   b.n_units = 0;
   for (int i = 0; i < a.n_jobs; i++)
@@ -330,10 +362,15 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
       b.unit_job[b.n_units] = (uint8_t)i;
       b.unit_slice[b.n_units++] = (uint8_t)s;
     }
-  int per_unit = (8 * 148 + b.n_units - 1) / b.n_units;
+  // kTcGroups groups on each of the 148 SMs, shared out evenly over the units
+  const int groups = kTcGroups * 148;
+  int per_unit = groups / b.n_units;
+  if (per_unit < 1) per_unit = 1;
   if (per_unit > kN / kTcTile) per_unit = kN / kTcTile;
-  dim3 grid(per_unit, b.n_units);
-  CFHE_CUDA(launch_kernel(ctx.use_pdl, bconv_tc_kernel, grid, dim3(kTcThreads), kTcSmemBytes, ctx.stream, b));
+  b.per_unit = per_unit;
+  const int ctas = (per_unit * b.n_units + kTcGroups - 1) / kTcGroups;
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, bconv_tc_kernel, dim3(ctas), dim3(kTcCtaThreads), kTcSmemBytes,
+                          ctx.stream, b));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -23,7 +23,7 @@
 // ws = floor(w * 2^32 / q) (Shoup); a product costs one high and two low
 // 32-bit multiplies and lands in [0, 2q). Limbs whose prime is below 2^30 use
 // the lazy [0,4q) butterfly (FAST); larger primes (the auxiliary primes reach
-// 2^31) keep every value in [0,2q) and detect the wrap with a carry compare.
+// 2^31) keep every value in [0,2q) and fold the butterfly's inputs to [0,q).
 // Results are folded to the canonical [0,q) range, so they are bit-identical
 // to any other correct evaluation of the same transform.
 #pragma once
@@ -101,7 +101,8 @@ CFHE_HD void ld_tws(const Tw *p, Tw *out) {
   }
 }
 
-// (X, Y) <- (X + w Y, X - w Y). FAST: in/out [0,4q); else in/out [0,2q).
+// (X, Y) <- (X + w Y, X - w Y). FAST: in/out [0,4q); else in/out [0,2q) with
+// X and the product folded to [0,q) first, so no sum leaves 32 bits.
 template <bool FAST>
 CFHE_HD void ct_bfly(uint32_t &X, uint32_t &Y, Tw t, uint32_t q, uint32_t q2) {
   if constexpr (FAST) {
@@ -110,13 +111,19 @@ CFHE_HD void ct_bfly(uint32_t &X, uint32_t &Y, Tw t, uint32_t q, uint32_t q2) {
     X = x + p;
     Y = x - p + q2;
   } else {
-    uint32_t pm = Y * t.w - q2 - umulhi32(Y, t.ws) * q;  // product - 2q
-    uint32_t p = pm + q2;
-    uint32_t r = X + pm;  // wraps exactly when X + product >= 2q
-    uint32_t d = X - p;
-    Y = (X < p) ? d + q2 : d;
-    X = (r < X) ? r : r + q2;
+    uint32_t x = umin32(X, X - q);
+    uint32_t p = shoup_mul(Y, t, q);
+    p = umin32(p, p - q);
+    X = x + p;
+    Y = x - p + q;
   }
+}
+
+// Canonical [0,q) from the range the forward butterflies leave.
+template <bool FAST>
+CFHE_HD uint32_t ct_fold(uint32_t u, uint32_t q, uint32_t q2) {
+  if constexpr (FAST) u = umin32(u, u - q2);
+  return umin32(u, u - q);
 }
 
 // (X, Y) <- (X + Y, (X - Y) w), everything in [0,2q).
@@ -128,12 +135,10 @@ CFHE_HD void gs_bfly(uint32_t &X, uint32_t &Y, Tw t, uint32_t q, uint32_t q2) {
     X = umin32(s, s - q2);
     Y = shoup_mul(d, t, q);
   } else {
-    uint32_t ym = Y - q2;
-    uint32_t r = X + ym;  // wraps exactly when X + Y >= 2q
-    uint32_t d = X - Y;
-    if (X < Y) d += q2;
-    X = (r < X) ? r : r + q2;
-    Y = shoup_mul(d, t, q);
+    uint32_t x = umin32(X, X - q);
+    uint32_t y = umin32(Y, Y - q);
+    X = x + y;
+    Y = shoup_mul(x - y + q, t, q);
   }
 }
 
@@ -325,9 +330,7 @@ CFHE_HD void fwd_cols_b(uint32_t *v, int c, int tid, const uint32_t *xbuf,
   ct_radix16<FAST>(v, tw, 4096 + 16 * R + g, q, q2);
 #pragma unroll
   for (int k = 0; k < 16; k++) {
-    uint32_t a = v[k];
-    if constexpr (FAST) a = umin32(a, a - q2);
-    v[k] = umin32(a, a - q);
+    v[k] = ct_fold<FAST>(v[k], q, q2);
   }
 }
 

@@ -115,9 +115,7 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
   ct_radix16_pre<FAST>(v, t, q, q2);
 #pragma unroll
   for (int k = 0; k < 16; k++) {
-    uint32_t u = v[k];
-    if constexpr (FAST) u = umin32(u, u - q2);
-    v[k] = umin32(u, u - q);
+    v[k] = ct_fold<FAST>(v[k], q, q2);
   }
   const int off = R * kRowWords + 16 * g;
   if (a.ep_mode) {
