@@ -11,8 +11,8 @@
 //   A (128 x K, K = 4*(ns+1) bytes): one pseudo source "number of residues
 //      above s_k/2" in word 0, then the canonical residues y[k][c] in [0,s_k)
 //      exactly as they sit in memory (little-endian words are their own byte
-//      planes). Words past the last source hold repeats of it; their table
-//      rows are zero;
+//      planes). Words past the last source are zero, and so are their
+//      table rows;
 //   B (N x K, N = 4*nd): byte planes of the table entries pre-multiplied by
 //      2^(8i), and for the pseudo source the byte planes of -(prod s)*2^64
 //      mod p_m, which turns the canonical residues back into the centred
@@ -104,34 +104,38 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
 }
 
 // KCH = 16-byte chunks of K per operand row (K = 16 * KCH bytes, 4 * KCH words:
-// the pseudo source and up to 4 * KCH - 1 residues).
+// the pseudo source and up to 4 * KCH - 1 residues). One group walks its tiles;
+// for every tile the operand rows are built once and every slice of 16
+// destination limbs is then converted in turn on the group's 64 accumulator
+// columns.
 template <int KCH>
 __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob &j, uint8_t *sA,
-                                         uint8_t *sB, uint64_t *bar, const uint4 *s_lim,
-                                         uint32_t tmem, int m_count, int group, int first_tile,
-                                         int tile_step) {
+                                         const uint8_t *sB, uint64_t *bar, const uint4 *s_lim,
+                                         uint32_t tmem, int group, int first_tile, int tile_step) {
   constexpr int kWords = 4 * KCH;
-  constexpr int npad = kTcSliceN;
   const int tid = threadIdx.x & (kTcThreads - 1), warp = tid >> 5;
-  // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = npad
-  const uint32_t idesc = (2u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
-  constexpr uint32_t a_lbo = (kTcTile / 8) * 128, b_lbo = (uint32_t)(npad / 8) * 128;
+  // instruction descriptor: D = s32, A = B = u8, both K-major, M = 128, N = 64
+  const uint32_t idesc =
+      (2u << 4) | ((uint32_t)(kTcSliceN >> 3) << 17) | ((uint32_t)(kTcTile >> 4) << 24);
+  constexpr uint32_t a_lbo = (kTcTile / 8) * 128;
+  const uint32_t b_lbo = (uint32_t)(j.npad / 8) * 128;  // the table keeps all its slices
+  const int n_slices = j.npad / kTcSliceN;
   uint32_t parity = 0;
   bool failed = false;
 
   // Residues of one coefficient. The loads of the next tile are issued before
   // the wait on the tensor core and the epilogue of the current one and are
   // not touched until the next iteration, so their latency hides behind that
-  // work. Source k >= ns re-reads the last source (its table rows are zero).
+  // work. Words past the last source stay zero (their table rows are zero).
   uint32_t yn[kWords - 1];
   const uint32_t *src = j.src + tid;
-  // everything above (table slice, constants, tensor memory) did not depend on
+  // everything above (table, constants, tensor memory) did not depend on
   // earlier kernels; the residues do
   pdl_wait();
   auto load_tile = [&](int tile) {
+    const uint32_t *p = src + tile * kTcTile;
 #pragma unroll
-    for (int k = 0; k < kWords - 1; k++)
-      yn[k] = __ldg(src + (size_t)min(k, j.ns - 1) * kN + tile * kTcTile);
+    for (int k = 0; k < kWords - 1; k++) yn[k] = k < j.ns ? __ldg(p + (size_t)k * kN) : 0u;
   };
   if (first_tile < kN / kTcTile) load_tile(first_tile);
 
@@ -153,79 +157,89 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     group_sync(group);
-    // 2. one thread issues the MMAs of this tile and commits them to the barrier
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    for (int slice = 0; slice < n_slices && !failed; slice++) {
+      // 2. one thread issues the MMAs of this slice and commits them to the barrier
+      if (tid == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int ks = 0; ks < KCH / 2; ks++) {
-        const uint64_t da = smem_desc(smem_u32(sA) + ks * 2 * a_lbo, a_lbo, 128);
-        const uint64_t db = smem_desc(smem_u32(sB) + ks * 2 * b_lbo, b_lbo, 128);
-        const uint32_t acc = ks > 0;
+        for (int ks = 0; ks < KCH / 2; ks++) {
+          const uint64_t da = smem_desc(smem_u32(sA) + ks * 2 * a_lbo, a_lbo, 128);
+          const uint64_t db = smem_desc(
+              smem_u32(sB) + ks * 2 * b_lbo + (uint32_t)slice * (kTcSliceN / 8) * 128, b_lbo, 128);
+          const uint32_t acc = ks > 0;
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t"
+              "setp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+              ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+              : "memory");
+        }
         asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+            "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                smem_u32(bar))
             : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                       smem_u32(bar))
-                   : "memory");
-    }
-    // the next tile's residues travel while the tensor core and the epilogue run
-    if (tile + tile_step < kN / kTcTile) load_tile(tile + tile_step);
-    // 3. wait for the accumulators (bounded)
-    uint32_t spins = 0;
-    while (!mbar_try_wait(smem_u32(bar), parity)) {
-      if (++spins > kSpinLimit) {
-        failed = true;
-        break;
+      // the next tile's residues travel while the tensor core and the epilogues run
+      if (slice == 0 && tile + tile_step < kN / kTcTile) load_tile(tile + tile_step);
+      // 3. wait for the accumulators (bounded)
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(bar), parity)) {
+        if (++spins > kSpinLimit) {
+          failed = true;
+          break;
+        }
       }
-    }
-    parity ^= 1;
-    if (__any_sync(0xffffffffu, failed)) {
-      failed = true;
-      if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // 4. epilogue: 8 destination limbs (32 accumulator columns) per load
-    if (!failed) {
-      const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-      uint32_t *out = j.dst + col;
+      parity ^= 1;
+      if (__any_sync(0xffffffffu, failed)) {
+        failed = true;
+        if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // 4. epilogue: 8 destination limbs (32 accumulator columns) per load
+      if (!failed) {
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const int m_count = min(j.nd - slice * (kTcSliceN / 4), kTcSliceN / 4);
+        const uint4 *lims = s_lim + slice * (kTcSliceN / 4);
+        uint32_t *out = j.dst + col;
 #pragma unroll
-      for (int m0 = 0; m0 < kTcSliceN / 4; m0 += 8) {
-        if (m0 < m_count) {
-          uint32_t d[32];
-          tmem_ld32(lane_base + 4 * m0, d);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int m0 = 0; m0 < kTcSliceN / 4; m0 += 8) {
+          if (m0 < m_count) {
+            uint32_t d[32];
+            tmem_ld32(lane_base + 4 * m0, d);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int e = 0; e < 8; e++) {
-            const uint4 lim = s_lim[m0 + e];
-            // V = d0 + d1*2^8 + d2*2^16 + d3*2^24; every d < 2^23, so the two
-            // 16-bit-apart halves fit 32 bits and one wide multiply-add joins them
-            const uint32_t lo = d[4 * e + 1] * 256u + d[4 * e];
-            const uint32_t hi = d[4 * e + 3] * 256u + d[4 * e + 2];
-            const uint64_t v = (uint64_t)hi * 65536u + lo;
-            const uint32_t r = mont_reduce(v, lim.x, lim.y);
-            if (lim.w) out[lim.z] = r;
+            for (int e = 0; e < 8; e++) {
+              const uint4 lim = lims[m0 + e];
+              // V = d0 + d1*2^8 + d2*2^16 + d3*2^24; every d < 2^23, so the two
+              // 16-bit-apart halves fit 32 bits and one wide multiply-add joins them
+              const uint32_t lo = d[4 * e + 1] * 256u + d[4 * e];
+              const uint32_t hi = d[4 * e + 3] * 256u + d[4 * e + 2];
+              const uint64_t v = (uint64_t)hi * 65536u + lo;
+              const uint32_t r = mont_reduce(v, lim.x, lim.y);
+              if (lim.w) out[lim.z] = r;
+            }
           }
         }
       }
+      // the accumulators (and, after the last slice, the operand tile) are reused
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      group_sync(group);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
-    // accumulators and the operand tile are reused by the next tile
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    group_sync(group);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
 }
 
-// shared memory of one group: table slice (6 KB), operand tile (12 KB), the
-// completion barrier and the per-limb constants, padded to a multiple of 128
-constexpr int kTcGroupSmem =
-    (kTcMaxK * kTcSliceN + kTcMaxK * kTcTile + 64 + 16 * (kTcSliceN / 4) + 127) / 128 * 128;
-// More than half of an SM's shared memory, so two of these CTAs never share an
-// SM and the tensor-memory allocation below cannot wait on another CTA.
-constexpr int kTcSmemBytes = kTcGroups * kTcGroupSmem + 16;
+constexpr int kTcMaxSlices = 4;  // 64 destination limbs
+// shared memory: the whole table of the CTA's job (all slices), the per-limb
+// constants, then per group an operand tile (12 KB) and a completion barrier
+constexpr int kTcTableBytes = kTcMaxK * kTcSliceN * kTcMaxSlices;        // 24 KB
+constexpr int kTcLimBytes = 16 * (kTcSliceN / 4) * kTcMaxSlices;          // 1 KB
+constexpr int kTcGroupSmem = kTcMaxK * kTcTile + 128;
+// Asked for: more than half of an SM's shared memory, so two of these CTAs
+// never share an SM and the tensor-memory allocation below cannot wait on
+// another CTA.
+constexpr int kTcUsedSmem = kTcTableBytes + kTcLimBytes + kTcGroups * kTcGroupSmem + 16;
+constexpr int kTcSmemBytes = kTcUsedSmem > 120 * 1024 ? kTcUsedSmem : 120 * 1024;
 static_assert(kTcSmemBytes > 116 * 1024, "one CTA per SM is what keeps the allocation from blocking");
 static_assert(kTcGroups * kTmemCols <= kTmemAlloc, "tensor memory columns");
 
@@ -233,40 +247,29 @@ __global__ void __launch_bounds__(kTcCtaThreads, 1)
     bconv_tc_kernel(const __grid_constant__ BconvTcArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
-  const int group = threadIdx.x / kTcThreads, tid = threadIdx.x & (kTcThreads - 1);
-  // virtual grid: per_unit groups share the tiles of one (job, slice) unit
-  const int vid = blockIdx.x * kTcGroups + group;
-  const int unit = vid / a.per_unit, first_tile = vid - unit * a.per_unit;
-  const bool active = unit < a.n_units;
-  uint8_t *gs = smem + group * kTcGroupSmem;
-  uint8_t *sB = gs;                                     // [K/16][8][8][16]
-  uint8_t *sA = gs + kTcMaxK * kTcSliceN;               // [K/16][16][8][16]
-  uint64_t *bar = reinterpret_cast<uint64_t *>(sA + kTcMaxK * kTcTile);
-  // per destination limb of the slice: {q, -q^-1, word offset of the limb, in range}
-  uint4 *s_lim = reinterpret_cast<uint4 *>(sA + kTcMaxK * kTcTile + 64);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kTcGroups * kTcGroupSmem);
-  const BconvTcJob &j = a.jobs[a.unit_job[active ? unit : 0]];
-  const int slice = a.unit_slice[active ? unit : 0];    // 16 destination limbs each
+  const int group = threadIdx.x / kTcThreads;
+  // a.per_unit CTAs share the tiles of one job; every group of a CTA takes its own tiles
+  const int job = blockIdx.x / a.per_unit, cta_in_job = blockIdx.x - job * a.per_unit;
+  const BconvTcJob &j = a.jobs[job];
+  const int first_tile = cta_in_job * kTcGroups + group, tile_step = a.per_unit * kTcGroups;
+  uint8_t *sB = smem;  // [K/16][npad/8][8][16]: the job's table as it lies in memory
+  // per destination limb: {q, -q^-1, word offset of the limb, in range}
+  uint4 *s_lim = reinterpret_cast<uint4 *>(smem + kTcTableBytes);
+  uint8_t *gs = smem + kTcTableBytes + kTcLimBytes + group * kTcGroupSmem;
+  uint8_t *sA = gs;    // [K/16][16][8][16]
+  uint64_t *bar = reinterpret_cast<uint64_t *>(gs + kTcMaxK * kTcTile);
+  uint32_t *tmem_slot =
+      reinterpret_cast<uint32_t *>(smem + kTcTableBytes + kTcLimBytes + kTcGroups * kTcGroupSmem);
   const int kbytes = j.kpad;
-  const int m_first = slice * (kTcSliceN / 4);
-  const int m_count = min(j.nd - m_first, kTcSliceN / 4);
 
-  if (active) {
-    // this slice of the conversion table -> shared memory (operand layout kept)
-    const uint32_t src_lbo = (uint32_t)(j.npad / 8) * 128;
-    for (int i = tid; i < kbytes / 16 * (kTcSliceN / 8) * 8; i += kTcThreads) {
-      const int t = i / (kTcSliceN / 8 * 8), r = i % (kTcSliceN / 8 * 8);
-      reinterpret_cast<uint4 *>(sB)[i] = *reinterpret_cast<const uint4 *>(
-          j.btile + (size_t)t * src_lbo + (size_t)slice * (kTcSliceN / 8) * 128 + r * 16);
-    }
-    if (tid < kTcSliceN / 4) {
-      const int m = m_first + tid;
-      const bool in = tid < m_count;
-      s_lim[tid] = in ? make_uint4(j.q[m], j.nqinv[m], (uint32_t)j.dst_limb[m] * kN, 1u)
-                      : make_uint4(3u, 1u, 0u, 0u);
-    }
-    if (tid == 0) mbar_init(smem_u32(bar), 1);
+  for (int i = threadIdx.x; i < kbytes * j.npad / 16; i += kTcCtaThreads)
+    reinterpret_cast<uint4 *>(sB)[i] = reinterpret_cast<const uint4 *>(j.btile)[i];
+  if ((int)threadIdx.x < j.npad / 4) {
+    const int m = threadIdx.x;
+    s_lim[m] = m < j.nd ? make_uint4(j.q[m], j.nqinv[m], (uint32_t)j.dst_limb[m] * kN, 1u)
+                        : make_uint4(3u, 1u, 0u, 0u);
   }
+  if ((threadIdx.x & (kTcThreads - 1)) == 0) mbar_init(smem_u32(bar), 1);
   if (threadIdx.x < 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
@@ -281,14 +284,12 @@ __global__ void __launch_bounds__(kTcCtaThreads, 1)
   const uint32_t tmem_cta = *tmem_slot;
   const uint32_t tmem = tmem_cta + (uint32_t)(group * kTmemCols);
 
-  if (active) {
-    if (kbytes == 32)
-      tc_tiles<2>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
-    else if (kbytes == 64)
-      tc_tiles<4>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
-    else
-      tc_tiles<6>(a, j, sA, sB, bar, s_lim, tmem, m_count, group, first_tile, a.per_unit);
-  }
+  if (kbytes == 32)
+    tc_tiles<2>(a, j, sA, sB, bar, s_lim, tmem, group, first_tile, tile_step);
+  else if (kbytes == 64)
+    tc_tiles<4>(a, j, sA, sB, bar, s_lim, tmem, group, first_tile, tile_step);
+  else
+    tc_tiles<6>(a, j, sA, sB, bar, s_lim, tmem, group, first_tile, tile_step);
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -350,27 +351,21 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
     configured = true;
   }
   if (a.n_jobs <= 0) return 0;
-  // work units = (job, slice of 16 destination limbs)
-  BconvTcArgs b = a;
-  b.n_units = 0;
   for (int i = 0; i < a.n_jobs; i++)
-    for (int s = 0; s * (kTcSliceN / 4) < a.jobs[i].nd; s++) {
-      if (b.n_units == kMaxTcUnits) {
-        set_error("bconv: too many (job, slice) units");
-        return -1;
-      }
-      b.unit_job[b.n_units] = (uint8_t)i;
-      b.unit_slice[b.n_units++] = (uint8_t)s;
+    if (a.jobs[i].npad > kTcSliceN * kTcMaxSlices || a.jobs[i].kpad > kTcMaxK) {
+      set_error("bconv: conversion too wide for the tensor-core kernel");
+      return -1;
     }
-  // kTcGroups groups on each of the 148 SMs, shared out evenly over the units
-  const int groups = kTcGroups * 148;
-  int per_unit = groups / b.n_units;
-  if (per_unit < 1) per_unit = 1;
-  if (per_unit > kN / kTcTile) per_unit = kN / kTcTile;
-  b.per_unit = per_unit;
-  const int ctas = (per_unit * b.n_units + kTcGroups - 1) / kTcGroups;
-  CFHE_CUDA(launch_kernel(ctx.use_pdl, bconv_tc_kernel, dim3(ctas), dim3(kTcCtaThreads), kTcSmemBytes,
-                          ctx.stream, b));
+  // one CTA per SM; the CTAs are shared out evenly over the jobs, and the
+  // kTcGroups groups of a CTA interleave over its job's tiles
+  BconvTcArgs b = a;
+  int per_job = 148 / a.n_jobs;
+  const int enough = (kN / kTcTile + kTcGroups - 1) / kTcGroups;
+  if (per_job < 1) per_job = 1;
+  if (per_job > enough) per_job = enough;
+  b.per_unit = per_job;
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, bconv_tc_kernel, dim3(per_job * a.n_jobs), dim3(kTcCtaThreads),
+                          kTcSmemBytes, ctx.stream, b));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -87,12 +87,10 @@ struct BconvTcJob {
   uint8_t dst_limb[kMaxLimbs];
   uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
 };
-constexpr int kMaxTcUnits = 48;
 struct BconvTcArgs {
-  int n_jobs, n_units;
-  int per_unit;     // 128-thread groups sharing the tiles of one unit (filled by the launcher)
+  int n_jobs;
+  int per_unit;     // CTAs sharing the tiles of one job (filled by the launcher)
   int *error_flag;  // set to 1 when a completion wait timed out
-  uint8_t unit_job[kMaxTcUnits], unit_slice[kMaxTcUnits];  // filled by the launcher
   BconvTcJob jobs[kMaxBconvJobs];
 };
 
