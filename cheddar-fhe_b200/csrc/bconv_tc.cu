@@ -51,7 +51,10 @@ constexpr int kTcMaxK = 96;      // bytes of K per tile row: 4 * (20 + 1) padded
 constexpr int kTcSliceN = 64;    // accumulator columns per CTA: 16 destination limbs
 constexpr int kTmemCols = 64;        // per group
 constexpr int kTmemAlloc = 512;      // per CTA: power of two >= kTcGroups * kTmemCols
-constexpr uint32_t kSpinLimit = 1u << 24;
+// A waiting warp sleeps in the barrier unit for up to kWaitHintNs per attempt
+// instead of spending issue slots on polling; kSpinLimit attempts bound the wait.
+constexpr uint32_t kWaitHintNs = 2000;
+constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -81,10 +84,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
