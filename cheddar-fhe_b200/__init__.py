@@ -123,6 +123,11 @@ class Engine:
     def synchronize(self):
         self._check(self.L.cfhe_synchronize(self.h))
 
+    def order_after(self, earlier):
+        """Work submitted to this engine from now on starts after everything
+        already submitted to `earlier` (another engine on the same GPU)."""
+        self._check(self.L.cfhe_order_after(self.h, earlier.h))
+
     # ---- helpers
     def to_dev(self, a):
         t = self.torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32))

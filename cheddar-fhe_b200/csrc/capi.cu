@@ -250,6 +250,16 @@ int cfhe_free(cfhe_context *h, void *ptr) {
   return 0;
 }
 
+int cfhe_order_after(cfhe_context *later, cfhe_context *earlier) {
+  if (!later || !earlier) return fail("null context");
+  if (later == earlier || later->c.stream == earlier->c.stream) return 0;
+  Context &e = earlier->c;
+  if (!e.order_event) CFHE_CUDA(cudaEventCreateWithFlags(&e.order_event, cudaEventDisableTiming));
+  CFHE_CUDA(cudaEventRecord(e.order_event, e.stream));
+  CFHE_CUDA(cudaStreamWaitEvent(later->c.stream, e.order_event, 0));
+  return 0;
+}
+
 int cfhe_copy_h2d(cfhe_context *h, void *dst, const void *src, size_t bytes) {
   if (!h) return fail("null context");
   CFHE_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, h->c.stream));

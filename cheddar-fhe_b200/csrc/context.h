@@ -96,6 +96,7 @@ struct Context {
   bool use_pdl = true;              // programmatic dependent launch between the kernels of a stream (CFHE_PDL=0 disables)
   bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
   int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out
+  cudaEvent_t order_event = nullptr;  // recorded by cfhe_order_after when this context is the earlier one
   std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
   // workspace arena for pipeline temporaries (grown on demand)
   uint32_t *ws = nullptr;

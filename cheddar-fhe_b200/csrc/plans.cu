@@ -188,6 +188,8 @@ void free_plans(Context &c) {
   c.ws_words = 0;
   if (c.d_error_flag) cudaFree(c.d_error_flag);
   c.d_error_flag = nullptr;
+  if (c.order_event) cudaEventDestroy(c.order_event);
+  c.order_event = nullptr;
 }
 
 void Context::mark(const char *stage) const {

@@ -650,7 +650,19 @@ class BootContext : public Context<word> {
       return;
     }
     eval_mod_ = std::make_unique<EvalMod<word>>(boot_param_);
+    // A second engine context (own stream, workspace and allocation cache) for
+    // the imaginary part: below the top levels one EvalMod leaves most of the
+    // GPU idle, two side by side do not. CHEDDAR_SIDE_STREAM=0 keeps one stream.
+    const char *env = std::getenv("CHEDDAR_SIDE_STREAM");
+    if (!(env && std::string(env) == "0")) {
+      cfhe_context *current = detail::CurrentHandle();
+      side_ = Context<word>::Create(this->param_);
+      detail::CurrentHandle() = current;
+    }
   }
+  // false: both EvalMods run on this context's stream (what per-stage device
+  // profiling needs, since it sees one context)
+  void UseSideStream(bool on) { use_side_ = on; }
 
   // Linear transforms for ciphertexts with num_slots slots (a power of two up to
   // degree / 2). Fewer slots mean a plaintext in the subring of X^(degree/2/num_slots):
@@ -963,9 +975,24 @@ class BootContext : public Context<word> {
       this->Sub(im, conj, slots);
       this->MultImaginaryUnit(im, im);
       phase("conjugate split");
-      EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
-      EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
-      this->MultImaginaryUnit(im_mod, im_mod);
+      if (side_ && use_side_) {
+        // im was produced on this stream and is read on the side stream; im_mod
+        // is produced there and read here: one ordering call each way. im_mod
+        // and every temporary of the side evaluation come from the side
+        // context's allocation cache, whose reuse is ordered on the side stream.
+        CheckAbi(cfhe_order_after(side_->h_, this->h_));
+        {
+          ScopedCurrentHandle on_side(side_->h_);
+          eval_mod_->Evaluate(side_, im_mod, im, evk_map.GetMultiplicationKey());
+          side_->MultImaginaryUnit(im_mod, im_mod);
+        }
+        EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
+        CheckAbi(cfhe_order_after(this->h_, side_->h_));
+      } else {
+        EvaluateMod(re_mod, re, evk_map.GetMultiplicationKey());
+        EvaluateMod(im_mod, im, evk_map.GetMultiplicationKey());
+        this->MultImaginaryUnit(im_mod, im_mod);
+      }
       this->Add(re_mod, re_mod, im_mod);
       phase("EvalMod x2");
     }
@@ -1019,6 +1046,8 @@ class BootContext : public Context<word> {
   double q0_prod_ = 1.0, boot_input_scale_ = 1.0, eval_mod_scale_ = 1.0, eval_mod_end_scale_ = 1.0;
   int log_scaleup_ = 0;
   std::unique_ptr<EvalMod<word>> eval_mod_;
+  ContextPtr<word> side_;
+  bool use_side_ = true;
   struct FftPlan {
     bool merged = false;  // fewer than degree / 2 slots: one EvalMod for both parts
     BootVariant variant = BootVariant::kNormal;

@@ -23,6 +23,7 @@
 #include <sstream>
 #include <string>
 #include <utility>
+#include <set>
 #include <vector>
 
 #include "cheddar_b200.h"
@@ -301,7 +302,27 @@ inline cfhe_context *&CurrentHandle() {
   static cfhe_context *h = nullptr;
   return h;
 }
+// engines that are alive: a vector outliving its engine has nothing left to free
+inline std::set<cfhe_context *> &LiveHandles() {
+  static std::set<cfhe_context *> s;
+  return s;
+}
 }  // namespace detail
+
+// Containers created inside the scope allocate from `h` (a second context
+// working beside the main one on its own stream).
+class ScopedCurrentHandle {
+ public:
+  explicit ScopedCurrentHandle(cfhe_context *h) : saved_(detail::CurrentHandle()) {
+    detail::CurrentHandle() = h;
+  }
+  ~ScopedCurrentHandle() { detail::CurrentHandle() = saved_; }
+  ScopedCurrentHandle(const ScopedCurrentHandle &) = delete;
+  ScopedCurrentHandle &operator=(const ScopedCurrentHandle &) = delete;
+
+ private:
+  cfhe_context *saved_;
+};
 
 // Move-only owner of device words (the reference's DeviceVector wraps
 // rmm::device_uvector, include/core/DeviceVector.h:81-92).
@@ -309,7 +330,8 @@ template <typename word>
 class DeviceVector {
  public:
   explicit DeviceVector(int size = 0) { resize(size); }
-  DeviceVector(DeviceVector &&o) noexcept : data_(o.data_), size_(o.size_), cap_(o.cap_) {
+  DeviceVector(DeviceVector &&o) noexcept
+      : data_(o.data_), size_(o.size_), cap_(o.cap_), owner_(o.owner_) {
     o.data_ = nullptr;
     o.size_ = o.cap_ = 0;
   }
@@ -319,6 +341,7 @@ class DeviceVector {
       data_ = o.data_;
       size_ = o.size_;
       cap_ = o.cap_;
+      owner_ = o.owner_;
       o.data_ = nullptr;
       o.size_ = o.cap_ = 0;
     }
@@ -334,7 +357,8 @@ class DeviceVector {
     }
     release();
     void *p = nullptr;
-    CheckAbi(cfhe_malloc(detail::CurrentHandle(), &p, (size_t)size * sizeof(word)));
+    owner_ = detail::CurrentHandle();
+    CheckAbi(cfhe_malloc(owner_, &p, (size_t)size * sizeof(word)));
     data_ = static_cast<word *>(p);
     size_ = cap_ = size;
   }
@@ -344,12 +368,15 @@ class DeviceVector {
 
  private:
   void release() {
-    if (data_) cfhe_free(detail::CurrentHandle(), data_);
+    // back to the allocation cache it came from (reuse there is ordered on that
+    // context's stream)
+    if (data_ && detail::LiveHandles().count(owner_)) cfhe_free(owner_, data_);
     data_ = nullptr;
     size_ = cap_ = 0;
   }
   word *data_ = nullptr;
   int size_ = 0, cap_ = 0;
+  cfhe_context *owner_ = nullptr;
 };
 
 template <typename word>
@@ -777,6 +804,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
                                  param.aux_primes_.data(), param.aux_primes_.size(), lc.data(),
                                  param.level_config_.size(), param.additional_base_.first,
                                  param.additional_base_.second));
+    detail::LiveHandles().insert(h_);
     detail::CurrentHandle() = h_;
     Container<word>::SetDegree(param.degree_);
     encoder_ = std::make_unique<Encoder<word>>(param, h_);
@@ -791,6 +819,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
   virtual ~Context() {
     encoder_.reset();
     if (detail::CurrentHandle() == h_) detail::CurrentHandle() = nullptr;
+    detail::LiveHandles().erase(h_);
     cfhe_context_destroy(h_);
   }
 

@@ -61,6 +61,13 @@ CFHE_API void cfhe_context_destroy(cfhe_context *ctx);
 CFHE_API int cfhe_set_stream(cfhe_context *ctx, void *cuda_stream);
 CFHE_API int cfhe_use_own_stream(cfhe_context *ctx);
 CFHE_API int cfhe_synchronize(cfhe_context *ctx);
+/* Two contexts of one GPU work side by side (each on its own stream, with its
+ * own workspace and allocation cache): everything submitted to `later` after
+ * this call starts after everything submitted to `earlier` before it. No host
+ * synchronisation. The reference runs on the legacy default stream
+ * (src/core/Context.cpp:584-871 launch without a stream argument), where this
+ * ordering is implicit; it has no counterpart there. */
+CFHE_API int cfhe_order_after(cfhe_context *later, cfhe_context *earlier);
 
 CFHE_API int cfhe_degree(const cfhe_context *ctx);
 CFHE_API int cfhe_num_primes(const cfhe_context *ctx);

@@ -198,6 +198,7 @@ int main(int argc, char **argv) {
     std::cout << std::endl;
     if (only.count("profile")) {
       // device time per pipeline stage (CUDA events after every stage), summed by name
+      boot_ctx->UseSideStream(false);
       CheckAbi(cfhe_profile_begin(ctx->h_));
       boot_ctx->Boot(out, ct, ui.GetEvkMap());
       std::vector<char> names(1 << 20);

@@ -83,6 +83,37 @@ def test_permute_matches_oracle(engine40, oracle40):
     assert np.array_equal(e.permute(a, gal, g, add=b), o.add(o.permute(a, gal), b, g))
 
 
+def test_two_contexts_ordered_across_streams(engine40, params40, pkg):
+    """A second context on its own stream consumes what the first produced and
+    hands its result back, with cfhe_order_after in both directions and no host
+    synchronisation in between; the words equal the single-context result."""
+    e = engine40
+    side = pkg.Engine(params40, device=0)
+    rng = np.random.default_rng(31)
+    level = 20
+    g = e.level_limbs(level)
+    nq, n = len(g), e.n
+    primes = np.array([e.primes[x] for x in g], dtype=np.uint64)
+    a = e.to_dev((rng.integers(0, 1 << 62, (nq, n), dtype=np.uint64) % primes[:, None]).astype(np.uint32))
+    b = e.to_dev((rng.integers(0, 1 << 62, (nq, n), dtype=np.uint64) % primes[:, None]).astype(np.uint32))
+    t = e.torch
+    ref1, ref2, ref3 = t.empty_like(a), t.empty_like(a), t.empty_like(a)
+    e.binary_(3, ref1, a, b, g)       # product on the main context
+    e.binary_(0, ref2, ref1, a, g)    # the step the side context takes below
+    e.binary_(1, ref3, ref2, b, g)    # back on the main context
+    e.synchronize()
+    for _ in range(20):               # many rounds: an ordering bug shows as a stale read
+        x1, x2, x3 = t.zeros_like(a), t.zeros_like(a), t.zeros_like(a)
+        e.synchronize()
+        e.binary_(3, x1, a, b, g)
+        side.order_after(e)
+        side.binary_(0, x2, x1, a, g)
+        e.order_after(side)
+        e.binary_(1, x3, x2, b, g)
+        e.synchronize()
+        assert t.equal(x3, ref3)
+
+
 def test_bconv_matches_oracle(engine40, oracle40):
     e, o = engine40, oracle40
     rng = np.random.default_rng(24)
