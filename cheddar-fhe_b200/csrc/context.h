@@ -42,6 +42,7 @@ struct NttArgs {
   Tw kc[kMaxLimbs];  // per-limb constant (Shoup pair)
   uint8_t ep_limb[kMaxLimbs];
   Tw ep_pad[kMaxLimbs], ep_scale[kMaxLimbs];
+  Tw ep_ps[kMaxLimbs];  // pad * scale, so that the epilogue is pad*scale*x - scale*ntt
 };
 
 // One base conversion S -> D with everything its three kernels need.

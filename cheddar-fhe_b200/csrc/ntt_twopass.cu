@@ -113,13 +113,11 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
     v[4 * i + 3] = t.w;
   }
   ct_radix16_pre<FAST>(v, t, q, q2);
-#pragma unroll
-  for (int k = 0; k < 16; k++) {
-    v[k] = ct_fold<FAST>(v[k], q, q2);
-  }
   const int off = R * kRowWords + 16 * g;
   if (a.ep_mode) {
-    // ModDown-family epilogue: ((pad * x) - ntt) * scale, canonical
+    // ModDown-family epilogue: (pad * x - ntt) * scale, canonical. The
+    // transform's values enter as the last stage left them (below 4q, or 2q
+    // for the large primes): a Shoup product takes any 32-bit word.
     const int l = j.l;
     const Tw scale = a.ep_scale[l];
     uint32_t x[16];
@@ -128,31 +126,50 @@ __device__ __forceinline__ void fwd_rows(const NttArgs &a, const Job &j, int blk
           a.ep_src + (size_t)j.p * a.ep_poly_stride + (size_t)a.ep_limb[l] * kN + off);
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        const uint4 t = xp[i];
-        x[4 * i] = t.x;
-        x[4 * i + 1] = t.y;
-        x[4 * i + 2] = t.z;
-        x[4 * i + 3] = t.w;
-      }
-      if (a.ep_mode == 2) {
-        const Tw pad = a.ep_pad[l];
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-          const uint32_t t = shoup_mul(x[k], pad, q);
-          x[k] = umin32(t, t - q);
-        }
+        const uint4 u = xp[i];
+        x[4 * i] = u.x;
+        x[4 * i + 1] = u.y;
+        x[4 * i + 2] = u.z;
+        x[4 * i + 3] = u.w;
       }
     } else {
 #pragma unroll
       for (int k = 0; k < 16; k++) x[k] = 0;
     }
+    if (a.ep_mode == 2) {
+      // pad*scale*x - scale*ntt: two independent products
+      const Tw ps = a.ep_ps[l];
 #pragma unroll
-    for (int k = 0; k < 16; k++) {
-      uint32_t d = x[k] - v[k];
-      if (x[k] < v[k]) d += q;
-      d = shoup_mul(d, scale, q);
-      v[k] = umin32(d, d - q);
+      for (int k = 0; k < 16; k++) {
+        uint32_t t1 = shoup_mul(x[k], ps, q), t2 = shoup_mul(v[k], scale, q);  // both below 2q
+        if constexpr (FAST) {
+          const uint32_t r = t1 - t2 + q2;  // (0, 4q)
+          v[k] = ct_fold<true>(r, q, q2);
+        } else {
+          t1 = umin32(t1, t1 - q);
+          t2 = umin32(t2, t2 - q);
+          const uint32_t r = t1 - t2 + q;  // (0, 2q)
+          v[k] = umin32(r, r - q);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; k++) {
+        uint32_t d;
+        if constexpr (FAST) {
+          const uint32_t y = umin32(v[k], v[k] - q2);  // below 2q
+          d = x[k] - y + q2;                            // (0, 3q)
+        } else {
+          const uint32_t y = umin32(v[k], v[k] - q);    // below q
+          d = x[k] - y + q;                             // (0, 2q)
+        }
+        d = shoup_mul(d, scale, q);
+        v[k] = umin32(d, d - q);
+      }
     }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 16; k++) v[k] = ct_fold<FAST>(v[k], q, q2);
   }
   uint4 *o = reinterpret_cast<uint4 *>(j.dst + off);
 #pragma unroll

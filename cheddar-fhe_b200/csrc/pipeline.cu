@@ -214,6 +214,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     a.ep_limb[m] = cv.ep_pos[m] < 0 ? 255 : (uint8_t)cv.ep_pos[m];
     a.ep_pad[m] = make_tw(cv.ep_pad[m], q);
     a.ep_scale[m] = make_tw(cv.ep_scale[m], q);
+    a.ep_ps[m] = make_tw(mulmod(cv.ep_pad[m] % q, cv.ep_scale[m] % q, q), q);
   }
   if (int r = launch_ntt(c, a, false)) return r;
   c.mark("moddown_ntt");
