@@ -280,3 +280,56 @@ def test_hoisted_rotations_equal_hrot(engine40, oracle40, level, rots):
         gal = o.galois(r)
         assert np.array_equal(got[i, 0], o.permute(sb, gal)), r
         assert np.array_equal(got[i, 1], o.permute(sa, gal)), r
+
+
+def _extra_ntt_primes(existing, count, n=1 << 16):
+    """`count` primes below 2^31, = 1 mod 2n, not in `existing` (deterministic Miller-Rabin)."""
+    def is_prime(p):
+        d, s = p - 1, 0
+        while d % 2 == 0:
+            d //= 2
+            s += 1
+        for a in (2, 3, 5, 7, 11, 13, 17):
+            x = pow(a, d, p)
+            if x in (1, p - 1):
+                continue
+            for _ in range(s - 1):
+                x = x * x % p
+                if x == p - 1:
+                    break
+            else:
+                return False
+        return True
+    out, p = [], (1 << 31) - (1 << 31) % (2 * n) + 1 - 2 * n * 300
+    while len(out) < count:
+        if p not in existing and is_prime(p):
+            out.append(p)
+        p -= 2 * n
+    return out
+
+
+def test_modup_moddown_with_sixteen_auxiliary_primes(pkg, params40):
+    """A parameter set with 16 auxiliary primes makes digits of 16 limbs, which
+    take the widest operand rows of the tensor-core base conversion (more than
+    15 source limbs); ModUp and the ModDown family still equal the golden model."""
+    import copy
+    import torch
+    from oracle import Oracle
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    p = copy.deepcopy(params40)
+    used = set(p["main_primes"]) | set(p["terminal_primes"]) | set(p["auxiliary_primes"])
+    p["auxiliary_primes"] = list(p["auxiliary_primes"]) + _extra_ntt_primes(used, 4)
+    e, o = pkg.Engine(p, device=0), Oracle(p)
+    rng = np.random.default_rng(77)
+    for level in (28, 20):
+        g = e.level_limbs(level)
+        src = rand_limbs(rng, o.primes, g, o.n)
+        assert e.beta(level) == o.beta(level)
+        assert np.array_equal(e.modup(level, src), o.modup(level, src)), level
+        full = e.level_limbs(level, 16)
+        acc = np.stack([rand_limbs(rng, o.primes, full, o.n) for _ in range(2)])
+        for kind in (0, 2):
+            got = e.moddown(level, kind, acc)
+            for i in range(2):
+                assert np.array_equal(got[i], o.moddown(level, kind, acc[i])), (level, kind)
