@@ -916,6 +916,10 @@ class BootContext : public Context<word> {
     auto last = std::chrono::steady_clock::now();
     auto phase = [&](const char *name) {
       if (!phase_ms) return;
+      // CHEDDAR_PHASE_ENQUEUE=1 also reports how long the host took to enqueue the phase
+      if (std::getenv("CHEDDAR_PHASE_ENQUEUE"))
+        phase_ms->emplace_back(std::string(name) + " (enqueue)",
+                               std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - last).count());
       this->Synchronize();
       auto now = std::chrono::steady_clock::now();
       phase_ms->emplace_back(name, std::chrono::duration<double, std::milli>(now - last).count());
