@@ -58,6 +58,9 @@ struct ConvPlan {
   std::vector<uint32_t> ep_pad;     // product of restored primes mod d (plain)
   std::vector<uint32_t> ep_scale;   // (prod S)^-1 mod d (plain)
   bool has_pad = false;
+  // the same constants as Shoup pairs, ready for the kernels' argument blocks
+  std::vector<Tw> pre_tw;           // pre * 2^-32 (the inverse transform's per-limb constant)
+  std::vector<Tw> ep_pad_tw, ep_scale_tw, ep_ps_tw;  // ep_ps = ep_pad * ep_scale
 };
 
 struct DigitPlan {

@@ -14,12 +14,6 @@
 namespace cfhe {
 namespace {
 
-Tw inv_const(uint32_t pre, uint32_t q) {
-  // the kernel multiplies the raw inverse transform by pre * 2^-32 so that
-  // M-form evaluations come out as plain, pre-scaled coefficients
-  return make_tw(mulmod(pre % q, rinv_mod(q), q), q);
-}
-
 void fill_bconv_job(const Context &c, BconvJob &j, const ConvPlan &cv,
                     const int32_t *src, uint32_t *dst,
                     const std::vector<int> *dst_pos) {
@@ -83,7 +77,7 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
       a.g[k] = (uint8_t)g;
       a.q[k] = c.q[g];
       a.src_limb[k] = a.dst_limb[k] = (uint16_t)k;
-      a.kc[k] = inv_const(d.conv.pre[k - d.s0], c.q[g]);
+      a.kc[k] = d.conv.pre_tw[k - d.s0];
     }
   if (int r = launch_ntt(c, a, true)) return r;
   c.mark("modup_intt");
@@ -172,7 +166,7 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     a.q[k] = c.q[g];
     a.src_limb[k] = (uint16_t)cv.src_pos[k];
     a.dst_limb[k] = (uint16_t)k;
-    a.kc[k] = inv_const(cv.pre[k], c.q[g]);
+    a.kc[k] = cv.pre_tw[k];
   }
   if (int r = launch_ntt(c, a, true)) return r;
   c.mark("moddown_intt");
@@ -212,9 +206,9 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     a.q[m] = q;
     a.src_limb[m] = a.dst_limb[m] = (uint16_t)m;
     a.ep_limb[m] = cv.ep_pos[m] < 0 ? 255 : (uint8_t)cv.ep_pos[m];
-    a.ep_pad[m] = make_tw(cv.ep_pad[m], q);
-    a.ep_scale[m] = make_tw(cv.ep_scale[m], q);
-    a.ep_ps[m] = make_tw(mulmod(cv.ep_pad[m] % q, cv.ep_scale[m] % q, q), q);
+    a.ep_pad[m] = cv.ep_pad_tw[m];
+    a.ep_scale[m] = cv.ep_scale_tw[m];
+    a.ep_ps[m] = cv.ep_ps_tw[m];
   }
   if (int r = launch_ntt(c, a, false)) return r;
   c.mark("moddown_ntt");

@@ -46,6 +46,16 @@ int finish_conv(const Context &c, ConvPlan &cv, const std::vector<int> &restored
   CFHE_CUDA(cudaMalloc(&cv.d_table, t.size() * sizeof(int32_t)));
   CFHE_CUDA(cudaMemcpy(cv.d_table, t.data(), t.size() * sizeof(int32_t),
                        cudaMemcpyHostToDevice));
+  for (size_t k = 0; k < cv.pre.size(); k++) {
+    const uint32_t q = c.q[cv.src_g[k]];
+    cv.pre_tw.push_back(make_tw(mulmod(cv.pre[k] % q, rinv_mod(q), q), q));
+  }
+  for (size_t m = 0; m < cv.ep_pad.size(); m++) {
+    const uint32_t q = c.q[cv.dst_g[m]];
+    cv.ep_pad_tw.push_back(make_tw(cv.ep_pad[m], q));
+    cv.ep_scale_tw.push_back(make_tw(cv.ep_scale[m], q));
+    cv.ep_ps_tw.push_back(make_tw(mulmod(cv.ep_pad[m] % q, cv.ep_scale[m] % q, q), q));
+  }
   return build_tc_table(c, cv);
 }
 
