@@ -64,21 +64,23 @@ __global__ void __launch_bounds__(kLtThreads)
 #pragma unroll 1
   for (int i = 0; i < a.n_baby; i++) {
     uint32_t rb0 = 0, rb1 = 0, ra0 = 0, ra1 = 0;  // rotated words at y and y + 1
-    if (i + 1 < a.n_baby) {
-      // The next rotation's key and plaintext words start their way from DRAM
-      // to L2 now: a thread's rotations are serial, so without this every
-      // iteration pays the full DRAM latency before its arithmetic.
-      const uint32_t xn = source_index(y, a.galois[i + 1]) & ~1u;
+    if (i + 2 < a.n_baby) {
+      // The key and plaintext words of the rotation after next start their
+      // way from DRAM to L2 now (distance 2 measured best; 1, 3 and 4 lose
+      // 1 % each): a thread's rotations are serial, so without this every
+      // iteration pays the full DRAM latency before its arithmetic. Written
+      // in line: as a lambda the same code cost 44 more registers.
+      const uint32_t xn = source_index(y, a.galois[i + 2]) & ~1u;
 #pragma unroll
       for (int d = 0; d < kMaxDigits; d++)
         if (d < a.n_digits) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.kb[(i + 1) * kMaxDigits + d] + koff + xn));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.ka[(i + 1) * kMaxDigits + d] + koff + xn));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.kb[(i + 2) * kMaxDigits + d] + koff + xn));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.ka[(i + 2) * kMaxDigits + d] + koff + xn));
         }
 #pragma unroll
       for (int j = 0; j < G; j++)
         if (j < a.n_giant) {
-          const uint32_t *p = a.pt[j * kMaxBaby + i + 1];
+          const uint32_t *p = a.pt[j * kMaxBaby + i + 2];
           if (p) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + limb + y));
         }
     }
