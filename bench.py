@@ -166,6 +166,7 @@ def run_reference(args, pkg):
         gidx = list(range(NTT_LIMBS))
         polys = max(2, min(NTT_POLYS, threads))
         times = []
+        ran_steps, ran_warmup = args.steps, 0
         for _ in range(args.steps):
             dt, nbytes = cpu_ntt_sample(params, gidx, polys, threads)
             times.append(dt)
@@ -175,8 +176,9 @@ def run_reference(args, pkg):
         workload = "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), 16 polynomials"
     else:
         count = threads
-        steps = max(1, min(args.steps, 2))
-        times = [cpu_hmult_sample(params, count, threads) for _ in range(steps)]
+        ran_steps = max(1, min(args.steps, 2))   # one step is `threads` HMults, about 2.5 s each
+        ran_warmup = 0
+        times = [cpu_hmult_sample(params, count, threads) for _ in range(ran_steps)]
         dt = float(np.mean(times)) / count
         val, unit, metric, hib = dt * 1e6, "us", "HMult us", False
         sample = (f"{count} independent HMult+relin+rescale (level 28, random residues) on {threads} "
@@ -184,7 +186,8 @@ def run_reference(args, pkg):
         workload = "HMult+relinearise+rescale, bootparam_40 level 28, N=2^16"
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": val, "unit": unit,
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": ran_steps, "warmup": ran_warmup,
+        "steps_requested": args.steps, "warmup_requested": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": hib, "scaling": "weak",
         "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": workload, "timed": sample,
@@ -197,7 +200,7 @@ def run_reference(args, pkg):
 # --------------------------------------------------------------------------
 # GPU legs
 # --------------------------------------------------------------------------
-def bench_ntt(eng, torch, steps, warmup, rank, barrier):
+def bench_ntt(eng, pkg, torch, steps, warmup, rank, barrier):
     gidx = list(range(NTT_LIMBS))
     rng = np.random.default_rng(0xC0FFEE01 + rank)
     host = make_batch(rng, eng.primes, gidx, NTT_POLYS)
@@ -217,12 +220,14 @@ def bench_ntt(eng, torch, steps, warmup, rank, barrier):
     assert torch.equal(out, src), "forward+inverse NTT is not the identity"
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     barrier()
+    launches0 = pkg.kernel_launch_count()
     for k in range(steps):
         ev[k][0].record()
         eng.ntt_(mid, src, gidx)
         ev[k][1].record()
         eng.intt_(out, mid, gidx, mont_keep=True)
         ev[k][2].record()
+    launches = pkg.kernel_launch_count() - launches0
     barrier()
     ms_total = ev[0][0].elapsed_time(ev[-1][2])
     fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
@@ -241,7 +246,7 @@ def bench_ntt(eng, torch, steps, warmup, rank, barrier):
     e1.record()
     barrier()
     return {"ms_step": ms_total / steps, "ms_e2e": e0.elapsed_time(e1) / steps, "fwd_ms": fwd_ms,
-            "inv_ms": inv_ms, "h2d": int(src.numel() * 4), "d2h": int(out.numel() * 4)}
+            "inv_ms": inv_ms, "h2d": int(src.numel() * 4), "d2h": int(out.numel() * 4), "launches": launches}
 
 
 # algorithmic bytes of each HMult stage at a level with nq Q limbs, alpha aux
@@ -250,6 +255,20 @@ def bench_ntt(eng, torch, steps, warmup, rank, barrier):
 HMULT_STAGE_TRAFFIC = {"tensor": 60_600_000, "modup_intt": 47_800_000, "modup_bconv": 30_100_000,
                        "modup_ntt": 69_600_000, "inner": 232_400_000, "moddown_intt": 13_200_000,
                        "moddown_bconv": 9_200_000, "moddown_ntt": 64_000_000}
+
+
+HMULT_TRAFFIC_SOURCE = ("ncu dram read+write of the stage's launches inside one HMult, warm L2 "
+                        "(--cache-control none), profiles/hmult_level28_dram_traffic.md")
+NTT_KERNEL_NOTE = "ntt_cols_kernel + ntt_rows_kernel, forward (one batch = 5 chunks x 2 passes)"
+NTT_TRAFFIC = 558_000_000
+NTT_TRAFFIC_SOURCE = ("ncu dram read+write summed over the launches of one forward batch, warm L2, "
+                      "profiles/ntt_twopass_kernel_batch16x40.md")
+
+
+def hmult_compulsory_bytes(nq, alpha, beta, nd):
+    """Bytes an HMult cannot avoid: four input polynomials, the key (both
+    halves, beta digits on nq + alpha limbs) and two output polynomials."""
+    return (4 * nq + 2 * beta * (nq + alpha) + 2 * nd) * LIMB
 
 
 def hmult_stage_bytes(nq, alpha, ds, nd, ns):
@@ -307,10 +326,12 @@ def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
         precision_bits = float(-np.log2(err.mean()))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = pkg.kernel_launch_count()
     e0.record()
     for _ in range(steps):
         step()
     e1.record()
+    launches = pkg.kernel_launch_count() - launches0
     barrier()
     ms_step = e0.elapsed_time(e1) / steps
     # per-stage device times, CUDA events inside the library on the same stream
@@ -366,7 +387,7 @@ def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
         assert torch.equal(pins_out[(steps - 1) & 1], dev_out.cpu()) or steps < 1, "pipelined result differs"
     return {"ms_step": ms_step, "ms_e2e": e0.elapsed_time(e1) / steps, "stage_ms": stage_ms,
             "h2d": int(dev_in.numel() * 4), "d2h": int(dev_out.numel() * 4),
-            "precision_bits": precision_bits}
+            "precision_bits": precision_bits, "launches": launches}
 
 
 def bench_reference_cuda(eng, torch, params, steps, with_boot=True):
@@ -479,6 +500,119 @@ def bench_hoisted(eng, torch, params, n_rot, steps):
             "key_bytes_resident": int(keys.numel() * 4)}
 
 
+def reduce_max(values, device="cpu"):
+    """Maximum over ranks of a list of numbers (every rank gets the result).
+    Works on whatever process group is initialised: NCCL with CUDA tensors in
+    the benchmark, gloo with CPU tensors in the world-size-2 CPU test."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.cpu()]
+
+
+def reduce_over_ranks(ntt, hm, boot, hoist, device="cpu"):
+    """Every time-like figure of the line is the maximum over ranks."""
+    red = {}
+    red["ntt_ms"], red["ntt_e2e"], red["fwd_ms"], red["inv_ms"] = reduce_max(
+        [ntt["ms_step"], ntt["ms_e2e"], ntt["fwd_ms"], ntt["inv_ms"]], device)
+    if hm:
+        red["hm_ms"], red["hm_e2e"] = reduce_max([hm["ms_step"], hm["ms_e2e"]], device)
+    if boot:
+        red["boot_ms"], red["boot_err"] = reduce_max([boot["boot_ms"], boot["mean_err"]], device)
+    if hoist:
+        red["hoisted_ms"], red["unhoisted_ms"] = reduce_max([hoist["hoisted_ms"], hoist["unhoisted_ms"]], device)
+    return red
+
+
+def assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape):
+    """The JSON line rank 0 prints. `red` holds the maxima over ranks, the
+    other arguments rank 0's own measurements (used for figures that are not
+    times: bytes, stage split, precision); `shape` = limb counts at the HMult
+    level. Values aggregate over ranks: `world` units were processed in the
+    maximum time."""
+    peak, how = measured_peaks()
+    ntt_ms, ntt_e2e, fwd_ms, inv_ms = red["ntt_ms"], red["ntt_e2e"], red["fwd_ms"], red["inv_ms"]
+    ntt_val = world * NTT_BYTES_PER_STEP / (ntt_ms * 1e-3) / 1e9
+    ntt_ach = NTT_BYTES_PER_LAUNCH / (fwd_ms * 1e-3) / 1e9
+    ntt_roof = {"bound": "hbm", "kernel": NTT_KERNEL_NOTE,
+                "achieved": ntt_ach,
+                "peak": peak, "unit": "GB/s", "frac": ntt_ach / peak, "peak_source": how,
+                "traffic": NTT_TRAFFIC, "traffic_source": NTT_TRAFFIC_SOURCE,
+                "fwd_ms": fwd_ms, "inv_ms": inv_ms,
+                "inv_achieved": NTT_BYTES_PER_LAUNCH / (inv_ms * 1e-3) / 1e9}
+    if hm:
+        hm_ms, hm_e2e = red["hm_ms"], red["hm_e2e"]
+        sb = hmult_stage_bytes(shape["nq"], shape["alpha"], [12, 12, 12, 11], shape["nd"], shape["alpha"] + 2)
+        stage = {k: {"ms": v, "GB/s": sb[k] / (v * 1e-3) / 1e9 if k in sb else None,
+                     "frac": sb[k] / (v * 1e-3) / 1e9 / peak if k in sb else None}
+                 for k, v in hm["stage_ms"].items()}
+        top = max(hm["stage_ms"], key=hm["stage_ms"].get)
+        compulsory = hmult_compulsory_bytes(shape["nq"], shape["alpha"], 4, shape["nd"])
+        line = {
+            "metric": "HMult us", "value": hm_ms * 1e3 / world, "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": hm_ms,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "HMult+relinearise+rescale, bootparam_40 level 28 (47+12 limbs, 4 digits), "
+                                   "N=2^16, 2^15 complex slots uniform in [-1,1]^2, one HMult per GPU per step",
+                       "value_is": "step time / n_gpus",
+                       "l2": "118 MiB key + 200 MiB of temporaries per step, larger than the 126 MB L2",
+                       "parallelism": f"independent ciphertexts x{world}",
+                       "e2e_note": "every step uploads its two ciphertexts from pinned host memory and downloads "
+                                   "its result; uploads, HMult and downloads run on three streams with double "
+                                   "buffers; the multiplication key stays resident"},
+            "e2e": {"value": hm_e2e * 1e3 / world, "unit": "us", "h2d_bytes_per_step": hm["h2d"],
+                    "d2h_bytes_per_step": hm["d2h"]},
+            "gpu_launches": hm["launches"],
+            "gpu_launches_note": "kernels the library launched inside the timed region of `value` (counted)",
+            "clocks": clocks,
+            "precision_bits": hm["precision_bits"],
+            "roofline": {"bound": "hbm",
+                         "kernel": f"stage {top}",
+                         "achieved": stage[top]["GB/s"],
+                         "peak": peak, "unit": "GB/s", "frac": stage[top]["frac"], "peak_source": how,
+                         "traffic": HMULT_STAGE_TRAFFIC.get(top),
+                         "traffic_source": HMULT_TRAFFIC_SOURCE},
+            "whole_op": {"compulsory_bytes": compulsory, "GB/s": compulsory / (hm_ms * 1e-3) / 1e9,
+                         "frac": compulsory / (hm_ms * 1e-3) / 1e9 / peak,
+                         "note": "inputs, key and outputs once each, over the whole HMult"},
+            "stages": stage,
+            "ntt": {"value": ntt_val, "unit": "GB/s", "ms_per_step": ntt_ms,
+                    "e2e": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "roofline": ntt_roof,
+                    "gpu_launches": ntt["launches"]},
+        }
+    else:
+        line = {
+            "metric": "NTT GB/s", "value": ntt_val, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ntt_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), "
+                                   "16 polynomials per GPU",
+                       "l2": "three 168 MB buffers per step, larger than L2",
+                       "parallelism": f"independent batches x{world}"},
+            "e2e": {"value": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
+            "gpu_launches": ntt["launches"], "clocks": clocks, "roofline": ntt_roof,
+        }
+    if hoist:
+        h = dict(hoist)
+        h["hoisted_ms"], h["unhoisted_ms"] = red["hoisted_ms"], red["unhoisted_ms"]
+        h["GB/s"] = h["algorithmic_bytes"] / (h["hoisted_ms"] * 1e-3) / 1e9
+        h["frac"] = h["GB/s"] / peak
+        h["rotations_per_s_all_ranks"] = world * h["rotations"] / (h["hoisted_ms"] * 1e-3)
+        line["hoisted_rotations"] = h
+    if boot:
+        line["bootstrap"] = {"ms": red["boot_ms"], "unit": "ms per bootstrap (max over ranks)",
+                             "bootstraps_per_s": world / (red["boot_ms"] * 1e-3),
+                             "precision_bits": -math.log2(red["boot_err"]), "rank0": boot,
+                             "workload": "bootparam_40, BootParameter(28,4,3), level 0 -> 13, 2^15 complex "
+                                         "slots uniform in [-1,1]^2, one ciphertext per GPU"}
+    return line
+
+
 def run_gpu(args, pkg):
     import torch
     import torch.distributed as dist
@@ -501,7 +635,7 @@ def run_gpu(args, pkg):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ntt = bench_ntt(eng, torch, args.steps, warmup, rank, barrier)
+    ntt = bench_ntt(eng, pkg, torch, args.steps, warmup, rank, barrier)
     hm = None
     if args.workload == "hmult":
         hm = bench_hmult(eng, pkg, torch, params, args.steps, warmup, rank, barrier, not args.no_check)
@@ -517,93 +651,10 @@ def run_gpu(args, pkg):
         barrier()
         boot = bench_bootstrap(pkg, local, min(max(args.steps, 2), 10), 3)
 
-    def reduce_max(x):
-        t = torch.tensor(x, device=f"cuda:{local}", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return [float(v) for v in t.cpu()]
-
-    ntt_ms, ntt_e2e, fwd_ms, inv_ms = reduce_max([ntt["ms_step"], ntt["ms_e2e"], ntt["fwd_ms"], ntt["inv_ms"]])
-    if hm:
-        hm_ms, hm_e2e = reduce_max([hm["ms_step"], hm["ms_e2e"]])
-    if boot:
-        boot_ms, boot_err = reduce_max([boot["boot_ms"], boot["mean_err"]])
+    shape = {"nq": len(eng.level_limbs(HM_LEVEL)), "nd": len(eng.level_limbs(HM_LEVEL - 1)), "alpha": eng.alpha}
+    red = reduce_over_ranks(ntt, hm, boot, hoist, device=f"cuda:{local}")
     if rank == 0:
-        peak, how = measured_peaks()
-        ntt_val = world * NTT_BYTES_PER_STEP / (ntt_ms * 1e-3) / 1e9
-        ntt_ach = NTT_BYTES_PER_LAUNCH / (fwd_ms * 1e-3) / 1e9
-        ntt_roof = {"bound": "hbm", "kernel": "ntt_twopass_kernel<forward> (4 chunks x 2 passes = one batch)",
-                    "achieved": ntt_ach,
-                    "peak": peak, "unit": "GB/s", "frac": ntt_ach / peak, "peak_source": how,
-                    "traffic": 558_000_000,
-                    "traffic_source": "ncu dram read+write summed over the 8 launches of one forward batch, warm L2 "
-                                      "(297 MB read incl. twiddle tables once per chunk, 261 MB written; 48 MiB "
-                                      "chunks keep about 60 % of a chunk in L2 between its two passes)",
-                    "fwd_ms": fwd_ms, "inv_ms": inv_ms,
-                    "inv_achieved": NTT_BYTES_PER_LAUNCH / (inv_ms * 1e-3) / 1e9}
-        if hm:
-            lp_q = len(eng.level_limbs(HM_LEVEL))
-            nd = len(eng.level_limbs(HM_LEVEL - 1))
-            sb = hmult_stage_bytes(lp_q, eng.alpha, [12, 12, 12, 11], nd, eng.alpha + 2)
-            stage = {k: {"ms": v, "GB/s": sb[k] / (v * 1e-3) / 1e9 if k in sb else None,
-                         "frac": sb[k] / (v * 1e-3) / 1e9 / peak if k in sb else None}
-                     for k, v in hm["stage_ms"].items()}
-            top = max(hm["stage_ms"], key=hm["stage_ms"].get)
-            line = {
-                "metric": "HMult us", "value": hm_ms * 1e3 / world, "unit": "us", "n_gpus": world,
-                "steps": args.steps, "warmup": warmup, "ms_per_step": hm_ms,
-                "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-                "dtype": "u32", "data": "synthetic",
-                "config": {"workload": "HMult+relinearise+rescale, bootparam_40 level 28 (47+12 limbs, 4 digits), "
-                                       "N=2^16, 2^15 complex slots uniform in [-1,1]^2, one HMult per GPU per step",
-                           "value_is": "step time / n_gpus",
-                           "l2": "118 MiB key + 200 MiB of temporaries per step, larger than the 126 MB L2",
-                           "parallelism": f"independent ciphertexts x{world}",
-                           "e2e_note": "every step uploads its two ciphertexts from pinned host memory and downloads "
-                                       "its result; uploads, HMult and downloads run on three streams with double "
-                                       "buffers; the multiplication key stays resident"},
-                "e2e": {"value": hm_e2e * 1e3 / world, "unit": "us", "h2d_bytes_per_step": hm["h2d"],
-                        "d2h_bytes_per_step": hm["d2h"]},
-                "gpu_launches": 14 * args.steps,
-                "clocks": clocks,
-                "precision_bits": hm["precision_bits"],
-                "roofline": {"bound": "hbm",
-                             "kernel": f"stage {top}" + (": ntt_twopass_kernel<forward>, column + row pass over the "
-                                                         "188 converted limbs of the 4 digits" if top == "modup_ntt" else ""),
-                             "achieved": stage[top]["GB/s"],
-                             "peak": peak, "unit": "GB/s", "frac": stage[top]["frac"], "peak_source": how,
-                             "traffic": HMULT_STAGE_TRAFFIC.get(top),
-                             "traffic_source": "ncu dram read+write of the stage's launches inside one HMult, warm L2 "
-                                               "(--cache-control none); the conversion output is still L2-resident, "
-                                               "35 MB of the reads are twiddle tables"},
-                "stages": stage,
-                "ntt": {"value": ntt_val, "unit": "GB/s", "ms_per_step": ntt_ms,
-                        "e2e": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "roofline": ntt_roof},
-            }
-        else:
-            line = {
-                "metric": "NTT GB/s", "value": ntt_val, "unit": "GB/s", "n_gpus": world,
-                "steps": args.steps, "warmup": warmup, "ms_per_step": ntt_ms,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "u32", "data": "synthetic",
-                "config": {"workload": "batched fwd+inv negacyclic NTT, N=2^16, 40 limbs (bootparam_40), "
-                                       "16 polynomials per GPU",
-                           "l2": "three 168 MB buffers per step, larger than L2",
-                           "parallelism": f"independent batches x{world}"},
-                "e2e": {"value": world * NTT_BYTES_PER_STEP / (ntt_e2e * 1e-3) / 1e9, "unit": "GB/s",
-                        "h2d_bytes_per_step": ntt["h2d"], "d2h_bytes_per_step": ntt["d2h"]},
-                "gpu_launches": 16 * args.steps, "clocks": clocks, "roofline": ntt_roof,
-            }
-        if hoist:
-            peak_, _ = measured_peaks()
-            hoist["frac"] = hoist["GB/s"] / peak_
-            line["hoisted_rotations"] = hoist
-        if boot:
-            line["bootstrap"] = {"ms": boot_ms, "unit": "ms per bootstrap (max over ranks)",
-                                 "bootstraps_per_s": world / (boot_ms * 1e-3),
-                                 "precision_bits": -math.log2(boot_err), "rank0": boot,
-                                 "workload": "bootparam_40, BootParameter(28,4,3), level 0 -> 13, 2^15 complex "
-                                             "slots uniform in [-1,1]^2, one ciphertext per GPU"}
+        line = assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:

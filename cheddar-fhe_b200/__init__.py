@@ -40,8 +40,14 @@ def lib():
         L = C.CDLL(LIB_PATH)
         L.cfhe_last_error.restype = C.c_char_p
         L.cfhe_prime.restype = C.c_uint32
+        L.cfhe_kernel_launch_count.restype = C.c_ulonglong
         _lib = L
     return _lib
+
+
+def kernel_launch_count():
+    """Kernels the library has launched in this process so far."""
+    return int(lib().cfhe_kernel_launch_count())
 
 
 class CfheError(RuntimeError):
@@ -239,6 +245,30 @@ class Engine:
         self._check(self.L.cfhe_permute(self.h, self._p(dst), self._p(src),
                                         self._p(add) if add is not None else None,
                                         C.c_uint32(int(galois)), gp, len(g)))
+
+    def nary_(self, kind, dsts, terms, gidx, consts=None, pts=None, galois=None, addend=None):
+        """Fused n-ary sums (cfhe_accum / cfhe_caccum / cfhe_paccum /
+        cfhe_permute_accum): dsts[p] = (addend[p]) + sum_t term_t(terms[t][p]).
+        kind: "sum", "const" (consts[t][limb], M-form), "plain" (pts[t]) or
+        "permute" (galois[t])."""
+        g, gp = _ints(gidx)
+        n_polys, n_terms = len(dsts), len(terms)
+        dst = self._ptrs(dsts)
+        src = self._ptrs([terms[t][p] for t in range(n_terms) for p in range(n_polys)])
+        add = self._ptrs(addend) if addend is not None else None
+        if kind == "sum":
+            rc = self.L.cfhe_accum(self.h, n_polys, dst, n_terms, src, gp, len(g))
+        elif kind == "const":
+            k, kp = _u32s(np.asarray(consts, dtype=np.uint32).reshape(-1))
+            rc = self.L.cfhe_caccum(self.h, n_polys, dst, n_terms, src, kp, add, gp, len(g))
+        elif kind == "plain":
+            rc = self.L.cfhe_paccum(self.h, n_polys, dst, n_terms, src, self._ptrs(pts), add, gp, len(g))
+        elif kind == "permute":
+            k, kp = _u32s(galois)
+            rc = self.L.cfhe_permute_accum(self.h, n_polys, dst, n_terms, src, kp, add, gp, len(g))
+        else:
+            raise ValueError(kind)
+        self._check(rc)
 
     def modup_(self, level, dst, src):
         self._check(self.L.cfhe_modup(self.h, level, self._p(dst), self._p(src)))

@@ -347,12 +347,13 @@ int build_tc_table(const Context &c, ConvPlan &cv) {
 
 
 int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
-  static bool configured = false;
-  if (!configured) {
-    CFHE_CUDA(cudaFuncSetAttribute(bconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kTcSmemBytes));
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  if (int r = once.run(ctx.device, [] {
+        CFHE_CUDA(cudaFuncSetAttribute(bconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kTcSmemBytes));
+        return 0;
+      }))
+    return r;
   if (a.n_jobs <= 0) return 0;
   for (int i = 0; i < a.n_jobs; i++)
     if (a.jobs[i].npad > kTcSliceN * kTcMaxSlices || a.jobs[i].kpad > kTcMaxK) {
@@ -362,7 +363,7 @@ int launch_bconv_tc(const Context &ctx, const BconvTcArgs &a) {
   // one CTA per SM; the CTAs are shared out evenly over the jobs, and the
   // kTcGroups groups of a CTA interleave over its job's tiles
   BconvTcArgs b = a;
-  int per_job = 148 / a.n_jobs;
+  int per_job = ctx.num_sms / a.n_jobs;
   const int enough = (kN / kTcTile + kTcGroups - 1) / kTcGroups;
   if (per_job < 1) per_job = 1;
   if (per_job > enough) per_job = enough;

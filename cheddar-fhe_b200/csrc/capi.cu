@@ -13,6 +13,7 @@
 #include "handle.h"
 
 namespace cfhe {
+std::atomic<unsigned long long> g_kernel_launches{0};
 static thread_local std::string g_error;
 void set_error(const std::string &msg) { g_error = msg; }
 const std::string &get_error() { return g_error; }
@@ -21,6 +22,32 @@ static int fail(const std::string &msg) {
   set_error(msg);
   return -1;
 }
+
+// Every entry point runs with the context's device current, whatever device
+// the calling thread had selected, and puts the caller's choice back on return
+// (kernel attributes, allocations and launches all bind to the current device).
+struct DeviceScope {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err;
+  explicit DeviceScope(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) {
+      err = cudaSetDevice(device);
+      switched = err == cudaSuccess;
+    }
+  }
+  ~DeviceScope() {
+    if (switched) cudaSetDevice(prev);
+  }
+  DeviceScope(const DeviceScope &) = delete;
+  DeviceScope &operator=(const DeviceScope &) = delete;
+};
+#define CFHE_ENTER(handle)                                                    \
+  if (!(handle)) return fail("null context");                                 \
+  DeviceScope device_scope_((handle)->c.device);                              \
+  if (device_scope_.err != cudaSuccess)                                       \
+    return fail(std::string("cannot select the context's device: ") + cudaGetErrorString(device_scope_.err))
 
 // Global prime indices of (num_main, num_ter, num_aux): terminal limbs come
 // from the tail of the reversed terminal block, main limbs from the head of
@@ -63,6 +90,10 @@ using namespace cfhe;
 extern "C" {
 
 const char *cfhe_last_error(void) { return get_error().c_str(); }
+
+unsigned long long cfhe_kernel_launch_count(void) {
+  return g_kernel_launches.load(std::memory_order_relaxed);
+}
 
 int cfhe_context_create(cfhe_context **out, int device, int log_degree,
                         const uint32_t *main_primes, int num_main,
@@ -110,17 +141,23 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
     cfhe_context_destroy(h);
     return fail(m);
   };
-  cudaError_t e = cudaSetDevice(device);
+  DeviceScope device_scope_(device);  // the caller's device is current again on return
+  cudaError_t e = device_scope_.err;
   if (e != cudaSuccess) return cleanup_fail(cudaGetErrorString(e));
+  if (cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || c.num_sms < 1)
+    c.num_sms = 148;
   e = cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) return cleanup_fail(cudaGetErrorString(e));
   c.own_stream = true;
   const size_t tsz = (size_t)c.NP * c.n;
   std::vector<Tw> fwd(tsz), inv(tsz);
   c.psi.resize(c.NP);
-  for (int g = 0; g < c.NP; g++)
+  c.inv_w1.resize(c.NP);
+  for (int g = 0; g < c.NP; g++) {
     build_twiddles(c.q[g], c.logn, fwd.data() + (size_t)g * c.n,
                    inv.data() + (size_t)g * c.n, &c.psi[g]);
+    c.inv_w1[g] = inv[(size_t)g * c.n + 1].w;
+  }
   e = cudaMalloc(&c.d_tw, tsz * sizeof(Tw));
   if (e == cudaSuccess) e = cudaMalloc(&c.d_itw, tsz * sizeof(Tw));
   if (e == cudaSuccess)
@@ -128,7 +165,7 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
   if (e == cudaSuccess)
     e = cudaMemcpy(c.d_itw, inv.data(), tsz * sizeof(Tw), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return cleanup_fail(cudaGetErrorString(e));
-  if (build_plans(c) != 0) {
+  if (build_plans(c) != 0 || noalloc_prepare(device) != 0) {
     std::string m = get_error();
     return cleanup_fail(m);
   }
@@ -141,6 +178,7 @@ static void pool_release_cached(Context &c);
 void cfhe_context_destroy(cfhe_context *h) {
   if (!h) return;
   Context &c = h->c;
+  DeviceScope device_scope_(c.device);
   pool_release_cached(c);
   for (auto &kv : c.pool_live) cudaFree(kv.first);
   c.pool_live.clear();
@@ -161,17 +199,26 @@ static void drop_own_stream(Context &c) {
 }
 
 int cfhe_set_stream(cfhe_context *h, void *cuda_stream) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
-  pool_release_cached(h->c);
-  drop_own_stream(h->c);
-  h->c.stream = (cudaStream_t)cuda_stream;
+  Context &c = h->c;
+  if ((cudaStream_t)cuda_stream == c.stream && !c.own_stream) return 0;
+  // Work already enqueued on the old stream may still use the workspace and
+  // cached blocks the new stream's work will touch: wait for it here (a stream
+  // change is a set-up step, not a hot-path call).
+  CFHE_CUDA(cudaStreamSynchronize(c.stream));
+  pool_release_cached(c);
+  drop_own_stream(c);
+  c.stream = (cudaStream_t)cuda_stream;
   return 0;
 }
 
 int cfhe_use_own_stream(cfhe_context *h) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   Context &c = h->c;
   if (c.own_stream) return 0;
+  CFHE_CUDA(cudaStreamSynchronize(c.stream));
   pool_release_cached(c);
   CFHE_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
   c.own_stream = true;
@@ -179,6 +226,7 @@ int cfhe_use_own_stream(cfhe_context *h) {
 }
 
 int cfhe_synchronize(cfhe_context *h) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   CFHE_CUDA(cudaStreamSynchronize(h->c.stream));
   int flag = 0;
@@ -213,6 +261,7 @@ static void pool_release_cached(Context &c) {
 }
 
 int cfhe_malloc(cfhe_context *h, void **ptr, size_t bytes) {
+  CFHE_ENTER(h);
   if (!h || !ptr) return fail("null argument");
   Context &c = h->c;
   // size classes: multiples of 4 KiB below 1 MiB, of 256 KiB (one limb at
@@ -252,6 +301,7 @@ int cfhe_free(cfhe_context *h, void *ptr) {
 
 int cfhe_order_after(cfhe_context *later, cfhe_context *earlier) {
   if (!later || !earlier) return fail("null context");
+  DeviceScope device_scope_(earlier->c.device);
   if (later == earlier || later->c.stream == earlier->c.stream) return 0;
   Context &e = earlier->c;
   if (!e.order_event) CFHE_CUDA(cudaEventCreateWithFlags(&e.order_event, cudaEventDisableTiming));
@@ -261,12 +311,14 @@ int cfhe_order_after(cfhe_context *later, cfhe_context *earlier) {
 }
 
 int cfhe_copy_h2d(cfhe_context *h, void *dst, const void *src, size_t bytes) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   CFHE_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, h->c.stream));
   return 0;
 }
 
 int cfhe_copy_d2h(cfhe_context *h, void *dst, const void *src, size_t bytes) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   CFHE_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, h->c.stream));
   CFHE_CUDA(cudaStreamSynchronize(h->c.stream));
@@ -277,6 +329,7 @@ int cfhe_ntt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
              const int *gidx, int n_limbs, int n_polys,
              long long dst_poly_stride, long long src_poly_stride,
              int mont_conv) {
+  CFHE_ENTER(h);
   if (!h || !dst || !src || !gidx) return fail("null argument");
   const Context &c = h->c;
   NttArgs a;
@@ -298,6 +351,7 @@ int cfhe_intt(cfhe_context *h, uint32_t *dst, const uint32_t *src,
               const int *gidx, int n_limbs, int n_polys,
               long long dst_poly_stride, long long src_poly_stride,
               const uint32_t *consts, int mont_keep, int centred) {
+  CFHE_ENTER(h);
   if (!h || !dst || !src || !gidx) return fail("null argument");
   const Context &c = h->c;
   NttArgs a;
@@ -345,6 +399,7 @@ static int fill_rows(const Context &c, EwArgs &e, uint32_t *dst,
 
 int cfhe_binary(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
                 const uint32_t *b, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   static const int map[4] = {EW_ADD, EW_SUB, EW_NEG, EW_MUL};
   if (op < 0 || op > 3) return fail("unknown binary op");
@@ -357,6 +412,7 @@ int cfhe_binary(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
 int cfhe_const_op(cfhe_context *h, int op, uint32_t *dst, const uint32_t *a,
                   const uint32_t *b, const uint32_t *consts, const int *gidx,
                   int n_limbs) {
+  CFHE_ENTER(h);
   if (!h || !consts) return fail("null argument");
   static const int map[5] = {EW_ADDC, EW_SUBC, EW_RSUBC, EW_MULC, EW_MULC_ADD};
   if (op < 0 || op > 4) return fail("unknown const op");
@@ -370,6 +426,7 @@ int cfhe_elementwise_multi(cfhe_context *h, int with_const, int op, int n_polys,
                            uint32_t *const *dst, const uint32_t *const *a,
                            const uint32_t *const *b, const uint32_t *consts,
                            const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
   if (!h || !dst || !a || !gidx) return fail("null argument");
   static const int bin[4] = {EW_ADD, EW_SUB, EW_NEG, EW_MUL};
   static const int con[5] = {EW_ADDC, EW_SUBC, EW_RSUBC, EW_MULC, EW_MULC_ADD};
@@ -396,6 +453,7 @@ int cfhe_elementwise_multi(cfhe_context *h, int with_const, int op, int n_polys,
 int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
                 const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
                 const uint32_t *a2, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
   if (!h || !d0 || !d1 || !d2 || !b1 || !a1 || !b2 || !a2 || !gidx)
     return fail("null argument");
   if (n_limbs < 0 || n_limbs > kMaxLimbs) return fail("too many limbs");
@@ -415,12 +473,108 @@ int cfhe_tensor(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
 int cfhe_permute(cfhe_context *h, uint32_t *dst, const uint32_t *src,
                  const uint32_t *add, uint32_t galois, const int *gidx,
                  int n_limbs) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   if (dst == src) return fail("permute cannot run in place");
   if ((galois & 1u) == 0 || galois >= 2u * kN) return fail("invalid Galois element");
   EwArgs e;
   if (int r = fill_rows(h->c, e, dst, src, add, nullptr, gidx, n_limbs)) return r;
   { int r_ = launch_permute(h->c, e, galois); h->c.mark("permute"); return r_; }
+}
+
+// Shared argument checks of the four n-ary entry points; src is
+// [term * n_polys + poly].
+static int fill_nary(const Context &c, NaryArgs &a, int mode, int n_polys, uint32_t *const *dst,
+                     int n_terms, const uint32_t *const *src, const uint32_t *const *addend,
+                     const int *gidx, int n_limbs) {
+  if (!dst || !src || !gidx) return fail("null argument");
+  if (n_polys < 1 || n_polys > kMaxNaryPolys) return fail("n-ary sum: one to three polynomials");
+  if (n_terms < 1 || n_terms > kMaxTerms) return fail("n-ary sum: one to eight terms");
+  if (n_limbs < 0 || n_limbs > kMaxLimbs) return fail("too many limbs");
+  memset(&a, 0, sizeof(a));
+  a.mode = mode;
+  a.n_terms = n_terms;
+  a.n_polys = n_polys;
+  a.n_limbs = n_limbs;
+  for (int p = 0; p < n_polys; p++) {
+    if (!dst[p]) return fail("null argument");
+    a.dst[p] = dst[p];
+    a.add[p] = addend ? addend[p] : nullptr;
+    for (int t = 0; t < n_terms; t++) {
+      if (!src[t * n_polys + p]) return fail("null argument");
+      a.src[t][p] = src[t * n_polys + p];
+    }
+  }
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= c.NP) return fail("prime index out of range");
+    a.q[l] = c.q[gidx[l]];
+    a.nqinv[l] = c.nqinv[gidx[l]];
+  }
+  return 0;
+}
+
+int cfhe_accum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n_terms,
+               const uint32_t *const *src, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  NaryArgs a;
+  if (int r = fill_nary(h->c, a, NARY_SUM, n_polys, dst, n_terms, src, nullptr, gidx, n_limbs)) return r;
+  { int r_ = launch_nary(h->c, a); h->c.mark("elementwise"); return r_; }
+}
+
+int cfhe_caccum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n_terms,
+                const uint32_t *const *src, const uint32_t *consts,
+                const uint32_t *const *addend, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!consts) return fail("null argument");
+  NaryArgs a;
+  if (int r = fill_nary(h->c, a, NARY_CONST, n_polys, dst, n_terms, src, addend, gidx, n_limbs)) return r;
+  for (int t = 0; t < n_terms; t++)
+    for (int l = 0; l < n_limbs; l++) a.c[t][l] = consts[t * n_limbs + l] % a.q[l];
+  { int r_ = launch_nary(h->c, a); h->c.mark("elementwise"); return r_; }
+}
+
+int cfhe_paccum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n_terms,
+                const uint32_t *const *src, const uint32_t *const *pt,
+                const uint32_t *const *addend, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!pt) return fail("null argument");
+  NaryArgs a;
+  if (int r = fill_nary(h->c, a, NARY_PLAIN, n_polys, dst, n_terms, src, addend, gidx, n_limbs)) return r;
+  for (int t = 0; t < n_terms; t++) {
+    if (!pt[t]) return fail("null argument");
+    a.pt[t] = pt[t];
+  }
+  { int r_ = launch_nary(h->c, a); h->c.mark("elementwise"); return r_; }
+}
+
+int cfhe_permute_accum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n_terms,
+                       const uint32_t *const *src, const uint32_t *galois,
+                       const uint32_t *const *addend, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!galois) return fail("null argument");
+  NaryArgs a;
+  if (int r = fill_nary(h->c, a, NARY_PERMUTE, n_polys, dst, n_terms, src, addend, gidx, n_limbs)) return r;
+  for (int t = 0; t < n_terms; t++) {
+    if ((galois[t] & 1u) == 0 || galois[t] >= 2u * kN) return fail("invalid Galois element");
+    a.galois[t] = galois[t];
+    for (int p = 0; p < n_polys; p++)
+      if (a.src[t][p] == a.dst[p]) return fail("permute cannot run in place");
+  }
+  { int r_ = launch_nary(h->c, a); h->c.mark("permute"); return r_; }
+}
+
+int cfhe_copy_d2d(cfhe_context *h, void *dst, const void *src, size_t bytes) {
+  CFHE_ENTER(h);
+  if (!dst || !src) return fail("null argument");
+  CFHE_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, h->c.stream));
+  return 0;
+}
+
+int cfhe_memset(cfhe_context *h, void *dst, int value, size_t bytes) {
+  CFHE_ENTER(h);
+  if (!dst) return fail("null argument");
+  CFHE_CUDA(cudaMemsetAsync(dst, value, bytes, h->c.stream));
+  return 0;
 }
 
 uint32_t cfhe_galois_for_rotation(const cfhe_context *h, int rot) {
@@ -434,6 +588,7 @@ uint32_t cfhe_galois_for_rotation(const cfhe_context *h, int rot) {
 
 int cfhe_mul_imag_unit(cfhe_context *h, uint32_t *dst, const uint32_t *src,
                        const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
   if (!h || !gidx) return fail("null argument");
   const Context &c = h->c;
   if (n_limbs < 0 || n_limbs > kMaxRows) return fail("too many limbs");
@@ -453,6 +608,7 @@ int cfhe_mul_imag_unit(cfhe_context *h, uint32_t *dst, const uint32_t *src,
 int cfhe_modup_to_max(cfhe_context *h, uint32_t *dst, const uint32_t *src,
                       const int *src_gidx, int n_src, const int *dst_gidx,
                       int n_dst) {
+  CFHE_ENTER(h);
   if (!h || !dst || !src || !src_gidx || !dst_gidx) return fail("null argument");
   const Context &c = h->c;
   if (n_src < 1 || n_src > 2) return fail("modup_to_max: one or two source limbs");
@@ -474,6 +630,7 @@ int cfhe_modup_to_max(cfhe_context *h, uint32_t *dst, const uint32_t *src,
 // ---------------------------------------------------------------------------
 int cfhe_bconv(cfhe_context *h, uint32_t *dst, const int32_t *y,
                const int *src_gidx, int n_src, const int *dst_gidx, int n_dst) {
+  CFHE_ENTER(h);
   if (!h || !dst || !y || !src_gidx || !dst_gidx) return fail("null argument");
   Context &c = h->c;
   if (n_src < 1 || n_src > kMaxBconvSrc || n_dst < 1 || n_dst > kMaxLimbs)
@@ -502,8 +659,12 @@ int cfhe_bconv(cfhe_context *h, uint32_t *dst, const int32_t *y,
   }
   int32_t *d_t = nullptr;
   CFHE_CUDA(cudaMalloc(&d_t, t.size() * sizeof(int32_t)));
-  CFHE_CUDA(cudaMemcpyAsync(d_t, t.data(), t.size() * sizeof(int32_t),
-                            cudaMemcpyHostToDevice, c.stream));
+  if (cudaError_t ce = cudaMemcpyAsync(d_t, t.data(), t.size() * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                       c.stream);
+      ce != cudaSuccess) {
+    cudaFree(d_t);
+    return fail(cudaGetErrorString(ce));
+  }
   j.src = y;
   j.dst = dst;
   j.table = d_t;
@@ -534,6 +695,7 @@ int cfhe_beta(const cfhe_context *h, int level) {
 }
 
 int cfhe_modup(cfhe_context *h, int level, uint32_t *dst, const uint32_t *src) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!dst || !src) return fail("null argument");
@@ -544,6 +706,7 @@ int cfhe_modup(cfhe_context *h, int level, uint32_t *dst, const uint32_t *src) {
 int cfhe_moddown(cfhe_context *h, int level, int type, uint32_t *dst,
                  const uint32_t *src, int n_polys, long long dst_poly_stride,
                  long long src_poly_stride) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!dst || !src) return fail("null argument");
@@ -560,6 +723,7 @@ int cfhe_evk_inner(cfhe_context *h, int level, uint32_t *acc_b, uint32_t *acc_a,
                    const uint32_t *modup, const uint32_t *c0, const uint32_t *c1,
                    const uint32_t *const *evk_b, const uint32_t *const *evk_a,
                    int key_main) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!acc_b || !acc_a || !modup || !evk_b || !evk_a) return fail("null argument");
@@ -571,6 +735,7 @@ int cfhe_keyswitch(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                    const uint32_t *d, const uint32_t *bx,
                    const uint32_t *const *evk_b, const uint32_t *const *evk_a,
                    int key_main) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!out_b || !out_a || !d || !evk_b || !evk_a) return fail("null argument");
@@ -583,6 +748,7 @@ int cfhe_hoisted_rotations(cfhe_context *h, int level, uint32_t *out,
                            const uint32_t *bx, const uint32_t *ax, int n_rot,
                            const int *rot, const uint32_t *const *evk_b,
                            const uint32_t *const *evk_a, int key_main) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!out || !bx || !ax || !rot || !evk_b || !evk_a) return fail("null argument");
@@ -604,6 +770,7 @@ int cfhe_linear_transform(cfhe_context *h, int level, int rescale, uint32_t *out
                           int n_giant, const int *giant_rot,
                           const uint32_t *const *giant_evk_b, const uint32_t *const *giant_evk_a,
                           const uint32_t *const *pt, int key_main) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!out_b || !out_a || !in_b || !in_a || !baby_rot || !giant_rot || !pt)
@@ -640,6 +807,7 @@ int cfhe_hmult(cfhe_context *h, int level, uint32_t *out_b, uint32_t *out_a,
                const uint32_t *b1, const uint32_t *a1, const uint32_t *b2,
                const uint32_t *a2, const uint32_t *const *evk_b,
                const uint32_t *const *evk_a, int key_main, int rescale) {
+  CFHE_ENTER(h);
   const LevelPlan *lp = get_plan(h, level);
   if (!lp) return -1;
   if (!out_b || !out_a || !b1 || !a1 || !b2 || !a2 || !evk_b || !evk_a)
@@ -668,6 +836,7 @@ int cfhe_profile_begin(cfhe_context *h) {
 
 int cfhe_profile_end(cfhe_context *h, char *names, size_t names_cap, float *ms,
                      int cap) {
+  CFHE_ENTER(h);
   if (!h) return fail("null context");
   Context &c = h->c;
   c.profiling = false;

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
 #include <string>
 #include <utility>
 #include <map>
@@ -82,6 +84,7 @@ struct LevelPlan {
 
 struct Context {
   int device = 0;
+  int num_sms = 148;  // of `device`, read at context creation
   int logn = 0, n = 0;
   std::vector<uint32_t> main_primes, ter_primes, aux_primes;
   std::vector<std::pair<int, int>> level_config;  // (num_main, num_ter)
@@ -99,6 +102,11 @@ struct Context {
   bool use_fused_lt = true;         // baby steps and plaintext accumulation in one kernel (CFHE_LT=unfused disables)
   bool use_pdl = true;              // programmatic dependent launch between the kernels of a stream (CFHE_PDL=0 disables)
   bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
+  // Pipelined NTT (ntt_tiled.cu), selected by CFHE_NTT=tiled
+  bool use_tiled_ntt = false;
+  int ntt_chunk = 0;                // limb transforms per launch pair, so that the passes meet in L2 (CFHE_NTT_CHUNK)
+  int ntt_unit = 0;                 // limb transforms of one prime per CTA (CFHE_NTT_UNIT)
+  std::vector<uint32_t> inv_w1;     // per prime: entry 1 of the inverse twiddle table (the last inverse stage's twiddle)
   int *d_error_flag = nullptr;      // raised by a kernel whose bounded wait ran out
   cudaEvent_t order_event = nullptr;  // recorded by cfhe_order_after when this context is the earlier one
   std::vector<LevelPlan> levels;    // index level + 1 (slot 0 = short base)
@@ -128,7 +136,27 @@ struct Context {
   }
 };
 
+// Kernel attributes (the opt-in to more than 48 KB of dynamic shared memory)
+// are per device: a launcher raises them the first time it runs on a device,
+// which is the current device of the calling thread at that moment.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+  // runs fn() unless it already succeeded on `device`; returns fn's code
+  template <typename F>
+  int run(int device, F fn) {
+    if (device < 0 || device >= kMaxDevices) return -1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device]) return 0;
+    const int r = fn();
+    if (r == 0) done[device] = true;
+    return r;
+  }
+};
+
 int build_plans(Context &ctx);
+int noalloc_prepare(int device);  // noalloc.cu: materialise the built-in scratch array on the current device
 void free_plans(Context &ctx);
 int ensure_workspace(Context &ctx, size_t words);
 
@@ -153,6 +181,9 @@ const std::string &get_error();
 // writes anything an earlier kernel touches. pdl_launch_dependents() at the
 // top of a kernel lets its own successor in as soon as all of its CTAs have
 // started. Both are no-ops in a kernel launched the ordinary way.
+// kernels launched by this library in this process (cfhe_kernel_launch_count)
+extern std::atomic<unsigned long long> g_kernel_launches;
+
 #if defined(__CUDACC__)
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -172,11 +203,14 @@ inline cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), dim3 grid, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 #endif
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse);
 int launch_ntt_twopass(const Context &ctx, const NttArgs &args, bool inverse);
+int launch_ntt_tiled(const Context &ctx, const NttArgs &args, bool inverse);
+bool ntt_tiled_usable(const Context &ctx, const NttArgs &args);
 
 }  // namespace cfhe

@@ -113,6 +113,73 @@ __global__ void __launch_bounds__(kEwThreads)
   reinterpret_cast<uint4 *>(r.dst)[v] = out;
 }
 
+// Fused n-ary sums (see NaryArgs). One thread owns four consecutive words of
+// one limb of every polynomial; each term costs one 128-bit load per
+// polynomial (four gathered words in the permuting mode), products are
+// accumulated in 64 bits with one Montgomery reduction per output word.
+template <int MODE>
+__global__ void __launch_bounds__(kEwThreads)
+    nary_kernel(const __grid_constant__ NaryArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int l = blockIdx.y, v = blockIdx.x * kEwThreads + threadIdx.x;
+  const size_t off = (size_t)l * kN;
+  const uint32_t q = a.q[l], nq = a.nqinv[l];
+  const uint64_t q32 = (uint64_t)q << 32;
+  uint32_t perm[4];
+  for (int p = 0; p < a.n_polys; p++) {
+    uint32_t out[4];
+    if constexpr (MODE == NARY_CONST || MODE == NARY_PLAIN) {
+      uint64_t acc[4] = {0, 0, 0, 0};
+      for (int t = 0; t < a.n_terms; t++) {
+        const uint4 x = reinterpret_cast<const uint4 *>(a.src[t][p] + off)[v];
+        uint4 k;
+        if constexpr (MODE == NARY_CONST) {
+          const uint32_t c = a.c[t][l];
+          k = make_uint4(c, c, c, c);
+        } else {
+          k = reinterpret_cast<const uint4 *>(a.pt[t] + off)[v];
+        }
+        mac_fold(acc[0], x.x, k.x, q32);
+        mac_fold(acc[1], x.y, k.y, q32);
+        mac_fold(acc[2], x.z, k.z, q32);
+        mac_fold(acc[3], x.w, k.w, q32);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e++) out[e] = mont_reduce(acc[e], q, nq);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; e++) out[e] = 0;
+      for (int t = 0; t < a.n_terms; t++) {
+        uint4 x;
+        if constexpr (MODE == NARY_PERMUTE) {
+          const uint32_t galois = a.galois[t];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const uint32_t i = 4 * v + e;
+            const uint32_t ex = (__brev(i) >> (31 - kLogN)) + 1;
+            perm[e] = __brev((ex * galois - 1) << (31 - kLogN)) & (kN - 1);
+          }
+          const uint32_t *s = a.src[t][p] + off;
+          x = make_uint4(s[perm[0]], s[perm[1]], s[perm[2]], s[perm[3]]);
+        } else {
+          x = reinterpret_cast<const uint4 *>(a.src[t][p] + off)[v];
+        }
+        out[0] = add_mod(out[0], x.x, q);
+        out[1] = add_mod(out[1], x.y, q);
+        out[2] = add_mod(out[2], x.z, q);
+        out[3] = add_mod(out[3], x.w, q);
+      }
+    }
+    uint4 o = make_uint4(out[0], out[1], out[2], out[3]);
+    if (a.add[p]) {
+      const uint4 b = reinterpret_cast<const uint4 *>(a.add[p] + off)[v];
+      o = map4(o, b, [=](uint32_t x, uint32_t y) { return add_mod(x, y, q); });
+    }
+    reinterpret_cast<uint4 *>(a.dst[p] + off)[v] = o;
+  }
+}
+
 // Key-switch inner product: for every limb l of the extended basis
 //   acc_b[l] = sum_i x_i[l] * kb_i[l] (+ P * c0[l] on Q limbs), same for a.
 // x_i[l] is the digit's own limb read in place from `d` when limb l belongs
@@ -319,6 +386,30 @@ int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois) {
   if (args.n_rows <= 0) return 0;
   dim3 grid(kEwBlocksX, args.n_rows), block(kEwThreads);
   CFHE_CUDA(launch_kernel(ctx.use_pdl, permute_kernel, grid, block, 0, ctx.stream, args, galois));
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_nary(const Context &ctx, const NaryArgs &args) {
+  if (args.n_limbs <= 0 || args.n_polys <= 0) return 0;
+  dim3 grid(kEwBlocksX, args.n_limbs), block(kEwThreads);
+  switch (args.mode) {
+    case NARY_SUM:
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, nary_kernel<NARY_SUM>, grid, block, 0, ctx.stream, args));
+      break;
+    case NARY_CONST:
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, nary_kernel<NARY_CONST>, grid, block, 0, ctx.stream, args));
+      break;
+    case NARY_PLAIN:
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, nary_kernel<NARY_PLAIN>, grid, block, 0, ctx.stream, args));
+      break;
+    case NARY_PERMUTE:
+      CFHE_CUDA(launch_kernel(ctx.use_pdl, nary_kernel<NARY_PERMUTE>, grid, block, 0, ctx.stream, args));
+      break;
+    default:
+      set_error("unknown n-ary mode");
+      return -1;
+  }
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

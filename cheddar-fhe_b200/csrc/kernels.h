@@ -44,6 +44,28 @@ struct TensorArgs {
   TensorRow rows[kMaxLimbs];
 };
 
+// Fused sums of up to kMaxTerms terms over n_polys polynomials (the
+// reference's Sum / Accum, CAccum, PAccum and PermuteAccum families,
+// src/core/ElementWise.cu:32-71, 225-366, 395-501):
+//   dst[p] = (add[p] if given) + sum_t term_t(p),
+//   term_t(p) = src[t][p]                          NARY_SUM
+//             = c[t][limb] * src[t][p]             NARY_CONST   (c in M-form)
+//             = pt[t] (*) src[t][p]                NARY_PLAIN   (one plaintext polynomial per term)
+//             = permute(src[t][p], galois[t])      NARY_PERMUTE
+constexpr int kMaxTerms = 8;
+constexpr int kMaxNaryPolys = 3;
+enum NaryMode { NARY_SUM = 0, NARY_CONST, NARY_PLAIN, NARY_PERMUTE };
+struct NaryArgs {
+  int mode, n_terms, n_polys, n_limbs;
+  uint32_t *dst[kMaxNaryPolys];
+  const uint32_t *add[kMaxNaryPolys];
+  const uint32_t *src[kMaxTerms][kMaxNaryPolys];
+  const uint32_t *pt[kMaxTerms];
+  uint32_t galois[kMaxTerms];
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
+  uint32_t c[kMaxTerms][kMaxLimbs];
+};
+
 constexpr int kMaxDigits = 8;
 struct InnerArgs {
   uint32_t *acc_b, *acc_a;
@@ -128,6 +150,7 @@ int launch_lt_baby(const Context &ctx, const LtBabyArgs &args);
 int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
+int launch_nary(const Context &ctx, const NaryArgs &args);
 int launch_inner(const Context &ctx, const InnerArgs &args);
 int launch_bconv(const Context &ctx, const BconvArgs &args);
 int launch_bconv_tc(const Context &ctx, const BconvTcArgs &args);

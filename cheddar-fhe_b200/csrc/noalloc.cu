@@ -31,7 +31,7 @@
 namespace {
 
 constexpr int kNoAllocMaxSrcLimbs = 16;
-constexpr int kMaxDevices = 64;
+using cfhe::kMaxDevices;
 
 // Lives in the module image of every device that loads this library. In host
 // code this name is only a handle for the runtime's symbol lookup, never an
@@ -43,6 +43,11 @@ uint32_t *g_scratch_addr[kMaxDevices] = {nullptr};
 
 // Looks up the device address of the array for `device`, which must be the
 // current device. Done once per device; later calls return the cached value.
+// With lazy module loading this first lookup is also the moment the array
+// comes into existence on that device, so cfhe_context_create() performs it
+// (through cfhe::noalloc_prepare) while it is allocating anyway; a host that
+// creates its contexts before it reserves the GPU's memory never sees the
+// entry point below allocate.
 int scratch_address(int device, uint32_t **out) {
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_addr[device]) {
@@ -59,6 +64,14 @@ int scratch_address(int device, uint32_t **out) {
 }
 
 }  // namespace
+
+namespace cfhe {
+int noalloc_prepare(int device) {
+  if (device < 0 || device >= kMaxDevices) return 0;  // the entry point refuses such a device itself
+  uint32_t *unused = nullptr;
+  return scratch_address(device, &unused);
+}
+}  // namespace cfhe
 
 extern "C" int cfhe_moddown_noalloc(cfhe_context *h, int level, int type,
                                     uint32_t *dst, const uint32_t *src) {

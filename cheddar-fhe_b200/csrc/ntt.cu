@@ -185,17 +185,17 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1)
 }  // namespace
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse) {
+  if (ctx.use_tiled_ntt && ntt_tiled_usable(ctx, args)) return launch_ntt_tiled(ctx, args, inverse);
   if (ctx.use_twopass_ntt) return launch_ntt_twopass(ctx, args, inverse);
-  static bool configured = false;
-  if (!configured) {
-    CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kNttSmemBytes));
-    CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kNttSmemBytes));
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  if (int r = once.run(ctx.device, [] {
+        CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kNttSmemBytes));
+        CFHE_CUDA(cudaFuncSetAttribute(ntt_cluster_kernel<true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kNttSmemBytes));
+        return 0;
+      }))
+    return r;
   const int total = args.n_limbs * args.n_polys;
   if (total <= 0) return 0;
   if (total > 65535) {

@@ -111,19 +111,22 @@ int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
   a.src = mu;
   a.table = c.d_tw;
   a.n_polys = 1;
+  // listed prime by prime, so that the copies of a prime in different digits
+  // are neighbours and one CTA can transform them with one set of twiddles
   int n = 0;
-  for (const DigitPlan &d : lp.digits)
-    for (size_t m = 0; m < d.dst_pos.size(); m++) {
-      if (n == kMaxJobs) {
-        set_error("ModUp: too many limb transforms");
-        return -1;
+  for (int g : lp.full_g)
+    for (const DigitPlan &d : lp.digits)
+      for (size_t m = 0; m < d.dst_pos.size(); m++) {
+        if (d.conv.dst_g[m] != g) continue;
+        if (n == kMaxJobs) {
+          set_error("ModUp: too many limb transforms");
+          return -1;
+        }
+        a.g[n] = (uint8_t)g;
+        a.q[n] = c.q[g];
+        a.src_limb[n] = a.dst_limb[n] = (uint16_t)(d.index * lp.ntot + d.dst_pos[m]);
+        n++;
       }
-      const int g = d.conv.dst_g[m];
-      a.g[n] = (uint8_t)g;
-      a.q[n] = c.q[g];
-      a.src_limb[n] = a.dst_limb[n] = (uint16_t)(d.index * lp.ntot + d.dst_pos[m]);
-      n++;
-    }
   a.n_limbs = n;
   if (int r = launch_ntt(c, a, false)) return r;
   c.mark("modup_ntt");

@@ -101,6 +101,15 @@ int build_plans(Context &c) {
   c.use_pdl = !(pdl && std::string(pdl) == "0");
   const char *ntt_mode = getenv("CFHE_NTT");
   c.use_twopass_ntt = !(ntt_mode && std::string(ntt_mode) == "cluster");
+  c.use_tiled_ntt = ntt_mode && std::string(ntt_mode) == "tiled";
+  {
+    const char *chunk = getenv("CFHE_NTT_CHUNK");
+    const char *unit = getenv("CFHE_NTT_UNIT");
+    c.ntt_chunk = chunk ? atoi(chunk) : 256;
+    if (c.ntt_chunk < 1 || c.ntt_chunk > 4096) c.ntt_chunk = 256;
+    c.ntt_unit = unit ? atoi(unit) : 4;
+    if (c.ntt_unit < 1 || c.ntt_unit > 255) c.ntt_unit = 4;
+  }
   CFHE_CUDA(cudaMalloc(&c.d_error_flag, sizeof(int)));
   CFHE_CUDA(cudaMemset(c.d_error_flag, 0, sizeof(int)));
   c.nqinv.resize(c.NP);

@@ -17,13 +17,15 @@ using word = uint32_t;
 
 int main(int argc, char **argv) {
   if (argc < 2) {
-    std::cerr << "usage: boot_bench <parameter.json> [--iters K] [--warmup W]\n";
+    std::cerr << "usage: boot_bench <parameter.json> [--iters K] [--warmup W] [--one-stream]\n";
     return 2;
   }
   int iters = 10, warmup = 3;
-  for (int i = 2; i + 1 < argc; i++) {
-    if (!strcmp(argv[i], "--iters")) iters = std::max(1, atoi(argv[++i]));
-    else if (!strcmp(argv[i], "--warmup")) warmup = std::max(0, atoi(argv[++i]));
+  bool one_stream = false;  // both EvalMods on the main context's stream
+  for (int i = 2; i < argc; i++) {
+    if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = std::max(1, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--warmup") && i + 1 < argc) warmup = std::max(0, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--one-stream")) one_stream = true;
   }
   Random::Seed(20240607);
   ParameterJson json = LoadParameterJson(argv[1]);
@@ -35,6 +37,7 @@ int main(int argc, char **argv) {
   UserInterface<word> ui(ctx);
   const int n = param->degree_ / 2;
   ctx->PrepareEvalMod();
+  if (one_stream) ctx->UseSideStream(false);
   ctx->PrepareEvalSpecialFFT(n);
   EvkRequest req;
   ctx->AddRequiredRotations(req, n);

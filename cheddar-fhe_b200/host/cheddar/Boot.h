@@ -22,7 +22,8 @@
 //    T_2(t) (five levels), followed by three double-angle steps (reference
 //    src/extension/EvalMod.cpp:8-61 uses the same function with K = 16 and
 //    the same eight levels).
-// Full-slot bootstrapping (2^(logN-1) slots) only.
+// Any power-of-two slot count up to 2^(logN-1): fewer slots go through Trace
+// onto the subring and transforms with periodic diagonals.
 #pragma once
 #include <chrono>
 #include <functional>
@@ -39,6 +40,23 @@ struct StripedMatrix {
   std::map<int, std::vector<Complex>> diag;
 
   explicit StripedMatrix(int size = 0) : n(size) {}
+  // the reference's form (include/extension/StripedMatrix.h:11-31): a map from
+  // diagonal offset to diagonal, square matrices only here
+  StripedMatrix(int height, int width) : n(height) {
+    AssertTrue(height == width, "StripedMatrix: square matrices only");
+  }
+  int GetHeight() const { return n; }
+  int GetWidth() const { return n; }
+  int GetNumDiag() const { return (int)diag.size(); }
+  auto begin() const { return diag.begin(); }
+  auto end() const { return diag.end(); }
+  auto find(int k) const { return diag.find(k); }
+  std::vector<Complex> &operator[](int k) { return At(k); }
+  static StripedMatrix Mult(const StripedMatrix &A, const Complex b) {
+    StripedMatrix C = A;
+    C.Scale(b);
+    return C;
+  }
   std::vector<Complex> &At(int k) {
     k = ((k % n) + n) % n;
     auto it = diag.find(k);
@@ -147,6 +165,34 @@ class LinearTransform {
     AssertTrue(giant_rot_.size() <= 16, "LinearTransform: more than 16 giant steps");
   }
 
+  // The reference's constructor (include/extension/LinearTransform.h:43-46,
+  // src/extension/LinearTransform.cpp:8-93): plaintexts at pt_level with scale
+  // pt_scale, the output scale follows from the input's
+  // (in.scale * pt_scale / rescaling ratio of pt_level). Diagonal i acts on the
+  // input rotated by i - pre_rotation, and every plaintext is additionally
+  // turned by additional_pt_rot slots:
+  //   out[p] = sum_i diag_i[p + additional_pt_rot] * in[p + i - pre_rotation].
+  // bs * gs must cover the diagonals as in the reference; the giant steps are
+  // then planned by this class (gs is an upper bound, not a layout).
+  LinearTransform(const ConstContextPtr<word> &ctx, const StripedMatrix &matrix, int pt_level, double pt_scale,
+                  int bs, int gs = 1, int pre_rotation = 0, int additional_pt_rot = 0)
+      : LinearTransform(ctx, Shifted(matrix, bs, gs, pre_rotation, additional_pt_rot), pt_level, 1.0,
+                        pt_scale / ctx->param_.GetRescalePrimeProd(pt_level), bs > 16 ? 16 : bs) {
+    relative_scale_ = true;
+    ref_bs_ = bs;
+    ref_gs_ = gs;
+    pre_rotation_ = pre_rotation;
+  }
+  bool IsUsingBSGS() const { return ref_bs_ > 1 && ref_gs_ > 1; }
+  int GetBS() const { return ref_bs_; }
+  int GetGS() const { return ref_gs_; }
+  int GetPreRotationAmount() const { return pre_rotation_; }
+  void AddRequiredRotations(EvkRequest &req, bool min_ks = false) const {
+    std::set<int> rots;
+    AddRequiredRotations(rots, min_ks);
+    for (int r : rots) req.AddRequest(r, level_);
+  }
+
   // min_ks: the plan that needs at most three keys per transform (the baby
   // stride, the giant stride and the first giant offset), at the price of
   // sequential, unhoisted rotations (the reference's minimum key-switching
@@ -203,7 +249,7 @@ class LinearTransform {
                                    in.ax_.data(), baby_rot_.size(), baby_rot_.data(), bkb.data(), bka.data(),
                                    giant_rot_.size(), giant_rot_.data(), gkb.data(), gka.data(), pt.data(),
                                    Max(key_main, 0)));
-    out.SetScale(scale_out_);
+    out.SetScale(relative_scale_ ? in.GetScale() * scale_out_ : scale_out_);
     out.SetNumSlots(in.GetNumSlots());
     res = std::move(out);
   }
@@ -267,22 +313,107 @@ class LinearTransform {
       sum = std::move(turned);
     }
     ctx->Rescale(res, sum);
-    res.SetScale(scale_out_);
+    res.SetScale(relative_scale_ ? in.GetScale() * scale_out_ : scale_out_);
   }
 
   int level() const { return level_; }
+  double OutputScaleFactor() const { return scale_out_; }  // output scale for an input of scale 1
   int NumBabySteps() const { return baby_rot_.size(); }
   int NumGiantSteps() const { return giant_rot_.size(); }
 
  private:
+  // the reference constructor's matrix in this class's convention
+  static StripedMatrix Shifted(const StripedMatrix &m, int bs, int gs, int pre_rotation, int additional_pt_rot) {
+    const int n = m.GetWidth();
+    AssertTrue(n > 0 && (n & (n - 1)) == 0, "LinearTransform requires power-of-two width");
+    AssertTrue(m.GetNumDiag() > 1, "LinearTransform requires at least 2 plaintexts");
+    StripedMatrix out(n);
+    int g = 0, max_rot = 0;
+    for (const auto &[i, d] : m) {
+      const int rot = (((i - pre_rotation) % n) + n) % n;
+      g = std::gcd(g, rot);
+      max_rot = std::max(max_rot, rot);
+      auto &o = out.At(rot);
+      for (int p = 0; p < n; p++) o[p] = d[(((p + additional_pt_rot) % n) + n) % n];
+    }
+    AssertTrue(g > 0, "Something went wrong during LinearTransform setup");
+    AssertTrue(max_rot <= (bs * gs - 1) * g,
+               "Incompatible matrix and LinearTransform parameters: bs (" + std::to_string(bs) + "), gs (" +
+                   std::to_string(gs) + "), pre_rotation (" + std::to_string(pre_rotation) + ")");
+    return out;
+  }
   int Mod(long long x) const { return (int)(((x % n_) + n_) % n_); }
   int level_, bs_, n_;
   double scale_out_;
+  bool relative_scale_ = false;  // scale_out_ multiplies the input's scale (reference-shaped constructor)
+  int ref_bs_ = 0, ref_gs_ = 0, pre_rotation_ = 0;
   int g_ = 0, giant_stride_ = 0, giant_first_ = 0;  // slot distances of the min_ks plan
   std::vector<int> baby_idx_, giant_jj_;            // baby multiple / giant position per entry
   std::vector<int> baby_rot_, giant_rot_;  // slot distances; baby_rot_[0] == 0
   std::vector<Pt> pts_;                    // [giant][baby], dense
   std::vector<bool> present_;
+};
+
+// ------------------------------------------------------------ HoistHandler
+// The reference's baby-step/giant-step evaluator (include/extension/Hoist.h:28-104):
+//   res = Rescale( sum_gs rot_gs( sum_bs hoist_map[gs][bs] (*) rot_bs(input) ) ).
+// Here it is an adapter: the map is turned back into the striped matrix it
+// came from (plaintext gs/bs holds diagonal gs + bs turned by gs slots) and
+// handed to LinearTransform, whose single engine call hoists both kinds of step.
+using Message = std::vector<Complex>;
+using PlainHoistMap = std::map<int, std::map<int, Message>>;
+
+template <typename word>
+class HoistHandler {
+  using Ct = Ciphertext<word>;
+
+ public:
+  HoistHandler(const ConstContextPtr<word> &context, const PlainHoistMap &hoist_map, int pt_level, double pt_scale,
+               bool suppress_bs_swap = false)
+      : lt_(context, ToMatrix(hoist_map), pt_level, 1.0,
+            pt_scale / context->param_.GetRescalePrimeProd(pt_level), BabySteps(hoist_map)),
+        pt_level_(pt_level) {
+    (void)suppress_bs_swap;  // a layout choice of the reference's kernels
+  }
+  HoistHandler(const HoistHandler &) = delete;
+  HoistHandler &operator=(const HoistHandler &) = delete;
+  HoistHandler(HoistHandler &&) = default;
+
+  void AddRequiredRotations(EvkRequest &req, bool min_ks = false) const {
+    std::set<int> rots;
+    lt_.AddRequiredRotations(rots, min_ks);
+    for (int r : rots) req.AddRequest(r, pt_level_);
+  }
+  void Evaluate(const ConstContextPtr<word> &context, Ct &res, const Ct &input, const EvkMap<word> &evk_map,
+                bool min_ks = false) const {
+    const double in_scale = input.GetScale();
+    lt_.Evaluate(context, res, input, evk_map, min_ks);
+    res.SetScale(in_scale * lt_.OutputScaleFactor());
+  }
+
+ private:
+  static StripedMatrix ToMatrix(const PlainHoistMap &map) {
+    AssertTrue(!map.empty() && !map.begin()->second.empty(), "HoistHandler: empty map");
+    const int n = (int)map.begin()->second.begin()->second.size();
+    StripedMatrix m(n);
+    for (const auto &[gs, row] : map)
+      for (const auto &[bs, pt] : row) {
+        AssertTrue((int)pt.size() == n, "HoistHandler: plaintexts of different sizes");
+        auto &d = m.At(gs + bs);
+        for (int p = 0; p < n; p++) d[p] = pt[(((p + gs) % n) + n) % n];
+      }
+    return m;
+  }
+  static int BabySteps(const PlainHoistMap &map) {
+    std::set<int> bs;
+    for (const auto &[gs, row] : map)
+      for (const auto &[b, pt] : row) bs.insert(b);
+    int k = 1;
+    while (k < (int)bs.size()) k <<= 1;
+    return std::min(k, 16);
+  }
+  LinearTransform<word> lt_;
+  int pt_level_;
 };
 
 // ------------------------------------------------------------ EvalPoly
@@ -293,6 +424,116 @@ class EvalPoly {
   using Evk = EvaluationKey<word>;
 
  public:
+  // ---- the reference's object interface (include/extension/EvalPoly.h:203-223) ----
+  // coefficients[k] multiplies x^k, or T_k(x) when `chebyshev` is set. The
+  // result sits ceil(log2(#coefficients)) levels below input_level at scale
+  // target_scale. Evaluation always runs in the Chebyshev basis (the power
+  // basis is converted exactly, as a polynomial identity), with the
+  // recursive splitting of EvaluateChebyshev below.
+  EvalPoly(const std::vector<double> &coefficients, int input_level, double input_scale, double target_scale,
+           bool chebyshev = false)
+      : coefficients_(coefficients),
+        chebyshev_(chebyshev),
+        input_level_(input_level),
+        input_scale_(input_scale),
+        target_scale_(target_scale) {
+    AssertTrue(!coefficients_.empty(), "EvalPoly: no coefficients");
+  }
+  EvalPoly(const EvalPoly &) = delete;
+  EvalPoly &operator=(const EvalPoly &) = delete;
+  EvalPoly(EvalPoly &&) = default;
+
+  int GetPolyDegree() const {
+    int d = (int)coefficients_.size() - 1;
+    while (d > 0 && coefficients_[d] == 0.0) d--;
+    return d;
+  }
+  void ConvertToChebyshevBasis() {
+    if (chebyshev_) return;
+    coefficients_ = PowerToChebyshev(coefficients_);
+    chebyshev_ = true;
+  }
+  void ConvertToNormalBasis() {
+    if (!chebyshev_) return;
+    coefficients_ = ChebyshevToPower(coefficients_);
+    chebyshev_ = false;
+  }
+  // Fixes the evaluation plan: the Chebyshev coefficients and the level budget.
+  void Compile(const ConstContextPtr<word> &context) {
+    compiled_ = chebyshev_ ? coefficients_ : PowerToChebyshev(coefficients_);
+    int k = 1;
+    while ((size_t(1) << k) < compiled_.size()) k++;
+    AssertTrue(input_level_ - k >= 0 && input_level_ <= context->param_.max_level_,
+               "EvalPoly: not enough levels below the input level");
+  }
+  void Evaluate(const ConstContextPtr<word> &context, Ct &res, const Ct &input, const Evk &mult_key) const {
+    AssertTrue(!compiled_.empty(), "EvalPoly: Compile first");
+    AssertTrue(context->param_.NPToLevel(input.GetNP()) == input_level_, "EvalPoly: wrong input level");
+    context->AssertSameScale(input.GetScale(), input_scale_);
+    EvaluateChebyshev(context, res, input, compiled_, mult_key, target_scale_);
+  }
+  double PlainEvaluate(double x) const {
+    if (!chebyshev_) {
+      double r = 0;
+      for (int k = (int)coefficients_.size() - 1; k >= 0; k--) r = r * x + coefficients_[k];
+      return r;
+    }
+    double b1 = 0, b2 = 0;  // Clenshaw
+    for (int k = (int)coefficients_.size() - 1; k >= 1; k--) {
+      const double b0 = coefficients_[k] + 2 * x * b1 - b2;
+      b2 = b1;
+      b1 = b0;
+    }
+    return coefficients_[0] + x * b1 - b2;
+  }
+  // x^k as a combination of T_0..T_k and back (long double, exact to rounding)
+  static std::vector<double> PowerToChebyshev(const std::vector<double> &a) {
+    const int n = a.size();
+    std::vector<long double> c(n, 0.0L), xk(n, 0.0L), next(n);
+    xk[0] = 1.0L;  // x^0 = T_0
+    for (int k = 0; k < n; k++) {
+      for (int j = 0; j <= k; j++) c[j] += (long double)a[k] * xk[j];
+      // x * T_j = (T_{j+1} + T_{|j-1|}) / 2
+      std::fill(next.begin(), next.end(), 0.0L);
+      for (int j = 0; j <= k && k + 1 < n; j++) {
+        if (j == 0) {
+          next[1] += xk[0];
+        } else {
+          next[j + 1] += xk[j] / 2;
+          next[j - 1] += xk[j] / 2;
+        }
+      }
+      xk = next;
+    }
+    return std::vector<double>(c.begin(), c.end());
+  }
+  static std::vector<double> ChebyshevToPower(const std::vector<double> &c) {
+    const int n = c.size();
+    std::vector<long double> a(n, 0.0L), t0(n, 0.0L), t1(n, 0.0L), t2(n);
+    t0[0] = 1.0L;
+    if (n > 1) t1[1] = 1.0L;
+    for (int k = 0; k < n; k++) {
+      const auto &tk = k == 0 ? t0 : t1;
+      for (int j = 0; j <= k; j++) a[j] += (long double)c[k] * tk[j];
+      if (k >= 1) {  // T_{k+1} = 2 x T_k - T_{k-1}
+        std::fill(t2.begin(), t2.end(), 0.0L);
+        for (int j = 0; j <= k && j + 1 < n; j++) t2[j + 1] += 2 * t1[j];
+        for (int j = 0; j < k; j++) t2[j] -= t0[j];
+        t0 = t1;
+        t1 = t2;
+      }
+    }
+    return std::vector<double>(a.begin(), a.end());
+  }
+
+ private:
+  std::vector<double> coefficients_, compiled_;
+  bool chebyshev_ = true;
+  int input_level_ = 0;
+  double input_scale_ = 0, target_scale_ = 0;
+
+ public:
+  // ---- the static form used by EvalMod ----
   // res = 2*A*B - C (C may be null: 2*A*B - c0 with the real constant c0),
   // one level below min(level A, level B). Everything is subtracted from the
   // unrelinearised product, so the node costs one RelinearizeRescale.
@@ -652,17 +893,16 @@ class BootContext : public Context<word> {
     eval_mod_ = std::make_unique<EvalMod<word>>(boot_param_);
     // A second engine context (own stream, workspace and allocation cache) for
     // the imaginary part: below the top levels one EvalMod leaves most of the
-    // GPU idle, two side by side do not. CHEDDAR_SIDE_STREAM=0 keeps one stream.
-    const char *env = std::getenv("CHEDDAR_SIDE_STREAM");
-    if (!(env && std::string(env) == "0")) {
-      cfhe_context *current = detail::CurrentHandle();
-      side_ = Context<word>::Create(this->param_);
-      detail::CurrentHandle() = current;
-    }
+    // GPU idle, two side by side do not. UseSideStream(false) keeps one stream.
+    cfhe_context *current = detail::CurrentHandle();
+    side_ = Context<word>::Create(this->param_);
+    detail::CurrentHandle() = current;
   }
   // false: both EvalMods run on this context's stream (what per-stage device
   // profiling needs, since it sees one context)
   void UseSideStream(bool on) { use_side_ = on; }
+  // true: Boot's phase report also says how long the host took to enqueue each phase
+  void ReportPhaseEnqueue(bool on) { report_enqueue_ = on; }
 
   // Linear transforms for ciphertexts with num_slots slots (a power of two up to
   // degree / 2). Fewer slots mean a plaintext in the subring of X^(degree/2/num_slots):
@@ -916,8 +1156,7 @@ class BootContext : public Context<word> {
     auto last = std::chrono::steady_clock::now();
     auto phase = [&](const char *name) {
       if (!phase_ms) return;
-      // CHEDDAR_PHASE_ENQUEUE=1 also reports how long the host took to enqueue the phase
-      if (std::getenv("CHEDDAR_PHASE_ENQUEUE"))
+      if (report_enqueue_)
         phase_ms->emplace_back(std::string(name) + " (enqueue)",
                                std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - last).count());
       this->Synchronize();
@@ -1052,6 +1291,7 @@ class BootContext : public Context<word> {
   std::unique_ptr<EvalMod<word>> eval_mod_;
   ContextPtr<word> side_;
   bool use_side_ = true;
+  bool report_enqueue_ = false;
   struct FftPlan {
     bool merged = false;  // fewer than degree / 2 slots: one EvalMod for both parts
     BootVariant variant = BootVariant::kNormal;

@@ -115,27 +115,26 @@ class Parameter {
     short_base_np_ = NPInfo(level_config_.at(0).first - additional_base_.first,
                             level_config_.at(0).second - additional_base_.second, 0);
     short_base_np_.num_aux_ = short_base_np_.num_main_ + short_base_np_.num_ter_;
-    rescale_prime_prod_.resize(max_level_ + 1);
-    scale_.resize(default_encryption_level_ + 1);
-    scale_[0] = base_scale_;
-    double new_scale = base_scale_;
+    // Rational rescaling: going from level i to i - 1 divides by the primes
+    // level i holds and level i - 1 does not and multiplies by those only the
+    // lower level holds. Levels up to the default encryption level keep
+    // scale_i^2 / ratio_i = scale_(i-1), i.e. scale_i = sqrt(scale_(i-1) * ratio_i)
+    // (reference src/core/Parameter.cu:100-194 computes the same ratios).
+    auto prime_product = [](const std::vector<word> &primes, int from, int to) {
+      double p = 1.0;
+      for (int j = from; j < to; j++) p *= (double)primes[j];
+      return p;
+    };
+    rescale_prime_prod_.assign(max_level_ + 1, 0.0);
+    scale_.assign(default_encryption_level_ + 1, base_scale_);
     for (int i = 1; i <= max_level_; i++) {
-      NPInfo up = LevelToNP(i), lo = LevelToNP(i - 1);
-      const int td = up.num_ter_ - lo.num_ter_, md = up.num_main_ - lo.num_main_;
-      double num = 1.0, den = 1.0;
-      if (td >= 0)
-        for (int j = 0; j < td; j++) num *= ter_primes_[lo.num_ter_ + j];
-      else
-        for (int j = 0; j < -td; j++) den *= ter_primes_[up.num_ter_ + j];
-      if (md >= 0)
-        for (int j = 0; j < md; j++) num *= main_primes_[lo.num_main_ + j];
-      else
-        for (int j = 0; j < -md; j++) den *= main_primes_[up.num_main_ + j];
-      rescale_prime_prod_[i] = num / den;
-      if (i <= default_encryption_level_) {
-        new_scale = std::sqrt(new_scale * rescale_prime_prod_[i]);
-        scale_[i] = new_scale;
-      }
+      const NPInfo up = LevelToNP(i), lo = LevelToNP(i - 1);
+      const double gained = prime_product(ter_primes_, lo.num_ter_, up.num_ter_) *
+                            prime_product(main_primes_, lo.num_main_, up.num_main_);
+      const double given_back = prime_product(ter_primes_, up.num_ter_, lo.num_ter_) *
+                                prime_product(main_primes_, up.num_main_, lo.num_main_);
+      rescale_prime_prod_[i] = gained / given_back;
+      if (i <= default_encryption_level_) scale_[i] = std::sqrt(scale_[i - 1] * rescale_prime_prod_[i]);
     }
   }
 
@@ -746,40 +745,123 @@ class Encoder {
       if (i < j) std::swap(v[i], v[j]);
     }
   }
-  void SpecialIFFT(std::vector<Complex> &d) const {
-    const int n = d.size();
-    for (int stride = n / 2; stride >= 1; stride /= 2) {
-      const int st8 = stride << 3, gap = M_ / st8;
-      for (int i = 0; i < n; i += 2 * stride)
-        for (int j = 0; j < stride; j++) {
-          const int tw = (st8 - (param_.GetGaloisFactor(j) % st8)) * gap;
-          Complex x = d[i + j] + d[i + j + stride];
-          Complex y = (d[i + j] - d[i + j + stride]) * twiddle_factors_[tw % M_];
-          d[i + j] = x;
-          d[i + j + stride] = y;
+  // The slot map of CKKS with n slots: slot j is the plaintext polynomial
+  // evaluated at zeta^(5^j), zeta = exp(2 pi i / 4n), the n complex numbers
+  // d[k] standing for the coefficients a[k] + i a[k + n]. Because
+  // 5^j = 4 t_j + 1 (mod 4n) and j -> t_j runs over all of [0, n), evaluating
+  // at every slot is three plain steps: multiply d[k] by zeta^k, take the
+  // length-n DFT with kernel exp(+2 pi i t k / n), read the result at t_j.
+  // The inverse map undoes them in reverse order. (Same linear map as the
+  // reference's special FFT, src/core/Encode.cpp:85-133, which interleaves the
+  // powers of five with the butterflies instead.)
+  static std::vector<int> SlotOrder(int n) {
+    std::vector<int> t(n);
+    const int64_t m = 4 * (int64_t)n;
+    int64_t e = 1;
+    for (int j = 0; j < n; j++) {
+      t[j] = (int)((e - 1) / 4);
+      e = e * 5 % m;
+    }
+    return t;
+  }
+  // in-place radix-2 DFT, natural order in and out, kernel exp(+-2 pi i t k / n)
+  void PlainFft(std::vector<Complex> &v, bool positive) const {
+    const int n = v.size();
+    BitReverse(v);
+    for (int len = 2; len <= n; len <<= 1) {
+      const int step = M_ / len, half = len / 2;
+      for (int base = 0; base < n; base += len)
+        for (int k = 0; k < half; k++) {
+          const Complex w = positive ? twiddle_factors_[k * step] : std::conj(twiddle_factors_[k * step]);
+          const Complex x = v[base + k], y = v[base + k + half] * w;
+          v[base + k] = x + y;
+          v[base + k + half] = x - y;
         }
     }
-    BitReverse(d);
-    for (auto &x : d) x /= n;
   }
   void SpecialFFT(std::vector<Complex> &d) const {
-    const int n = d.size();
-    BitReverse(d);
-    for (int stride = 1; stride < n; stride *= 2) {
-      const int st8 = stride << 3, gap = M_ / st8;
-      for (int i = 0; i < n; i += 2 * stride)
-        for (int j = 0; j < stride; j++) {
-          const int tw = (param_.GetGaloisFactor(j) % st8) * gap;
-          Complex x = d[i + j], y = d[i + j + stride] * twiddle_factors_[tw];
-          d[i + j] = x + y;
-          d[i + j + stride] = x - y;
-        }
-    }
+    const int n = d.size(), zeta_step = M_ / (4 * n);
+    for (int k = 0; k < n; k++) d[k] *= twiddle_factors_[k * zeta_step];
+    PlainFft(d, true);
+    const std::vector<int> t = SlotOrder(n);
+    std::vector<Complex> slots(n);
+    for (int j = 0; j < n; j++) slots[j] = d[t[j]];
+    d.swap(slots);
+  }
+  void SpecialIFFT(std::vector<Complex> &d) const {
+    const int n = d.size(), zeta_step = M_ / (4 * n);
+    const std::vector<int> t = SlotOrder(n);
+    std::vector<Complex> y(n);
+    for (int j = 0; j < n; j++) y[t[j]] = d[j];
+    PlainFft(y, false);
+    for (int k = 0; k < n; k++) d[k] = y[k] * std::conj(twiddle_factors_[k * zeta_step]) / (double)n;
   }
   const Parameter<word> &param_;
   cfhe_context *h_;
   const int M_;
   std::vector<Complex> twiddle_factors_;
+};
+
+// ---------------------------------------------------------------- MultiLevelCiphertext
+// One message held at several levels at once (reference
+// include/core/MultiLevelCiphertext.h, src/core/MultiLevelCiphertext.cpp:1-86):
+// polynomial evaluation asks for the same ciphertext at whatever level an
+// operand needs, and Context::AddLowerLevelsUntil fills in the missing ones by
+// multiplying with the constant 1 encoded at the level's rescaling ratio and
+// rescaling. The per-level constants are shared by all instances and set up by
+// StaticInit (Context::Create calls it).
+template <typename word>
+class MultiLevelCiphertext {
+  using Ct = Ciphertext<word>;
+
+ public:
+  static void StaticInit(const Parameter<word> &param, const Encoder<word> &encoder) {
+    param_ = &param;
+    level_down_consts_.clear();
+    level_down_consts_.resize(param.max_level_ + 1);
+    for (int i = 1; i <= param.max_level_; i++)
+      encoder.EncodeConstant(level_down_consts_.at(i), i, param.GetRescalePrimeProd(i), 1.0);
+  }
+  static void StaticDestroy() {
+    param_ = nullptr;
+    level_down_consts_.clear();
+  }
+  static const Constant<word> &GetLevelDownConst(int level) { return level_down_consts_.at(level); }
+
+  explicit MultiLevelCiphertext(Ct &&ct) {
+    AssertTrue(param_ != nullptr, "MultiLevelCiphertext: StaticInit has not run");
+    AssertTrue(!ct.HasRx(), "MultiLevelCiphertext: Rx is not allowed.");
+    AssertTrue(ct.GetNP().num_aux_ == 0, "MultiLevelCiphertext: Aux primes are not allowed.");
+    const int level = param_->NPToLevel(ct.GetNP());
+    level_map_.try_emplace(level, std::move(ct));
+  }
+  void AllocateLevel(int level) {
+    AssertTrue(!Exists(level), "AddCiphertextAtLevel: Level " + std::to_string(level) + " already exists");
+    level_map_.try_emplace(level, param_->LevelToNP(level, 0));
+  }
+  int GetMaxLevel() const {
+    AssertTrue(!level_map_.empty(), "MultiLevelCiphertext: level_map_ is empty.");
+    return level_map_.rbegin()->first;
+  }
+  int GetMinLevel() const {
+    AssertTrue(!level_map_.empty(), "MultiLevelCiphertext: level_map_ is empty.");
+    return level_map_.begin()->first;
+  }
+  Ct &AtLevel(int level) {
+    AssertTrue(Exists(level), "Level does not exist");
+    return level_map_.at(level);
+  }
+  const Ct &AtLevel(int level) const {
+    AssertTrue(Exists(level), "Level does not exist");
+    return level_map_.at(level);
+  }
+  bool Exists(int level) const { return level_map_.find(level) != level_map_.end(); }
+  void Clear() { level_map_.clear(); }
+
+ private:
+  static inline const Parameter<word> *param_ = nullptr;
+  static inline std::vector<Constant<word>> level_down_consts_{};
+  std::map<int, Ct> level_map_;
 };
 
 // ---------------------------------------------------------------- Context
@@ -791,7 +873,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
   using Const = Constant<word>;
   using Evk = EvaluationKey<word>;
 
-  explicit Context(const Parameter<word> &param) : param_{param} {
+  explicit Context(const Parameter<word> &param, int device = 0) : param_{param} {
     std::vector<int> lc;
     for (auto &c : param.level_config_) {
       lc.push_back(c.first);
@@ -799,7 +881,7 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     }
     std::vector<word> ter = param.ter_primes_;
     if (ter.empty()) ter.push_back(0);
-    CheckAbi(cfhe_context_create(&h_, 0, param.log_degree_, param.main_primes_.data(),
+    CheckAbi(cfhe_context_create(&h_, device, param.log_degree_, param.main_primes_.data(),
                                  param.main_primes_.size(), ter.data(), param.ter_primes_.size(),
                                  param.aux_primes_.data(), param.aux_primes_.size(), lc.data(),
                                  param.level_config_.size(), param.additional_base_.first,
@@ -808,11 +890,13 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     detail::CurrentHandle() = h_;
     Container<word>::SetDegree(param.degree_);
     encoder_ = std::make_unique<Encoder<word>>(param, h_);
+    MultiLevelCiphertext<word>::StaticInit(param, *encoder_);
   }
 
  public:
-  static ContextPtr<word> Create(const Parameter<word> &param) {
-    return ContextPtr<word>(new Context<word>(param));
+  // `device`: the GPU the engine context lives on (the reference is single-device)
+  static ContextPtr<word> Create(const Parameter<word> &param, int device = 0) {
+    return ContextPtr<word>(new Context<word>(param, device));
   }
   Context(const Context &) = delete;
   Context &operator=(const Context &) = delete;
@@ -1082,6 +1166,45 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     out.SetScale(a.GetScale());
     out.SetNumSlots(a.GetNumSlots());
     res = std::move(out);
+  }
+
+  // The key product on the extended basis, before ModDown (reference
+  // include/core/Context.h:421-423, src/core/Context.cpp:649-737):
+  //   a without rx:  accum = <ModUp(a.ax), key> + P * (a.bx, 0)
+  //   a with rx:     accum = <ModUp(a.rx), key> + P * (a.bx, a.ax)
+  // accum carries the level's Q limbs and all auxiliary limbs.
+  void MultKeyNoModDown(Ct &accum, const Ct &a, const Evk &key) const {
+    NPInfo np = a.GetNP();
+    AssertTrue(np.num_aux_ == 0, "MultKeyNoModDown is not supported for ciphertexts with p primes");
+    AssertTrue(&accum != &a, "In-place operation is not supported for MultKeyNoModDown");
+    const int level = param_.NPToLevel(np), beta = cfhe_beta(h_, level);
+    CheckKey(key, level);
+    NPInfo ext(np.num_main_, np.num_ter_, param_.alpha_);
+    const size_t ext_words = (size_t)ext.GetNumTotal() * param_.degree_;
+    DeviceVector<word> mod_up(ext_words * beta);
+    CheckAbi(cfhe_modup(h_, level, mod_up.data(), a.HasRx() ? a.rx_.data() : a.ax_.data()));
+    Ct out(ext);
+    auto kb = KeyPtrs(key.bx_), ka = KeyPtrs(key.ax_);
+    CheckAbi(cfhe_evk_inner(h_, level, out.bx_.data(), out.ax_.data(), mod_up.data(), a.bx_.data(),
+                            a.HasRx() ? a.ax_.data() : nullptr, kb.data(), ka.data(), key.GetNP().num_main_));
+    out.SetScale(a.GetScale());
+    out.SetNumSlots(a.GetNumSlots());
+    accum = std::move(out);
+  }
+
+  // Fills ml_ct with every level from its lowest one down to min_level
+  // (reference src/core/Context.cpp:931-949).
+  void AddLowerLevelsUntil(MultiLevelCiphertext<word> &ml_ct, int min_level) const {
+    if (ml_ct.Exists(min_level)) return;
+    const int max_level = ml_ct.GetMaxLevel(), old_min_level = ml_ct.GetMinLevel();
+    AssertTrue(min_level <= max_level && min_level >= 0,
+               "AddLowerLevelsUntil: Invalid level " + std::to_string(min_level));
+    Ct tmp;
+    for (int i = old_min_level - 1; i >= min_level; i--) {
+      ml_ct.AllocateLevel(i);
+      Mult(tmp, ml_ct.AtLevel(i + 1), MultiLevelCiphertext<word>::GetLevelDownConst(i + 1));
+      Rescale(ml_ct.AtLevel(i), tmp);
+    }
   }
 
   void HRot(Ct &res, const Ct &a, const Evk &rot_key, int rot_dist) const {

@@ -40,6 +40,10 @@ extern "C" {
 typedef struct cfhe_context cfhe_context;
 
 CFHE_API const char *cfhe_last_error(void);
+/* Number of kernels this library has launched in the calling process so far
+ * (all contexts). No counterpart in the reference; benchmarks take the
+ * difference around a timed region to report how many launches it held. */
+CFHE_API unsigned long long cfhe_kernel_launch_count(void);
 
 /* Builds per-prime tables on `device`. level_config holds (num_main, num_ter)
  * per level. Replaces Context<word>::Create + NTTHandler /
@@ -144,6 +148,36 @@ CFHE_API int cfhe_permute(cfhe_context *ctx, uint32_t *dst, const uint32_t *src,
                           const uint32_t *add, uint32_t galois,
                           const int *gidx, int n_limbs);
 CFHE_API uint32_t cfhe_galois_for_rotation(const cfhe_context *ctx, int rot);
+/* Fused n-ary sums over n_polys (1..3) polynomials and n_terms (1..8) terms, one
+ * launch each; `src` is [term * n_polys + poly], `addend` (n_polys pointers or
+ * NULL) an optional extra summand per polynomial. They replace the
+ * reference's variadic kernels and the workers that pick an instantiation:
+ *   cfhe_accum          dst[p] = sum_t src[t][p]
+ *       ElementWiseHandler::Accum / Add (:1246, kernel Sum :32-71)
+ *   cfhe_caccum         dst[p] = sum_t consts[t*n_limbs + l] * src[t][p] (+ addend[p])
+ *       ElementWiseHandler::CAccum (:1355-1394, kernels CPAccum / CPAccumAdd
+ *       <const_accum = true> :225-366); consts are M-form words per term and limb
+ *   cfhe_paccum         dst[p] = sum_t pt[t] (*) src[t][p] (+ addend[p])
+ *       ElementWiseHandler::PAccum (:1396-1435, CPAccum<false>); one plaintext
+ *       polynomial per term, shared by the polynomials
+ *   cfhe_permute_accum  dst[p] = sum_t automorphism_{galois[t]}(src[t][p]) (+ addend[p])
+ *       ElementWiseHandler::PermuteAccum (:1002-1226, kernels :395-501);
+ *       no source may alias its destination. */
+CFHE_API int cfhe_accum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
+                        const uint32_t *const *src, const int *gidx, int n_limbs);
+CFHE_API int cfhe_caccum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
+                         const uint32_t *const *src, const uint32_t *consts,
+                         const uint32_t *const *addend, const int *gidx, int n_limbs);
+CFHE_API int cfhe_paccum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
+                         const uint32_t *const *src, const uint32_t *const *pt,
+                         const uint32_t *const *addend, const int *gidx, int n_limbs);
+CFHE_API int cfhe_permute_accum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
+                                const uint32_t *const *src, const uint32_t *galois,
+                                const uint32_t *const *addend, const int *gidx, int n_limbs);
+/* Device-to-device copy and fill on the context's stream (the reference's
+ * DeviceVector copies, src/core/DeviceVector.cpp, and cudaMemsetAsync calls). */
+CFHE_API int cfhe_copy_d2d(cfhe_context *ctx, void *dst, const void *src, size_t bytes);
+CFHE_API int cfhe_memset(cfhe_context *ctx, void *dst, int value, size_t bytes);
 /* dst = src * X^(N/2): ElementWiseHandler::MultImaginaryUnit (:1673). */
 CFHE_API int cfhe_mul_imag_unit(cfhe_context *ctx, uint32_t *dst,
                                 const uint32_t *src, const int *gidx,

@@ -5,6 +5,7 @@
 // slot (Testbed.h:93); the mean |diff| is printed as precision bits.
 //
 //   basic_test <parameter.json> [--levels 0,1,28 | --all-levels] [--only HMult,HRot]
+#include <algorithm>
 #include <chrono>
 #include <cstring>
 #include <functional>
@@ -277,6 +278,49 @@ int main(int argc, char **argv) {
       tb.CompareMessages("HRot", level, want, res);
     });
   }
+  // Config 3 of the benchmark set: 64 rotations of one ciphertext at the top
+  // level sharing a single ModUp, by powers of two and seeded random offsets,
+  // with Galois keys generated from the secret key; every output is decrypted
+  // and compared with the rotated message (body of the reference's HRot test,
+  // unittest/BasicTest.cpp:376-399, applied to each rotation). Only on request:
+  // 64 keys take a while to generate.
+  if (only.count("HoistedRot64")) {
+    const int num_slots = (1 << tb.log_degree_) / 2, level = max_level;
+    std::vector<int> dists;
+    for (int r = 1; r < num_slots; r <<= 1) dists.push_back(r);
+    uint64_t lcg = 0x9E3779B97F4A7C15ull;
+    while (dists.size() < 64) {
+      lcg = lcg * 6364136223846793005ull + 1442695040888963407ull;
+      const int r = 1 + (int)((lcg >> 33) % (uint64_t)(num_slots - 1));
+      if (std::find(dists.begin(), dists.end(), r) == dists.end()) dists.push_back(r);
+    }
+    std::vector<const EvaluationKey<word> *> keys;
+    for (int r : dists) {
+      tb.interface_->PrepareRotationKey(r, max_level);
+      keys.push_back(&tb.interface_->GetRotationKey(r));
+    }
+    Msg m, res;
+    tb.GenerateRandomMessage(m);
+    Ct c;
+    tb.EncodeAndEncrypt(c, m, level);
+    std::vector<Ct> out;
+    ctx.HoistedRotate(out, c, dists, keys);
+    for (size_t i = 0; i < dists.size(); i++) {
+      Msg want;
+      for (int k = 0; k < num_slots; k++) want.push_back(m[(k + dists[i]) % num_slots]);
+      tb.DecryptAndDecode(res, out[i]);
+      tb.CompareMessages("HoistedRot64 by " + std::to_string(dists[i]), level, want, res);
+    }
+    // and the unhoisted operator gives the same slots for the first and the last distance
+    for (size_t i : {(size_t)0, dists.size() - 1}) {
+      Ct r1;
+      ctx.HRot(r1, c, *keys[i], dists[i]);
+      Msg a1, a2;
+      tb.DecryptAndDecode(a1, r1);
+      tb.DecryptAndDecode(a2, out[i]);
+      tb.CompareMessages("HoistedRot64 vs HRot by " + std::to_string(dists[i]), level, a1, a2);
+    }
+  }
   run("HConj", 0, [&](int level) {
     Msg m, res, want;
     tb.GenerateRandomMessage(m);
@@ -336,6 +380,43 @@ int main(int argc, char **argv) {
     tb.DecryptAndDecode(res, r3);
     tb.CompareMessages("MultUnsafe ct x pt", lo - 1, binary_msg(m1, m2, [](Complex a, Complex b) { return a * b; }),
                        res);
+  });
+  run("MultKeyNoModDown", 1, [&](int level) {
+    // the key product on the extended basis, then ModDown by hand, equals MultKey
+    // (reference src/core/Context.cpp:584-607)
+    Msg m, a1, a2;
+    tb.GenerateRandomMessage(m);
+    Ct c, r, acc;
+    tb.EncodeAndEncrypt(c, m, level);
+    const auto &key = tb.interface_->GetConjugationKey();
+    ctx.MultKey(r, c, key);
+    ctx.MultKeyNoModDown(acc, c, key);
+    Ct down(c.GetNP());
+    CheckAbi(cfhe_moddown(ctx.h_, level, 0, down.bx_.data(), acc.bx_.data(), 1, 0, 0));
+    CheckAbi(cfhe_moddown(ctx.h_, level, 0, down.ax_.data(), acc.ax_.data(), 1, 0, 0));
+    down.SetScale(c.GetScale());
+    tb.DecryptAndDecode(a1, r);
+    tb.DecryptAndDecode(a2, down);
+    tb.CompareMessages("MultKeyNoModDown + ModDown vs MultKey", level, a1, a2);
+  });
+  run("MultiLevel", 2, [&](int level) {
+    if (level > tb.default_encryption_level_) return;
+    Msg m, res;
+    tb.GenerateRandomMessage(m);
+    Ct c;
+    tb.EncodeAndEncrypt(c, m, level);
+    MultiLevelCiphertext<word> ml(std::move(c));
+    ctx.AddLowerLevelsUntil(ml, level - 2);
+    bool ok = ml.GetMaxLevel() == level && ml.GetMinLevel() == level - 2 && ml.Exists(level - 1);
+    for (int l = level; l >= level - 2 && ok; l--) {
+      ok = tb.param_->NPToLevel(ml.AtLevel(l).GetNP()) == l;
+      tb.DecryptAndDecode(res, ml.AtLevel(l));
+      tb.CompareMessages("MultiLevelCiphertext at level " + std::to_string(l), level, m, res);
+    }
+    if (!ok) {
+      std::cout << "[FAIL] MultiLevelCiphertext bookkeeping at level " << level << std::endl;
+      tb.failures++;
+    }
   });
   run("LevelDown", 1, [&](int level) {
     if (level > tb.default_encryption_level_) return;

@@ -127,6 +127,93 @@ int main(int argc, char **argv) {
     Report("EvalPoly Chebyshev degree 15 (level 24)", expect, got, 1e-5);
   }
 
+  if (want("adapters")) {
+    // The reference's extension interfaces (include/extension/{EvalPoly,LinearTransform,Hoist}.h)
+    // as callers of the reference write them.
+    {
+      // EvalPoly object: power-basis coefficients, Compile, Evaluate, PlainEvaluate
+      const int level = 20;
+      std::vector<double> c = {0.3, -0.7, 0.11, 0.5, -0.25, 0.06, 0.02, -0.13};
+      const double s = (double)(UINT64_C(1) << (int)std::lround(std::log2(scale_of(level))));
+      EvalPoly<word> poly(c, level, s, s, false);
+      if (poly.GetPolyDegree() != 7) {
+        std::cout << "[FAIL] EvalPoly::GetPolyDegree" << std::endl;
+        failures++;
+      }
+      poly.Compile(ctx);
+      Msg x, got, expect;
+      random_msg(x, -1, 1, false);
+      for (auto &v : x) expect.push_back(Complex(poly.PlainEvaluate(v.real()), 0));
+      Ct ct, out;
+      encrypt(ct, x, level, s);
+      poly.Evaluate(ctx, out, ct, ui.GetMultiplicationKey());
+      decrypt(got, out);
+      Report("EvalPoly(coefficients, level, scale, target).Compile/Evaluate, power basis degree 7", expect, got, 1e-5);
+      // basis conversion is an identity on the function
+      EvalPoly<word> twin(c, level, s, s, false);
+      twin.ConvertToChebyshevBasis();
+      double worst = 0;
+      for (double t : {-1.0, -0.3, 0.0, 0.77, 1.0}) worst = std::max(worst, std::abs(twin.PlainEvaluate(t) - poly.PlainEvaluate(t)));
+      twin.ConvertToNormalBasis();
+      for (double t : {-1.0, 0.4, 1.0}) worst = std::max(worst, std::abs(twin.PlainEvaluate(t) - poly.PlainEvaluate(t)));
+      std::cout << (worst < 1e-12 ? "[ OK ] " : "[FAIL] ") << "EvalPoly basis conversions, max difference " << worst << std::endl;
+      if (!(worst < 1e-12)) failures++;
+    }
+    {
+      // LinearTransform(context, matrix, pt_level, pt_scale, bs, gs, pre_rotation, additional_pt_rot)
+      const int level = 18, pre = 3, extra = 5;
+      StripedMatrix M(n, n);
+      for (int i : {3, 4, 5, 7, 11, 19, 35}) {  // offsets i - pre are 0, 1, 2, 4, 8, 16, 32
+        auto &d = M[i];
+        Random::SampleUniformComplex(d.data(), n, -1.0, 1.0);
+      }
+      Msg z, got, expect(n, Complex(0, 0));
+      random_msg(z, -1, 1, true);
+      for (const auto &[i, d] : M)
+        for (int p = 0; p < n; p++) expect[p] += d[(p + extra) % n] * z[((p + i - pre) % n + n) % n];
+      const double s = scale_of(level), pt_scale = param->GetRescalePrimeProd(level);
+      Ct ct, out;
+      encrypt(ct, z, level, s);
+      LinearTransform<word> lt(ctx, M, level, pt_scale, 8, 8, pre, extra);
+      EvkRequest req;
+      lt.AddRequiredRotations(req);
+      ui.PrepareRotationKey(req);
+      lt.Evaluate(ctx, out, ct, ui.GetEvkMap());
+      ctx->AssertSameScale(out.GetScale(), s);
+      decrypt(got, out);
+      Report("LinearTransform reference constructor (bs 8, gs 8, pre_rotation 3, additional_pt_rot 5)", expect, got, 1e-4);
+      if (!lt.IsUsingBSGS() || lt.GetBS() != 8 || lt.GetGS() != 8 || lt.GetPreRotationAmount() != pre) {
+        std::cout << "[FAIL] LinearTransform accessors" << std::endl;
+        failures++;
+      }
+    }
+    {
+      // HoistHandler(context, hoist_map, pt_level, pt_scale): plaintext [gs][bs] multiplies
+      // rot_bs(input) and the sum over bs is rotated by gs
+      const int level = 16;
+      PlainHoistMap map;
+      Msg z, got, expect(n, Complex(0, 0));
+      random_msg(z, -1, 1, true);
+      for (int gs : {0, 8, 16})
+        for (int bs : {0, 1, 2, 5}) {
+          Msg pt(n);
+          Random::SampleUniformComplex(pt.data(), n, -1.0, 1.0);
+          for (int p = 0; p < n; p++) expect[p] += pt[(p + gs) % n] * z[(p + gs + bs) % n];
+          map[gs][bs] = std::move(pt);
+        }
+      const double s = scale_of(level), pt_scale = param->GetRescalePrimeProd(level);
+      Ct ct, out;
+      encrypt(ct, z, level, s);
+      HoistHandler<word> hoist(ctx, map, level, pt_scale);
+      EvkRequest req;
+      hoist.AddRequiredRotations(req);
+      ui.PrepareRotationKey(req);
+      hoist.Evaluate(ctx, out, ct, ui.GetEvkMap());
+      decrypt(got, out);
+      Report("HoistHandler (3 giant x 4 baby plaintexts)", expect, got, 1e-4);
+    }
+  }
+
   if (want("evalmod")) {
     const BootParameter &bp = boot_param;
     const int level = bp.GetEvalModStartLevel();

@@ -141,11 +141,16 @@ def build_boot_test(pkg):
                                                      ("bootparam_30.json", "boot", 12.0)])
 def test_bootstrapping(pkg, param_set, only, min_bits):
     """Building blocks and full bootstrapping of 2^15 random complex slots on
-    the parameter sets the reference's boot_test runs; the reference accepts
-    1e-3 per component (unittest/Testbed.h:93), its own result on B200 with
-    bootparam_40 is 8e-7 at worst, 21.9 bits on average. The floor is the noise
-    of a fresh encryption at the set's scale (2^40, 2^35, 2^30), hence the
-    per-set minimum."""
+    the parameter sets the reference's boot_test runs
+    (unittest/Bootstrapping.cpp:43-51). The reference accepts 1e-3 per
+    component (unittest/Testbed.h:93); the bound asserted here is tighter: the
+    mean precision, -log2(mean |error| per slot), must be within 0.5 bit of
+    what the reference's own BootContext::Boot reaches on the same parameter
+    set, measured in this test by running the reference library when it has
+    been built. The per-set floor (the noise of a fresh encryption at the
+    set's scale 2^40, 2^35, 2^30) is kept as a second, absolute check."""
+    import math
+    from oracle import ref_binding
     exe = build_boot_test(pkg)
     cmd = [exe, os.path.join(pkg.PARAM_DIR, param_set)] + (["--only", only] if only else [])
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
@@ -154,4 +159,12 @@ def test_bootstrapping(pkg, param_set, only, min_bits):
     assert r.returncode == 0, "boot_test reported failures"
     assert "PASSED" in r.stdout and "[FAIL]" not in r.stdout
     m = re.search(r"Boot, 2\^15 complex slots.*precision ([0-9.]+) bits", r.stdout)
-    assert m and float(m.group(1)) > min_bits
+    assert m
+    bits = float(m.group(1))
+    assert bits > min_bits
+    if not ref_binding.available():
+        pytest.skip("reference library not built: the 0.5-bit comparison needs oracle/_ref")
+    ref = ref_binding.boot(pkg.load_params(param_set), iters=1)
+    ref_bits = -math.log2(ref["mean_err"])
+    print(f"{param_set}: engine {bits:.2f} bits, reference {ref_bits:.2f} bits")
+    assert bits >= ref_bits - 0.5, (bits, ref_bits)

@@ -50,6 +50,22 @@ def test_basic_test_bodies(pkg, param_set):
 
 
 @pytest.mark.gpu
+def test_sixty_four_hoisted_rotations_with_generated_keys(pkg):
+    """Config 3 as stated: one ciphertext at the top level of bootparam_40,
+    64 rotations (powers of two and seeded random offsets) through one shared
+    ModUp with Galois keys generated from the secret key; each output decrypts
+    to the rotated message within the reference's 1e-3."""
+    exe = build_driver(pkg)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--only", "HoistedRot64"],
+                       capture_output=True, text=True, timeout=1500)
+    print(r.stdout[-6000:])
+    print(r.stderr[-2000:])
+    assert r.returncode == 0, "HoistedRot64 reported failures"
+    assert "PASSED" in r.stdout and "[FAIL]" not in r.stdout
+    assert r.stdout.count("HoistedRot64 by") == 64
+
+
+@pytest.mark.gpu
 def test_wrong_usage_exits_like_the_reference(pkg):
     """A scale mismatch prints an error and exits non-zero (the reference's
     AssertTrue -> exit(EXIT_FAILURE), include/common/Assert.h:9-21)."""

@@ -39,6 +39,37 @@ def test_noalloc_moddown_equals_regular_twice(engine40, oracle40):
         assert e.torch.equal(got, want), (level, kind)
 
 
+def test_noalloc_moddown_on_a_fresh_context_allocates_nothing(pkg, params40, oracle40):
+    """A context that has run no other operator (its workspace arena is still
+    empty) converts through the allocation-free entry point and returns the
+    golden model's words; a second call leaves the amount of free device
+    memory exactly where the first left it."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    e = pkg.Engine(params40, device=0)
+    rng = np.random.default_rng(778)
+    level, kind = 16, 2
+    full = e.level_limbs(level, 12)
+    host = rand_limbs(rng, oracle40.primes, full, e.n)
+    src = e.to_dev(host)
+    got = e.empty(len(e.level_limbs(level - 1)), e.n)
+    got.fill_(-1)
+    e.moddown_noalloc_(level, kind, got, src)   # first call on this context: nothing else has run
+    e.synchronize()
+    assert np.array_equal(e.to_host(got), oracle40.moddown(level, kind, host))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    got.fill_(-1)
+    e.moddown_noalloc_(level, kind, got, src)
+    e.synchronize()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert np.array_equal(e.to_host(got), oracle40.moddown(level, kind, host))
+    e.close()
+
+
 def test_noalloc_moddown_rejects_bad_requests(engine40, pkg):
     e = engine40
     a = e.empty(2, e.n)
