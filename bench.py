@@ -423,12 +423,23 @@ def bench_reference_cuda(eng, torch, params, steps, with_boot=True):
     b = torch.empty_like(a)
     torch.cuda.synchronize()
     ntt_us = ref.ntt_batch_time(a, b, NTT_POLYS, NTT_LIMBS - T, T, max(steps, 2))
+    # config 3: 64 rotations at the top level, unhoisted and with the reference's hoisted baby step
+    rots = [1 << i for i in range(15)]
+    r3 = np.random.default_rng(0xC0FFEE03)
+    while len(rots) < 64:
+        r = int(r3.integers(1, N // 2))
+        if r not in rots:
+            rots.append(r)
+    hrot_us, hoisted_us = ref.rotations_time(HM_LEVEL, ins[0], ins[1], kb, ka, M, rots, iters=2)
     ref.close()
     boot = None
     if with_boot:
         torch.cuda.empty_cache()
         boot = ref_binding.boot(params, iters=min(max(steps, 2), 10))
     return {"bootstrap": boot, "hmult_us": hm_us, "hmult_words_equal_engine": same,
+            "rotations64_unhoisted_ms": hrot_us / 1e3, "rotations64_hoisted_baby_step_ms": hoisted_us / 1e3,
+            "rotations_note": "64 x Context::HRot, and HoistHandler::EvaluateBabyStep (one shared ModUp; its "
+                              "outputs stay on the extended basis, no ModDown per rotation)",
             "ntt_fwd_inv_us": ntt_us, "ntt_GBps": NTT_BYTES_PER_STEP / (ntt_us * 1e-6) / 1e9,
             "how": "unmodified reference sources compiled for sm_100a, legacy stream, CUDA events"}
 

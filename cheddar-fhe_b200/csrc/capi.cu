@@ -563,6 +563,41 @@ int cfhe_permute_accum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n
   { int r_ = launch_nary(h->c, a); h->c.mark("permute"); return r_; }
 }
 
+int cfhe_sample_uniform(cfhe_context *h, uint32_t *dst, const int *gidx, int n_limbs,
+                        unsigned long long seed, unsigned int stream) {
+  CFHE_ENTER(h);
+  { int r_ = launch_sample_uniform(h->c, dst, gidx, n_limbs, seed, stream); h->c.mark("sample"); return r_; }
+}
+
+int cfhe_sample_error(cfhe_context *h, uint32_t *dst, const int *gidx, int n_limbs, double sigma,
+                      unsigned long long seed, unsigned int stream) {
+  CFHE_ENTER(h);
+  { int r_ = launch_sample_error(h->c, dst, gidx, n_limbs, sigma, seed, stream); h->c.mark("sample"); return r_; }
+}
+
+int cfhe_error_cdf(double sigma, unsigned long long *cdf, int entries) {
+  if (!cdf || entries != kErrorCdfEntries) return fail("cfhe_error_cdf: the table has 97 entries");
+  if (!(sigma > 0.0) || sigma > 8.0) return fail("error sampling: standard deviation must be in (0, 8]");
+  static_assert(sizeof(unsigned long long) == sizeof(uint64_t), "64-bit table entries");
+  error_cdf_table(sigma, reinterpret_cast<uint64_t *>(cdf));
+  return 0;
+}
+
+int cfhe_encrypt(cfhe_context *h, uint32_t *b, const uint32_t *a, const uint32_t *s, const uint32_t *e,
+                 const uint32_t *m, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  { int r_ = launch_encrypt(h->c, b, a, s, e, m, gidx, n_limbs); h->c.mark("encrypt"); return r_; }
+}
+
+int cfhe_add_evk_part(cfhe_context *h, uint32_t *bx, const uint32_t *s_target, const uint32_t *p_prod,
+                      const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!p_prod) return fail("null argument");
+  EwArgs e;
+  if (int r = fill_rows(h->c, e, bx, s_target, bx, p_prod, gidx, n_limbs)) return r;
+  { int r_ = launch_ew(h->c, EW_MULC_ADD, e); h->c.mark("elementwise"); return r_; }
+}
+
 int cfhe_copy_d2d(cfhe_context *h, void *dst, const void *src, size_t bytes) {
   CFHE_ENTER(h);
   if (!dst || !src) return fail("null argument");
@@ -692,6 +727,16 @@ int cfhe_beta(const cfhe_context *h, int level) {
   const LevelPlan *lp = h->c.plan(level);
   if (!lp) return fail("invalid level");
   return lp->beta;
+}
+
+int cfhe_pseudo_modup(cfhe_context *h, int level, uint32_t *dst, const uint32_t *src) {
+  CFHE_ENTER(h);
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return -1;
+  if (!dst || !src) return fail("null argument");
+  EwArgs e;
+  if (int r = fill_rows(h->c, e, dst, src, nullptr, lp->p_mont.data(), lp->q_g.data(), lp->nq)) return r;
+  { int r_ = launch_ew(h->c, EW_MULC, e); h->c.mark("elementwise"); return r_; }
 }
 
 int cfhe_modup(cfhe_context *h, int level, uint32_t *dst, const uint32_t *src) {

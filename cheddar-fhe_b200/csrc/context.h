@@ -102,8 +102,9 @@ struct Context {
   bool use_fused_lt = true;         // baby steps and plaintext accumulation in one kernel (CFHE_LT=unfused disables)
   bool use_pdl = true;              // programmatic dependent launch between the kernels of a stream (CFHE_PDL=0 disables)
   bool use_twopass_ntt = true;      // two-pass NTT meeting in L2 (CFHE_NTT=cluster selects the cluster kernels)
-  // Pipelined NTT (ntt_tiled.cu), selected by CFHE_NTT=tiled
-  bool use_tiled_ntt = false;
+  // Pipelined NTT (ntt_tiled.cu): 0 never, 1 when the call batches enough limb
+  // transforms per prime to amortise its set-up (the default), 2 always
+  int ntt_policy = 1;
   int ntt_chunk = 0;                // limb transforms per launch pair, so that the passes meet in L2 (CFHE_NTT_CHUNK)
   int ntt_unit = 0;                 // limb transforms of one prime per CTA (CFHE_NTT_UNIT)
   std::vector<uint32_t> inv_w1;     // per prime: entry 1 of the inverse twiddle table (the last inverse stage's twiddle)

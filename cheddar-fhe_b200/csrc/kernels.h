@@ -151,6 +151,15 @@ int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
 int launch_nary(const Context &ctx, const NaryArgs &args);
+// sampling.cu: client-side sampling and encryption
+constexpr int kErrorCdfEntries = 97;
+void error_cdf_table(double sigma, uint64_t *cdf);
+int launch_sample_uniform(const Context &c, uint32_t *dst, const int *gidx, int n_limbs, uint64_t seed,
+                          uint32_t stream);
+int launch_sample_error(const Context &c, uint32_t *dst, const int *gidx, int n_limbs, double sigma,
+                        uint64_t seed, uint32_t stream);
+int launch_encrypt(const Context &c, uint32_t *b, const uint32_t *a, const uint32_t *s, const uint32_t *e,
+                   const uint32_t *m, const int *gidx, int n_limbs);
 int launch_inner(const Context &ctx, const InnerArgs &args);
 int launch_bconv(const Context &ctx, const BconvArgs &args);
 int launch_bconv_tc(const Context &ctx, const BconvTcArgs &args);

@@ -185,7 +185,7 @@ __global__ void __cluster_dims__(kClusterSize, 1, 1)
 }  // namespace
 
 int launch_ntt(const Context &ctx, const NttArgs &args, bool inverse) {
-  if (ctx.use_tiled_ntt && ntt_tiled_usable(ctx, args)) return launch_ntt_tiled(ctx, args, inverse);
+  if (ctx.ntt_policy && ntt_tiled_usable(ctx, args)) return launch_ntt_tiled(ctx, args, inverse);
   if (ctx.use_twopass_ntt) return launch_ntt_twopass(ctx, args, inverse);
   static PerDeviceOnce once;
   if (int r = once.run(ctx.device, [] {

@@ -436,13 +436,19 @@ __device__ __forceinline__ void fwd_rows_finish(const NttArgs &a, const Member &
 
 // v holds the member's words as the caller took them out of the row buffer:
 // forward the strided set (g + 16k), inverse the block (16g .. 16g+15).
-template <bool INV, bool FAST>
+// `release` hands the row buffer back for refilling. It runs after the first
+// phase, whose butterflies have consumed every loaded word: the shared-memory
+// loads have then completed, not merely been issued, before the asynchronous
+// copy engine (which does not queue behind them) may overwrite the buffer.
+template <bool INV, bool FAST, typename Release>
 __device__ __forceinline__ void rows_body(const NttArgs &a, const Member &m, uint32_t q, int R, int rho, int g,
-                                          uint32_t *ex, const TwLevels &strided, const Tw *tb, uint32_t *v) {
+                                          uint32_t *ex, const TwLevels &strided, const Tw *tb, uint32_t *v,
+                                          Release release) {
   const uint32_t q2 = 2 * q;
   uint32_t *row = ex + rho * kRowStride;
   if constexpr (!INV) {
     ct_radix16_s<FAST>(v, strided, q, q2);
+    release();
 #pragma unroll
     for (int k = 0; k < 16; k++) row[g + 20 * k] = v[k];
     __syncwarp();  // a row lives in one half-warp
@@ -464,6 +470,7 @@ __device__ __forceinline__ void rows_body(const NttArgs &a, const Member &m, uin
     for (int i = 0; i < 4; i++) o[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   } else {
     gs_radix16_pre<FAST>(v, tb, q, q2);
+    release();
 #pragma unroll
     for (int i = 0; i < 4; i++)
       reinterpret_cast<uint4 *>(row + 20 * g)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -570,20 +577,23 @@ __global__ void __launch_bounds__(kThreads, 3)
         v[4 * c + 3] = w.w;
       }
     }
-    if (i + 2 < cnt) {
-      __syncthreads();  // every thread has taken its words out of the buffer
-      if (tid < 32) {
-        if (tid == 0) mbar_expect_tx(smem_u32(&full[b]), kTile * kRowWords * 4);
-        __syncwarp();
-        if (tid < kTile)
-          bulk_load(smem_u32(rowbuf + b * kRowBufWords + tid * kRowPitch), tile_src(ahead) + tid * kRowWords,
-                    kRowWords * 4, smem_u32(&full[b]));
+    auto release = [&]() {
+      if (i + 2 < cnt) {
+        fence_async_smem();
+        __syncthreads();  // every thread has consumed its words of the buffer
+        if (tid < 32) {
+          if (tid == 0) mbar_expect_tx(smem_u32(&full[b]), kTile * kRowWords * 4);
+          __syncwarp();
+          if (tid < kTile)
+            bulk_load(smem_u32(rowbuf + b * kRowBufWords + tid * kRowPitch), tile_src(ahead) + tid * kRowWords,
+                      kRowWords * 4, smem_u32(&full[b]));
+        }
       }
-    }
+    };
     if (fast)
-      rows_body<INV, true>(a, m, q, R, rho, g, ex, strided, tb, v);
+      rows_body<INV, true>(a, m, q, R, rho, g, ex, strided, tb, v, release);
     else
-      rows_body<INV, false>(a, m, q, R, rho, g, ex, strided, tb, v);
+      rows_body<INV, false>(a, m, q, R, rho, g, ex, strided, tb, v, release);
     next_member(m, a.n_polys);
   }
 }
@@ -642,7 +652,12 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // false: the call has to take the plain two-pass kernels (operands the
 // asynchronous copies cannot address)
 bool ntt_tiled_usable(const Context &ctx, const NttArgs &args) {
-  (void)ctx;
+  // Measured on B200: the pipelined kernels win once a prime's twiddles serve
+  // four or more limb transforms and the call is large enough to fill the GPU
+  // several times over (16 polynomials x 40 limbs: 158 / 151 us against 195 /
+  // 208 us); on the single-ciphertext shapes of HMult (one to three copies of
+  // a prime per call) the plain two-pass kernels are 5 to 15 % faster.
+  if (ctx.ntt_policy == 1 && (args.n_polys < 4 || args.n_limbs * args.n_polys < 256)) return false;
   if (!aligned16(args.src) || !aligned16(args.dst)) return false;
   if (args.n_polys > 1 && ((args.src_poly_stride & 3) || (args.dst_poly_stride & 3))) return false;
   if (args.n_polys > 1 && (args.src_poly_stride <= 0 || args.dst_poly_stride <= 0)) return false;

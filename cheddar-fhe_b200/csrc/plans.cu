@@ -101,12 +101,13 @@ int build_plans(Context &c) {
   c.use_pdl = !(pdl && std::string(pdl) == "0");
   const char *ntt_mode = getenv("CFHE_NTT");
   c.use_twopass_ntt = !(ntt_mode && std::string(ntt_mode) == "cluster");
-  c.use_tiled_ntt = ntt_mode && std::string(ntt_mode) == "tiled";
+  // CFHE_NTT: "tiled" = always the pipelined kernels, "twopass" / "cluster" = never, otherwise by shape
+  c.ntt_policy = !ntt_mode ? 1 : std::string(ntt_mode) == "tiled" ? 2 : 0;
   {
     const char *chunk = getenv("CFHE_NTT_CHUNK");
     const char *unit = getenv("CFHE_NTT_UNIT");
-    c.ntt_chunk = chunk ? atoi(chunk) : 256;
-    if (c.ntt_chunk < 1 || c.ntt_chunk > 4096) c.ntt_chunk = 256;
+    c.ntt_chunk = chunk ? atoi(chunk) : 320;
+    if (c.ntt_chunk < 1 || c.ntt_chunk > 4096) c.ntt_chunk = 320;
     c.ntt_unit = unit ? atoi(unit) : 4;
     if (c.ntt_unit < 1 || c.ntt_unit > 255) c.ntt_unit = 4;
   }

@@ -496,6 +496,7 @@ class EvaluationKey : public Container<word> {
 class Random {
  public:
   static void Seed(uint64_t s) { gen_.seed(s); }
+  static uint64_t Draw64() { return gen_(); }
   template <typename word>
   static void SampleUniformWord(word *p, int n, word lo, word hi) {
     std::uniform_int_distribution<word> d(lo, hi);
@@ -1574,14 +1575,12 @@ class UserInterface {
     ctxt.SetNumSlots(ptxt.GetNumSlots());
     auto g = param.GetLimbIndices(np);
     SampleRandomPolynomial(ctxt.ax_, np);
-    Dv ex, as(g.size() * param.degree_);
+    Dv ex;
     SampleError(ex, np);
     Dv s = SecretLimbs(main_secret_, np);
-    cfhe_context *h = context_->h_;
-    // b = m - a*s + e  (reference kernel Encrypt, src/UserInterface.cu:17-50)
-    CheckAbi(cfhe_binary(h, 3, as.data(), ctxt.ax_.data(), s.data(), g.data(), g.size()));
-    CheckAbi(cfhe_binary(h, 1, ctxt.bx_.data(), ptxt.mx_.data(), as.data(), g.data(), g.size()));
-    CheckAbi(cfhe_binary(h, 0, ctxt.bx_.data(), ctxt.bx_.data(), ex.data(), g.data(), g.size()));
+    // b = m - a*s + e in one launch (reference kernel Encrypt, src/UserInterface.cu:17-50)
+    CheckAbi(cfhe_encrypt(context_->h_, ctxt.bx_.data(), ctxt.ax_.data(), s.data(), ex.data(), ptxt.mx_.data(),
+                          g.data(), g.size()));
     context_->Synchronize();
   }
 
@@ -1622,6 +1621,7 @@ class UserInterface {
                           cfhe_galois_for_rotation(context_->h_, half - rot_idx), g.data(), g.size()));
     PrepareEvk(rot_idx, GetNPForEvk(max_level), s_rot, main_secret_);
   }
+  void UseDeviceSampling(bool on) { device_sampling_ = on; }
   void PrepareRotationKey(const EvkRequest &req) {
     for (auto &[rot, level] : req)
       if (evk_map_.find(rot) == evk_map_.end()) PrepareRotationKey(rot, level);
@@ -1708,25 +1708,35 @@ class UserInterface {
     evk_map_.erase(key_idx);
     evk_map_.try_emplace(key_idx, np, beta);
     auto &evk = evk_map_.at(key_idx);
-    Dv as(g.size() * n);
     for (int i = 0; i < beta; i++) {
       SampleRandomPolynomial(evk.ax_[i], np);
       Dv ex;
       SampleError(ex, np);
-      CheckAbi(cfhe_binary(h, 3, as.data(), evk.ax_[i].data(), s_enc.data(), g.data(), g.size()));
-      CheckAbi(cfhe_binary(h, 1, evk.bx_[i].data(), ex.data(), as.data(), g.data(), g.size()));
+      // an encryption of zero (EncryptZero, src/UserInterface.cu:55-80) plus
+      // P * s_target on the digit's own limbs (AddEvkPart, :82-108)
+      CheckAbi(cfhe_encrypt(h, evk.bx_[i].data(), evk.ax_[i].data(), s_enc.data(), ex.data(), nullptr, g.data(),
+                            g.size()));
       const int lo = i * alpha, hi = Min((i + 1) * alpha, num_q);
-      word *part = evk.bx_[i].data() + (size_t)lo * n;
-      CheckAbi(cfhe_const_op(h, 4, part, s_tgt.data() + (size_t)lo * n, part, p_prod.data() + lo,
-                             g.data() + lo, hi - lo));
+      CheckAbi(cfhe_add_evk_part(h, evk.bx_[i].data() + (size_t)lo * n, s_tgt.data() + (size_t)lo * n,
+                                 p_prod.data() + lo, g.data() + lo, hi - lo));
       context_->Synchronize();
     }
   }
 
+  // Uniform ring element and error polynomial. By default the words are
+  // generated on the device (cfhe_sample_uniform / cfhe_sample_error) from a
+  // 64-bit seed drawn from the host generator, so Random::Seed still fixes
+  // everything; UseDeviceSampling(false) restores the reference's host
+  // sampling and upload (src/UserInterface.cu:223-276).
   void SampleRandomPolynomial(Dv &poly, const NPInfo &np) const {
     const auto &param = context_->param_;
     const int n = param.degree_;
     auto g = param.GetLimbIndices(np);
+    if (device_sampling_) {
+      poly.resize(g.size() * n);
+      CheckAbi(cfhe_sample_uniform(context_->h_, poly.data(), g.data(), g.size(), Random::Draw64(), 0));
+      return;
+    }
     std::vector<word> host(g.size() * n);
     for (size_t i = 0; i < g.size(); i++) Random::SampleUniformBelow(host.data() + i * n, n, all_primes_[g[i]]);
     CopyHostToDevice(poly, host);
@@ -1736,14 +1746,20 @@ class UserInterface {
     const auto &param = context_->param_;
     const int n = param.degree_;
     auto g = param.GetLimbIndices(np);
-    std::vector<int> err(n);
-    Random::SampleDiscreteNormal(err.data(), n, 0, kErrorStandardDeviation);
-    std::vector<word> host(g.size() * n);
-    for (size_t i = 0; i < g.size(); i++) {
-      const word q = all_primes_[g[i]];
-      for (int j = 0; j < n; j++) host[i * n + j] = err[j] < 0 ? q - (word)(-err[j]) : (word)err[j];
+    if (device_sampling_) {
+      poly.resize(g.size() * n);
+      CheckAbi(cfhe_sample_error(context_->h_, poly.data(), g.data(), g.size(), kErrorStandardDeviation,
+                                 Random::Draw64(), 1));
+    } else {
+      std::vector<int> err(n);
+      Random::SampleDiscreteNormal(err.data(), n, 0, kErrorStandardDeviation);
+      std::vector<word> host(g.size() * n);
+      for (size_t i = 0; i < g.size(); i++) {
+        const word q = all_primes_[g[i]];
+        for (int j = 0; j < n; j++) host[i * n + j] = err[j] < 0 ? q - (word)(-err[j]) : (word)err[j];
+      }
+      CopyHostToDevice(poly, host);
     }
-    CopyHostToDevice(poly, host);
     CheckAbi(cfhe_ntt(context_->h_, poly.data(), poly.data(), g.data(), g.size(), 1, 0, 0, 1));
   }
 
@@ -1757,6 +1773,7 @@ class UserInterface {
   }
 
   ContextPtr<word> context_;
+  bool device_sampling_ = true;
   NPInfo all_np_;
   std::vector<word> all_primes_;  // every prime, global order (index = limb index g)
   Dv main_secret_;                // NTT, M-form, on every prime

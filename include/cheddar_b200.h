@@ -174,6 +174,34 @@ CFHE_API int cfhe_paccum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, i
 CFHE_API int cfhe_permute_accum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
                                 const uint32_t *const *src, const uint32_t *galois,
                                 const uint32_t *const *addend, const int *gidx, int n_limbs);
+/* Client-side sampling and encryption on the device (the reference samples on
+ * the host and uploads: src/UserInterface.cu:223-276, 366-458; Random,
+ * include/Random.h). Words are a pure function of (seed, stream, prime index,
+ * word index) through the Philox-4x32-10 counter-based generator, so a draw
+ * can be reproduced anywhere.
+ *   cfhe_sample_uniform  n_limbs limbs of residues uniform in [0, q) (exactly
+ *       uniform: multiply-and-reject). Replaces Random::SampleUniformWord +
+ *       upload in UserInterface::SampleRandomPolynomial.
+ *   cfhe_sample_error    ONE polynomial of rounded-normal integers (standard
+ *       deviation sigma <= 8, tail cut at +-48), written mod every prime of the
+ *       list in coefficient order; the caller transforms it (cfhe_ntt with
+ *       mont_conv). Replaces Random::SampleDiscreteNormal + upload.
+ *   cfhe_error_cdf       the 97-entry cumulative table (64-bit fixed point)
+ *       the error sampler walks, for hosts that want to reproduce a draw.
+ *   cfhe_encrypt         b = m + e - a * s, m == NULL for an encryption of
+ *       zero: the reference's Encrypt / EncryptZero kernels (:17-80); s in
+ *       M-form, everything in the NTT domain.
+ *   cfhe_add_evk_part    bx += p_prod[l] * s_target on the listed limbs: the
+ *       reference's AddEvkPart kernel (:82-108); p_prod in M-form. */
+CFHE_API int cfhe_sample_uniform(cfhe_context *ctx, uint32_t *dst, const int *gidx, int n_limbs,
+                                 unsigned long long seed, unsigned int stream);
+CFHE_API int cfhe_sample_error(cfhe_context *ctx, uint32_t *dst, const int *gidx, int n_limbs,
+                               double sigma, unsigned long long seed, unsigned int stream);
+CFHE_API int cfhe_error_cdf(double sigma, unsigned long long *cdf, int entries);
+CFHE_API int cfhe_encrypt(cfhe_context *ctx, uint32_t *b, const uint32_t *a, const uint32_t *s,
+                          const uint32_t *e, const uint32_t *m, const int *gidx, int n_limbs);
+CFHE_API int cfhe_add_evk_part(cfhe_context *ctx, uint32_t *bx, const uint32_t *s_target,
+                               const uint32_t *p_prod, const int *gidx, int n_limbs);
 /* Device-to-device copy and fill on the context's stream (the reference's
  * DeviceVector copies, src/core/DeviceVector.cpp, and cudaMemsetAsync calls). */
 CFHE_API int cfhe_copy_d2d(cfhe_context *ctx, void *dst, const void *src, size_t bytes);
@@ -207,6 +235,10 @@ CFHE_API int cfhe_beta(const cfhe_context *ctx, int level);
  * this level are left untouched. */
 CFHE_API int cfhe_modup(cfhe_context *ctx, int level, uint32_t *dst,
                         const uint32_t *src);
+/* ModSwitchHandler::PseudoModUp (:413-428): dst = (P mod q_l) * src on the
+ * level's Q limbs, the extended-basis image of a polynomial that needs no
+ * conversion (used by the reference's hoisting for the unrotated term). */
+CFHE_API int cfhe_pseudo_modup(cfhe_context *ctx, int level, uint32_t *dst, const uint32_t *src);
 /* type 0 ModDown (:511-527), 1 Rescale (:529-545), 2 ModDownAndRescale
  * (:547-563), all through ModDownWorker (:566-684); n_polys polynomials with
  * the given strides (words) are processed together. */

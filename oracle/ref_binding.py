@@ -62,6 +62,20 @@ class Reference:
         assert rc == 0, rc
         return usec.value
 
+    def rotations_time(self, level, bx, ax, kb, ka, key_main, rots, iters=3):
+        """Config 3 on the reference: (microseconds for len(rots) x Context::HRot,
+        microseconds for one hoisted HoistHandler::EvaluateBabyStep over the
+        same rotations); see ref_rotations_time in ref_driver.cu."""
+        beta = len(kb)
+        pb = (C.c_void_p * beta)(*[t.data_ptr() for t in kb])
+        pa = (C.c_void_p * beta)(*[t.data_ptr() for t in ka])
+        r = np.ascontiguousarray(rots, dtype=np.int32)
+        usec = (C.c_float * 2)()
+        rc = self.L.ref_rotations_time(self.h, level, self._p(bx), self._p(ax), pb, pa, key_main, beta,
+                                       len(r), r.ctypes.data_as(C.c_void_p), iters, usec)
+        assert rc == 0, rc
+        return float(usec[0]), float(usec[1])
+
     def ntt_batch_time(self, buf_a, buf_b, polys, num_main, num_ter, iters):
         usec = C.c_float(0)
         rc = self.L.ref_ntt_batch_time(self.h, self._p(buf_a), self._p(buf_b), polys, num_main, num_ter,

@@ -19,7 +19,9 @@
 #include "Random.h"
 #include "UserInterface.h"
 #include "core/Context.h"
+#include "core/EvkMap.h"
 #include "extension/BootContext.h"
+#include "extension/Hoist.h"
 
 using word = uint32_t;
 using namespace cheddar;
@@ -191,6 +193,59 @@ int ref_ntt_batch_time(RefHandle *h, word *buf_a, word *buf_b, int polys, int nu
   *usec = ms * 1000.0f / iters;
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
+  return (int)cudaDeviceSynchronize();
+}
+
+// Config 3 on the reference: n_rot rotations of one ciphertext at `level`.
+//   usec[0]: n_rot calls of Context::HRot (src/core/Context.cpp:776-791), one
+//            full key switch per rotation;
+//   usec[1]: HoistHandler::EvaluateBabyStep (src/extension/Hoist.cu:578-691),
+//            the reference's hoisted form: one ModUp shared by all rotations.
+// The same key digits are installed for every distance (timing does not depend
+// on key values). Mean device time of one sweep in microseconds, CUDA events
+// on the legacy stream after warm-up sweeps.
+int ref_rotations_time(RefHandle *h, int level, const word *b, const word *a, const word *const *kb,
+                       const word *const *ka, int key_main, int beta, int n_rot, const int *rots,
+                       int iters, float *usec) {
+  Ciphertext<word> x, res;
+  fill_ct(h, x, level, b, a);
+  const int num_slots = h->param->degree_ / 2;
+  x.SetNumSlots(num_slots);
+  EvkMap<word> keys;
+  for (int i = 0; i < n_rot; i++) {
+    EvaluationKey<word> key;
+    fill_key(h, key, key_main, kb, ka, beta);
+    keys.emplace(rots[i], std::move(key));
+  }
+  auto timed = [&](auto &&sweep, float *out) {
+    for (int i = 0; i < 2; i++) sweep();
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, cudaStreamLegacy);
+    for (int i = 0; i < iters; i++) sweep();
+    cudaEventRecord(e1, cudaStreamLegacy);
+    cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    *out = ms * 1000.0f / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  };
+  timed([&]() {
+    for (int i = 0; i < n_rot; i++) h->ctx->HRot(res, x, keys.GetRotationKey(rots[i]), rots[i]);
+  }, &usec[0]);
+  if (cudaDeviceSynchronize() != cudaSuccess) return (int)cudaGetLastError();
+  // hoisted baby step: a hoist map with one (unit) plaintext per rotation in giant step 0
+  PlainHoistMap map;
+  for (int i = 0; i < n_rot; i++) map[0].try_emplace(rots[i], num_slots, Complex(1.0, 0.0));
+  {
+    HoistHandler<word> hoist(h->ctx, map, level, 1.0, true);
+    timed([&]() {
+      std::map<int, Ciphertext<word>> bs;
+      hoist.EvaluateBabyStep(h->ctx, bs, x, keys, false);
+    }, &usec[1]);
+  }
   return (int)cudaDeviceSynchronize();
 }
 
