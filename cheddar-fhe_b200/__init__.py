@@ -270,6 +270,52 @@ class Engine:
             raise ValueError(kind)
         self._check(rc)
 
+    def gemm_pack_weights(self, weights, gidx):
+        """weights: uint32 [n_limbs][n_in][n_out] in M-form; returns the packed device buffer."""
+        w = np.ascontiguousarray(weights, dtype=np.uint32)
+        n_limbs, n_in, n_out = w.shape
+        g, gp = _ints(gidx)
+        self.L.cfhe_gemm_weight_bytes.restype = C.c_size_t
+        nbytes = self.L.cfhe_gemm_weight_bytes(n_in, n_out, n_limbs)
+        packed = self.torch.empty(nbytes, dtype=self.torch.uint8, device=f"cuda:{self.device}")
+        self._check(self.L.cfhe_gemm_pack_weights(self.h, C.c_void_p(packed.data_ptr()),
+                                                  w.ctypes.data_as(C.POINTER(C.c_uint32)), n_in, n_out, gp, len(g)))
+        return packed
+
+    def ctpt_gemm_(self, ys, xs, packed, gidx):
+        """ys[j] = sum_k W[k][j] * xs[k] on the tensor cores (cfhe_ctpt_gemm)."""
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_ctpt_gemm(self.h, self._ptrs(ys), self._ptrs(xs), C.c_void_p(packed.data_ptr()),
+                                          len(xs), len(ys), gp, len(g)))
+
+    def sample_uniform_(self, dst, gidx, seed, stream=0):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_sample_uniform(self.h, self._p(dst), gp, len(g), C.c_ulonglong(seed),
+                                               C.c_uint(stream)))
+
+    def sample_error_(self, dst, gidx, sigma, seed, stream=0):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_sample_error(self.h, self._p(dst), gp, len(g), C.c_double(sigma),
+                                             C.c_ulonglong(seed), C.c_uint(stream)))
+
+    def error_cdf(self, sigma):
+        out = np.zeros(97, dtype=np.uint64)
+        self._check(self.L.cfhe_error_cdf(C.c_double(sigma), out.ctypes.data_as(C.c_void_p), 97))
+        return out
+
+    def encrypt_(self, b, a, s, e, m, gidx):
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_encrypt(self.h, self._p(b), self._p(a), self._p(s), self._p(e),
+                                        self._p(m) if m is not None else None, gp, len(g)))
+
+    def add_evk_part_(self, bx, s_target, p_prod, gidx):
+        g, gp = _ints(gidx)
+        k, kp = _u32s(p_prod)
+        self._check(self.L.cfhe_add_evk_part(self.h, self._p(bx), self._p(s_target), kp, gp, len(g)))
+
+    def pseudo_modup_(self, level, dst, src):
+        self._check(self.L.cfhe_pseudo_modup(self.h, level, self._p(dst), self._p(src)))
+
     def modup_(self, level, dst, src):
         self._check(self.L.cfhe_modup(self.h, level, self._p(dst), self._p(src)))
 

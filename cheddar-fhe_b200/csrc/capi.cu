@@ -563,6 +563,54 @@ int cfhe_permute_accum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n
   { int r_ = launch_nary(h->c, a); h->c.mark("permute"); return r_; }
 }
 
+size_t cfhe_gemm_weight_bytes(int n_in, int n_out, int n_limbs) {
+  if (n_in < 1 || n_out < 1 || n_limbs < 1) return 0;
+  return gemm_packed_weight_bytes(n_in, n_out) * (size_t)n_limbs;
+}
+
+int cfhe_gemm_pack_weights(cfhe_context *h, void *packed, const uint32_t *weights, int n_in, int n_out,
+                           const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!packed || !weights || !gidx) return fail("null argument");
+  if (n_in < 1 || n_in > 8192 || n_out < 1 || n_limbs < 1 || n_limbs > kMaxLimbs)
+    return fail("ct-pt GEMM: unsupported shape");
+  const Context &c = h->c;
+  const size_t per_limb = gemm_packed_weight_bytes(n_in, n_out);
+  std::vector<uint8_t> host(per_limb);
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= c.NP) return fail("prime index out of range");
+    gemm_pack_weights_limb(host.data(), weights + (size_t)l * n_in * n_out, n_in, n_out, c.q[gidx[l]]);
+    CFHE_CUDA(cudaMemcpyAsync((uint8_t *)packed + (size_t)l * per_limb, host.data(), per_limb,
+                              cudaMemcpyHostToDevice, c.stream));
+    CFHE_CUDA(cudaStreamSynchronize(c.stream));  // the staging buffer is reused
+  }
+  return 0;
+}
+
+int cfhe_ctpt_gemm(cfhe_context *h, uint32_t *const *y, const uint32_t *const *x, const void *packed,
+                   int n_in, int n_out, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!y || !x || !packed || !gidx) return fail("null argument");
+  if (n_in < 1 || n_in > 8192 || n_out < 1 || n_out > 8192 || n_limbs < 1 || n_limbs > kMaxLimbs)
+    return fail("ct-pt GEMM: unsupported shape");
+  Context &c = h->c;
+  // workspace: packed activations of one limb, then the two pointer tables
+  const size_t scratch = (gemm_scratch_bytes(n_in) + 255) / 256 * 256;
+  const size_t tables = (size_t)(n_in + n_out) * sizeof(void *);
+  if (int r = ensure_workspace(c, (scratch + tables + 3) / 4)) return r;
+  uint8_t *base = reinterpret_cast<uint8_t *>(c.ws);
+  const uint32_t **dx = reinterpret_cast<const uint32_t **>(base + scratch);
+  uint32_t **dy = reinterpret_cast<uint32_t **>(base + scratch + (size_t)n_in * sizeof(void *));
+  for (int k = 0; k < n_in; k++)
+    if (!x[k]) return fail("null argument");
+  for (int j = 0; j < n_out; j++)
+    if (!y[j]) return fail("null argument");
+  CFHE_CUDA(cudaMemcpyAsync(dx, x, (size_t)n_in * sizeof(void *), cudaMemcpyHostToDevice, c.stream));
+  CFHE_CUDA(cudaMemcpyAsync(dy, y, (size_t)n_out * sizeof(void *), cudaMemcpyHostToDevice, c.stream));
+  CFHE_CUDA(cudaStreamSynchronize(c.stream));  // the host tables may go away after the call
+  { int r_ = launch_ctpt_gemm(c, dy, dx, (const uint8_t *)packed, base, n_in, n_out, gidx, n_limbs); c.mark("gemm"); return r_; }
+}
+
 int cfhe_sample_uniform(cfhe_context *h, uint32_t *dst, const int *gidx, int n_limbs,
                         unsigned long long seed, unsigned int stream) {
   CFHE_ENTER(h);

@@ -151,6 +151,12 @@ int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
 int launch_nary(const Context &ctx, const NaryArgs &args);
+// gemm_tc.cu: ciphertext x plaintext RNS GEMM on the tensor cores
+size_t gemm_packed_weight_bytes(int n_in, int n_out);  // per limb
+size_t gemm_scratch_bytes(int n_in);
+void gemm_pack_weights_limb(uint8_t *out, const uint32_t *w, int n_in, int n_out, uint32_t q);
+int launch_ctpt_gemm(const Context &c, uint32_t *const *y, const uint32_t *const *x, const uint8_t *wp,
+                     uint8_t *scratch, int n_in, int n_out, const int *gidx, int n_limbs);
 // sampling.cu: client-side sampling and encryption
 constexpr int kErrorCdfEntries = 97;
 void error_cdf_table(double sigma, uint64_t *cdf);

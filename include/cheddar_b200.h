@@ -174,6 +174,23 @@ CFHE_API int cfhe_paccum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, i
 CFHE_API int cfhe_permute_accum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
                                 const uint32_t *const *src, const uint32_t *galois,
                                 const uint32_t *const *addend, const int *gidx, int n_limbs);
+/* Ciphertext x plaintext RNS GEMM on the tensor cores (tcgen05 kind::i8, exact):
+ *   y[j] = sum_k W[l][k][j] * x[k]  on every listed limb l,
+ * n_in input and n_out output polynomials of n_limbs limbs each, W words in
+ * M-form. Same words as cfhe_caccum applied to eight terms at a time. The
+ * reference has no kernel for this contraction (its CAccum,
+ * src/core/ElementWise.cu:1355-1394, is the closest operator); it is the
+ * projection step of the encrypted transformer layer (one ciphertext
+ * polynomial per input feature, plaintext weight matrix).
+ *   cfhe_gemm_weight_bytes   device bytes of the packed weights
+ *   cfhe_gemm_pack_weights   weights: HOST array [n_limbs][n_in][n_out]; packed:
+ *                            DEVICE buffer of cfhe_gemm_weight_bytes bytes
+ *   cfhe_ctpt_gemm           x, y: HOST arrays of n_in / n_out DEVICE pointers */
+CFHE_API size_t cfhe_gemm_weight_bytes(int n_in, int n_out, int n_limbs);
+CFHE_API int cfhe_gemm_pack_weights(cfhe_context *ctx, void *packed, const uint32_t *weights, int n_in,
+                                    int n_out, const int *gidx, int n_limbs);
+CFHE_API int cfhe_ctpt_gemm(cfhe_context *ctx, uint32_t *const *y, const uint32_t *const *x,
+                            const void *packed, int n_in, int n_out, const int *gidx, int n_limbs);
 /* Client-side sampling and encryption on the device (the reference samples on
  * the host and uploads: src/UserInterface.cu:223-276, 366-458; Random,
  * include/Random.h). Words are a pure function of (seed, stream, prime index,

@@ -177,7 +177,9 @@ int main(int argc, char **argv) {
       LinearTransform<word> lt(ctx, M, level, pt_scale, 8, 8, pre, extra);
       EvkRequest req;
       lt.AddRequiredRotations(req);
-      ui.PrepareRotationKey(req);
+      // one key shape for all rotations of a transform (some exist already at the top level)
+      for (auto &[rot, lvl] : req)
+        if (ui.GetEvkMap().find(rot) == ui.GetEvkMap().end()) ui.PrepareRotationKey(rot, param->max_level_);
       lt.Evaluate(ctx, out, ct, ui.GetEvkMap());
       ctx->AssertSameScale(out.GetScale(), s);
       decrypt(got, out);
@@ -207,7 +209,8 @@ int main(int argc, char **argv) {
       HoistHandler<word> hoist(ctx, map, level, pt_scale);
       EvkRequest req;
       hoist.AddRequiredRotations(req);
-      ui.PrepareRotationKey(req);
+      for (auto &[rot, lvl] : req)
+        if (ui.GetEvkMap().find(rot) == ui.GetEvkMap().end()) ui.PrepareRotationKey(rot, param->max_level_);
       hoist.Evaluate(ctx, out, ct, ui.GetEvkMap());
       decrypt(got, out);
       Report("HoistHandler (3 giant x 4 baby plaintexts)", expect, got, 1e-4);
