@@ -624,6 +624,97 @@ def assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
     return line
 
 
+def run_limb_sharded(args, pkg):
+    """One HMult (no rescale) at level 28 with the RNS limbs sharded over the
+    ranks: rank r owns the limbs at positions r mod G of ciphertexts, key and
+    result; all-gathers at the two base conversions (cheddar-fhe_b200/sharded.py).
+    Strong scaling of ONE operation: reports its latency at G GPUs, the share
+    of the collectives, the same HMult on one GPU, and checks that the gathered
+    result equals the one-GPU words."""
+    import torch
+    import torch.distributed as dist
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("cfhe_sharded", os.path.join(ROOT, "cheddar-fhe_b200", "sharded.py"))
+    sh = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sh)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    params = pkg.load_params("bootparam_40.json")
+    eng = pkg.Engine(params, device=local)
+    plan = sh.LimbShardPlan(params, HM_LEVEL, world)
+    rng = np.random.default_rng(0xC0FFEE44)  # the same data on every rank
+    M, T = len(params["main_primes"]), len(params["terminal_primes"])
+    g = list(eng.level_limbs(HM_LEVEL))
+    kg = list(range(T + M)) + [T + M + a for a in range(eng.alpha)]
+    beta = eng.beta(HM_LEVEL)
+    ins = [rand_limbs(rng, eng.primes, g) for _ in range(4)]
+    kb = [rand_limbs(rng, eng.primes, kg) for _ in range(beta)]
+    ka = [rand_limbs(rng, eng.primes, kg) for _ in range(beta)]
+    own, own_q = plan.owned(rank), plan.owned_q(rank)
+    key_rows = [kg.index(plan.full_g[k]) for k in own]   # rows of the full key that this rank keeps
+    mine = [eng.to_dev(x[own_q]) for x in ins]
+    kb_own = [eng.to_dev(x[key_rows]) for x in kb]
+    ka_own = [eng.to_dev(x[key_rows]) for x in ka]
+    warmup = max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        out_b, out_a, _ = sh.sharded_hmult(eng, plan, rank, dist, *mine, kb_own, ka_own)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    coll = 0.0
+    e0.record()
+    for _ in range(args.steps):
+        out_b, out_a, c = sh.sharded_hmult(eng, plan, rank, dist, *mine, kb_own, ka_own)
+        coll += c
+    e1.record()
+    barrier()
+    ms, coll_ms = reduce_max([e0.elapsed_time(e1) / args.steps, coll * 1e3 / args.steps], f"cuda:{local}")
+    # assemble the result on every rank and compare with the one-GPU operator on rank 0
+    gathered = [sh.gather_limbs(dist, torch, t, list(range(plan.nq)), plan, rank) for t in (out_b, out_a)]
+    same, single_ms = None, None
+    if rank == 0:
+        full = [eng.to_dev(x) for x in ins]
+        dkb, dka = [eng.to_dev(x) for x in kb], [eng.to_dev(x) for x in ka]
+        rb, ra = eng.empty(len(g), N), eng.empty(len(g), N)
+        for _ in range(warmup):
+            eng.hmult_(HM_LEVEL, rb, ra, *full, dkb, dka, M, False)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            eng.hmult_(HM_LEVEL, rb, ra, *full, dkb, dka, M, False)
+        e1.record()
+        torch.cuda.synchronize()
+        single_ms = e0.elapsed_time(e1) / args.steps
+        same = all(torch.equal(gathered[0][k], rb[k]) and torch.equal(gathered[1][k], ra[k]) for k in range(plan.nq))
+        exchanged = (plan.nq + 2 * plan.alpha) * LIMB
+        print(json.dumps({
+            "metric": "HMult us (limb-sharded, no rescale)", "value": ms * 1e3, "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "one HMult + relinearise (ModDown, no rescale), bootparam_40 level 28, limbs "
+                                   "sharded by position mod n_gpus, all-gather before each base conversion",
+                       "parallelism": f"limbs x{world}"},
+            "collective_ms": coll_ms, "collective_share": coll_ms / ms,
+            "bytes_exchanged_per_hmult": exchanged,
+            "one_gpu_fused_operator_us": single_ms * 1e3,
+            "words_equal_one_gpu": bool(same),
+            "note": "the sharded path is orchestrated per limb group from Python with the library's fine-grained "
+                    "operators (more launches than the fused one-GPU cfhe_hmult), so its one-rank time is above "
+                    "the fused operator's"}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_gpu(args, pkg):
     import torch
     import torch.distributed as dist
@@ -633,6 +724,9 @@ def run_gpu(args, pkg):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        # keep the communicator's set-up lines (ranks, transports) in the log
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     params = pkg.load_params("bootparam_40.json")
     eng = pkg.Engine(params, device=local)
@@ -695,10 +789,14 @@ def main():
     ap.add_argument("--no-hoist", action="store_true", help="skip the 64-rotation hoisting sweep")
     ap.add_argument("--no-ref", action="store_true", help="skip timing the reference's CUDA library")
     ap.add_argument("--no-boot", action="store_true", help="skip the bootstrapping workload")
+    ap.add_argument("--shard", default="ciphertexts", choices=["ciphertexts", "limbs"],
+                    help="limbs: one HMult with its RNS limbs sharded over the ranks (strong scaling)")
     args = ap.parse_args()
     pkg = load_package()
     if args.impl == "reference":
         run_reference(args, pkg)
+    elif args.shard == "limbs":
+        run_limb_sharded(args, pkg)
     else:
         run_gpu(args, pkg)
 

@@ -438,6 +438,13 @@ class Engine:
         self._check(self.L.cfhe_mul_imag_unit(self.h, self._p(d), self._p(da), gp, len(g)))
         return self.to_host(d)
 
+    def bconv_(self, dst, y, src_gidx, dst_gidx):
+        """Base conversion of centred residues y [n_src][N] (int32 words) into
+        the limbs dst_gidx, device-resident (cfhe_bconv)."""
+        sg, sp = _ints(src_gidx)
+        dg, dp = _ints(dst_gidx)
+        self._check(self.L.cfhe_bconv(self.h, self._p(dst), self._p(y), sp, len(sg), dp, len(dg)))
+
     def bconv(self, y, src_gidx, dst_gidx):
         dy = self.to_dev(np.ascontiguousarray(y, dtype=np.int32).view(np.uint32))
         sg, sp = _ints(src_gidx)

@@ -333,3 +333,34 @@ def test_modup_moddown_with_sixteen_auxiliary_primes(pkg, params40):
             got = e.moddown(level, kind, acc)
             for i in range(2):
                 assert np.array_equal(got[i], o.moddown(level, kind, acc[i])), (level, kind)
+
+
+def test_limb_sharded_hmult_on_one_rank_equals_hmult(engine40, params40):
+    """The limb-sharded HMult (cheddar-fhe_b200/sharded.py) run with a single
+    rank, i.e. the same per-limb algebra without the all-gathers, returns the
+    words of cfhe_hmult without rescaling. (With more ranks the exchanged limbs
+    are the same tensors, moved by NCCL; bench.py --shard limbs checks that on
+    the GPUs it runs on.)"""
+    import importlib.util
+    import os
+    e = engine40
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("cfhe_sharded", os.path.join(root, "cheddar-fhe_b200", "sharded.py"))
+    sh = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sh)
+    for level in (28, 9):
+        plan = sh.LimbShardPlan(params40, level, 1)
+        rng = np.random.default_rng(7700 + level)
+        g = list(e.level_limbs(level))
+        T, M = len(params40["terminal_primes"]), len(params40["main_primes"])
+        kg = list(range(T + M)) + [T + M + a for a in range(e.alpha)]
+        ins = [rand_limbs(rng, e.primes, g, e.n) for _ in range(4)]
+        kb = [rand_limbs(rng, e.primes, kg, e.n) for _ in range(e.beta(28))]
+        ka = [rand_limbs(rng, e.primes, kg, e.n) for _ in range(e.beta(28))]
+        rows = [kg.index(x) for x in plan.full_g]
+        active = [d[0] for d in plan.digits]
+        got_b, got_a, _ = sh.sharded_hmult(e, plan, 0, None, *[e.to_dev(x) for x in ins],
+                                           [e.to_dev(kb[i][rows]) for i in active],
+                                           [e.to_dev(ka[i][rows]) for i in active])
+        want_b, want_a = e.hmult(level, *ins, kb, ka, M, False)
+        assert np.array_equal(e.to_host(got_b), want_b) and np.array_equal(e.to_host(got_a), want_a), level
