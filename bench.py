@@ -624,6 +624,45 @@ def assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
     return line
 
 
+def bench_gemm(eng, torch, steps, n_in=768, n_out=768, n_limbs=8):
+    """Config 5's projection step: y_j = sum_k W[k][j] x_k for 768 input and 768
+    output polynomials (one ciphertext polynomial per hidden feature of
+    BERT-base) on n_limbs limbs, exact, on the tensor cores (cfhe_ctpt_gemm).
+    Inputs are uniform residues (what NTT-domain ciphertext limbs look like),
+    weights uniform words standing in for N(0, 0.02) weights times the scale
+    reduced modulo each prime (equally uniform)."""
+    rng = np.random.default_rng(0xC0FFEE05)
+    g = list(range(4, 4 + n_limbs))
+    dev = f"cuda:{eng.device}"
+    x = torch.randint(0, 1 << 24, (n_in, n_limbs, N), dtype=torch.int32, device=dev)
+    y = torch.empty((n_out, n_limbs, N), dtype=torch.int32, device=dev)
+    w = np.stack([rng.integers(0, int(eng.primes[gi]), (n_in, n_out), dtype=np.uint64).astype(np.uint32) for gi in g])
+    packed = eng.gemm_pack_weights(w, g)
+    xs, ys = [x[k] for k in range(n_in)], [y[j] for j in range(n_out)]
+    for _ in range(2):
+        eng.ctpt_gemm_(ys, xs, packed, g)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.ctpt_gemm_(ys, xs, packed, g)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    ops = 2.0 * N * (4 * n_in) * (4 * n_out) * n_limbs       # 8-bit multiply-adds of the byte-plane GEMM, x2
+    useful = 2.0 * N * n_in * n_out * n_limbs                # modular multiply-adds, x2
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = None
+    if os.path.exists(p):
+        with open(p) as f:
+            peak = 2.0 * json.load(f)["bf16_tflops"]         # dense 8-bit rate is twice the bf16 rate
+    return {"n_in": n_in, "n_out": n_out, "n_limbs": n_limbs, "ms": ms, "int8_TOPS": ops / (ms * 1e-3) / 1e12,
+            "modular_GMACs_per_s": useful / 2 / (ms * 1e-3) / 1e9,
+            "tensor_peak_TOPS": peak, "peak_source": "2 x measured bf16 burst (MEASURED_PEAKS.json)" if peak else None,
+            "frac": ops / (ms * 1e-3) / 1e12 / peak if peak else None,
+            "includes": "packing the activations into operand layout (one pass over the inputs per limb)"}
+
+
 def run_limb_sharded(args, pkg):
     """One HMult (no rescale) at level 28 with the RNS limbs sharded over the
     ranks: rank r owns the limbs at positions r mod G of ciphertexts, key and
@@ -737,6 +776,14 @@ def run_gpu(args, pkg):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.workload == "gemm":
+        # the projection kernel alone (profiling runs): no other workload is launched
+        if rank == 0:
+            print(json.dumps({"metric": "ct-pt GEMM", "ctpt_gemm": bench_gemm(eng, torch, args.steps,
+                                                                             n_limbs=args.gemm_limbs)}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -748,6 +795,10 @@ def run_gpu(args, pkg):
     hoist = None
     if args.workload == "hmult" and not args.no_hoist:
         hoist = bench_hoisted(eng, torch, params, 64, max(2, args.steps // 5))
+    gemm = None
+    if rank == 0 and args.workload == "hmult" and not args.no_gemm:
+        gemm = bench_gemm(eng, torch, max(2, args.steps // 5))
+        torch.cuda.empty_cache()
     ref_cuda = None
     if rank == 0 and world == 1 and not args.no_ref:
         ref_cuda = bench_reference_cuda(eng, torch, params, args.steps, not args.no_boot)
@@ -760,6 +811,8 @@ def run_gpu(args, pkg):
     red = reduce_over_ranks(ntt, hm, boot, hoist, device=f"cuda:{local}")
     if rank == 0:
         line = assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
+        if gemm:
+            line["ctpt_gemm"] = gemm
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:
@@ -783,7 +836,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hmult", choices=["hmult", "ntt"])
+    ap.add_argument("--workload", default="hmult", choices=["hmult", "ntt", "gemm"])
+    ap.add_argument("--no-gemm", action="store_true", help="skip the ct-pt GEMM (config 5 projection) leg")
+    ap.add_argument("--gemm-limbs", type=int, default=8, help="limbs of the --workload gemm run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip decrypting the HMult result")
     ap.add_argument("--no-hoist", action="store_true", help="skip the 64-rotation hoisting sweep")
