@@ -542,15 +542,27 @@ class EvalPoly {
     const auto &param = ctx->param_;
     const int la = param.NPToLevel(A.GetNP()), lb = param.NPToLevel(B.GetNP());
     const int l = Min(la, lb);
-    Ct prod;
-    ctx->MultUnsafe(prod, A, B, l);  // operands of a higher level are read in place
+    Ct prod, lowered;
+    const NPInfo np = param.LevelToNP(l);
+    if (np.IsSubsetOf(A.GetNP()) && np.IsSubsetOf(B.GetNP())) {
+      ctx->MultUnsafe(prod, A, B, l);  // operands of a higher level are read in place
+    } else {
+      // levels that do not nest (rational rescaling): bring the higher operand down
+      ctx->LevelDown(lowered, la > lb ? A : B, l);
+      ctx->MultUnsafe(prod, la > lb ? lowered : A, la > lb ? B : lowered, l);
+    }
     ctx->Add(prod, prod, prod);
     const double s = prod.GetScale();
     if (C) {
-      Ct cs;
+      Ct cs, c_low;
+      const Ct *c_at = C;
+      if (!np.IsSubsetOf(C->GetNP())) {
+        ctx->LevelDown(c_low, *C, l);
+        c_at = &c_low;
+      }
       Constant<word> one;
-      ctx->encoder().EncodeConstant(one, l, s / C->GetScale(), 1.0, 0);
-      ctx->MultUnsafe(cs, *C, one, l);
+      ctx->encoder().EncodeConstant(one, l, s / c_at->GetScale(), 1.0, 0);
+      ctx->MultUnsafe(cs, *c_at, one, l);
       cs.SetScale(s);
       ctx->Sub(prod, prod, cs);
     } else if (c0 != 0.0) {
@@ -580,9 +592,10 @@ class EvalPoly {
     int k = 1;
     while ((size_t(1) << k) < c.size()) k++;
     // T_1, T_2, T_4, ... each one level below the previous
-    std::map<int, Ct> T;
-    ctx->Copy(T[1], x);
-    for (int j = 1; j < k; j++) Node(ctx, T[1 << j], T.at(1 << (j - 1)), T.at(1 << (j - 1)), nullptr, 1.0, mult_key);
+    Basis T;
+    ctx->Copy(T.top[1], x);
+    for (int j = 1; j < k; j++)
+      Node(ctx, T.top[1 << j], T.top.at(1 << (j - 1)), T.top.at(1 << (j - 1)), nullptr, 1.0, mult_key);
     const int top = param.NPToLevel(x.GetNP()) - (k - 1);
     AssertTrue(top > 0, "EvaluateChebyshev: not enough levels");
     Ct sum;
@@ -596,8 +609,28 @@ class EvalPoly {
   // share the relinearisation that Finish performs).
   // T_{m+j} = 2 T_m T_j - T_{m-j} turns p into q * T_m + r with
   //   q_0 = c_m, q_j = 2 c_{m+j};  r_0 = c_0, r_k = c_k - c_{2m-k}.
+  // T_1, T_2, T_4, ... as computed, and their copies on lower levels for the
+  // parameter sets whose levels do not nest (a product reads the limbs of its
+  // own level in place out of a higher operand only when they are all there;
+  // otherwise the operand is brought down with LevelDown, once per level, as
+  // the reference does with its MultiLevelCiphertext, src/extension/EvalPoly.cpp:408-661)
+  struct Basis {
+    std::map<int, Ct> top;
+    std::map<std::pair<int, int>, Ct> low;
+    const Ct &At(const ConstContextPtr<word> &ctx, int m, int level) {
+      const Ct &t = top.at(m);
+      if (ctx->param_.LevelToNP(level).IsSubsetOf(t.GetNP())) return t;
+      auto it = low.find({m, level});
+      if (it == low.end()) {
+        Ct down;
+        ctx->LevelDown(down, t, level);
+        it = low.emplace(std::make_pair(m, level), std::move(down)).first;
+      }
+      return it->second;
+    }
+  };
   static void Sum(const ConstContextPtr<word> &ctx, Ct &res, const std::vector<double> &c, double W,
-                  int level, const std::map<int, Ct> &T, const Evk &mult_key) {
+                  int level, Basis &T, const Evk &mult_key) {
     const auto &param = ctx->param_;
     const int len = c.size();
     auto add_const = [&](Ct &ct, double v) {
@@ -613,7 +646,7 @@ class EvalPoly {
       out.SetScale(W);
     };
     if (len <= 2) {
-      scaled(res, T.at(1), len == 2 ? c[1] : 0.0);
+      scaled(res, T.At(ctx, 1, level), len == 2 ? c[1] : 0.0);
       add_const(res, c[0]);
       return;
     }
@@ -625,10 +658,10 @@ class EvalPoly {
     for (int i = 0; i < m; i++) r[i] = c[i] - (i > 0 && 2 * m - i < len ? c[2 * m - i] : 0.0);
     Ct high;
     if (q.size() == 1) {
-      scaled(high, T.at(m), q[0]);
+      scaled(high, T.At(ctx, m, level), q[0]);
     } else {
       Ct qsum, qv;
-      const Ct &tm = T.at(m);
+      const Ct &tm = T.At(ctx, m, level);
       Sum(ctx, qsum, q, (W / tm.GetScale()) * param.GetRescalePrimeProd(level + 1), level + 1, T, mult_key);
       Finish(ctx, qv, qsum, mult_key);
       ctx->MultUnsafe(high, qv, tm, level);

@@ -1,0 +1,684 @@
+// One encrypted transformer encoder layer (BERT shape: multi-head self
+// attention, residual + LayerNorm, GELU feed-forward, residual + LayerNorm)
+// composed from the operators of this library: the tensor-core ciphertext x
+// plaintext contraction (cfhe_ctpt_gemm), hoisted rotations, HMult, Chebyshev
+// polynomial evaluation (EvalPoly) and bootstrapping (BootContext::Boot).
+//
+// The reference has no transformer code (its extension directory holds
+// BootContext, EvalMod, EvalPoly, EvalSpecialFFT, Hoist, LinearTransform and
+// StripedMatrix only, CMakeLists.txt:63-75); this file composes the layer from
+// the counterparts of those pieces (src/extension/EvalPoly.cpp:408-661,
+// src/extension/BootContext.cpp:299-365, src/extension/Hoist.cu:578-691).
+//
+// Packing. One ciphertext per feature. Slot t * B + b of feature ciphertext j
+// holds x[b][t][j] / act_div: token t of sequence b of a batch of
+// B = num_slots / seq_len sequences (256 for 128 tokens at N = 2^16). With
+// that layout
+//   * a projection y_j = sum_k W[k][j] x_k is a contraction ACROSS ciphertexts
+//     by plaintext scalars: an exact integer GEMM over the RNS limbs, run on
+//     the tensor cores;
+//   * a rotation by r * B slots moves token t + r onto token t in every
+//     sequence at once, so score offset r of a head is
+//     sum_d Q_d * rot_r(K_d): rotations come in baby steps (hoisted, one ModUp
+//     per ciphertext) and giant steps;
+//   * the softmax denominator and the LayerNorm statistics are sums across
+//     ciphertexts, no rotation at all, and live in ONE ciphertext per head or
+//     per LayerNorm: those are the ciphertexts whose reciprocal / reciprocal
+//     square root is evaluated (bootstrapped first, so that the expensive
+//     polynomial costs levels of one ciphertext, not of hundreds).
+//
+// Every non-linear function is a Chebyshev series on [-1, 1] (TransformerPolys);
+// the float64 layer used as the checker in the tests evaluates the same series.
+#pragma once
+#include <chrono>
+#include <random>
+#include <tuple>
+
+#include "cheddar/Boot.h"
+
+namespace cheddar {
+
+struct TransformerConfig {
+  int seq_len = 128, hidden = 768, heads = 12, head_dim = 64, ffn = 3072;
+  int baby = 16;             // baby steps of the token rotations (divides seq_len)
+  double act_div = 8.0;      // ciphertexts of the residual stream hold value / act_div
+  double score_range = 2.0;  // bound on |q . k| / sqrt(head_dim)
+  double sum_lo = 0.04, sum_hi = 0.8;  // bounds on mean_r exp(s_r - score_range)
+  double var_lo = 0.3, var_hi = 6.5;   // bounds on the LayerNorm variance
+  double gelu_range = 4.0;             // bound on the feed-forward pre-activation
+  double ln_eps = 1e-5;
+  int exp_degree = 15, inv_degree = 63, rsqrt_degree = 63, gelu_degree = 31;
+  bool pair_boot = true;  // bootstrap two real ciphertexts as one complex one
+  static TransformerConfig BertBase() { return TransformerConfig{}; }
+  static TransformerConfig Small() {
+    TransformerConfig c;
+    c.seq_len = 16;
+    c.hidden = 32;
+    c.heads = 2;
+    c.head_dim = 16;
+    c.ffn = 64;
+    c.baby = 4;
+    c.var_lo = 0.15;  // the variance of 32 features spreads wider than that of 768
+    return c;
+  }
+};
+
+// Row-major [in][out] matrices, as a framework stores nn.Linear weights transposed.
+struct TransformerWeights {
+  std::vector<double> wq, wk, wv, wo, w1, w2;
+  std::vector<double> bq, bk, bv, bo, b1, b2;
+  std::vector<double> gamma1, beta1, gamma2, beta2;
+  static TransformerWeights Random(const TransformerConfig &c, uint64_t seed, double stddev) {
+    std::mt19937_64 gen(seed);
+    std::normal_distribution<double> nd(0.0, stddev);
+    auto fill = [&](std::vector<double> &v, size_t n, double centre) {
+      v.resize(n);
+      for (auto &x : v) x = centre + nd(gen);
+    };
+    TransformerWeights w;
+    const size_t H = c.hidden, F = c.ffn;
+    fill(w.wq, H * H, 0);
+    fill(w.wk, H * H, 0);
+    fill(w.wv, H * H, 0);
+    fill(w.wo, H * H, 0);
+    fill(w.w1, H * F, 0);
+    fill(w.w2, F * H, 0);
+    fill(w.bq, H, 0);
+    fill(w.bk, H, 0);
+    fill(w.bv, H, 0);
+    fill(w.bo, H, 0);
+    fill(w.b1, F, 0);
+    fill(w.b2, H, 0);
+    fill(w.gamma1, H, 1);
+    fill(w.beta1, H, 0);
+    fill(w.gamma2, H, 1);
+    fill(w.beta2, H, 0);
+    return w;
+  }
+};
+
+// The four Chebyshev series of the layer, each on its own affine image of [-1, 1].
+struct TransformerPolys {
+  std::vector<double> exp_c;    // u in [-1,1] -> exp(R (u - 1)),               u = s / R
+  std::vector<double> inv_c;    // w -> 1 / (T m),  m = ((hi-lo) w + hi+lo)/2 the mean of the exponentials
+  std::vector<double> rsqrt_c;  // w -> 1 / (2 sqrt(v + eps)), v = ((hi-lo) w + hi+lo)/2 the variance
+  std::vector<double> gelu_c;   // t -> GELU(G t) / G,          t = a / G
+  explicit TransformerPolys(const TransformerConfig &c) {
+    using P = EvalPoly<uint32_t>;
+    const double R = c.score_range, T = c.seq_len, G = c.gelu_range;
+    exp_c = P::ChebyshevCoefficients([=](double u) { return std::exp(R * (u - 1.0)); }, c.exp_degree);
+    inv_c = P::ChebyshevCoefficients(
+        [=](double w) { return 1.0 / (T * 0.5 * ((c.sum_hi - c.sum_lo) * w + c.sum_hi + c.sum_lo)); },
+        c.inv_degree);
+    rsqrt_c = P::ChebyshevCoefficients(
+        [=](double w) {
+          return 0.5 / std::sqrt(0.5 * ((c.var_hi - c.var_lo) * w + c.var_hi + c.var_lo) + c.ln_eps);
+        },
+        c.rsqrt_degree);
+    gelu_c = P::ChebyshevCoefficients(
+        [=](double t) {
+          const double a = G * t;
+          return 0.5 * a * (1.0 + std::erf(a / std::sqrt(2.0))) / G;
+        },
+        c.gelu_degree);
+  }
+};
+
+// A plaintext matrix encoded on the limbs of one level and packed for the
+// tensor-core contraction.
+template <typename word>
+class PlainMatrix {
+  using Ct = Ciphertext<word>;
+
+ public:
+  // w: [n_in][n_out] real weights, encoded as round(w * scale) mod every prime of `level`
+  PlainMatrix(const Context<word> &ctx, const std::vector<double> &w, int n_in, int n_out, int level,
+              double scale)
+      : n_in_{n_in}, n_out_{n_out}, level_{level}, scale_{scale} {
+    AssertTrue((size_t)n_in * n_out == w.size(), "PlainMatrix: wrong weight count");
+    const NPInfo np = ctx.param_.LevelToNP(level);
+    g_ = ctx.param_.GetLimbIndices(np);
+    const auto primes = ctx.param_.GetPrimeVector(np);
+    const size_t per = (size_t)n_in * n_out;
+    std::vector<uint32_t> host(per * primes.size());
+    for (size_t i = 0; i < per; i++) {
+      const double scaled = std::nearbyint(w[i] * scale);
+      AssertTrue(std::abs(scaled) < 9.0e18, "PlainMatrix: weight too large for the scale");
+      const int64_t v = (int64_t)scaled;
+      for (size_t l = 0; l < primes.size(); l++) {
+        int64_t r = v % (int64_t)primes[l];
+        if (r < 0) r += primes[l];
+        host[l * per + i] = detail::ToMontgomery((word)r, primes[l]);
+      }
+    }
+    const size_t bytes = cfhe_gemm_weight_bytes(n_in, n_out, (int)g_.size());
+    packed_.resize((int)((bytes + sizeof(word) - 1) / sizeof(word)));
+    CheckAbi(cfhe_gemm_pack_weights(ctx.h_, packed_.data(), host.data(), n_in, n_out, g_.data(), (int)g_.size()));
+    ctx.Synchronize();
+  }
+  int level() const { return level_; }
+  double scale() const { return scale_; }
+  // y[j] = sum_k w[k][j] x[k] on both polynomials, at the level of x, scale
+  // x.scale * scale, not rescaled
+  void Apply(const Context<word> &ctx, std::vector<Ct> &y, const std::vector<const Ct *> &x) const {
+    AssertTrue((int)x.size() == n_in_, "PlainMatrix: wrong input count");
+    const NPInfo np = ctx.param_.LevelToNP(level_);
+    std::vector<const word *> xb(n_in_), xa(n_in_);
+    for (int k = 0; k < n_in_; k++) {
+      AssertTrue(x[k]->GetNP() == np && !x[k]->HasRx(), "PlainMatrix: input at the wrong level");
+      xb[k] = x[k]->bx_.data();
+      xa[k] = x[k]->ax_.data();
+    }
+    y.clear();
+    y.reserve(n_out_);
+    std::vector<word *> yb(n_out_), ya(n_out_);
+    for (int j = 0; j < n_out_; j++) {
+      y.emplace_back(np);
+      y[j].SetScale(x[0]->GetScale() * scale_);
+      y[j].SetNumSlots(x[0]->GetNumSlots());
+      yb[j] = y[j].bx_.data();
+      ya[j] = y[j].ax_.data();
+    }
+    CheckAbi(cfhe_ctpt_gemm(ctx.h_, yb.data(), xb.data(), packed_.data(), n_in_, n_out_, g_.data(), (int)g_.size()));
+    CheckAbi(cfhe_ctpt_gemm(ctx.h_, ya.data(), xa.data(), packed_.data(), n_in_, n_out_, g_.data(), (int)g_.size()));
+  }
+  // 8-bit multiply-accumulates of one Apply (both polynomials, all limbs)
+  double Int8Macs(int degree) const { return 2.0 * g_.size() * 16.0 * n_in_ * (double)n_out_ * degree; }
+
+ private:
+  int n_in_, n_out_, level_;
+  double scale_;
+  std::vector<int> g_;
+  DeviceVector<word> packed_;
+};
+
+template <typename word>
+class EncryptedTransformerLayer {
+  using Ct = Ciphertext<word>;
+  using Const = Constant<word>;
+  using Evk = EvaluationKey<word>;
+  using Boot = BootContext<word>;
+
+ public:
+  EncryptedTransformerLayer(std::shared_ptr<Boot> ctx, const TransformerConfig &cfg, const TransformerWeights &w)
+      : ctx_{std::move(ctx)}, cfg_{cfg}, w_{w}, polys_{cfg} {
+    AssertTrue(cfg.heads * cfg.head_dim == cfg.hidden, "Transformer: heads * head_dim != hidden");
+    AssertTrue(cfg.seq_len % cfg.baby == 0, "Transformer: baby must divide seq_len");
+    slots_ = ctx_->param_.degree_ / 2;
+    AssertTrue(slots_ % cfg.seq_len == 0, "Transformer: seq_len must divide the slot count");
+    lane_ = slots_ / cfg.seq_len;
+  }
+  int BatchSize() const { return lane_; }
+  // Called after every stage with its name, the ciphertexts it produced and the
+  // factor that turns their slot values into the layer's natural units (for
+  // tests that decrypt intermediate results).
+  using Probe = std::function<void(const std::string &, const std::vector<Ct> &, double)>;
+  void SetProbe(Probe p) { probe_ = std::move(p); }
+  const TransformerPolys &polys() const { return polys_; }
+
+  // rotation keys of the token shifts (the bootstrapping keys are requested by the BootContext)
+  void AddRequiredRotations(EvkRequest &req) const {
+    const int level = ctx_->param_.max_level_;
+    for (int b = 1; b < cfg_.baby; b++) req.AddRequest(b * lane_, level);
+    for (int g = 1; g < cfg_.seq_len / cfg_.baby; g++) req.AddRequest(g * cfg_.baby * lane_, level);
+  }
+
+  // x: `hidden` ciphertexts at the level bootstrapping ends on, slot t * B + b
+  // holding x[b][t][j] / act_div. out: the same layout and level.
+  void Forward(std::vector<Ct> &out, const std::vector<Ct> &x, const EvkMap<word> &evk) {
+    const int H = cfg_.hidden, heads = cfg_.heads, D = cfg_.head_dim, F = cfg_.ffn;
+    const double A = cfg_.act_div;
+    AssertTrue((int)x.size() == H, "Transformer: wrong number of input ciphertexts");
+    const Evk &mult = evk.GetMultiplicationKey();
+    stage_s_.clear();
+    gemm_s_ = 0;
+    gemm_macs_ = 0;
+    boots_ = 0;
+    ctx_->Synchronize();
+    last_ = std::chrono::steady_clock::now();
+
+    // ---- attention
+    std::vector<Ct> qkv;
+    {
+      // Q is pre-divided by sqrt(head_dim) * score_range: the score ciphertexts hold s / score_range
+      const double qs = 1.0 / (std::sqrt((double)D) * cfg_.score_range);
+      if (!m_qkv_) {
+        std::vector<double> wm((size_t)H * 3 * H);
+        for (int k = 0; k < H; k++)
+          for (int j = 0; j < H; j++) {
+            wm[(size_t)k * 3 * H + j] = w_.wq[(size_t)k * H + j] * A * qs;
+            wm[(size_t)k * 3 * H + H + j] = w_.wk[(size_t)k * H + j] * A;
+            wm[(size_t)k * 3 * H + 2 * H + j] = w_.wv[(size_t)k * H + j] * A;
+          }
+        m_qkv_ = MakeMatrix(wm, H, 3 * H, x[0]);
+      }
+      std::vector<double> bias(3 * H);
+      for (int j = 0; j < H; j++) {
+        bias[j] = w_.bq[j] * qs;
+        bias[H + j] = w_.bk[j];
+        bias[2 * H + j] = w_.bv[j];
+      }
+      Project(qkv, *m_qkv_, Pointers(x), bias);
+    }
+    Mark("QKV projection");
+    if (probe_) probe_("qkv", qkv, 1.0);
+    std::vector<Ct> o_un(H), stat(heads);
+    for (int h = 0; h < heads; h++) AttentionHead(h, qkv, o_un, stat[h], evk);
+    qkv.clear();
+    Mark("scores, exponentials, weighted values");
+    std::vector<Ct> o(H);
+    {
+      BootAll(stat, evk, true);
+      for (int h = 0; h < heads; h++) {
+        Ct p;
+        Poly(p, stat[h], polys_.inv_c, mult);
+        LevelTo(p, Level(o_un[h * D]));
+        for (int d = 0; d < D; d++) {
+          Ct &src = o_un[h * D + d];
+          LevelTo(src, Level(p));
+          ctx_->HMult(o[h * D + d], src, p, mult);
+          src = Ct();
+        }
+      }
+    }
+    Mark("softmax normaliser");
+    if (probe_) probe_("attention", o, 1.0);
+    std::vector<Ct> y1;
+    {
+      // the mean over the features is removed here: C = I - 11^T / H commutes
+      // with the residual sum, so C is folded into the weights and the bias
+      if (!m_wo_) m_wo_ = MakeMatrix(Centred(w_.wo, H, H, 1.0 / A), H, H, o[0]);
+      Project(y1, *m_wo_, Pointers(o), CentredBias(w_.bo, 1.0 / A));
+      o.clear();
+      AddCentredResidual(y1, x);
+    }
+    Mark("output projection, residual");
+    if (probe_) probe_("centred sum 1", y1, A);
+    std::vector<Ct> z;
+    LayerNorm(z, y1, w_.gamma1, w_.beta1, evk);
+    y1.clear();
+    Mark("LayerNorm 1");
+    if (probe_) probe_("LayerNorm 1", z, A);
+    BootAll(z, evk);
+    Mark("bootstrap (before the feed-forward block)");
+    if (probe_) probe_("LayerNorm 1, refreshed", z, A);
+
+    // ---- feed-forward
+    std::vector<Ct> act;
+    {
+      const double G = cfg_.gelu_range;
+      if (!m_w1_) {
+        std::vector<double> wm(w_.w1);
+        for (auto &v : wm) v *= A / G;
+        m_w1_ = MakeMatrix(wm, H, F, z[0]);
+      }
+      std::vector<double> bias(F);
+      for (int j = 0; j < F; j++) bias[j] = w_.b1[j] / G;
+      std::vector<Ct> pre;
+      Project(pre, *m_w1_, Pointers(z), bias);
+      Mark("feed-forward projection 1");
+      if (probe_) probe_("pre-activation", pre, cfg_.gelu_range);
+      act.resize(F);
+      for (int j = 0; j < F; j++) {
+        Poly(act[j], pre[j], polys_.gelu_c, mult);
+        pre[j] = Ct();
+      }
+      Mark("GELU");
+      if (probe_) probe_("GELU", act, cfg_.gelu_range);
+      if (!m_w2_) m_w2_ = MakeMatrix(Centred(w_.w2, F, H, G / A), F, H, act[0]);
+    }
+    std::vector<Ct> y2;
+    Project(y2, *m_w2_, Pointers(act), CentredBias(w_.b2, 1.0 / A));
+    act.clear();
+    AddCentredResidual(y2, z);
+    z.clear();
+    Mark("feed-forward projection 2, residual");
+    if (probe_) probe_("centred sum 2", y2, A);
+    LayerNorm(out, y2, w_.gamma2, w_.beta2, evk);
+    y2.clear();
+    Mark("LayerNorm 2");
+    if (probe_) probe_("LayerNorm 2", out, A);
+    BootAll(out, evk);
+    Mark("bootstrap (end of the layer)");
+  }
+
+  // seconds per stage of the last Forward (the host synchronises between stages)
+  const std::vector<std::pair<std::string, double>> &StageSeconds() const { return stage_s_; }
+  double GemmSeconds() const { return gemm_s_; }
+  double GemmInt8Macs() const { return gemm_macs_; }
+  int Bootstraps() const { return boots_; }
+
+ private:
+  int Level(const Ct &c) const { return ctx_->param_.NPToLevel(c.GetNP()); }
+  double Canon(int level) const { return ctx_->param_.GetScale(level); }
+  static std::vector<const Ct *> Pointers(const std::vector<Ct> &v) {
+    std::vector<const Ct *> p(v.size());
+    for (size_t i = 0; i < v.size(); i++) p[i] = &v[i];
+    return p;
+  }
+  void Mark(const char *name) {
+    ctx_->Synchronize();
+    const auto now = std::chrono::steady_clock::now();
+    stage_s_.emplace_back(name, std::chrono::duration<double>(now - last_).count());
+    last_ = now;
+  }
+  void LevelTo(Ct &c, int level) const {
+    if (Level(c) <= level) return;
+    Ct t;
+    ctx_->LevelDown(t, c, level);
+    c = std::move(t);
+  }
+  // res = value * a one level below a, at the canonical scale of that level
+  void MultConstRescale(Ct &res, const Ct &a, double value) const {
+    const int l = Level(a);
+    Const k;
+    ctx_->encoder().EncodeConstant(k, l, Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / a.GetScale(), value);
+    Ct t;
+    ctx_->Mult(t, a, k);
+    ctx_->Rescale(res, t);
+  }
+  void AddConst(Ct &c, double value) const {
+    if (value == 0.0) return;
+    Const k;
+    ctx_->encoder().EncodeConstant(k, Level(c), c.GetScale(), value);
+    ctx_->Add(c, c, k);
+  }
+  void Poly(Ct &res, const Ct &x, const std::vector<double> &coeffs, const Evk &mult) const {
+    int k = 1;
+    while ((size_t(1) << k) < coeffs.size()) k++;
+    EvalPoly<word>::EvaluateChebyshev(ctx_, res, x, coeffs, mult, Canon(Level(x) - k));
+  }
+  // acc (+)= a * b as an unrelinearised three-part product
+  void TensorAccumulate(Ct &acc, bool first, const Ct &a, const Ct &b) const {
+    if (first) {
+      ctx_->MultUnsafe(acc, a, b);
+    } else {
+      Ct t;
+      ctx_->MultUnsafe(t, a, b);
+      ctx_->Add(acc, acc, t);
+    }
+  }
+
+  std::unique_ptr<PlainMatrix<word>> MakeMatrix(const std::vector<double> &wm, int n_in, int n_out,
+                                                const Ct &sample) const {
+    const int l = Level(sample);
+    const double s = Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / sample.GetScale();
+    return std::make_unique<PlainMatrix<word>>(*ctx_, wm, n_in, n_out, l, s);
+  }
+  // y = rescale(W x) + bias, one level below x at the canonical scale
+  void Project(std::vector<Ct> &y, const PlainMatrix<word> &m, const std::vector<const Ct *> &x,
+               const std::vector<double> &bias) {
+    AssertTrue(Level(*x[0]) == m.level(), "Transformer: the matrix was prepared for another level");
+    ctx_->AssertSameScale(x[0]->GetScale() * m.scale(),
+                          Canon(m.level() - 1) * ctx_->param_.GetRescalePrimeProd(m.level()));
+    std::vector<Ct> raw;
+    ctx_->Synchronize();
+    const auto t0 = std::chrono::steady_clock::now();
+    m.Apply(*ctx_, raw, x);
+    ctx_->Synchronize();
+    gemm_s_ += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    gemm_macs_ += m.Int8Macs(ctx_->param_.degree_);
+    y.clear();
+    y.resize(raw.size());
+    for (size_t j = 0; j < raw.size(); j++) {
+      ctx_->Rescale(y[j], raw[j]);
+      raw[j] = Ct();
+      AddConst(y[j], bias[j]);
+    }
+  }
+  // W (I - 11^T / n_out) * factor: every row loses its mean
+  static std::vector<double> Centred(const std::vector<double> &w, int n_in, int n_out, double factor) {
+    std::vector<double> r(w.size());
+    for (int k = 0; k < n_in; k++) {
+      double mean = 0;
+      for (int j = 0; j < n_out; j++) mean += w[(size_t)k * n_out + j];
+      mean /= n_out;
+      for (int j = 0; j < n_out; j++) r[(size_t)k * n_out + j] = (w[(size_t)k * n_out + j] - mean) * factor;
+    }
+    return r;
+  }
+  static std::vector<double> CentredBias(const std::vector<double> &b, double factor) {
+    double mean = 0;
+    for (double v : b) mean += v;
+    mean /= b.size();
+    std::vector<double> r(b.size());
+    for (size_t j = 0; j < b.size(); j++) r[j] = (b[j] - mean) * factor;
+    return r;
+  }
+  // y[j] += x[j] - mean_j x[j], x brought down to the level of y
+  void AddCentredResidual(std::vector<Ct> &y, const std::vector<Ct> &x) const {
+    const int H = x.size(), lx = Level(x[0]), ly = Level(y[0]);
+    AssertTrue(lx > ly, "Transformer: the residual must sit above the block's output");
+    Ct sum;
+    ctx_->Copy(sum, x[0]);
+    for (int j = 1; j < H; j++) ctx_->Add(sum, sum, x[j]);
+    const double s = Canon(lx - 1) * ctx_->param_.GetRescalePrimeProd(lx) / x[0].GetScale();
+    Const one, inv;
+    ctx_->encoder().EncodeConstant(one, lx, s, 1.0);
+    ctx_->encoder().EncodeConstant(inv, lx, s, 1.0 / H);
+    Ct mean;
+    ctx_->Mult(mean, sum, inv);
+    for (int j = 0; j < H; j++) {
+      Ct t, c;
+      ctx_->Mult(t, x[j], one);
+      ctx_->Sub(t, t, mean);
+      ctx_->Rescale(c, t);
+      LevelTo(c, ly);
+      ctx_->Add(y[j], y[j], c);
+    }
+  }
+
+  // out[0] = a, out[b] = a rotated by b tokens, b < baby (one ModUp for all of them)
+  void BabyRotations(std::vector<Ct> &out, const Ct &a, const EvkMap<word> &evk) const {
+    std::vector<int> dists;
+    std::vector<const Evk *> keys;
+    for (int b = 1; b < cfg_.baby; b++) {
+      dists.push_back(b * lane_);
+      keys.push_back(&evk.GetRotationKey(b * lane_));
+    }
+    std::vector<Ct> rot;
+    if (!dists.empty()) ctx_->HoistedRotate(rot, a, dists, keys);
+    out.clear();
+    out.resize(cfg_.baby);
+    ctx_->Copy(out[0], a);
+    for (int b = 1; b < cfg_.baby; b++) out[b] = std::move(rot[b - 1]);
+  }
+  void RotateTokens(Ct &res, const Ct &a, int tokens, const EvkMap<word> &evk) const {
+    const int dist = ((tokens % cfg_.seq_len) + cfg_.seq_len) % cfg_.seq_len * lane_;
+    ctx_->HRot(res, a, evk.GetRotationKey(dist), dist);
+  }
+
+  // Head h: e_r = exp(s_r - R) for the 'seq_len' offsets r, stat = their mean
+  // mapped to [-1, 1], o_un[d] = sum_r e_r * rot_r(V_d) (not yet normalised).
+  void AttentionHead(int h, const std::vector<Ct> &qkv, std::vector<Ct> &o_un, Ct &stat,
+                     const EvkMap<word> &evk) {
+    const int H = cfg_.hidden, D = cfg_.head_dim, T = cfg_.seq_len, nb = cfg_.baby, ng = T / nb;
+    const Evk &mult = evk.GetMultiplicationKey();
+    auto Q = [&](int d) -> const Ct & { return qkv[h * D + d]; };
+    auto K = [&](int d) -> const Ct & { return qkv[H + h * D + d]; };
+    auto V = [&](int d) -> const Ct & { return qkv[2 * H + h * D + d]; };
+    std::vector<Ct> e(T);
+    {
+      std::vector<std::vector<Ct>> kb(D);
+      for (int d = 0; d < D; d++) BabyRotations(kb[d], K(d), evk);
+      for (int g = 0; g < ng; g++) {
+        // s_{g nb + b}[t] = sum_d Q_d[t] K_d[t + g nb + b]
+        //                 = rot_{g nb}( sum_d rot_{-g nb}(Q_d) * rot_b(K_d) )[t]
+        std::vector<Ct> qg(g ? D : 0);
+        for (int d = 0; d < D && g; d++) RotateTokens(qg[d], Q(d), -g * nb, evk);
+        for (int b = 0; b < nb; b++) {
+          Ct acc, u;
+          for (int d = 0; d < D; d++) TensorAccumulate(acc, d == 0, g ? qg[d] : Q(d), kb[d][b]);
+          ctx_->RelinearizeRescale(u, acc, mult);
+          if (g) {
+            Ct r;
+            RotateTokens(r, u, g * nb, evk);
+            u = std::move(r);
+          }
+          Poly(e[g * nb + b], u, polys_.exp_c, mult);
+        }
+      }
+    }
+    {
+      Ct sum;
+      ctx_->Copy(sum, e[0]);
+      for (int r = 1; r < T; r++) ctx_->Add(sum, sum, e[r]);
+      const double span = cfg_.sum_hi - cfg_.sum_lo;
+      MaskedAffine(stat, sum, 2.0 / (T * span), -(cfg_.sum_hi + cfg_.sum_lo) / span);
+    }
+    const int le = Level(e[0]);
+    std::vector<std::vector<Ct>> vb(D);
+    for (int d = 0; d < D; d++) {
+      Ct low;
+      ctx_->LevelDown(low, V(d), le);
+      BabyRotations(vb[d], low, evk);
+    }
+    for (int g = 0; g < ng; g++) {
+      // o_d[t] += sum_b e_{g nb + b}[t] V_d[t + g nb + b]
+      //         = rot_{g nb}( sum_b rot_{-g nb}(e_{g nb + b}) * rot_b(V_d) )[t]
+      std::vector<Ct> eg(g ? nb : 0);
+      for (int b = 0; b < nb && g; b++) RotateTokens(eg[b], e[g * nb + b], -g * nb, evk);
+      for (int d = 0; d < D; d++) {
+        Ct acc, t;
+        for (int b = 0; b < nb; b++) TensorAccumulate(acc, b == 0, g ? eg[b] : e[b], vb[d][b]);
+        ctx_->RelinearizeRescale(t, acc, mult);
+        if (g) {
+          Ct r;
+          RotateTokens(r, t, g * nb, evk);
+          ctx_->Add(o_un[h * D + d], o_un[h * D + d], r);
+        } else {
+          o_un[h * D + d] = std::move(t);
+        }
+      }
+    }
+  }
+
+  // z[j] = gamma_j y[j] / sqrt(var + eps) + beta_j / act_div for centred y
+  // (mean already removed), var = (act_div^2 / H) sum_j y[j]^2
+  void LayerNorm(std::vector<Ct> &z, std::vector<Ct> &y, const std::vector<double> &gamma,
+                 const std::vector<double> &beta, const EvkMap<word> &evk) {
+    const int H = y.size();
+    const double A = cfg_.act_div, span = cfg_.var_hi - cfg_.var_lo;
+    const Evk &mult = evk.GetMultiplicationKey();
+    Ct acc, ss, w;
+    for (int j = 0; j < H; j++) TensorAccumulate(acc, j == 0, y[j], y[j]);
+    ctx_->RelinearizeRescale(ss, acc, mult);
+    MaskedAffine(w, ss, 2.0 * A * A / (H * span), -(cfg_.var_hi + cfg_.var_lo) / span);
+    std::vector<Ct> one(1);
+    one[0] = std::move(w);
+    BootAll(one, evk, true);
+    Ct f;
+    Poly(f, one[0], polys_.rsqrt_c, mult);  // 1 / (2 sqrt(var + eps))
+    const int target = Min(Level(f), Level(y[0]) - 1);
+    LevelTo(f, target);
+    z.clear();
+    z.resize(H);
+    for (int j = 0; j < H; j++) {
+      Ct t;
+      MultConstRescale(t, y[j], 2.0 * gamma[j]);
+      y[j] = Ct();
+      LevelTo(t, target);
+      ctx_->HMult(z[j], t, f, mult);
+      AddConst(z[j], beta[j] / A);
+    }
+  }
+
+  // A statistic (softmax denominator, LayerNorm variance) is nearly the same
+  // number in every slot, so its plaintext polynomial is one large coefficient,
+  // and the sine that bootstrapping evaluates coefficient by coefficient is
+  // only accurate to (2 pi c / q0)^2 / 6 relative on a coefficient c: half a
+  // percent for a constant 0.8. Multiplying the slots by a fixed public pattern
+  // of +-1 spreads the plaintext over all coefficients (each of size about
+  // |value| / sqrt(n), as for random data); the same pattern takes it off after
+  // the bootstrap. Both multiplications ride on constants that are needed anyway.
+  const Plaintext<word> &Mask(int level, double scale, double factor) {
+    const auto key = std::make_tuple(level, scale, factor);
+    auto it = masks_.find(key);
+    if (it == masks_.end()) {
+      if (mask_signs_.empty()) {
+        std::mt19937_64 gen(0x5EEDull);
+        mask_signs_.resize(slots_);
+        for (auto &v : mask_signs_) v = (gen() & 1) ? 1.0 : -1.0;
+      }
+      std::vector<Complex> msg(slots_);
+      for (int i = 0; i < slots_; i++) msg[i] = Complex(mask_signs_[i] * factor, 0.0);
+      Plaintext<word> pt;
+      ctx_->encoder().Encode(pt, level, scale, msg, 0);
+      it = masks_.emplace(key, std::move(pt)).first;
+    }
+    return it->second;
+  }
+  // res = mask * (mul * a + add), one level below a at the canonical scale
+  void MaskedAffine(Ct &res, const Ct &a, double mul, double add) {
+    const int l = Level(a);
+    Ct t;
+    ctx_->Mult(t, a, Mask(l, Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / a.GetScale(), mul));
+    ctx_->Rescale(res, t);
+    ctx_->Add(res, res, Mask(l - 1, res.GetScale(), add));
+  }
+  void MultMaskRescale(Ct &res, const Ct &a, double factor) {
+    const int l = Level(a);
+    Ct t;
+    ctx_->Mult(t, a, Mask(l, Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / a.GetScale(), factor));
+    ctx_->Rescale(res, t);
+  }
+
+  // Refreshes every ciphertext. Slot values are real, so two ciphertexts ride
+  // through one bootstrap as a + i b and are separated by the conjugate
+  // afterwards: a = (c + conj c) / 2, b = (c - conj c) / 2i. The halving is
+  // one constant product with a rescale, so a pair-bootstrapped ciphertext
+  // ends one level lower. masked: the inputs carry the +-1 pattern of Mask,
+  // taken off by the same product.
+  void BootAll(std::vector<Ct> &v, const EvkMap<word> &evk, bool masked = false) {
+    const size_t n = v.size();
+    auto finish = [&](Ct &dst, Ct &src, double factor, bool needed) {
+      if (masked) {
+        MultMaskRescale(dst, src, factor);
+      } else if (needed) {
+        MultConstRescale(dst, src, factor);
+      } else {
+        dst = std::move(src);
+      }
+    };
+    const bool pairs = cfg_.pair_boot && n > 1;
+    const Evk &conj = evk.GetConjugationKey();
+    for (size_t i = 0; i < n; i += 2) {
+      if (!pairs || i + 1 == n) {
+        for (size_t j = i; j < Min(i + 2, n); j++) {
+          Ct fresh;
+          ctx_->Boot(fresh, v[j], evk);
+          boots_++;
+          finish(v[j], fresh, 1.0, pairs);  // in a paired run every output ends on one level
+        }
+        continue;
+      }
+      Ct im, both, fresh, cj, re2, im2;
+      ctx_->MultImaginaryUnit(im, v[i + 1]);
+      ctx_->Add(both, v[i], im);
+      ctx_->Boot(fresh, both, evk);
+      boots_++;
+      ctx_->HConj(cj, fresh, conj);
+      ctx_->Add(re2, fresh, cj);  // 2 a
+      ctx_->Sub(im2, cj, fresh);  // -2 i b
+      ctx_->MultImaginaryUnit(im2, im2);  // 2 b
+      finish(v[i], re2, 0.5, true);
+      finish(v[i + 1], im2, 0.5, true);
+    }
+  }
+
+  std::shared_ptr<Boot> ctx_;
+  TransformerConfig cfg_;
+  TransformerWeights w_;
+  TransformerPolys polys_;
+  int slots_ = 0, lane_ = 0;
+  std::unique_ptr<PlainMatrix<word>> m_qkv_, m_wo_, m_w1_, m_w2_;
+  Probe probe_;
+  std::map<std::tuple<int, double, double>, Plaintext<word>> masks_;
+  std::vector<double> mask_signs_;
+  std::vector<std::pair<std::string, double>> stage_s_;
+  std::chrono::steady_clock::time_point last_;
+  double gemm_s_ = 0, gemm_macs_ = 0;
+  int boots_ = 0;
+};
+
+}  // namespace cheddar

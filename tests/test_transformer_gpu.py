@@ -1,0 +1,40 @@
+"""The encrypted transformer encoder layer (one attention block and one
+feed-forward block, with both LayerNorms and the bootstraps between them)
+against the float64 layer that evaluates the same Chebyshev series.
+
+Parity unpinned by the reference: the reference has no transformer code
+(CMakeLists.txt:63-75 lists every extension source), so the checker is the
+textbook layer in double precision (oracle/transformer_plain.h). The bar is
+stated in bits: max over every slot of every output ciphertext of
+|encrypted - float64| must stay below 2^-12 on outputs of magnitude up to ~5
+(the two bootstraps on the way each leave about 2^-19 on values scaled to
+[-1, 1], the LayerNorms multiply that by up to 1/sqrt(var_lo))."""
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CPP = os.path.join(ROOT, "tests", "cpp")
+pytestmark = pytest.mark.gpu
+
+
+def build_transformer_test(pkg):
+    if not os.path.exists(pkg.LIB_PATH):
+        pkg.build()
+    subprocess.check_call(["make", "-s", "-C", CPP, "transformer_test"])
+    return os.path.join(CPP, "transformer_test")
+
+
+@pytest.mark.parametrize("extra", [[], ["--no-pair", "--seed", "7"]], ids=["paired-bootstraps", "single-bootstraps"])
+def test_encrypted_layer_matches_float64_layer(pkg, extra):
+    exe = build_transformer_test(pkg)
+    cmd = [exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json")] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    print(r.stdout[-6000:])
+    print(r.stderr[-3000:])
+    assert r.returncode == 0, "transformer_test failed"
+    assert "PASS" in r.stdout
+    bits = float(re.search(r"precision_bits ([0-9.]+)", r.stdout).group(1))
+    assert bits >= 12.0
