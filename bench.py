@@ -464,6 +464,53 @@ def bench_bootstrap(pkg, local, iters, warmup):
     return json.loads(r.stdout.strip().splitlines()[-1])
 
 
+def bench_bert_layer(pkg, local):
+    """Config 5: one encrypted BERT-base encoder layer (128 tokens, hidden 768,
+    12 heads of 64, feed-forward 3072; weights N(0, 0.02), activations N(0, 1))
+    on 256 sequences at once, one ciphertext per feature, through the C++
+    layer driver (host/cheddar/Transformer.h) built on cfhe_ctpt_gemm, hoisted
+    rotations, EvalPoly and Boot. The host program lib/bert_bench generates the
+    keys, encrypts the 768 input ciphertexts and packs the weights (untimed,
+    reported), then times one layer stage by stage with the host clock around
+    device synchronisations. The reference has no transformer code, so there is
+    no reference figure."""
+    exe = os.path.join(os.path.dirname(pkg.LIB_PATH), "bert_bench")
+    if not os.path.exists(exe):
+        raise RuntimeError("lib/bert_bench is missing: run the package build")
+    env = dict(os.environ)
+    visible = env.get("CUDA_VISIBLE_DEVICES")
+    env["CUDA_VISIBLE_DEVICES"] = visible.split(",")[local] if visible else str(local)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--warmup", "1", "--passes", "1"],
+                       capture_output=True, text=True, env=env, timeout=1500)
+    if r.returncode != 0:
+        raise RuntimeError("bert_bench failed: " + r.stderr[-500:])
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def bert_entry(bert, seconds_max, world):
+    """The `bert_layer` object of the line: rank 0's run with the layer time
+    replaced by the maximum over ranks; every rank runs its own batch of
+    sequences (no collective), so the throughput adds up."""
+    peak = None
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            peak = 2.0 * json.load(f)["bf16_tflops"]
+    out = dict(bert)
+    out["seconds_per_layer"] = seconds_max
+    out["unit"] = "s per layer call of 256 sequences (max over ranks)"
+    out["sequences_per_s_all_ranks"] = world * bert["sequences_per_layer_call"] / seconds_max
+    out["seconds_per_sequence"] = seconds_max / (world * bert["sequences_per_layer_call"])
+    out["projection_tensor_pipe"] = {
+        "int8_TOPS": bert["gemm_int8_TOPS"], "peak_TOPS": peak,
+        "frac": bert["gemm_int8_TOPS"] / peak if peak else None,
+        "peak_source": "2 x measured bf16 burst (MEASURED_PEAKS.json)" if peak else None,
+        "share_of_layer_time": bert["gemm_seconds_per_layer"] / bert["seconds_per_layer"]}
+    out["parity"] = ("unpinned by the reference (it has no transformer code); tests/test_transformer_gpu.py "
+                     "checks the same driver against a float64 layer at reduced width")
+    return out
+
+
 def bench_hoisted(eng, torch, params, n_rot, steps):
     """Config 3: n_rot rotations of one level-28 ciphertext sharing one ModUp
     (power-of-two distances first, then seeded random ones). Keys hold random
@@ -807,12 +854,21 @@ def run_gpu(args, pkg):
         barrier()
         boot = bench_bootstrap(pkg, local, min(max(args.steps, 2), 10), 3)
 
+    bert = None
+    if args.workload == "hmult" and not args.no_bert:
+        torch.cuda.empty_cache()
+        barrier()
+        bert = bench_bert_layer(pkg, local)
+        bert_s = reduce_max([bert["seconds_per_layer"]], device=f"cuda:{local}")[0]
+
     shape = {"nq": len(eng.level_limbs(HM_LEVEL)), "nd": len(eng.level_limbs(HM_LEVEL - 1)), "alpha": eng.alpha}
     red = reduce_over_ranks(ntt, hm, boot, hoist, device=f"cuda:{local}")
     if rank == 0:
         line = assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
         if gemm:
             line["ctpt_gemm"] = gemm
+        if bert:
+            line["bert_layer"] = bert_entry(bert, bert_s, world)
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:
@@ -844,6 +900,7 @@ def main():
     ap.add_argument("--no-hoist", action="store_true", help="skip the 64-rotation hoisting sweep")
     ap.add_argument("--no-ref", action="store_true", help="skip timing the reference's CUDA library")
     ap.add_argument("--no-boot", action="store_true", help="skip the bootstrapping workload")
+    ap.add_argument("--no-bert", action="store_true", help="skip the encrypted transformer layer (about a minute)")
     ap.add_argument("--shard", default="ciphertexts", choices=["ciphertexts", "limbs"],
                     help="limbs: one HMult with its RNS limbs sharded over the ranks (strong scaling)")
     args = ap.parse_args()

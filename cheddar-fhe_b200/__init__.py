@@ -240,6 +240,13 @@ class Engine:
         g, gp = _ints(gidx)
         self._check(self.L.cfhe_tensor(self.h, *[self._p(t) for t in (d0, d1, d2, b1, a1, b2, a2)], gp, len(g)))
 
+    def tensor_accum_(self, d0, d1, d2, b1s, a1s, b2s, a2s, gidx, accumulate=False):
+        """(d0, d1, d2) (+)= sum_t tensor(b1s[t], a1s[t], b2s[t], a2s[t]) (cfhe_tensor_accum)."""
+        g, gp = _ints(gidx)
+        self._check(self.L.cfhe_tensor_accum(self.h, self._p(d0), self._p(d1), self._p(d2), len(b1s),
+                                             self._ptrs(b1s), self._ptrs(a1s), self._ptrs(b2s), self._ptrs(a2s),
+                                             1 if accumulate else 0, gp, len(g)))
+
     def permute_(self, dst, src, add, galois, gidx):
         g, gp = _ints(gidx)
         self._check(self.L.cfhe_permute(self.h, self._p(dst), self._p(src),

@@ -174,14 +174,13 @@ int cfhe_context_create(cfhe_context **out, int device, int log_degree,
 }
 
 static void pool_release_cached(Context &c);
+static void pool_destroy(Context &c);
 
 void cfhe_context_destroy(cfhe_context *h) {
   if (!h) return;
   Context &c = h->c;
   DeviceScope device_scope_(c.device);
-  pool_release_cached(c);
-  for (auto &kv : c.pool_live) cudaFree(kv.first);
-  c.pool_live.clear();
+  pool_destroy(c);
   free_plans(c);
   if (c.d_tw) cudaFree(c.d_tw);
   if (c.d_itw) cudaFree(c.d_itw);
@@ -252,38 +251,118 @@ int cfhe_level_limbs(const cfhe_context *h, int level, int num_aux, int *gidx) {
   return np_limbs(h->c, nm, nt, num_aux, gidx);
 }
 
+constexpr size_t kSlabGranule = 256u << 10;
+constexpr size_t kSlabBytes = size_t(1) << 30;
+constexpr size_t kSmallLimit = 1u << 20;
+
+static void slab_insert_free(Context &c, char *p, size_t bytes) {
+  c.slab_free_by_addr.emplace(p, bytes);
+  c.slab_free_by_size.emplace(bytes, p);
+}
+
+static void slab_erase_free(Context &c, char *p, size_t bytes) {
+  c.slab_free_by_addr.erase(p);
+  auto range = c.slab_free_by_size.equal_range(bytes);
+  for (auto it = range.first; it != range.second; ++it)
+    if (it->second == p) {
+      c.slab_free_by_size.erase(it);
+      return;
+    }
+}
+
+// Gives back to the driver what nobody uses: cached small blocks and slabs
+// that are free from end to end.
 static void pool_release_cached(Context &c) {
-  if (c.pool_free.empty()) return;
+  if (c.pool_free.empty() && c.slab_free_by_addr.empty()) return;
   cudaStreamSynchronize(c.stream);
   for (auto &kv : c.pool_free) cudaFree(kv.second);
   c.pool_free.clear();
+  for (auto it = c.slabs.begin(); it != c.slabs.end();) {
+    auto f = c.slab_free_by_addr.find(it->first);
+    if (f != c.slab_free_by_addr.end() && f->second == it->second) {
+      slab_erase_free(c, it->first, it->second);
+      cudaFree(it->first);
+      it = c.slabs.erase(it);
+    } else {
+      ++it;
+    }
+  }
   c.pool_cached_bytes = 0;
+  for (auto &kv : c.slab_free_by_addr) c.pool_cached_bytes += kv.second;
+}
+
+static void pool_destroy(Context &c) {
+  cudaStreamSynchronize(c.stream);
+  for (auto &kv : c.pool_free) cudaFree(kv.second);
+  for (auto &kv : c.pool_live)
+    if (kv.second < kSmallLimit) cudaFree(kv.first);
+  for (auto &kv : c.slabs) cudaFree(kv.first);
+  c.pool_free.clear();
+  c.pool_live.clear();
+  c.slabs.clear();
+  c.slab_free_by_addr.clear();
+  c.slab_free_by_size.clear();
+  c.pool_cached_bytes = 0;
+}
+
+static cudaError_t malloc_retry(Context &c, void **ptr, size_t bytes) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    pool_release_cached(c);
+    e = cudaMalloc(ptr, bytes);
+  }
+  return e;
 }
 
 int cfhe_malloc(cfhe_context *h, void **ptr, size_t bytes) {
   CFHE_ENTER(h);
   if (!h || !ptr) return fail("null argument");
   Context &c = h->c;
-  // size classes: multiples of 4 KiB below 1 MiB, of 256 KiB (one limb at
-  // N = 2^16) above; a cached block is reused only for its exact class
-  const size_t unit = bytes < (1u << 20) ? 4096 : (256u << 10);
-  const size_t rounded = bytes ? (bytes + unit - 1) / unit * unit : unit;
-  auto it = c.pool_free.find(rounded);
-  if (it != c.pool_free.end()) {
-    *ptr = it->second;
-    c.pool_free.erase(it);
-    c.pool_cached_bytes -= rounded;
+  if (bytes < kSmallLimit) {
+    // size classes of 4 KiB; a cached block is reused only for its exact class
+    const size_t rounded = bytes ? (bytes + 4095) / 4096 * 4096 : 4096;
+    auto it = c.pool_free.find(rounded);
+    if (it != c.pool_free.end()) {
+      *ptr = it->second;
+      c.pool_free.erase(it);
+      c.pool_cached_bytes -= rounded;
+      c.pool_live[*ptr] = rounded;
+      return 0;
+    }
+    cudaError_t e = malloc_retry(c, ptr, rounded);
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     c.pool_live[*ptr] = rounded;
     return 0;
   }
-  cudaError_t e = cudaMalloc(ptr, rounded);
-  if (e == cudaErrorMemoryAllocation) {
-    cudaGetLastError();
-    pool_release_cached(c);
-    e = cudaMalloc(ptr, rounded);
+  const size_t rounded = (bytes + kSlabGranule - 1) / kSlabGranule * kSlabGranule;
+  auto it = c.slab_free_by_size.lower_bound(rounded);
+  if (it == c.slab_free_by_size.end()) {
+    // a new slab; when the device cannot give a whole one, just the request
+    void *slab = nullptr;
+    size_t slab_bytes = rounded > kSlabBytes ? rounded : kSlabBytes;
+    cudaError_t e = cudaMalloc(&slab, slab_bytes);
+    if (e == cudaErrorMemoryAllocation && slab_bytes > rounded) {
+      cudaGetLastError();
+      slab_bytes = rounded;
+      e = malloc_retry(c, &slab, slab_bytes);
+    } else if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();
+      e = malloc_retry(c, &slab, slab_bytes);
+    }
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+    c.slabs.emplace((char *)slab, slab_bytes);
+    slab_insert_free(c, (char *)slab, slab_bytes);
+    c.pool_cached_bytes += slab_bytes;
+    it = c.slab_free_by_size.lower_bound(rounded);
   }
-  if (e != cudaSuccess) return fail(cudaGetErrorString(e));
-  c.pool_live[*ptr] = rounded;
+  char *p = it->second;
+  const size_t have = it->first;
+  slab_erase_free(c, p, have);
+  if (have > rounded) slab_insert_free(c, p + rounded, have - rounded);
+  c.pool_cached_bytes -= rounded;
+  c.pool_live[p] = rounded;
+  *ptr = p;
   return 0;
 }
 
@@ -293,9 +372,33 @@ int cfhe_free(cfhe_context *h, void *ptr) {
   Context &c = h->c;
   auto it = c.pool_live.find(ptr);
   if (it == c.pool_live.end()) return fail("cfhe_free: pointer was not returned by cfhe_malloc");
-  c.pool_free.emplace(it->second, ptr);
-  c.pool_cached_bytes += it->second;
+  size_t bytes = it->second;
   c.pool_live.erase(it);
+  c.pool_cached_bytes += bytes;
+  if (bytes < kSmallLimit) {
+    c.pool_free.emplace(bytes, ptr);
+    return 0;
+  }
+  // merge with the free neighbours of the same slab (a slab start is never merged into)
+  char *p = (char *)ptr;
+  auto next = c.slab_free_by_addr.lower_bound(p);
+  if (next != c.slab_free_by_addr.end() && next->first == p + bytes && !c.slabs.count(next->first)) {
+    const size_t nb = next->second;
+    slab_erase_free(c, next->first, nb);
+    bytes += nb;
+  }
+  auto after = c.slab_free_by_addr.lower_bound(p);
+  if (after != c.slab_free_by_addr.begin() && !c.slabs.count(p)) {
+    auto prev = std::prev(after);
+    if (prev->first + prev->second == p) {
+      char *pp = prev->first;
+      const size_t pb = prev->second;
+      slab_erase_free(c, pp, pb);
+      p = pp;
+      bytes += pb;
+    }
+  }
+  slab_insert_free(c, p, bytes);
   return 0;
 }
 
@@ -561,6 +664,36 @@ int cfhe_permute_accum(cfhe_context *h, int n_polys, uint32_t *const *dst, int n
       if (a.src[t][p] == a.dst[p]) return fail("permute cannot run in place");
   }
   { int r_ = launch_nary(h->c, a); h->c.mark("permute"); return r_; }
+}
+
+int cfhe_tensor_accum(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2, int n_terms,
+                      const uint32_t *const *b1, const uint32_t *const *a1, const uint32_t *const *b2,
+                      const uint32_t *const *a2, int accumulate, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!d0 || !d1 || !d2 || !b1 || !a1 || !b2 || !a2 || !gidx) return fail("null argument");
+  if (n_terms < 1 || n_terms > kMaxTensorTerms) return fail("tensor accumulate: one to sixteen terms");
+  if (n_limbs < 0 || n_limbs > kMaxLimbs) return fail("too many limbs");
+  TensorAccArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n_terms = n_terms;
+  a.n_limbs = n_limbs;
+  a.accumulate = accumulate != 0;
+  a.d[0] = d0;
+  a.d[1] = d1;
+  a.d[2] = d2;
+  for (int t = 0; t < n_terms; t++) {
+    if (!b1[t] || !a1[t] || !b2[t] || !a2[t]) return fail("null argument");
+    a.b1[t] = b1[t];
+    a.a1[t] = a1[t];
+    a.b2[t] = b2[t];
+    a.a2[t] = a2[t];
+  }
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= h->c.NP) return fail("prime index out of range");
+    a.q[l] = h->c.q[gidx[l]];
+    a.nqinv[l] = h->c.nqinv[gidx[l]];
+  }
+  { int r_ = launch_tensor_accum(h->c, a); h->c.mark("elementwise"); return r_; }
 }
 
 size_t cfhe_gemm_weight_bytes(int n_in, int n_out, int n_limbs) {

@@ -115,13 +115,21 @@ struct Context {
   uint32_t *ws = nullptr;
   size_t ws_words = 0;
 
-  // Caching device allocator behind cfhe_malloc / cfhe_free. A freed block is
-  // kept and handed to a later request of the same rounded size; since every
-  // kernel of this context runs on one stream, the next user's work is ordered
-  // after the previous user's without a synchronisation. Blocks go back to
-  // the driver when an allocation fails, on a stream change and on destroy.
-  std::multimap<size_t, void *> pool_free;
-  std::unordered_map<void *, size_t> pool_live;
+  // Device allocator behind cfhe_malloc / cfhe_free. Requests of 1 MiB and
+  // more (polynomials) are carved, best fit, out of slabs of 1 GiB taken from
+  // the driver, in units of 256 KiB (one limb at N = 2^16); freed ranges merge
+  // with their free neighbours inside a slab. Smaller requests keep a cache
+  // of blocks per 4 KiB size class. Either way a freed block goes to a later
+  // request without a driver call (cudaMalloc synchronises the device), and
+  // since every kernel of this context runs on one stream, the next user's
+  // work is ordered after the previous user's. Slabs that are wholly free go
+  // back to the driver when an allocation fails and on a stream change;
+  // everything does on destroy.
+  std::multimap<size_t, void *> pool_free;            // small classes: size -> block
+  std::unordered_map<void *, size_t> pool_live;       // every block handed out -> its rounded size
+  std::multimap<size_t, char *> slab_free_by_size;    // free ranges inside slabs
+  std::map<char *, size_t> slab_free_by_addr;
+  std::map<char *, size_t> slabs;                     // slab start -> bytes
   size_t pool_cached_bytes = 0;
 
   // optional stage timing: one CUDA event after each pipeline stage

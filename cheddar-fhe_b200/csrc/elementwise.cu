@@ -180,6 +180,49 @@ __global__ void __launch_bounds__(kEwThreads)
   }
 }
 
+// Sum of tensor products, each of the three outputs accumulated in 64 bits
+// (folded below q * 2^32 after every product) with one Montgomery reduction
+// per output word: the inner sums of an encrypted matrix product, where the
+// reference would run Tensor (src/core/ElementWise.cu:504-546) and Add once per
+// term. With `accumulate` the previous contents of the outputs are added.
+__global__ void __launch_bounds__(kEwThreads)
+    tensor_accum_kernel(const __grid_constant__ TensorAccArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int l = blockIdx.y, v = blockIdx.x * kEwThreads + threadIdx.x;
+  const size_t off = (size_t)l * (kN / 4) + v;
+  const uint32_t q = a.q[l], nq = a.nqinv[l];
+  const uint64_t q32 = (uint64_t)q << 32;
+  uint64_t s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
+  for (int t = 0; t < a.n_terms; t++) {
+    const uint4 b1 = reinterpret_cast<const uint4 *>(a.b1[t])[off];
+    const uint4 a1 = reinterpret_cast<const uint4 *>(a.a1[t])[off];
+    const uint4 b2 = reinterpret_cast<const uint4 *>(a.b2[t])[off];
+    const uint4 a2 = reinterpret_cast<const uint4 *>(a.a2[t])[off];
+    const uint32_t xb1[4] = {b1.x, b1.y, b1.z, b1.w}, xa1[4] = {a1.x, a1.y, a1.z, a1.w};
+    const uint32_t xb2[4] = {b2.x, b2.y, b2.z, b2.w}, xa2[4] = {a2.x, a2.y, a2.z, a2.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      mac_fold(s0[e], xb1[e], xb2[e], q32);
+      mac_fold(s1[e], xb1[e], xa2[e], q32);
+      mac_fold(s1[e], xa1[e], xb2[e], q32);
+      mac_fold(s2[e], xa1[e], xa2[e], q32);
+    }
+  }
+  uint64_t *const sums[3] = {s0, s1, s2};
+#pragma unroll
+  for (int p = 0; p < 3; p++) {
+    uint4 o = make_uint4(mont_reduce(sums[p][0], q, nq), mont_reduce(sums[p][1], q, nq),
+                         mont_reduce(sums[p][2], q, nq), mont_reduce(sums[p][3], q, nq));
+    uint4 *dst = reinterpret_cast<uint4 *>(a.d[p]) + off;
+    if (a.accumulate) {
+      const uint4 old = *dst;
+      o = map4(o, old, [=](uint32_t x, uint32_t y) { return add_mod(x, y, q); });
+    }
+    *dst = o;
+  }
+}
+
 // Key-switch inner product: for every limb l of the extended basis
 //   acc_b[l] = sum_i x_i[l] * kb_i[l] (+ P * c0[l] on Q limbs), same for a.
 // x_i[l] is the digit's own limb read in place from `d` when limb l belongs
@@ -410,6 +453,14 @@ int launch_nary(const Context &ctx, const NaryArgs &args) {
       set_error("unknown n-ary mode");
       return -1;
   }
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_tensor_accum(const Context &ctx, const TensorAccArgs &args) {
+  if (args.n_limbs <= 0) return 0;
+  dim3 grid(kEwBlocksX, args.n_limbs), block(kEwThreads);
+  CFHE_CUDA(launch_kernel(ctx.use_pdl, tensor_accum_kernel, grid, block, 0, ctx.stream, args));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -66,6 +66,16 @@ struct NaryArgs {
   uint32_t c[kMaxTerms][kMaxLimbs];
 };
 
+// Sum of up to kMaxTensorTerms tensor products in one pass:
+//   (d0, d1, d2) (+)= sum_t (b1_t b2_t, b1_t a2_t + a1_t b2_t, a1_t a2_t)
+constexpr int kMaxTensorTerms = 16;
+struct TensorAccArgs {
+  int n_terms, n_limbs, accumulate;
+  uint32_t *d[3];
+  const uint32_t *b1[kMaxTensorTerms], *a1[kMaxTensorTerms], *b2[kMaxTensorTerms], *a2[kMaxTensorTerms];
+  uint32_t q[kMaxLimbs], nqinv[kMaxLimbs];
+};
+
 constexpr int kMaxDigits = 8;
 struct InnerArgs {
   uint32_t *acc_b, *acc_a;
@@ -151,6 +161,7 @@ int launch_tensor(const Context &ctx, const TensorArgs &args);
 int launch_lift(const Context &ctx, const EwArgs &args, const uint32_t *src, uint32_t q0, uint32_t q1);
 int launch_permute(const Context &ctx, const EwArgs &args, uint32_t galois);
 int launch_nary(const Context &ctx, const NaryArgs &args);
+int launch_tensor_accum(const Context &ctx, const TensorAccArgs &args);
 // gemm_tc.cu: ciphertext x plaintext RNS GEMM on the tensor cores
 size_t gemm_packed_weight_bytes(int n_in, int n_out);  // per limb
 size_t gemm_scratch_bytes(int n_in);

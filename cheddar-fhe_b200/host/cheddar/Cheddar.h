@@ -1021,6 +1021,41 @@ class Context : public std::enable_shared_from_this<Context<word>> {
     CheckAbi(cfhe_tensor(h_, res.bx_.data(), res.ax_.data(), res.rx_.data(), a.bx_.data() + ao,
                          a.ax_.data() + ao, b.bx_.data() + bo, b.ax_.data() + bo, g.data(), g.size()));
   }
+  // res = sum_t a[t] * b[t] as ONE unrelinearised three-part product (all
+  // operands on the same level, without aux primes): one pass over the
+  // operands instead of a MultUnsafe and an Add per term. The reference has no
+  // n-ary tensor product; the words equal those of that composition.
+  void MultSumUnsafe(Ct &res, const std::vector<const Ct *> &a, const std::vector<const Ct *> &b) const {
+    AssertTrue(!a.empty() && a.size() == b.size(), "MultSumUnsafe: bad operand lists");
+    const NPInfo np = a[0]->GetNP();
+    AssertTrue(np.num_aux_ == 0, "MultSumUnsafe should be only used for ciphertexts without aux primes");
+    int slots = 0;
+    for (size_t t = 0; t < a.size(); t++) {
+      AssertFalse(a[t]->HasRx() || b[t]->HasRx(), "Relinearization required before MultSumUnsafe");
+      AssertTrue(a[t]->GetNP() == np && b[t]->GetNP() == np, "MultSumUnsafe: operands on different levels");
+      AssertTrue(&res != a[t] && &res != b[t], "MultSumUnsafe cannot run in place");
+      AssertSameScale(a[t]->GetScale() * b[t]->GetScale(), a[0]->GetScale() * b[0]->GetScale());
+      slots = Max(slots, Max(a[t]->GetNumSlots(), b[t]->GetNumSlots()));
+    }
+    res.ModifyNP(np);
+    res.PrepareRx();
+    res.SetNumSlots(slots);
+    res.SetScale(a[0]->GetScale() * b[0]->GetScale());
+    auto g = param_.GetLimbIndices(np);
+    constexpr size_t kChunk = 16;
+    for (size_t t0 = 0; t0 < a.size(); t0 += kChunk) {
+      const size_t n = Min(kChunk, a.size() - t0);
+      std::vector<const word *> b1(n), a1(n), b2(n), a2(n);
+      for (size_t t = 0; t < n; t++) {
+        b1[t] = a[t0 + t]->bx_.data();
+        a1[t] = a[t0 + t]->ax_.data();
+        b2[t] = b[t0 + t]->bx_.data();
+        a2[t] = b[t0 + t]->ax_.data();
+      }
+      CheckAbi(cfhe_tensor_accum(h_, res.bx_.data(), res.ax_.data(), res.rx_.data(), (int)n, b1.data(), a1.data(),
+                                 b2.data(), a2.data(), t0 > 0, g.data(), g.size()));
+    }
+  }
   void MultUnsafe(Ct &res, const Ct &a, const Pt &b, int level = -1) const {
     const NPInfo a_np = a.GetNP(), b_np = b.GetNP();
     if (level == -1) level = Min(param_.NPToLevel(a_np), param_.NPToLevel(b_np));

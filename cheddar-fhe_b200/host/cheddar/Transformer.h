@@ -232,6 +232,7 @@ class EncryptedTransformerLayer {
     const Evk &mult = evk.GetMultiplicationKey();
     stage_s_.clear();
     gemm_s_ = 0;
+    pack_s_ = 0;
     gemm_macs_ = 0;
     boots_ = 0;
     ctx_->Synchronize();
@@ -345,6 +346,7 @@ class EncryptedTransformerLayer {
   // seconds per stage of the last Forward (the host synchronises between stages)
   const std::vector<std::pair<std::string, double>> &StageSeconds() const { return stage_s_; }
   double GemmSeconds() const { return gemm_s_; }
+  double PackSeconds() const { return pack_s_; }  // encoding and packing the weights (first Forward only)
   double GemmInt8Macs() const { return gemm_macs_; }
   int Bootstraps() const { return boots_; }
 
@@ -388,22 +390,19 @@ class EncryptedTransformerLayer {
     while ((size_t(1) << k) < coeffs.size()) k++;
     EvalPoly<word>::EvaluateChebyshev(ctx_, res, x, coeffs, mult, Canon(Level(x) - k));
   }
-  // acc (+)= a * b as an unrelinearised three-part product
-  void TensorAccumulate(Ct &acc, bool first, const Ct &a, const Ct &b) const {
-    if (first) {
-      ctx_->MultUnsafe(acc, a, b);
-    } else {
-      Ct t;
-      ctx_->MultUnsafe(t, a, b);
-      ctx_->Add(acc, acc, t);
-    }
-  }
-
+  // Encoding and packing a matrix happens once, on the first Forward, and is
+  // kept out of the stage times (reported by PackSeconds).
   std::unique_ptr<PlainMatrix<word>> MakeMatrix(const std::vector<double> &wm, int n_in, int n_out,
-                                                const Ct &sample) const {
+                                                const Ct &sample) {
+    ctx_->Synchronize();
+    const auto t0 = std::chrono::steady_clock::now();
     const int l = Level(sample);
     const double s = Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / sample.GetScale();
-    return std::make_unique<PlainMatrix<word>>(*ctx_, wm, n_in, n_out, l, s);
+    auto m = std::make_unique<PlainMatrix<word>>(*ctx_, wm, n_in, n_out, l, s);
+    const auto d = std::chrono::steady_clock::now() - t0;
+    last_ += d;
+    pack_s_ += std::chrono::duration<double>(d).count();
+    return m;
   }
   // y = rescale(W x) + bias, one level below x at the canonical scale
   void Project(std::vector<Ct> &y, const PlainMatrix<word> &m, const std::vector<const Ct *> &x,
@@ -508,7 +507,12 @@ class EncryptedTransformerLayer {
         for (int d = 0; d < D && g; d++) RotateTokens(qg[d], Q(d), -g * nb, evk);
         for (int b = 0; b < nb; b++) {
           Ct acc, u;
-          for (int d = 0; d < D; d++) TensorAccumulate(acc, d == 0, g ? qg[d] : Q(d), kb[d][b]);
+          std::vector<const Ct *> left(D), right(D);
+          for (int d = 0; d < D; d++) {
+            left[d] = g ? &qg[d] : &Q(d);
+            right[d] = &kb[d][b];
+          }
+          ctx_->MultSumUnsafe(acc, left, right);
           ctx_->RelinearizeRescale(u, acc, mult);
           if (g) {
             Ct r;
@@ -540,7 +544,12 @@ class EncryptedTransformerLayer {
       for (int b = 0; b < nb && g; b++) RotateTokens(eg[b], e[g * nb + b], -g * nb, evk);
       for (int d = 0; d < D; d++) {
         Ct acc, t;
-        for (int b = 0; b < nb; b++) TensorAccumulate(acc, b == 0, g ? eg[b] : e[b], vb[d][b]);
+        std::vector<const Ct *> left(nb), right(nb);
+        for (int b = 0; b < nb; b++) {
+          left[b] = g ? &eg[b] : &e[b];
+          right[b] = &vb[d][b];
+        }
+        ctx_->MultSumUnsafe(acc, left, right);
         ctx_->RelinearizeRescale(t, acc, mult);
         if (g) {
           Ct r;
@@ -561,7 +570,7 @@ class EncryptedTransformerLayer {
     const double A = cfg_.act_div, span = cfg_.var_hi - cfg_.var_lo;
     const Evk &mult = evk.GetMultiplicationKey();
     Ct acc, ss, w;
-    for (int j = 0; j < H; j++) TensorAccumulate(acc, j == 0, y[j], y[j]);
+    ctx_->MultSumUnsafe(acc, Pointers(y), Pointers(y));
     ctx_->RelinearizeRescale(ss, acc, mult);
     MaskedAffine(w, ss, 2.0 * A * A / (H * span), -(cfg_.var_hi + cfg_.var_lo) / span);
     std::vector<Ct> one(1);
@@ -677,7 +686,7 @@ class EncryptedTransformerLayer {
   std::vector<double> mask_signs_;
   std::vector<std::pair<std::string, double>> stage_s_;
   std::chrono::steady_clock::time_point last_;
-  double gemm_s_ = 0, gemm_macs_ = 0;
+  double gemm_s_ = 0, gemm_macs_ = 0, pack_s_ = 0;
   int boots_ = 0;
 };
 

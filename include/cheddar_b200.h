@@ -174,6 +174,16 @@ CFHE_API int cfhe_paccum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, i
 CFHE_API int cfhe_permute_accum(cfhe_context *ctx, int n_polys, uint32_t *const *dst, int n_terms,
                                 const uint32_t *const *src, const uint32_t *galois,
                                 const uint32_t *const *addend, const int *gidx, int n_limbs);
+/* (d0,d1,d2) (+)= sum over n_terms (<= 16) of the tensor products
+ * (b1*b2, b1*a2 + a1*b2, a1*a2); accumulate != 0 adds to what d0..d2 hold.
+ * One pass over the operands instead of one Tensor and one Add per term
+ * (ElementWiseHandler::Tensor, src/core/ElementWise.cu:922, kernel :504-546;
+ * the reference has no n-ary form of it). Operand tables: HOST arrays of
+ * DEVICE pointers. Same words as cfhe_tensor followed by cfhe_binary(add). */
+CFHE_API int cfhe_tensor_accum(cfhe_context *ctx, uint32_t *d0, uint32_t *d1, uint32_t *d2, int n_terms,
+                               const uint32_t *const *b1, const uint32_t *const *a1,
+                               const uint32_t *const *b2, const uint32_t *const *a2, int accumulate,
+                               const int *gidx, int n_limbs);
 /* Ciphertext x plaintext RNS GEMM on the tensor cores (tcgen05 kind::i8, exact):
  *   y[j] = sum_k W[l][k][j] * x[k]  on every listed limb l,
  * n_in input and n_out output polynomials of n_limbs limbs each, W words in

@@ -56,3 +56,34 @@ def test_allocator_reuses_blocks(engine40):
     assert p1.value == p2.value  # the freed block is handed out again, no cudaMalloc
     e._check(e.L.cfhe_free(e.h, p2))
     e._check(e.L.cfhe_free(e.h, None))  # freeing NULL is a no-op
+
+
+def test_allocator_merges_free_neighbours(engine40):
+    """Three blocks carved side by side out of one slab, freed in the order
+    first, last, middle, come back as one range: a request of their total size
+    gets the first block's address, and the words written through it survive."""
+    e = engine40
+    sizes = [3 << 20, 5 << 20, (1 << 20) + 1]
+    ptrs = [C.c_void_p() for _ in sizes]
+    for p, s in zip(ptrs, sizes):
+        e._check(e.L.cfhe_malloc(e.h, C.byref(p), C.c_size_t(s)))
+    rounded = [(s + (256 << 10) - 1) // (256 << 10) * (256 << 10) for s in sizes]
+    if ptrs[1].value != ptrs[0].value + rounded[0] or ptrs[2].value != ptrs[1].value + rounded[1]:
+        for p in ptrs:
+            e._check(e.L.cfhe_free(e.h, p))
+        pytest.skip("the three blocks did not come out of one free range")
+    for i in (0, 2, 1):
+        e._check(e.L.cfhe_free(e.h, ptrs[i]))
+    big = C.c_void_p()
+    e._check(e.L.cfhe_malloc(e.h, C.byref(big), C.c_size_t(sum(rounded))))
+    assert big.value == ptrs[0].value
+    words = sum(rounded) // 4
+    host = np.arange(words, dtype=np.uint32)
+    back = np.empty_like(host)
+    e._check(e.L.cfhe_copy_h2d(e.h, big, host.ctypes.data_as(C.c_void_p), C.c_size_t(host.nbytes)))
+    e._check(e.L.cfhe_copy_d2h(e.h, back.ctypes.data_as(C.c_void_p), big, C.c_size_t(host.nbytes)))
+    e.synchronize()
+    assert np.array_equal(host, back)
+    e._check(e.L.cfhe_free(e.h, big))
+    with pytest.raises(Exception, match="not returned"):
+        e._check(e.L.cfhe_free(e.h, big))  # double free is refused

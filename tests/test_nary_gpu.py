@@ -96,3 +96,29 @@ def test_nary_argument_checks(engine40, pkg):
         e.nary_("permute", [a], [[a]], g, galois=[5])   # in place
     with pytest.raises(pkg.CfheError):
         e.nary_("permute", [a], [[b]], g, galois=[4])   # even Galois element
+
+
+@pytest.mark.parametrize("n_terms,accumulate", [(1, False), (3, True), (16, False), (16, True)])
+def test_tensor_accum(engine40, oracle40, n_terms, accumulate):
+    """cfhe_tensor_accum against the golden model's Tensor and Add applied term by term."""
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(1300 + n_terms)
+    g = e.level_limbs(12)
+    ops = [[rand_limbs(rng, o.primes, g, o.n) for _ in range(4)] for _ in range(n_terms)]
+    for l, gi in enumerate(g):  # extreme residues: the 64-bit accumulators see their largest sums
+        q = int(o.primes[gi])
+        for t in range(n_terms):
+            for x in ops[t]:
+                x[l, :2] = [q - 1, q - 1]
+            ops[t][0][l, 2:4] = [0, 1]
+    dev = [[e.to_dev(x) for x in term] for term in ops]
+    start = [rand_limbs(rng, o.primes, g, o.n) for _ in range(3)]
+    out = [e.to_dev(x) for x in start]
+    e.tensor_accum_(out[0], out[1], out[2], [t[0] for t in dev], [t[1] for t in dev], [t[2] for t in dev],
+                    [t[3] for t in dev], g, accumulate=accumulate)
+    want = [x.copy() for x in start] if accumulate else None
+    for t in range(n_terms):
+        d = o.tensor(ops[t][0], ops[t][1], ops[t][2], ops[t][3], g)
+        want = list(d) if want is None else [o.add(w, x, g) for w, x in zip(want, d)]
+    for p in range(3):
+        assert np.array_equal(e.to_host(out[p]), want[p]), p
