@@ -247,6 +247,16 @@ class Engine:
                                              self._ptrs(b1s), self._ptrs(a1s), self._ptrs(b2s), self._ptrs(a2s),
                                              1 if accumulate else 0, gp, len(g)))
 
+    def giantstep_paccum_(self, acc, rot, pts, gidx):
+        """acc[j] = sum_i pts[j][i] (*) rot[i] (cfhe_giantstep_paccum); rot [n_baby][2][limbs][N],
+        acc [n_giant][2][limbs][N], pts[j][i] a tensor or None."""
+        g, gp = _ints(gidx)
+        n_giant, n_baby = len(pts), len(pts[0])
+        flat = (C.c_void_p * (n_giant * n_baby))(*[self._p(t) if t is not None else None
+                                                     for row in pts for t in row])
+        self._check(self.L.cfhe_giantstep_paccum(self.h, self._p(acc), self._p(rot), n_baby, n_giant, flat,
+                                                 gp, len(g)))
+
     def permute_(self, dst, src, add, galois, gidx):
         g, gp = _ints(gidx)
         self._check(self.L.cfhe_permute(self.h, self._p(dst), self._p(src),

@@ -696,6 +696,30 @@ int cfhe_tensor_accum(cfhe_context *h, uint32_t *d0, uint32_t *d1, uint32_t *d2,
   { int r_ = launch_tensor_accum(h->c, a); h->c.mark("elementwise"); return r_; }
 }
 
+int cfhe_giantstep_paccum(cfhe_context *h, uint32_t *acc, const uint32_t *rot, int n_baby, int n_giant,
+                          const uint32_t *const *pt, const int *gidx, int n_limbs) {
+  CFHE_ENTER(h);
+  if (!acc || !rot || !pt || !gidx) return fail("null argument");
+  if (n_baby < 1 || n_baby > kMaxBaby || n_giant < 1 || n_giant > kMaxGiant)
+    return fail("giant-step accumulate: 1 to 16 baby and giant steps");
+  if (n_limbs < 1 || n_limbs > kMaxLimbs) return fail("too many limbs");
+  PtAccumArgs a;
+  memset(&a, 0, sizeof(a));
+  a.rot = rot;
+  a.acc = acc;
+  a.n_baby = n_baby;
+  a.n_giant = n_giant;
+  a.ntot = n_limbs;
+  for (int j = 0; j < n_giant; j++)
+    for (int i = 0; i < n_baby; i++) a.pt[j * kMaxBaby + i] = pt[j * n_baby + i];
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= h->c.NP) return fail("prime index out of range");
+    a.q[l] = h->c.q[gidx[l]];
+    a.nqinv[l] = h->c.nqinv[gidx[l]];
+  }
+  { int r_ = launch_pt_accum(h->c, a); h->c.mark("elementwise"); return r_; }
+}
+
 size_t cfhe_gemm_weight_bytes(int n_in, int n_out, int n_limbs) {
   if (n_in < 1 || n_out < 1 || n_limbs < 1) return 0;
   return gemm_packed_weight_bytes(n_in, n_out) * (size_t)n_limbs;

@@ -184,6 +184,16 @@ CFHE_API int cfhe_tensor_accum(cfhe_context *ctx, uint32_t *d0, uint32_t *d1, ui
                                const uint32_t *const *b1, const uint32_t *const *a1,
                                const uint32_t *const *b2, const uint32_t *const *a2, int accumulate,
                                const int *gidx, int n_limbs);
+/* Plaintext products of a baby-step/giant-step linear transform, all giant
+ * steps in one launch (the reference's GSFusedKernel, src/extension/Hoist.cu:80-118):
+ *   acc[j] = sum_i pt[j * n_baby + i] (*) rot[i]   on both polynomials,
+ * a NULL plaintext is skipped. rot: [n_baby][2][n_limbs][N] (b, a of every
+ * baby rotation), acc: [n_giant][2][n_limbs][N], pt: HOST array of
+ * n_giant * n_baby DEVICE pointers ([n_limbs][N] each); at most 16 baby and 16
+ * giant steps. (The reference passes tables of polynomial pointers instead of
+ * two contiguous buffers.) */
+CFHE_API int cfhe_giantstep_paccum(cfhe_context *ctx, uint32_t *acc, const uint32_t *rot, int n_baby,
+                                   int n_giant, const uint32_t *const *pt, const int *gidx, int n_limbs);
 /* Ciphertext x plaintext RNS GEMM on the tensor cores (tcgen05 kind::i8, exact):
  *   y[j] = sum_k W[l][k][j] * x[k]  on every listed limb l,
  * n_in input and n_out output polynomials of n_limbs limbs each, W words in

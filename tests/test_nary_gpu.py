@@ -122,3 +122,34 @@ def test_tensor_accum(engine40, oracle40, n_terms, accumulate):
         want = list(d) if want is None else [o.add(w, x, g) for w, x in zip(want, d)]
     for p in range(3):
         assert np.array_equal(e.to_host(out[p]), want[p]), p
+
+
+@pytest.mark.parametrize("n_baby,n_giant", [(1, 1), (5, 3), (16, 4)])
+def test_giantstep_paccum(engine40, oracle40, n_baby, n_giant):
+    """cfhe_giantstep_paccum (the reference's GSFusedKernel, src/extension/Hoist.cu:80-118)
+    against products and sums of the golden model; some plaintexts absent."""
+    e, o = engine40, oracle40
+    t = e.torch
+    rng = np.random.default_rng(1400 + n_baby)
+    g = e.level_limbs(16, 12)
+    rot_h = np.stack([np.stack([rand_limbs(rng, o.primes, g, o.n) for _ in range(2)]) for _ in range(n_baby)])
+    for l, gi in enumerate(g):
+        rot_h[:, :, l, :2] = int(o.primes[gi]) - 1
+    pts_h = [[None if (i + j) % 4 == 3 else rand_limbs(rng, o.primes, g, o.n) for i in range(n_baby)]
+             for j in range(n_giant)]
+    for l, gi in enumerate(g):
+        for row in pts_h:
+            if row[0] is not None:
+                row[0][l, :2] = int(o.primes[gi]) - 1
+    rot = e.to_dev(rot_h.reshape(-1, o.n)).reshape(n_baby, 2, len(g), o.n)
+    pts = [[None if p is None else e.to_dev(p) for p in row] for row in pts_h]
+    acc = t.empty((n_giant, 2, len(g), o.n), dtype=t.int32, device=rot.device)
+    e.giantstep_paccum_(acc, rot, pts, g)
+    got = e.to_host(acc.reshape(-1, o.n)).reshape(n_giant, 2, len(g), o.n)
+    for j in range(n_giant):
+        for part in range(2):
+            want = np.zeros((len(g), o.n), dtype=np.uint32)
+            for i in range(n_baby):
+                if pts_h[j][i] is not None:
+                    want = o.add(want, o.mul(rot_h[i, part], pts_h[j][i], g), g)
+            assert np.array_equal(got[j, part], want), (j, part)
