@@ -1,9 +1,11 @@
 /*
  * Scalar CPU golden model of the CKKS RNS hot path. TEST INFRASTRUCTURE ONLY
  * (see cfhe_oracle.h). Every function names the reference code it restates.
- * Parity with the reference at limb level is not pinned by any vector the
- * reference ships ("parity unpinned" except through algebraic identities and
- * the reference's own CUDA build on identical buffers).
+ * The reference ships no golden vectors for this path; parity is pinned by the
+ * reference itself: its CUDA sources, built unmodified, are fed the same device
+ * buffers on a GPU and agree word for word with these functions, and the
+ * SHA-256 digests of 27 of its outputs (tests/golden/reference_digests.json)
+ * are checked against this file on the CPU.
  */
 #include "cfhe_oracle.h"
 

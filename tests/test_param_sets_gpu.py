@@ -89,8 +89,8 @@ def fake_key(rng, e, o, p, key_main, beta):
 
 def _hmult_levels(name):
     n = _levels(name)
-    # the top level, the level the parameter files encrypt at, one in the
-    # terminal/main trading range, and level 1 (the last that can be rescaled)
+    # the top level, the middle level, level 4 (inside the range where levels
+    # trade terminal for main primes) and level 1 (the last that can be rescaled)
     return sorted({n - 1, n // 2, 4, 1})
 
 
