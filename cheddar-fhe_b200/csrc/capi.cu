@@ -206,7 +206,10 @@ int cfhe_set_stream(cfhe_context *h, void *cuda_stream) {
   // cached blocks the new stream's work will touch: wait for it here (a stream
   // change is a set-up step, not a hot-path call).
   CFHE_CUDA(cudaStreamSynchronize(c.stream));
-  pool_release_cached(c);
+  {
+    std::lock_guard<std::mutex> pool_lock(c.pool_mutex);
+    pool_release_cached(c);
+  }
   drop_own_stream(c);
   c.stream = (cudaStream_t)cuda_stream;
   return 0;
@@ -218,7 +221,10 @@ int cfhe_use_own_stream(cfhe_context *h) {
   Context &c = h->c;
   if (c.own_stream) return 0;
   CFHE_CUDA(cudaStreamSynchronize(c.stream));
-  pool_release_cached(c);
+  {
+    std::lock_guard<std::mutex> pool_lock(c.pool_mutex);
+    pool_release_cached(c);
+  }
   CFHE_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
   c.own_stream = true;
   return 0;
@@ -319,6 +325,7 @@ int cfhe_malloc(cfhe_context *h, void **ptr, size_t bytes) {
   CFHE_ENTER(h);
   if (!h || !ptr) return fail("null argument");
   Context &c = h->c;
+  std::lock_guard<std::mutex> pool_lock(c.pool_mutex);
   if (bytes < kSmallLimit) {
     // size classes of 4 KiB; a cached block is reused only for its exact class
     const size_t rounded = bytes ? (bytes + 4095) / 4096 * 4096 : 4096;
@@ -370,6 +377,7 @@ int cfhe_free(cfhe_context *h, void *ptr) {
   if (!h) return fail("null context");
   if (!ptr) return 0;
   Context &c = h->c;
+  std::lock_guard<std::mutex> pool_lock(c.pool_mutex);
   auto it = c.pool_live.find(ptr);
   if (it == c.pool_live.end()) return fail("cfhe_free: pointer was not returned by cfhe_malloc");
   size_t bytes = it->second;

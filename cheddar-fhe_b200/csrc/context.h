@@ -125,6 +125,9 @@ struct Context {
   // work is ordered after the previous user's. Slabs that are wholly free go
   // back to the driver when an allocation fails and on a stream change;
   // everything does on destroy.
+  // cfhe_malloc / cfhe_free may be called from several host threads (a
+  // container is freed by whichever thread drops it); the maps are guarded.
+  std::mutex pool_mutex;
   std::multimap<size_t, void *> pool_free;            // small classes: size -> block
   std::unordered_map<void *, size_t> pool_live;       // every block handed out -> its rounded size
   std::multimap<size_t, char *> slab_free_by_size;    // free ranges inside slabs

@@ -106,8 +106,8 @@ int build_plans(Context &c) {
   {
     const char *chunk = getenv("CFHE_NTT_CHUNK");
     const char *unit = getenv("CFHE_NTT_UNIT");
-    c.ntt_chunk = chunk ? atoi(chunk) : 320;
-    if (c.ntt_chunk < 1 || c.ntt_chunk > 4096) c.ntt_chunk = 320;
+    c.ntt_chunk = chunk ? atoi(chunk) : 640;
+    if (c.ntt_chunk < 1 || c.ntt_chunk > 4096) c.ntt_chunk = 640;
     c.ntt_unit = unit ? atoi(unit) : 4;
     if (c.ntt_unit < 1 || c.ntt_unit > 255) c.ntt_unit = 4;
   }

@@ -5,7 +5,7 @@
 // reference has no transformer code (CMakeLists.txt:63-75), so there is no
 // reference figure for this workload.
 //
-//   bert_bench <parameter.json> [--passes K] [--warmup W] [--small] [--no-pair]
+//   bert_bench <parameter.json> [--passes K] [--warmup W] [--workers T] [--small] [--no-pair]
 //
 // W warm-up passes (default 1) come before the K timed ones (default 1); the
 // first pass also encodes and packs the weight matrices (pack_weights_s, kept
@@ -21,10 +21,10 @@ using word = uint32_t;
 
 int main(int argc, char **argv) {
   if (argc < 2) {
-    std::cerr << "usage: bert_bench <parameter.json> [--passes K] [--warmup W] [--small] [--no-pair]\n";
+    std::cerr << "usage: bert_bench <parameter.json> [--passes K] [--warmup W] [--workers T] [--small] [--no-pair]\n";
     return 2;
   }
-  int passes = 1, warmup = 1;
+  int passes = 1, warmup = 1, workers = 4;
   TransformerConfig cfg = TransformerConfig::BertBase();
   double stddev = 0.02;
   for (int i = 2; i < argc; i++) {
@@ -36,7 +36,9 @@ int main(int argc, char **argv) {
       cfg.pair_boot = pair;
       stddev = 0.08;
     } else if (!strcmp(argv[i], "--no-pair")) cfg.pair_boot = false;
+    else if (!strcmp(argv[i], "--workers") && i + 1 < argc) workers = std::max(1, atoi(argv[++i]));
   }
+  cfg.workers = workers;
   Random::Seed(20241125);
   auto clock = [] { return std::chrono::steady_clock::now(); };
   auto since = [&](std::chrono::steady_clock::time_point t) {
@@ -133,7 +135,7 @@ int main(int argc, char **argv) {
              << ", \"warmup_passes\": " << warmup << ", \"warmup_s\": " << warm_s << ", \"pack_weights_s\": " << pack_s << ", \"keys_s\": " << keys_s << ", \"encrypt_s\": " << encrypt_s
             << ", \"shape\": {\"seq_len\": " << T << ", \"hidden\": " << H << ", \"heads\": " << cfg.heads
             << ", \"head_dim\": " << cfg.head_dim << ", \"ffn\": " << cfg.ffn << "}"
-            << ", \"bootstraps_per_layer\": " << layer.Bootstraps() << ", \"paired_bootstraps\": "
+             << ", \"host_threads\": " << cfg.workers << ", \"bootstraps_per_layer\": " << layer.Bootstraps() << ", \"paired_bootstraps\": "
             << (cfg.pair_boot ? "true" : "false") << ", \"level_in_out\": " << level
             << ", \"gemm_seconds_per_layer\": " << gemm_s / timed << ", \"gemm_int8_TOPS\": "
             << 2.0 * gemm_macs / gemm_s * 1e-12 << ", \"output_token_mean_abs_max\": " << worst_mean

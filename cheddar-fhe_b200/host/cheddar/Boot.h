@@ -622,8 +622,12 @@ class EvalPoly {
       if (ctx->param_.LevelToNP(level).IsSubsetOf(t.GetNP())) return t;
       auto it = low.find({m, level});
       if (it == low.end()) {
+        // start from the lowest copy above `level` that exists already
+        const Ct *from = &t;
+        auto above = low.upper_bound({m, level});
+        if (above != low.end() && above->first.first == m) from = &above->second;
         Ct down;
-        ctx->LevelDown(down, t, level);
+        ctx->LevelDown(down, *from, level);
         it = low.emplace(std::make_pair(m, level), std::move(down)).first;
       }
       return it->second;

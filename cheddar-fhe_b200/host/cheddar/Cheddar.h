@@ -297,8 +297,11 @@ std::unique_ptr<Parameter<word>> MakeParameter(const ParameterJson &j) {
 
 // ---------------------------------------------------------------- device memory
 namespace detail {
+// The context new containers of this thread allocate from. Per thread: a
+// host thread drives one context at a time (worker threads of a parallel
+// stage each set their own with ScopedCurrentHandle).
 inline cfhe_context *&CurrentHandle() {
-  static cfhe_context *h = nullptr;
+  static thread_local cfhe_context *h = nullptr;
   return h;
 }
 // engines that are alive: a vector outliving its engine has nothing left to free

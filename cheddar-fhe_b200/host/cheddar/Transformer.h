@@ -29,9 +29,21 @@
 //
 // Every non-linear function is a Chebyshev series on [-1, 1] (TransformerPolys);
 // the float64 layer used as the checker in the tests evaluates the same series.
+//
+// Host threads. Below level 13 a ciphertext operator is a few small kernels,
+// and a degree-31 series is about 400 launches: one host thread cannot enqueue
+// them as fast as the GPU runs them, and one stream leaves SMs idle. Stages
+// that are independent per ciphertext (series, rotations, rescales, products)
+// therefore run as a parallel loop over `workers` host threads, each with its
+// own engine context (stream, workspace, allocation pool); the streams are
+// ordered after the main stream when the loop starts and the main stream after
+// them when it ends. Inside such a loop an item frees only what it allocated
+// itself, so no block changes pool while another stream may still read it.
 #pragma once
 #include <chrono>
+#include <atomic>
 #include <random>
+#include <thread>
 #include <tuple>
 
 #include "cheddar/Boot.h"
@@ -49,6 +61,7 @@ struct TransformerConfig {
   double ln_eps = 1e-5;
   int exp_degree = 15, inv_degree = 63, rsqrt_degree = 63, gelu_degree = 31;
   bool pair_boot = true;  // bootstrap two real ciphertexts as one complex one
+  int workers = 4;        // host threads (and streams) of the per-ciphertext stages
   static TransformerConfig BertBase() { return TransformerConfig{}; }
   static TransformerConfig Small() {
     TransformerConfig c;
@@ -207,6 +220,10 @@ class EncryptedTransformerLayer {
     slots_ = ctx_->param_.degree_ / 2;
     AssertTrue(slots_ % cfg.seq_len == 0, "Transformer: seq_len must divide the slot count");
     lane_ = slots_ / cfg.seq_len;
+    main_ = ctx_;
+    cfhe_context *current = detail::CurrentHandle();
+    for (int k = 1; k < cfg.workers; k++) workers_.push_back(Context<word>::Create(ctx_->param_));
+    detail::CurrentHandle() = current;
   }
   int BatchSize() const { return lane_; }
   // Called after every stage with its name, the ciphertexts it produced and the
@@ -272,15 +289,14 @@ class EncryptedTransformerLayer {
       BootAll(stat, evk, true);
       for (int h = 0; h < heads; h++) {
         Ct p;
-        Poly(p, stat[h], polys_.inv_c, mult);
-        LevelTo(p, Level(o_un[h * D]));
-        for (int d = 0; d < D; d++) {
-          Ct &src = o_un[h * D + d];
-          LevelTo(src, Level(p));
-          ctx_->HMult(o[h * D + d], src, p, mult);
-          src = Ct();
-        }
+        Poly(main_, p, stat[h], polys_.inv_c, mult);
+        LevelTo(main_, p, Level(o_un[h * D]));
+        AssertTrue(Level(p) == Level(o_un[h * D]), "Transformer: the normaliser ended below the weighted values");
+        ParallelFor(D, [&](const ConstContextPtr<word> &c, int d) {
+          c->HMult(o[h * D + d], o_un[h * D + d], p, mult);
+        });
       }
+      o_un.clear();
     }
     Mark("softmax normaliser");
     if (probe_) probe_("attention", o, 1.0);
@@ -320,10 +336,8 @@ class EncryptedTransformerLayer {
       Mark("feed-forward projection 1");
       if (probe_) probe_("pre-activation", pre, cfg_.gelu_range);
       act.resize(F);
-      for (int j = 0; j < F; j++) {
-        Poly(act[j], pre[j], polys_.gelu_c, mult);
-        pre[j] = Ct();
-      }
+      ParallelFor(F, [&](const ConstContextPtr<word> &c, int j) { Poly(c, act[j], pre[j], polys_.gelu_c, mult); });
+      pre.clear();
       Mark("GELU");
       if (probe_) probe_("GELU", act, cfg_.gelu_range);
       if (!m_w2_) m_w2_ = MakeMatrix(Centred(w_.w2, F, H, G / A), F, H, act[0]);
@@ -364,31 +378,52 @@ class EncryptedTransformerLayer {
     stage_s_.emplace_back(name, std::chrono::duration<double>(now - last_).count());
     last_ = now;
   }
-  void LevelTo(Ct &c, int level) const {
+  // fn(context, i) for every i in [0, n), shared out over the worker threads
+  template <typename F>
+  void ParallelFor(int n, F &&fn) {
+    if (workers_.empty() || n < 2) {
+      for (int i = 0; i < n; i++) fn(main_, i);
+      return;
+    }
+    for (auto &w : workers_) CheckAbi(cfhe_order_after(w->h_, ctx_->h_));
+    std::atomic<int> next{0};
+    auto run = [&](const ConstContextPtr<word> &c) {
+      ScopedCurrentHandle scope(c->h_);
+      for (int i; (i = next.fetch_add(1)) < n;) fn(c, i);
+    };
+    std::vector<std::thread> threads;
+    for (auto &w : workers_) threads.emplace_back(run, w);
+    run(main_);
+    for (auto &t : threads) t.join();
+    for (auto &w : workers_) CheckAbi(cfhe_order_after(ctx_->h_, w->h_));
+  }
+  // c must be a ciphertext the calling item owns
+  void LevelTo(const ConstContextPtr<word> &cx, Ct &c, int level) const {
     if (Level(c) <= level) return;
     Ct t;
-    ctx_->LevelDown(t, c, level);
+    cx->LevelDown(t, c, level);
     c = std::move(t);
   }
   // res = value * a one level below a, at the canonical scale of that level
-  void MultConstRescale(Ct &res, const Ct &a, double value) const {
+  void MultConstRescale(const ConstContextPtr<word> &cx, Ct &res, const Ct &a, double value) const {
     const int l = Level(a);
     Const k;
-    ctx_->encoder().EncodeConstant(k, l, Canon(l - 1) * ctx_->param_.GetRescalePrimeProd(l) / a.GetScale(), value);
+    cx->encoder().EncodeConstant(k, l, Canon(l - 1) * cx->param_.GetRescalePrimeProd(l) / a.GetScale(), value);
     Ct t;
-    ctx_->Mult(t, a, k);
-    ctx_->Rescale(res, t);
+    cx->Mult(t, a, k);
+    cx->Rescale(res, t);
   }
-  void AddConst(Ct &c, double value) const {
+  void AddConst(const ConstContextPtr<word> &cx, Ct &c, double value) const {
     if (value == 0.0) return;
     Const k;
-    ctx_->encoder().EncodeConstant(k, Level(c), c.GetScale(), value);
-    ctx_->Add(c, c, k);
+    cx->encoder().EncodeConstant(k, Level(c), c.GetScale(), value);
+    cx->Add(c, c, k);
   }
-  void Poly(Ct &res, const Ct &x, const std::vector<double> &coeffs, const Evk &mult) const {
+  void Poly(const ConstContextPtr<word> &cx, Ct &res, const Ct &x, const std::vector<double> &coeffs,
+            const Evk &mult) const {
     int k = 1;
     while ((size_t(1) << k) < coeffs.size()) k++;
-    EvalPoly<word>::EvaluateChebyshev(ctx_, res, x, coeffs, mult, Canon(Level(x) - k));
+    EvalPoly<word>::EvaluateChebyshev(cx, res, x, coeffs, mult, Canon(Level(x) - k));
   }
   // Encoding and packing a matrix happens once, on the first Forward, and is
   // kept out of the stage times (reported by PackSeconds).
@@ -419,11 +454,10 @@ class EncryptedTransformerLayer {
     gemm_macs_ += m.Int8Macs(ctx_->param_.degree_);
     y.clear();
     y.resize(raw.size());
-    for (size_t j = 0; j < raw.size(); j++) {
-      ctx_->Rescale(y[j], raw[j]);
-      raw[j] = Ct();
-      AddConst(y[j], bias[j]);
-    }
+    ParallelFor((int)raw.size(), [&](const ConstContextPtr<word> &c, int j) {
+      c->Rescale(y[j], raw[j]);
+      AddConst(c, y[j], bias[j]);
+    });
   }
   // W (I - 11^T / n_out) * factor: every row loses its mean
   static std::vector<double> Centred(const std::vector<double> &w, int n_in, int n_out, double factor) {
@@ -445,7 +479,7 @@ class EncryptedTransformerLayer {
     return r;
   }
   // y[j] += x[j] - mean_j x[j], x brought down to the level of y
-  void AddCentredResidual(std::vector<Ct> &y, const std::vector<Ct> &x) const {
+  void AddCentredResidual(std::vector<Ct> &y, const std::vector<Ct> &x) {
     const int H = x.size(), lx = Level(x[0]), ly = Level(y[0]);
     AssertTrue(lx > ly, "Transformer: the residual must sit above the block's output");
     Ct sum;
@@ -457,18 +491,19 @@ class EncryptedTransformerLayer {
     ctx_->encoder().EncodeConstant(inv, lx, s, 1.0 / H);
     Ct mean;
     ctx_->Mult(mean, sum, inv);
-    for (int j = 0; j < H; j++) {
+    ParallelFor(H, [&](const ConstContextPtr<word> &cx, int j) {
       Ct t, c;
-      ctx_->Mult(t, x[j], one);
-      ctx_->Sub(t, t, mean);
-      ctx_->Rescale(c, t);
-      LevelTo(c, ly);
-      ctx_->Add(y[j], y[j], c);
-    }
+      cx->Mult(t, x[j], one);
+      cx->Sub(t, t, mean);
+      cx->Rescale(c, t);
+      LevelTo(cx, c, ly);
+      cx->Add(y[j], y[j], c);  // in place: y[j] keeps its buffers
+    });
   }
 
   // out[0] = a, out[b] = a rotated by b tokens, b < baby (one ModUp for all of them)
-  void BabyRotations(std::vector<Ct> &out, const Ct &a, const EvkMap<word> &evk) const {
+  void BabyRotations(const ConstContextPtr<word> &cx, std::vector<Ct> &out, const Ct &a,
+                     const EvkMap<word> &evk) const {
     std::vector<int> dists;
     std::vector<const Evk *> keys;
     for (int b = 1; b < cfg_.baby; b++) {
@@ -476,15 +511,16 @@ class EncryptedTransformerLayer {
       keys.push_back(&evk.GetRotationKey(b * lane_));
     }
     std::vector<Ct> rot;
-    if (!dists.empty()) ctx_->HoistedRotate(rot, a, dists, keys);
+    if (!dists.empty()) cx->HoistedRotate(rot, a, dists, keys);
     out.clear();
     out.resize(cfg_.baby);
-    ctx_->Copy(out[0], a);
+    cx->Copy(out[0], a);
     for (int b = 1; b < cfg_.baby; b++) out[b] = std::move(rot[b - 1]);
   }
-  void RotateTokens(Ct &res, const Ct &a, int tokens, const EvkMap<word> &evk) const {
+  void RotateTokens(const ConstContextPtr<word> &cx, Ct &res, const Ct &a, int tokens,
+                    const EvkMap<word> &evk) const {
     const int dist = ((tokens % cfg_.seq_len) + cfg_.seq_len) % cfg_.seq_len * lane_;
-    ctx_->HRot(res, a, evk.GetRotationKey(dist), dist);
+    cx->HRot(res, a, evk.GetRotationKey(dist), dist);
   }
 
   // Head h: e_r = exp(s_r - R) for the 'seq_len' offsets r, stat = their mean
@@ -496,32 +532,35 @@ class EncryptedTransformerLayer {
     auto Q = [&](int d) -> const Ct & { return qkv[h * D + d]; };
     auto K = [&](int d) -> const Ct & { return qkv[H + h * D + d]; };
     auto V = [&](int d) -> const Ct & { return qkv[2 * H + h * D + d]; };
+    using Cx = ConstContextPtr<word>;
     std::vector<Ct> e(T);
     {
-      std::vector<std::vector<Ct>> kb(D);
-      for (int d = 0; d < D; d++) BabyRotations(kb[d], K(d), evk);
-      for (int g = 0; g < ng; g++) {
-        // s_{g nb + b}[t] = sum_d Q_d[t] K_d[t + g nb + b]
-        //                 = rot_{g nb}( sum_d rot_{-g nb}(Q_d) * rot_b(K_d) )[t]
-        std::vector<Ct> qg(g ? D : 0);
-        for (int d = 0; d < D && g; d++) RotateTokens(qg[d], Q(d), -g * nb, evk);
-        for (int b = 0; b < nb; b++) {
-          Ct acc, u;
-          std::vector<const Ct *> left(D), right(D);
-          for (int d = 0; d < D; d++) {
-            left[d] = g ? &qg[d] : &Q(d);
-            right[d] = &kb[d][b];
-          }
-          ctx_->MultSumUnsafe(acc, left, right);
-          ctx_->RelinearizeRescale(u, acc, mult);
-          if (g) {
-            Ct r;
-            RotateTokens(r, u, g * nb, evk);
-            u = std::move(r);
-          }
-          Poly(e[g * nb + b], u, polys_.exp_c, mult);
+      // s_{g nb + b}[t] = sum_d Q_d[t] K_d[t + g nb + b]
+      //                 = rot_{g nb}( sum_d rot_{-g nb}(Q_d) * rot_b(K_d) )[t]
+      std::vector<std::vector<Ct>> kb(D), qg(ng);
+      ParallelFor(D, [&](const Cx &c, int d) { BabyRotations(c, kb[d], K(d), evk); });
+      for (int g = 1; g < ng; g++) qg[g].resize(D);
+      ParallelFor((ng - 1) * D, [&](const Cx &c, int i) {
+        const int g = 1 + i / D, d = i % D;
+        RotateTokens(c, qg[g][d], Q(d), -g * nb, evk);
+      });
+      ParallelFor(T, [&](const Cx &c, int r) {
+        const int g = r / nb, b = r % nb;
+        Ct acc, u;
+        std::vector<const Ct *> left(D), right(D);
+        for (int d = 0; d < D; d++) {
+          left[d] = g ? &qg[g][d] : &Q(d);
+          right[d] = &kb[d][b];
         }
-      }
+        c->MultSumUnsafe(acc, left, right);
+        c->RelinearizeRescale(u, acc, mult);
+        if (g) {
+          Ct rot;
+          RotateTokens(c, rot, u, g * nb, evk);
+          u = std::move(rot);
+        }
+        Poly(c, e[r], u, polys_.exp_c, mult);
+      });
     }
     {
       Ct sum;
@@ -530,41 +569,45 @@ class EncryptedTransformerLayer {
       const double span = cfg_.sum_hi - cfg_.sum_lo;
       MaskedAffine(stat, sum, 2.0 / (T * span), -(cfg_.sum_hi + cfg_.sum_lo) / span);
     }
+    // o_d[t] = sum_g rot_{g nb}( sum_b rot_{-g nb}(e_{g nb + b}) * rot_b(V_d) )[t]
     const int le = Level(e[0]);
-    std::vector<std::vector<Ct>> vb(D);
-    for (int d = 0; d < D; d++) {
+    std::vector<std::vector<Ct>> vb(D), eg(ng), part(ng);
+    ParallelFor(D, [&](const Cx &c, int d) {
       Ct low;
-      ctx_->LevelDown(low, V(d), le);
-      BabyRotations(vb[d], low, evk);
-    }
-    for (int g = 0; g < ng; g++) {
-      // o_d[t] += sum_b e_{g nb + b}[t] V_d[t + g nb + b]
-      //         = rot_{g nb}( sum_b rot_{-g nb}(e_{g nb + b}) * rot_b(V_d) )[t]
-      std::vector<Ct> eg(g ? nb : 0);
-      for (int b = 0; b < nb && g; b++) RotateTokens(eg[b], e[g * nb + b], -g * nb, evk);
-      for (int d = 0; d < D; d++) {
-        Ct acc, t;
-        std::vector<const Ct *> left(nb), right(nb);
-        for (int b = 0; b < nb; b++) {
-          left[b] = g ? &eg[b] : &e[b];
-          right[b] = &vb[d][b];
-        }
-        ctx_->MultSumUnsafe(acc, left, right);
-        ctx_->RelinearizeRescale(t, acc, mult);
-        if (g) {
-          Ct r;
-          RotateTokens(r, t, g * nb, evk);
-          ctx_->Add(o_un[h * D + d], o_un[h * D + d], r);
-        } else {
-          o_un[h * D + d] = std::move(t);
-        }
+      c->LevelDown(low, V(d), le);
+      BabyRotations(c, vb[d], low, evk);
+    });
+    for (int g = 1; g < ng; g++) eg[g].resize(nb);
+    ParallelFor((ng - 1) * nb, [&](const Cx &c, int i) {
+      const int g = 1 + i / nb, b = i % nb;
+      RotateTokens(c, eg[g][b], e[g * nb + b], -g * nb, evk);
+    });
+    for (int g = 0; g < ng; g++) part[g].resize(D);
+    ParallelFor(ng * D, [&](const Cx &c, int i) {
+      const int g = i / D, d = i % D;
+      Ct acc, t;
+      std::vector<const Ct *> left(nb), right(nb);
+      for (int b = 0; b < nb; b++) {
+        left[b] = g ? &eg[g][b] : &e[b];
+        right[b] = &vb[d][b];
       }
-    }
+      c->MultSumUnsafe(acc, left, right);
+      c->RelinearizeRescale(t, acc, mult);
+      if (g)
+        RotateTokens(c, part[g][d], t, g * nb, evk);
+      else
+        part[0][d] = std::move(t);
+    });
+    ParallelFor(D, [&](const Cx &c, int d) {
+      Ct &dst = o_un[h * D + d];
+      c->Copy(dst, part[0][d]);
+      for (int g = 1; g < ng; g++) c->Add(dst, dst, part[g][d]);
+    });
   }
 
   // z[j] = gamma_j y[j] / sqrt(var + eps) + beta_j / act_div for centred y
   // (mean already removed), var = (act_div^2 / H) sum_j y[j]^2
-  void LayerNorm(std::vector<Ct> &z, std::vector<Ct> &y, const std::vector<double> &gamma,
+  void LayerNorm(std::vector<Ct> &z, const std::vector<Ct> &y, const std::vector<double> &gamma,
                  const std::vector<double> &beta, const EvkMap<word> &evk) {
     const int H = y.size();
     const double A = cfg_.act_div, span = cfg_.var_hi - cfg_.var_lo;
@@ -577,19 +620,18 @@ class EncryptedTransformerLayer {
     one[0] = std::move(w);
     BootAll(one, evk, true);
     Ct f;
-    Poly(f, one[0], polys_.rsqrt_c, mult);  // 1 / (2 sqrt(var + eps))
+    Poly(main_, f, one[0], polys_.rsqrt_c, mult);  // 1 / (2 sqrt(var + eps))
     const int target = Min(Level(f), Level(y[0]) - 1);
-    LevelTo(f, target);
+    LevelTo(main_, f, target);
     z.clear();
     z.resize(H);
-    for (int j = 0; j < H; j++) {
+    ParallelFor(H, [&](const ConstContextPtr<word> &c, int j) {
       Ct t;
-      MultConstRescale(t, y[j], 2.0 * gamma[j]);
-      y[j] = Ct();
-      LevelTo(t, target);
-      ctx_->HMult(z[j], t, f, mult);
-      AddConst(z[j], beta[j] / A);
-    }
+      MultConstRescale(c, t, y[j], 2.0 * gamma[j]);
+      LevelTo(c, t, target);
+      c->HMult(z[j], t, f, mult);
+      AddConst(c, z[j], beta[j] / A);
+    });
   }
 
   // A statistic (softmax denominator, LayerNorm variance) is nearly the same
@@ -644,7 +686,7 @@ class EncryptedTransformerLayer {
       if (masked) {
         MultMaskRescale(dst, src, factor);
       } else if (needed) {
-        MultConstRescale(dst, src, factor);
+        MultConstRescale(main_, dst, src, factor);
       } else {
         dst = std::move(src);
       }
@@ -676,6 +718,8 @@ class EncryptedTransformerLayer {
   }
 
   std::shared_ptr<Boot> ctx_;
+  ConstContextPtr<word> main_;                 // ctx_ as the type the operators take
+  std::vector<ContextPtr<word>> workers_;      // one more engine context per extra host thread
   TransformerConfig cfg_;
   TransformerWeights w_;
   TransformerPolys polys_;

@@ -3,7 +3,7 @@
 // unpinned by the reference: the reference has no transformer code, so the
 // checker is the textbook layer in double precision.
 //
-//   transformer_test <parameter.json> [--stddev s] [--seed n] [--no-pair]
+//   transformer_test <parameter.json> [--stddev s] [--seed n] [--no-pair] [--workers T]
 //
 // Reduced dimensions (16 tokens, hidden 32, 2 heads of 16, feed-forward 64,
 // batch 2048 sequences per ciphertext); every stage of the full-size layer runs:
@@ -20,7 +20,7 @@ using word = uint32_t;
 
 int main(int argc, char **argv) {
   if (argc < 2) {
-    std::cerr << "usage: transformer_test <parameter.json> [--stddev s] [--seed n] [--no-pair]\n";
+    std::cerr << "usage: transformer_test <parameter.json> [--stddev s] [--seed n] [--no-pair] [--workers T]\n";
     return 2;
   }
   double stddev = 0.08;
@@ -32,6 +32,7 @@ int main(int argc, char **argv) {
     else if (!strcmp(argv[i], "--seed") && i + 1 < argc) seed = strtoull(argv[++i], nullptr, 10);
     else if (!strcmp(argv[i], "--no-pair")) cfg.pair_boot = false;
     else if (!strcmp(argv[i], "--trace")) trace = true;
+    else if (!strcmp(argv[i], "--workers") && i + 1 < argc) cfg.workers = std::max(1, atoi(argv[++i]));
   }
   Random::Seed(0xBE27 + seed);
   ParameterJson json = LoadParameterJson(argv[1]);

@@ -27,7 +27,8 @@ def build_transformer_test(pkg):
     return os.path.join(CPP, "transformer_test")
 
 
-@pytest.mark.parametrize("extra", [[], ["--no-pair", "--seed", "7"]], ids=["paired-bootstraps", "single-bootstraps"])
+@pytest.mark.parametrize("extra", [[], ["--no-pair", "--seed", "7", "--workers", "1"]],
+                         ids=["paired-bootstraps-4-host-threads", "single-bootstraps-1-host-thread"])
 def test_encrypted_layer_matches_float64_layer(pkg, extra):
     exe = build_transformer_test(pkg)
     cmd = [exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json")] + extra
