@@ -259,10 +259,10 @@ HMULT_STAGE_TRAFFIC = {"tensor": 60_600_000, "modup_intt": 47_800_000, "modup_bc
 
 HMULT_TRAFFIC_SOURCE = ("ncu dram read+write of the stage's launches inside one HMult, warm L2 "
                         "(--cache-control none), profiles/hmult_level28_dram_traffic.md")
-NTT_KERNEL_NOTE = "ntt_cols_kernel + ntt_rows_kernel, forward (one batch = 5 chunks x 2 passes)"
-NTT_TRAFFIC = 558_000_000
-NTT_TRAFFIC_SOURCE = ("ncu dram read+write summed over the launches of one forward batch, warm L2, "
-                      "profiles/ntt_twopass_kernel_batch16x40.md")
+NTT_KERNEL_NOTE = "ntt_cols_kernel + ntt_rows_kernel, forward (one batch = one column-pass and one row-pass launch)"
+NTT_TRAFFIC = 652_600_000
+NTT_TRAFFIC_SOURCE = ("ncu dram read+write summed over the two launches of one forward batch, warm L2, "
+                      "profiles/ntt_cols_rows_kernels_batch16x40.md")
 
 
 def hmult_compulsory_bytes(nq, alpha, beta, nd):
