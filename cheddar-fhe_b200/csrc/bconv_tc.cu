@@ -76,6 +76,20 @@ __device__ __forceinline__ void group_sync(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kTcThreads) : "memory");
 }
 
+// the same barrier, returning whether any of the 128 threads passed a true predicate
+__device__ __forceinline__ bool group_sync_or(int group, bool pred) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any)
+      : "r"(group + 1), "n"(kTcThreads), "r"((uint32_t)pred)
+      : "memory");
+  return any != 0;
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -194,7 +208,7 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
       }
       parity ^= 1;
       if (__any_sync(0xffffffffu, failed)) {
-        failed = true;
+        failed = true;  // this warp skips the epilogue of the slice
         if (a.error_flag && (tid & 31) == 0) atomicExch(a.error_flag, 1);
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -225,8 +239,11 @@ __device__ __forceinline__ void tc_tiles(const BconvTcArgs &a, const BconvTcJob 
         }
       }
       // the accumulators (and, after the last slice, the operand tile) are reused
+      // A wait that ran out is a decision of the whole group: the barrier that
+      // ends the slice also ORs the warps' flags, so all four warps leave the
+      // loops together (a warp leaving alone would starve the next barrier).
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      group_sync(group);
+      failed = group_sync_or(group, failed);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
   }
