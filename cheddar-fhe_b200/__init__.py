@@ -325,6 +325,14 @@ class Engine:
         self._check(self.L.cfhe_encrypt(self.h, self._p(b), self._p(a), self._p(s), self._p(e),
                                         self._p(m) if m is not None else None, gp, len(g)))
 
+    def encode_coeffs_(self, dst, coeffs, gidx):
+        """dst = NTT (M-form) of the residues of trunc(coeffs[i]) on the limbs of gidx
+        (cfhe_encode_coeffs); coeffs: N float64 values on the host."""
+        g, gp = _ints(gidx)
+        c = np.ascontiguousarray(coeffs, dtype=np.float64)
+        assert c.shape == (self.n,)
+        self._check(self.L.cfhe_encode_coeffs(self.h, self._p(dst), c.ctypes.data_as(C.c_void_p), gp, len(g)))
+
     def add_evk_part_(self, bx, s_target, p_prod, gidx):
         g, gp = _ints(gidx)
         k, kp = _u32s(p_prod)

@@ -802,6 +802,23 @@ int cfhe_encrypt(cfhe_context *h, uint32_t *b, const uint32_t *a, const uint32_t
   { int r_ = launch_encrypt(h->c, b, a, s, e, m, gidx, n_limbs); h->c.mark("encrypt"); return r_; }
 }
 
+int cfhe_encode_coeffs(cfhe_context *h, uint32_t *dst, const double *coeffs, const int *gidx, int n_limbs) {
+  if (!h || !dst || !coeffs || !gidx) return fail("null argument");
+  void *staging = nullptr;
+  if (int r = cfhe_malloc(h, &staging, (size_t)kN * sizeof(double))) return r;
+  int rc;
+  {
+    CFHE_ENTER(h);
+    cudaError_t e = cudaMemcpyAsync(staging, coeffs, (size_t)kN * sizeof(double), cudaMemcpyHostToDevice, h->c.stream);
+    rc = e == cudaSuccess ? 0 : fail(cudaGetErrorString(e));
+    if (!rc) rc = launch_rns_split(h->c, dst, (const double *)staging, gidx, n_limbs);
+    h->c.mark("encode");
+  }
+  cfhe_free(h, staging);  // reused in stream order, after the kernel above
+  if (rc) return rc;
+  return cfhe_ntt(h, dst, dst, gidx, n_limbs, 1, 0, 0, 1);
+}
+
 int cfhe_add_evk_part(cfhe_context *h, uint32_t *bx, const uint32_t *s_target, const uint32_t *p_prod,
                       const int *gidx, int n_limbs) {
   CFHE_ENTER(h);

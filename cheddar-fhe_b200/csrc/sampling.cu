@@ -156,6 +156,46 @@ __global__ void __launch_bounds__(kSampleThreads) encrypt_kernel(const __grid_co
   reinterpret_cast<uint4 *>(a.b)[off] = r;
 }
 
+// Encoding, device half: residues of trunc(v[i]) modulo every listed prime, v
+// the plaintext polynomial's coefficients times the scale as doubles
+// (reference Encoder::Encode, src/core/Encode.cpp:136-248, converts each
+// coefficient to a big integer and reduces it prime by prime on the host). A
+// double of magnitude below 2^63 converts exactly to a 64-bit integer; a
+// larger one is m * 2^e with a 53-bit integer m and e > 0, so its residue is
+// (m mod q) * (2^e mod q): no big integers either way.
+struct SplitArgs {
+  uint32_t *dst;
+  const double *v;
+  uint32_t q[kMaxLimbs];
+};
+
+__global__ void __launch_bounds__(kSampleThreads) rns_split_kernel(const __grid_constant__ SplitArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int l = blockIdx.y, i = blockIdx.x * kSampleThreads + threadIdx.x;
+  const uint32_t q = a.q[l];
+  const double v = a.v[i];
+  const double mag = fabs(v);
+  uint32_t r;
+  if (mag < 9223372036854775808.0) {  // 2^63
+    r = (uint32_t)((unsigned long long)mag % q);  // conversion truncates toward zero
+  } else {
+    int e;
+    const double f = frexp(mag, &e);                              // mag = f * 2^e, f in [0.5, 1)
+    const unsigned long long m = (unsigned long long)ldexp(f, 53);  // exact 53-bit integer
+    int shift = e - 53;                                           // > 0 here
+    uint32_t p2 = 1u % q, base = 2u % q;
+    while (shift > 0) {  // 2^shift mod q by square and multiply
+      if (shift & 1) p2 = (uint32_t)((uint64_t)p2 * base % q);
+      base = (uint32_t)((uint64_t)base * base % q);
+      shift >>= 1;
+    }
+    r = (uint32_t)((m % q) * p2 % q);
+  }
+  if (v < 0.0 && r != 0) r = q - r;
+  a.dst[(size_t)l * kN + i] = r;
+}
+
 int fill_sample(const Context &c, SampleArgs &s, uint32_t *dst, const int *gidx, int n_limbs, uint64_t seed,
                 uint32_t stream) {
   if (!dst || !gidx) {
@@ -215,6 +255,31 @@ int launch_sample_error(const Context &c, uint32_t *dst, const int *gidx, int n_
   error_cdf_table(sigma, e.cdf);
   CFHE_CUDA(launch_kernel(c.use_pdl, sample_error_kernel, dim3(kN / 2 / kSampleThreads), dim3(kSampleThreads), 0,
                           c.stream, e));
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_rns_split(const Context &c, uint32_t *dst, const double *v, const int *gidx, int n_limbs) {
+  if (!dst || !v || !gidx) {
+    set_error("null argument");
+    return -1;
+  }
+  if (n_limbs < 1 || n_limbs > kMaxLimbs) {
+    set_error("too many limbs");
+    return -1;
+  }
+  SplitArgs x;
+  x.dst = dst;
+  x.v = v;
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= c.NP) {
+      set_error("prime index out of range");
+      return -1;
+    }
+    x.q[l] = c.q[gidx[l]];
+  }
+  CFHE_CUDA(launch_kernel(c.use_pdl, rns_split_kernel, dim3(kN / kSampleThreads, n_limbs), dim3(kSampleThreads), 0,
+                          c.stream, x));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

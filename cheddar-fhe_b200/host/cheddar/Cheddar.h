@@ -650,34 +650,20 @@ class Encoder {
     const int degree = param_.degree_, half = degree / 2, gap = half / num_slots;
     AssertTrue(num_slots <= half, "Encode: Too many slots");
     NPInfo np = param_.LevelToNP(level, num_aux);
-    auto primes = param_.GetPrimeVector(np);
     const int nt = np.GetNumTotal();
-    std::vector<word> mx((size_t)nt * degree, 0);
+    // coefficients times the scale; the engine truncates them toward zero (as
+    // the reference's BigInt(double) does), reduces them modulo every prime of
+    // the level and transforms the limbs, all on the device
+    std::vector<double> coeffs(degree, 0.0);
     for (int i = 0; i < num_slots; i++) {
-      // truncation toward zero, as the reference's BigInt(double)
-      const double fr = data[i].real() * scale, fi = data[i].imag() * scale;
-      if (std::abs(fr) < 0x1p62 && std::abs(fi) < 0x1p62) {  // 64-bit remainders are much cheaper
-        const int64_t re = (int64_t)fr, im = (int64_t)fi;
-        for (int j = 0; j < nt; j++) {
-          const int64_t q = primes[j];
-          int64_t a = re % q, b = im % q;
-          mx[(size_t)j * degree + i * gap] = (word)(a < 0 ? a + q : a);
-          mx[(size_t)j * degree + i * gap + half] = (word)(b < 0 ? b + q : b);
-        }
-        continue;
-      }
-      const __int128 re = (__int128)fr, im = (__int128)fi;
-      for (int j = 0; j < nt; j++) {
-        mx[(size_t)j * degree + i * gap] = detail::ModI128(re, primes[j]);
-        mx[(size_t)j * degree + i * gap + half] = detail::ModI128(im, primes[j]);
-      }
+      coeffs[(size_t)i * gap] = data[i].real() * scale;
+      coeffs[(size_t)i * gap + half] = data[i].imag() * scale;
     }
     ptxt.ModifyNP(np);
     ptxt.SetNumSlots(num_slots);
     ptxt.SetScale(scale);
-    CopyHostToDevice(ptxt.mx_, mx);
     auto g = param_.GetLimbIndices(np);
-    CheckAbi(cfhe_ntt(h_, ptxt.mx_.data(), ptxt.mx_.data(), g.data(), nt, 1, 0, 0, 1));
+    CheckAbi(cfhe_encode_coeffs(h_, ptxt.mx_.data(), coeffs.data(), g.data(), nt));
   }
 
   void Decode(std::vector<Complex> &message, const Plaintext<word> &ptxt) const {

@@ -239,6 +239,16 @@ CFHE_API int cfhe_encrypt(cfhe_context *ctx, uint32_t *b, const uint32_t *a, con
                           const uint32_t *e, const uint32_t *m, const int *gidx, int n_limbs);
 CFHE_API int cfhe_add_evk_part(cfhe_context *ctx, uint32_t *bx, const uint32_t *s_target,
                                const uint32_t *p_prod, const int *gidx, int n_limbs);
+/* Encoding, device half (Encoder::Encode, src/core/Encode.cpp:136-248, after
+ * its special inverse FFT): coeffs is a HOST array of N doubles, the
+ * plaintext polynomial's coefficients already multiplied by the scale; dst
+ * receives, on every listed limb, the residues of trunc(coeffs[i]) (toward
+ * zero, as the reference's conversion to a big integer truncates), transformed
+ * to the evaluation domain in M-form: a finished plaintext. Any magnitude a
+ * double can hold is reduced exactly (m * 2^e mod q), without big integers;
+ * one 512 KiB upload instead of n_limbs * 256 KiB. */
+CFHE_API int cfhe_encode_coeffs(cfhe_context *ctx, uint32_t *dst, const double *coeffs, const int *gidx,
+                                int n_limbs);
 /* Device-to-device copy and fill on the context's stream (the reference's
  * DeviceVector copies, src/core/DeviceVector.cpp, and cudaMemsetAsync calls). */
 CFHE_API int cfhe_copy_d2d(cfhe_context *ctx, void *dst, const void *src, size_t bytes);

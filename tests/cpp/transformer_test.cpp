@@ -26,12 +26,23 @@ int main(int argc, char **argv) {
   double stddev = 0.08;
   uint64_t seed = 2024;
   bool trace = false;  // decrypt after every stage and compare sequence 0 with the float64 layer
+  int lanes = 0;       // sequences checked against the float64 layer (0 = all of them)
   TransformerConfig cfg = TransformerConfig::Small();
   for (int i = 2; i < argc; i++) {
     if (!strcmp(argv[i], "--stddev") && i + 1 < argc) stddev = atof(argv[++i]);
     else if (!strcmp(argv[i], "--seed") && i + 1 < argc) seed = strtoull(argv[++i], nullptr, 10);
     else if (!strcmp(argv[i], "--no-pair")) cfg.pair_boot = false;
     else if (!strcmp(argv[i], "--trace")) trace = true;
+    else if (!strcmp(argv[i], "--base")) {
+      // BERT-base shape; the float64 layer is evaluated for the first `lanes` sequences only
+      const bool pair = cfg.pair_boot;
+      const int workers = cfg.workers;
+      cfg = TransformerConfig::BertBase();
+      cfg.pair_boot = pair;
+      cfg.workers = workers;
+      stddev = 0.02;
+      lanes = 2;
+    } else if (!strcmp(argv[i], "--lanes") && i + 1 < argc) lanes = std::max(1, atoi(argv[++i]));
     else if (!strcmp(argv[i], "--workers") && i + 1 < argc) cfg.workers = std::max(1, atoi(argv[++i]));
   }
   Random::Seed(0xBE27 + seed);
@@ -147,7 +158,8 @@ int main(int argc, char **argv) {
 
   plain_transformer::Ranges ranges;
   double err_series = 0, err_exact = 0, approx_gap = 0, sum_sq = 0;
-  for (int b = 0; b < B; b++) {
+  const int checked = lanes > 0 ? std::min(lanes, B) : B;
+  for (int b = 0; b < checked; b++) {
     std::vector<double> xb(x.begin() + (size_t)b * T * H, x.begin() + (size_t)(b + 1) * T * H), series, exact;
     spec.exact = false;
     plain_transformer::Layer(series, xb, spec, pw, &ranges);
@@ -161,7 +173,8 @@ int main(int argc, char **argv) {
       sum_sq += (g - series[i]) * (g - series[i]);
     }
   }
-  const double rms = std::sqrt(sum_sq / ((double)B * T * H));
+  const double rms = std::sqrt(sum_sq / ((double)checked * T * H));
+  std::cout << "sequences checked against the float64 layer: " << checked << " of " << B << "\n";
   std::cout << std::scientific << std::setprecision(3);
   std::cout << "ranges: |score| " << ranges.score_abs << " of " << cfg.score_range << ", exp mean [" << ranges.sum_min
             << ", " << ranges.sum_max << "] of [" << cfg.sum_lo << ", " << cfg.sum_hi << "], variance ["

@@ -121,3 +121,29 @@ def test_fused_client_kernels_match_the_composition(engine40, oracle40):
     out = e.empty(len(g), e.n)
     e.pseudo_modup_(level, out, da)
     assert np.array_equal(e.to_host(out), o.const_op(a, pm, g, 3))
+
+
+def test_encode_coeffs_reduces_any_double_exactly(engine40, oracle40):
+    """cfhe_encode_coeffs against exact integer arithmetic: residues of
+    trunc(v) (toward zero, as the reference's conversion of a scaled
+    coefficient to a big integer, src/core/Encode.cpp:136-248) for magnitudes
+    from fractions to 2^120, then the golden model's forward NTT with
+    Montgomery conversion. Every word must match."""
+    e, o = engine40, oracle40
+    rng = np.random.default_rng(4242)
+    n = o.n
+    v = np.zeros(n, dtype=np.float64)
+    mags = [0.0, 0.49, 0.99, 1.0, 1.5, 2.0 ** 31, 2.0 ** 40 + 0.75, 2.0 ** 52 + 1, 2.0 ** 53, 2.0 ** 62,
+            2.0 ** 63, 2.0 ** 64 + 2.0 ** 13, 2.0 ** 80 * 1.2345678901234567, 2.0 ** 100 * 1.999999, 2.0 ** 120]
+    for i, m in enumerate(mags):
+        v[2 * i], v[2 * i + 1] = m, -m
+    k = 2 * len(mags)
+    expo = rng.integers(-3, 110, n - k)
+    v[k:] = rng.uniform(-1.0, 1.0, n - k) * np.exp2(expo.astype(np.float64))
+    g = e.level_limbs(16, 12)  # main, terminal and auxiliary primes
+    want_coeff = np.stack([np.array([int(x) % int(o.primes[gi]) for x in v], dtype=np.uint64).astype(np.uint32)
+                           for gi in g])
+    want = o.ntt(want_coeff, g, mont_conv=True)
+    dst = e.empty(len(g), n)
+    e.encode_coeffs_(dst, v, g)
+    assert np.array_equal(e.to_host(dst), want)

@@ -39,3 +39,18 @@ def test_encrypted_layer_matches_float64_layer(pkg, extra):
     assert "PASS" in r.stdout
     bits = float(re.search(r"precision_bits ([0-9.]+)", r.stdout).group(1))
     assert bits >= 12.0
+
+
+def test_bert_base_layer_matches_float64_layer(pkg):
+    """The full BERT-base shape (128 tokens, hidden 768, 12 heads, feed-forward
+    3072; weights N(0, 0.02), activations N(0, 1)), 256 sequences encrypted,
+    the first two compared slot by slot with the float64 layer; the test also
+    fails when any value leaves the interval its series was fitted on."""
+    exe = build_transformer_test(pkg)
+    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--base"], capture_output=True,
+                       text=True, timeout=1500)
+    print(r.stdout[-6000:])
+    print(r.stderr[-3000:])
+    assert r.returncode == 0, "transformer_test --base failed"
+    assert "PASS" in r.stdout
+    assert float(re.search(r"precision_bits ([0-9.]+)", r.stdout).group(1)) >= 12.0
