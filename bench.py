@@ -390,6 +390,51 @@ def bench_hmult(eng, pkg, torch, params, steps, warmup, rank, barrier, check):
             "precision_bits": precision_bits, "launches": launches}
 
 
+def bench_hmult_level(eng, torch, params, level, steps, with_ref):
+    """HMult + relinearise + rescale at another level (16 = the default
+    encryption level) on random residues and a random key: device-resident
+    time of the engine and, when it is built, of the reference's library on the
+    same buffers."""
+    rng = np.random.default_rng(0xC0FFEE16)
+    g = eng.level_limbs(level)
+    M, T = len(params["main_primes"]), len(params["terminal_primes"])
+    kg = list(range(T + M)) + [T + M + a for a in range(eng.alpha)]
+    beta = eng.beta(level)                                  # digits this level uses
+    key_digits = eng.beta(len(params["level_config"]) - 1)  # digits a key holds
+    ins = [eng.to_dev(rand_limbs(rng, eng.primes, g)) for _ in range(4)]
+    kb = [eng.to_dev(rand_limbs(rng, eng.primes, kg)) for _ in range(key_digits)]
+    ka = [eng.to_dev(rand_limbs(rng, eng.primes, kg)) for _ in range(key_digits)]
+    nd = len(eng.level_limbs(level - 1))
+    ob, oa = eng.empty(nd, N), eng.empty(nd, N)
+    for _ in range(3):
+        eng.hmult_(level, ob, oa, *ins, kb, ka, M, True)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.hmult_(level, ob, oa, *ins, kb, ka, M, True)
+    e1.record()
+    torch.cuda.synchronize()
+    nq = len(g)
+    out = {"level": level, "us": e0.elapsed_time(e1) / steps * 1e3,
+           "compulsory_bytes": (4 * nq + 2 * beta * (nq + eng.alpha) + 2 * nd) * N * 4,
+           "note": "inputs, the key limbs of the level and outputs once each; one key and two ciphertexts "
+                   "are smaller than L2 at this level, so repeated calls find part of them there"}
+    out["GB/s"] = out["compulsory_bytes"] / (out["us"] * 1e-6) / 1e9
+    if with_ref:
+        try:
+            from oracle import ref_binding
+            if ref_binding.available():
+                ref = ref_binding.Reference(params)
+                rb, ra = eng.empty(nd, N), eng.empty(nd, N)
+                out["reference_cuda_us"] = ref.hmult(level, rb, ra, *ins, kb, ka, M, True, iters=max(steps, 2))
+                out["words_equal_reference"] = bool(torch.equal(rb, ob) and torch.equal(ra, oa))
+                ref.close()
+        except Exception as exc:  # the reference library is optional
+            out["reference_cuda_error"] = str(exc)[:200]
+    return out
+
+
 def bench_reference_cuda(eng, torch, params, steps, with_boot=True):
     """The reference's own CUDA library (oracle/_ref, built unmodified from
     the reference tree) on the same GPU: HMult at level 28 on random residues
@@ -846,6 +891,10 @@ def run_gpu(args, pkg):
     if rank == 0 and args.workload == "hmult" and not args.no_gemm:
         gemm = bench_gemm(eng, torch, max(2, args.steps // 5))
         torch.cuda.empty_cache()
+    hm16 = None
+    if rank == 0 and args.workload == "hmult":
+        hm16 = bench_hmult_level(eng, torch, params, 16, args.steps, world == 1 and not args.no_ref)
+        torch.cuda.empty_cache()
     ref_cuda = None
     if rank == 0 and world == 1 and not args.no_ref:
         ref_cuda = bench_reference_cuda(eng, torch, params, args.steps, not args.no_boot)
@@ -867,6 +916,8 @@ def run_gpu(args, pkg):
         line = assemble_line(args, world, warmup, clocks, red, ntt, hm, hoist, boot, shape)
         if gemm:
             line["ctpt_gemm"] = gemm
+        if hm16:
+            line["hmult_level16"] = hm16
         if bert:
             line["bert_layer"] = bert_entry(bert, bert_s, world)
         if ref_cuda:

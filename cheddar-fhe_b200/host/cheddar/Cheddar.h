@@ -15,6 +15,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <fstream>
+#include <cstring>
 #include <iostream>
 #include <map>
 #include <memory>
@@ -492,6 +493,115 @@ class EvaluationKey : public Container<word> {
   int GetBeta() const { return bx_.size(); }
   void ModifyNP(const NPInfo &) override { Fail("EvaluationKey::ModifyNP is not supported"); }
 };
+
+// ---------------------------------------------------------------- wire format
+// Ciphertexts, plaintexts and evaluation keys as byte streams (the reference
+// has no serialisation: its containers live and die in one process). Layout,
+// little endian: "CFHE", u32 version = 1, u32 kind (1 ciphertext, 2 plaintext,
+// 3 evaluation key), u32 bytes per word, u32 ring degree, i32 num_main,
+// num_ter, num_aux, f64 scale, i32 num_slots, u32 polynomial count, then the
+// polynomials limb-major, words exactly as they lie in device memory
+// (evaluation domain, M-form): b, a[, r] for a ciphertext; b_0, a_0, b_1, a_1,
+// ... for a key. A reader checks the header against its own ring.
+namespace detail {
+struct WireHeader {
+  char magic[4];
+  uint32_t version, kind, word_bytes, degree;
+  int32_t num_main, num_ter, num_aux;
+  double scale;
+  int32_t num_slots;
+  uint32_t polys;
+};
+template <typename word>
+void WritePoly(std::ostream &os, const DeviceVector<word> &v) {
+  std::vector<word> host;
+  CopyDeviceToHost(host, v);
+  CheckAbi(cfhe_synchronize(CurrentHandle()));
+  os.write(reinterpret_cast<const char *>(host.data()), (std::streamsize)(host.size() * sizeof(word)));
+}
+template <typename word>
+void ReadPoly(std::istream &is, DeviceVector<word> &v, size_t words) {
+  std::vector<word> host(words);
+  is.read(reinterpret_cast<char *>(host.data()), (std::streamsize)(words * sizeof(word)));
+  AssertTrue((size_t)is.gcount() == words * sizeof(word), "wire format: truncated stream");
+  CopyHostToDevice(v, host);
+}
+template <typename word>
+void WriteHeader(std::ostream &os, uint32_t kind, const NPInfo &np, double scale, int num_slots, uint32_t polys) {
+  WireHeader h{{'C', 'F', 'H', 'E'}, 1u, kind, (uint32_t)sizeof(word), (uint32_t)Container<word>::Degree(),
+               np.num_main_, np.num_ter_, np.num_aux_, scale, num_slots, polys};
+  os.write(reinterpret_cast<const char *>(&h), sizeof(h));
+}
+template <typename word>
+WireHeader ReadHeader(std::istream &is, uint32_t kind) {
+  WireHeader h;
+  is.read(reinterpret_cast<char *>(&h), sizeof(h));
+  AssertTrue((size_t)is.gcount() == sizeof(h) && !std::memcmp(h.magic, "CFHE", 4) && h.version == 1,
+             "wire format: not a container stream");
+  AssertTrue(h.kind == kind, "wire format: another kind of container");
+  AssertTrue(h.word_bytes == sizeof(word) && (int)h.degree == Container<word>::Degree(),
+             "wire format: written for another ring");
+  return h;
+}
+}  // namespace detail
+
+template <typename word>
+void Save(std::ostream &os, const Ciphertext<word> &ct) {
+  detail::WriteHeader<word>(os, 1, ct.GetNP(), ct.GetScale(), ct.GetNumSlots(), ct.HasRx() ? 3 : 2);
+  detail::WritePoly(os, ct.bx_);
+  detail::WritePoly(os, ct.ax_);
+  if (ct.HasRx()) detail::WritePoly(os, ct.rx_);
+}
+template <typename word>
+void Load(std::istream &is, Ciphertext<word> &ct) {
+  const auto h = detail::ReadHeader<word>(is, 1);
+  AssertTrue(h.polys == 2 || h.polys == 3, "wire format: bad polynomial count");
+  const NPInfo np(h.num_main, h.num_ter, h.num_aux);
+  const size_t words = (size_t)np.GetNumTotal() * h.degree;
+  Ciphertext<word> out(np, h.polys == 3);
+  detail::ReadPoly(is, out.bx_, words);
+  detail::ReadPoly(is, out.ax_, words);
+  if (h.polys == 3) detail::ReadPoly(is, out.rx_, words);
+  out.SetScale(h.scale);
+  out.SetNumSlots(h.num_slots);
+  ct = std::move(out);
+}
+template <typename word>
+void Save(std::ostream &os, const Plaintext<word> &pt) {
+  detail::WriteHeader<word>(os, 2, pt.GetNP(), pt.GetScale(), pt.GetNumSlots(), 1);
+  detail::WritePoly(os, pt.mx_);
+}
+template <typename word>
+void Load(std::istream &is, Plaintext<word> &pt) {
+  const auto h = detail::ReadHeader<word>(is, 2);
+  const NPInfo np(h.num_main, h.num_ter, h.num_aux);
+  Plaintext<word> out(np);
+  detail::ReadPoly(is, out.mx_, (size_t)np.GetNumTotal() * h.degree);
+  out.SetScale(h.scale);
+  out.SetNumSlots(h.num_slots);
+  pt = std::move(out);
+}
+template <typename word>
+void Save(std::ostream &os, const EvaluationKey<word> &key) {
+  detail::WriteHeader<word>(os, 3, key.GetNP(), key.GetScale(), 0, 2 * (uint32_t)key.GetBeta());
+  for (int j = 0; j < key.GetBeta(); j++) {
+    detail::WritePoly(os, key.bx_[j]);
+    detail::WritePoly(os, key.ax_[j]);
+  }
+}
+template <typename word>
+void Load(std::istream &is, EvaluationKey<word> &key) {
+  const auto h = detail::ReadHeader<word>(is, 3);
+  AssertTrue(h.polys % 2 == 0, "wire format: bad polynomial count");
+  const NPInfo np(h.num_main, h.num_ter, h.num_aux);
+  EvaluationKey<word> out(np, (int)h.polys / 2);
+  for (int j = 0; j < (int)h.polys / 2; j++) {
+    detail::ReadPoly(is, out.bx_[j], (size_t)np.GetNumTotal() * h.degree);
+    detail::ReadPoly(is, out.ax_[j], (size_t)np.GetNumTotal() * h.degree);
+  }
+  out.SetScale(h.scale);
+  key = std::move(out);
+}
 
 // ---------------------------------------------------------------- random
 // Same distributions as the reference's Random (include/Random.h:16-81); the

@@ -418,6 +418,39 @@ int main(int argc, char **argv) {
       tb.failures++;
     }
   });
+  run("WireFormat", 1, [&](int level) {
+    // a ciphertext and the multiplication key through a byte stream and back:
+    // the product of the restored pair must decrypt like the original's
+    Msg m1, m2, a1, a2;
+    tb.GenerateRandomMessage(m1);
+    tb.GenerateRandomMessage(m2);
+    Ct c1, c2, back, r1, r2;
+    tb.EncodeAndEncrypt(c1, m1, level);
+    tb.EncodeAndEncrypt(c2, m2, level);
+    std::stringstream wire(std::ios::in | std::ios::out | std::ios::binary);
+    Save(wire, c1);
+    Save(wire, tb.interface_->GetMultiplicationKey());
+    Load(wire, back);
+    EvaluationKey<word> key;
+    Load(wire, key);
+    bool ok = back.GetNP() == c1.GetNP() && back.GetScale() == c1.GetScale() &&
+              back.GetNumSlots() == c1.GetNumSlots() &&
+              key.GetBeta() == tb.interface_->GetMultiplicationKey().GetBeta();
+    std::vector<word> w1, w2;
+    CopyDeviceToHost(w1, c1.ax_);
+    CopyDeviceToHost(w2, back.ax_);
+    ctx.Synchronize();
+    ok = ok && w1 == w2;
+    if (!ok) {
+      std::cout << "[FAIL] WireFormat round trip at level " << level << std::endl;
+      tb.failures++;
+    }
+    ctx.HMult(r1, c1, c2, tb.interface_->GetMultiplicationKey());
+    ctx.HMult(r2, back, c2, key);
+    tb.DecryptAndDecode(a1, r1);
+    tb.DecryptAndDecode(a2, r2);
+    tb.CompareMessages("WireFormat: product with the restored ciphertext and key", level, a1, a2);
+  });
   run("LevelDown", 1, [&](int level) {
     if (level > tb.default_encryption_level_) return;
     Msg m, res;
