@@ -115,32 +115,40 @@ def _mont(x, q):
 
 def gather_limbs(dist, torch, local, positions, plan, rank, events=None):
     """All-gather of limb buffers: `local` holds this rank's limbs of
-    `positions` (in order); returns {position: tensor} for all of them.
-    `events`: list that receives a (start, end) CUDA event pair around the collective."""
+    `positions` (in order); returns one tensor [len(positions)][N] with the
+    limbs of all ranks in the order of `positions` (one all-gather, one row
+    selection). `events`: list that receives a (start, end) CUDA event pair
+    around the collective."""
     mine = [k for k in positions if plan.owner(k) == rank]
     width = plan.max_owned(positions)
     n = local.shape[-1]
-    pad = torch.zeros((width, n), dtype=local.dtype, device=local.device)
-    if mine:
-        pad[:len(mine)] = local
-    bufs = [torch.empty_like(pad) for _ in range(plan.world)]
+    if len(mine) == width:
+        pad = local.contiguous()
+    else:
+        pad = torch.zeros((width, n), dtype=local.dtype, device=local.device)
+        if mine:
+            pad[:len(mine)] = local
+    allbuf = torch.empty((plan.world, width, n), dtype=local.dtype, device=local.device)
     timed = events is not None and pad.is_cuda
     if timed:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
     if plan.world > 1:
-        dist.all_gather(bufs, pad)
+        dist.all_gather_into_tensor(allbuf.view(plan.world * width, n), pad)
     else:
-        bufs[0] = pad
+        allbuf[0] = pad
     if timed:
         e1.record()
         events.append((e0, e1))
-    out = {}
-    for r in range(plan.world):
-        theirs = [k for k in positions if plan.owner(k) == r]
-        for i, k in enumerate(theirs):
-            out[k] = bufs[r][i]
-    return out
+    # row of position k inside the gathered buffer: owner * width + its rank among the owner's positions
+    seen = [0] * plan.world
+    rows = []
+    for k in positions:
+        r = plan.owner(k)
+        rows.append(r * width + seen[r])
+        seen[r] += 1
+    idx = torch.tensor(rows, dtype=torch.long, device=local.device)
+    return allbuf.view(plan.world * width, n).index_select(0, idx)
 
 
 def sharded_hmult(eng, plan, rank, dist, b1, a1, b2, a2, kb, ka):
@@ -164,25 +172,26 @@ def sharded_hmult(eng, plan, rank, dist, b1, a1, b2, a2, kb, ka):
         pre.update(plan.modup_prescale(dg))
     y_own = eng.empty(len(own_q), n)
     eng.intt_(y_own, d2, gq, consts=[pre[k] for k in own_q], centred=True)
-    y_all = gather_limbs(dist, torch, y_own, list(range(plan.nq)), plan, rank, events)
-    # per digit: the owned limbs outside the digit are converted and transformed,
-    # the owned limbs inside it are d2 itself
+    y_all = gather_limbs(dist, torch, y_own, list(range(plan.nq)), plan, rank, events)  # [nq][N]
+    # per digit: the owned limbs outside the digit are converted and transformed
+    # straight into their rows, the owned limbs inside it are d2 itself
+    dev = d2.device
     mu = []
     for (_, s0, s1) in plan.digits:
-        src = torch.stack([y_all[k] for k in range(s0, s1)]).contiguous()
+        src = y_all[s0:s1]
         src_g = [plan.full_g[k] for k in range(s0, s1)]
         buf = eng.empty(len(own), n)
         outside = [i for i, k in enumerate(own) if k < s0 or k >= s1]
+        inside = [i for i, k in enumerate(own) if s0 <= k < s1]
         if outside:
             dst_g = [plan.full_g[own[i]] for i in outside]
             conv = eng.empty(len(outside), n)
             eng.bconv_(conv, src, src_g, dst_g)
             eng.ntt_(conv, conv, dst_g)
-            for j, i in enumerate(outside):
-                buf[i].copy_(conv[j])
-        for i, k in enumerate(own):
-            if s0 <= k < s1:
-                buf[i].copy_(d2[own_q.index(k)])
+            buf.index_copy_(0, torch.tensor(outside, dtype=torch.long, device=dev), conv)
+        if inside:
+            rows = torch.tensor([own_q.index(own[i]) for i in inside], dtype=torch.long, device=dev)
+            buf.index_copy_(0, torch.tensor(inside, dtype=torch.long, device=dev), d2.index_select(0, rows))
         mu.append(buf)
     # 3. inner product with the key on the owned limbs, plus P * (d0, d1) on the Q limbs
     pm = [_mont(plan.p_mod(k), plan.q(k)) for k in own_q]
@@ -204,10 +213,10 @@ def sharded_hmult(eng, plan, rank, dist, b1, a1, b2, a2, kb, ka):
         z = eng.empty(len(own_aux), n)
         if own_aux:
             eng.intt_(z, acc[part][len(own_q):], g_aux, consts=[pre_d[k] for k in own_aux], centred=True)
-        gathered.append(gather_limbs(dist, torch, z, aux_pos, plan, rank, events))
+        gathered.append(gather_limbs(dist, torch, z, aux_pos, plan, rank, events))  # [alpha][N]
     pinv = [_mont(pow(plan.p_mod(k), -1, plan.q(k)), plan.q(k)) for k in own_q]
     for part in range(2):
-        src = torch.stack([gathered[part][k] for k in aux_pos]).contiguous()
+        src = gathered[part]
         t = eng.empty(len(own_q), n)
         res = eng.empty(len(own_q), n)
         if own_q:

@@ -66,7 +66,9 @@ SCRIPT = textwrap.dedent("""
     mine = [k for k in positions if plan.owner(k) == rank]
     local = torch.stack([torch.full((n,), 1000 * k + rank, dtype=torch.int32) for k in mine])
     got = sh.gather_limbs(dist, torch, local, positions, plan, rank)
-    ok = sorted(got) == positions and all(int(got[k][0]) == 1000 * k + plan.owner(k) for k in positions)
+    ok = tuple(got.shape) == (len(positions), n) and all(
+        int(got[i][0]) == 1000 * k + plan.owner(k) and int(got[i][n - 1]) == 1000 * k + plan.owner(k)
+        for i, k in enumerate(positions))
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
