@@ -509,7 +509,7 @@ def bench_bootstrap(pkg, local, iters, warmup):
     return json.loads(r.stdout.strip().splitlines()[-1])
 
 
-def bench_bert_layer(pkg, local):
+def bench_bert_layer(pkg, local, rank=0, world=1, rendezvous=None):
     """Config 5: one encrypted BERT-base encoder layer (128 tokens, hidden 768,
     12 heads of 64, feed-forward 3072; weights N(0, 0.02), activations N(0, 1))
     on 256 sequences at once, one ciphertext per feature, through the C++
@@ -517,35 +517,42 @@ def bench_bert_layer(pkg, local):
     rotations, EvalPoly and Boot. The host program lib/bert_bench generates the
     keys, encrypts the 768 input ciphertexts and packs the weights (untimed,
     reported), then times one layer stage by stage with the host clock around
-    device synchronisations. The reference has no transformer code, so there is
-    no reference figure."""
+    device synchronisations. With several ranks the ONE layer call is sharded
+    over the GPUs by heads and blocks of ciphertexts (NCCL all-gathers between
+    the stages, strong scaling); rank 0's process reports. The reference has no
+    transformer code, so there is no reference figure."""
     exe = os.path.join(os.path.dirname(pkg.LIB_PATH), "bert_bench")
     if not os.path.exists(exe):
         raise RuntimeError("lib/bert_bench is missing: run the package build")
     env = dict(os.environ)
     visible = env.get("CUDA_VISIBLE_DEVICES")
     env["CUDA_VISIBLE_DEVICES"] = visible.split(",")[local] if visible else str(local)
-    r = subprocess.run([exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--warmup", "1", "--passes", "1"],
-                       capture_output=True, text=True, env=env, timeout=1500)
+    cmd = [exe, os.path.join(pkg.PARAM_DIR, "bootparam_40.json"), "--warmup", "1", "--passes", "1"]
+    if world > 1:
+        cmd += ["--rank", str(rank), "--world", str(world), "--rendezvous", rendezvous]
+        env.setdefault("NCCL_DEBUG", "WARN")
+        env.setdefault("NCCL_NVLS_ENABLE", "0")  # plain peer transfers: broadcasts gain nothing from multicast
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1500)
     if r.returncode != 0:
         raise RuntimeError("bert_bench failed: " + r.stderr[-500:])
+    if rank != 0:
+        return None
     return json.loads(r.stdout.strip().splitlines()[-1])
 
 
-def bert_entry(bert, seconds_max, world):
-    """The `bert_layer` object of the line: rank 0's run with the layer time
-    replaced by the maximum over ranks; every rank runs its own batch of
-    sequences (no collective), so the throughput adds up."""
+def bert_entry(bert, world):
+    """The `bert_layer` object of the line, from rank 0's process: one layer
+    call of 256 sequences on all `world` GPUs together (its stage times include
+    the waits inside the all-gathers, so they are the job's times)."""
     peak = None
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
             peak = 2.0 * json.load(f)["bf16_tflops"]
     out = dict(bert)
-    out["seconds_per_layer"] = seconds_max
-    out["unit"] = "s per layer call of 256 sequences (max over ranks)"
-    out["sequences_per_s_all_ranks"] = world * bert["sequences_per_layer_call"] / seconds_max
-    out["seconds_per_sequence"] = seconds_max / (world * bert["sequences_per_layer_call"])
+    out["unit"] = f"s per layer call of 256 sequences on {world} GPU(s)"
+    out["scaling"] = "strong: one call sharded by heads and ciphertext blocks" if world > 1 else "one GPU"
+    out["sequences_per_s"] = bert["sequences_per_layer_call"] / bert["seconds_per_layer"]
     out["projection_tensor_pipe"] = {
         "int8_TOPS": bert["gemm_int8_TOPS"], "peak_TOPS": peak,
         "frac": bert["gemm_int8_TOPS"] / peak if peak else None,
@@ -907,8 +914,11 @@ def run_gpu(args, pkg):
     if args.workload == "hmult" and not args.no_bert:
         torch.cuda.empty_cache()
         barrier()
-        bert = bench_bert_layer(pkg, local)
-        bert_s = reduce_max([bert["seconds_per_layer"]], device=f"cuda:{local}")[0]
+        token = [f"/tmp/cfhe_bert_{os.getpid()}_{int(time.time())}"]
+        if world > 1:
+            dist.broadcast_object_list(token, src=0)
+        bert = bench_bert_layer(pkg, local, rank, world, token[0])
+        barrier()
 
     shape = {"nq": len(eng.level_limbs(HM_LEVEL)), "nd": len(eng.level_limbs(HM_LEVEL - 1)), "alpha": eng.alpha}
     red = reduce_over_ranks(ntt, hm, boot, hoist, device=f"cuda:{local}")
@@ -919,7 +929,7 @@ def run_gpu(args, pkg):
         if hm16:
             line["hmult_level16"] = hm16
         if bert:
-            line["bert_layer"] = bert_entry(bert, bert_s, world)
+            line["bert_layer"] = bert_entry(bert, world)
         if ref_cuda:
             line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu:

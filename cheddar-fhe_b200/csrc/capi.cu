@@ -230,6 +230,8 @@ int cfhe_use_own_stream(cfhe_context *h) {
   return 0;
 }
 
+void *cfhe_get_stream(cfhe_context *h) { return h ? (void *)h->c.stream : nullptr; }
+
 int cfhe_synchronize(cfhe_context *h) {
   CFHE_ENTER(h);
   if (!h) return fail("null context");

@@ -6,6 +6,13 @@
 // reference figure for this workload.
 //
 //   bert_bench <parameter.json> [--passes K] [--warmup W] [--workers T] [--small] [--no-pair]
+//              [--rank r --world G --rendezvous path]
+//
+// With --world G > 1, G processes (one per GPU, each given its rank and the same
+// rendezvous path) run ONE layer call together, sharded by heads and blocks of
+// ciphertexts with NCCL all-gathers between the stages; every rank builds the
+// same keys and inputs from the same seeds, rank 0 prints the line. The
+// output_digest (a hash of three output ciphertexts) is the same for every G.
 //
 // W warm-up passes (default 1) come before the K timed ones (default 1); the
 // first pass also encodes and packs the weight matrices (pack_weights_s, kept
@@ -16,6 +23,20 @@
 
 #include "cheddar/Transformer.h"
 
+// FNV-1a over the words of a ciphertext, continued from h
+static uint64_t Digest(uint64_t h, const cheddar::Ciphertext<uint32_t> &ct) {
+  std::vector<uint32_t> w;
+  for (const auto *poly : {&ct.bx_, &ct.ax_}) {
+    cheddar::CopyDeviceToHost(w, *poly);
+    cheddar::CheckAbi(cfhe_synchronize(cheddar::detail::CurrentHandle()));
+    for (uint32_t x : w) {
+      h ^= x;
+      h *= 1099511628211ull;
+    }
+  }
+  return h;
+}
+
 using namespace cheddar;
 using word = uint32_t;
 
@@ -24,7 +45,8 @@ int main(int argc, char **argv) {
     std::cerr << "usage: bert_bench <parameter.json> [--passes K] [--warmup W] [--workers T] [--small] [--no-pair]\n";
     return 2;
   }
-  int passes = 1, warmup = 1, workers = 4;
+  int passes = 1, warmup = 1, workers = 4, rank = 0, world = 1;
+  std::string rendezvous;
   TransformerConfig cfg = TransformerConfig::BertBase();
   double stddev = 0.02;
   for (int i = 2; i < argc; i++) {
@@ -37,6 +59,9 @@ int main(int argc, char **argv) {
       stddev = 0.08;
     } else if (!strcmp(argv[i], "--no-pair")) cfg.pair_boot = false;
     else if (!strcmp(argv[i], "--workers") && i + 1 < argc) workers = std::max(1, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--rank") && i + 1 < argc) rank = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--world") && i + 1 < argc) world = std::max(1, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--rendezvous") && i + 1 < argc) rendezvous = argv[++i];
   }
   cfg.workers = workers;
   Random::Seed(20241125);
@@ -56,7 +81,16 @@ int main(int argc, char **argv) {
   ctx->PrepareEvalMod();
   ctx->PrepareEvalSpecialFFT(slots);
   TransformerWeights w = TransformerWeights::Random(cfg, 1, stddev);
-  EncryptedTransformerLayer<word> layer(ctx, cfg, w);
+  std::shared_ptr<RankGroup> group;
+  if (world > 1) {
+#ifdef CHEDDAR_WITH_NCCL
+    AssertTrue(!rendezvous.empty() && rank >= 0 && rank < world, "bert_bench: --rank, --world and --rendezvous go together");
+    group = std::make_shared<NcclRankGroup>(rank, world, rendezvous);
+#else
+    Fail("bert_bench: built without NCCL");
+#endif
+  }
+  EncryptedTransformerLayer<word> layer(ctx, cfg, w, group);
   EvkRequest req;
   ctx->AddRequiredRotations(req, slots);
   layer.AddRequiredRotations(req);
@@ -129,13 +163,16 @@ int main(int argc, char **argv) {
       var_hi = std::max(var_hi, v);
     }
   }
+  uint64_t digest = 14695981039346656037ull;
+  for (int j : {0, H / 2, H - 1}) digest = Digest(digest, cur[j]);
+  if (rank != 0) return 0;
   std::cout << std::setprecision(6);
   std::cout << "{\"seconds_per_layer\": " << timed_s / timed << ", \"sequences_per_layer_call\": " << B
             << ", \"seconds_per_sequence\": " << timed_s / timed / B << ", \"passes_timed\": " << timed
              << ", \"warmup_passes\": " << warmup << ", \"warmup_s\": " << warm_s << ", \"pack_weights_s\": " << pack_s << ", \"keys_s\": " << keys_s << ", \"encrypt_s\": " << encrypt_s
             << ", \"shape\": {\"seq_len\": " << T << ", \"hidden\": " << H << ", \"heads\": " << cfg.heads
             << ", \"head_dim\": " << cfg.head_dim << ", \"ffn\": " << cfg.ffn << "}"
-             << ", \"host_threads\": " << cfg.workers << ", \"bootstraps_per_layer\": " << layer.Bootstraps() << ", \"paired_bootstraps\": "
+             << ", \"gpus\": " << world << ", \"output_digest\": \"" << std::hex << digest << std::dec << "\", \"host_threads\": " << cfg.workers << ", \"bootstraps_per_layer\": " << layer.Bootstraps() << ", \"paired_bootstraps\": "
             << (cfg.pair_boot ? "true" : "false") << ", \"level_in_out\": " << level
             << ", \"gemm_seconds_per_layer\": " << gemm_s / timed << ", \"gemm_int8_TOPS\": "
             << 2.0 * gemm_macs / gemm_s * 1e-12 << ", \"output_token_mean_abs_max\": " << worst_mean

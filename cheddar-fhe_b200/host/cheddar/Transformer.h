@@ -39,6 +39,16 @@
 // ordered after the main stream when the loop starts and the main stream after
 // them when it ends. Inside such a loop an item frees only what it allocated
 // itself, so no block changes pool while another stream may still read it.
+//
+// Several GPUs (one process each, RankGroup). One layer call is sharded by
+// heads and by blocks of ciphertexts: a rank projects Q, K, V for its heads
+// only and runs their attention; the attention outputs are all-gathered; the
+// output projection, the residual sums and the LayerNorms (cheap, and their
+// statistics need every feature) run on every rank alike; each rank
+// bootstraps its block of the 768 residual ciphertexts and its block of the
+// feed-forward features, with an all-gather after each. Every rank starts
+// from the same ciphertexts and keys and all arithmetic is exact, so the
+// sharded result is bit-identical to the one-GPU result.
 #pragma once
 #include <chrono>
 #include <atomic>
@@ -47,6 +57,7 @@
 #include <tuple>
 
 #include "cheddar/Boot.h"
+#include "cheddar/RankGroup.h"
 
 namespace cheddar {
 
@@ -213,8 +224,11 @@ class EncryptedTransformerLayer {
   using Boot = BootContext<word>;
 
  public:
-  EncryptedTransformerLayer(std::shared_ptr<Boot> ctx, const TransformerConfig &cfg, const TransformerWeights &w)
-      : ctx_{std::move(ctx)}, cfg_{cfg}, w_{w}, polys_{cfg} {
+  EncryptedTransformerLayer(std::shared_ptr<Boot> ctx, const TransformerConfig &cfg, const TransformerWeights &w,
+                            std::shared_ptr<RankGroup> group = nullptr)
+      : ctx_{std::move(ctx)}, cfg_{cfg}, w_{w}, polys_{cfg}, group_{std::move(group)} {
+    if (!group_) group_ = std::make_shared<RankGroup>();
+    AssertTrue(group_->world() <= cfg.heads, "Transformer: more ranks than heads");
     AssertTrue(cfg.heads * cfg.head_dim == cfg.hidden, "Transformer: heads * head_dim != hidden");
     AssertTrue(cfg.seq_len % cfg.baby == 0, "Transformer: baby must divide seq_len");
     slots_ = ctx_->param_.degree_ / 2;
@@ -247,6 +261,10 @@ class EncryptedTransformerLayer {
     const double A = cfg_.act_div;
     AssertTrue((int)x.size() == H, "Transformer: wrong number of input ciphertexts");
     const Evk &mult = evk.GetMultiplicationKey();
+    const int rank = group_->rank(), world = group_->world();
+    const auto [head0, head1] = Block(heads, rank);   // this rank's heads
+    const auto [res0, res1] = Block(H, rank);         // its block of the residual ciphertexts
+    const auto [ffn0, ffn1] = Block(F, rank);         // its block of the feed-forward features
     stage_s_.clear();
     gemm_s_ = 0;
     pack_s_ = 0;
@@ -260,36 +278,42 @@ class EncryptedTransformerLayer {
     {
       // Q is pre-divided by sqrt(head_dim) * score_range: the score ciphertexts hold s / score_range
       const double qs = 1.0 / (std::sqrt((double)D) * cfg_.score_range);
+      // columns of this rank's heads only: Q, K and V of head h are features h D .. (h+1) D - 1
+      std::vector<int> cols;
+      for (int part = 0; part < 3; part++)
+        for (int j = head0 * D; j < head1 * D; j++) cols.push_back(part * H + j);
+      const int nc = cols.size();
       if (!m_qkv_) {
-        std::vector<double> wm((size_t)H * 3 * H);
+        std::vector<double> wm((size_t)H * nc);
         for (int k = 0; k < H; k++)
-          for (int j = 0; j < H; j++) {
-            wm[(size_t)k * 3 * H + j] = w_.wq[(size_t)k * H + j] * A * qs;
-            wm[(size_t)k * 3 * H + H + j] = w_.wk[(size_t)k * H + j] * A;
-            wm[(size_t)k * 3 * H + 2 * H + j] = w_.wv[(size_t)k * H + j] * A;
+          for (int c = 0; c < nc; c++) {
+            const int part = cols[c] / H, j = cols[c] % H;
+            const double v = part == 0 ? w_.wq[(size_t)k * H + j] * A * qs
+                                       : part == 1 ? w_.wk[(size_t)k * H + j] * A : w_.wv[(size_t)k * H + j] * A;
+            wm[(size_t)k * nc + c] = v;
           }
-        m_qkv_ = MakeMatrix(wm, H, 3 * H, x[0]);
+        m_qkv_ = MakeMatrix(wm, H, nc, x[0]);
       }
-      std::vector<double> bias(3 * H);
-      for (int j = 0; j < H; j++) {
-        bias[j] = w_.bq[j] * qs;
-        bias[H + j] = w_.bk[j];
-        bias[2 * H + j] = w_.bv[j];
+      std::vector<double> bias(nc);
+      for (int c = 0; c < nc; c++) {
+        const int part = cols[c] / H, j = cols[c] % H;
+        bias[c] = part == 0 ? w_.bq[j] * qs : part == 1 ? w_.bk[j] : w_.bv[j];
       }
-      Project(qkv, *m_qkv_, Pointers(x), bias);
+      qkv.resize(3 * H);
+      Project(qkv, *m_qkv_, Pointers(x), bias, cols);
     }
     Mark("QKV projection");
     if (probe_) probe_("qkv", qkv, 1.0);
-    std::vector<Ct> o_un(H), stat(heads);
-    for (int h = 0; h < heads; h++) AttentionHead(h, qkv, o_un, stat[h], evk);
+    std::vector<Ct> o_un(H), stat(head1 - head0);
+    for (int h = head0; h < head1; h++) AttentionHead(h, qkv, o_un, stat[h - head0], evk);
     qkv.clear();
     Mark("scores, exponentials, weighted values");
     std::vector<Ct> o(H);
     {
       BootAll(stat, evk, true);
-      for (int h = 0; h < heads; h++) {
+      for (int h = head0; h < head1; h++) {
         Ct p;
-        Poly(main_, p, stat[h], polys_.inv_c, mult);
+        Poly(main_, p, stat[h - head0], polys_.inv_c, mult);
         LevelTo(main_, p, Level(o_un[h * D]));
         AssertTrue(Level(p) == Level(o_un[h * D]), "Transformer: the normaliser ended below the weighted values");
         ParallelFor(D, [&](const ConstContextPtr<word> &c, int d) {
@@ -299,6 +323,10 @@ class EncryptedTransformerLayer {
       o_un.clear();
     }
     Mark("softmax normaliser");
+    if (world > 1) {
+      AllGather(o, [&](int j) { return BlockOwner(heads, j / D); });
+      Mark("all-gather: attention outputs");
+    }
     if (probe_) probe_("attention", o, 1.0);
     std::vector<Ct> y1;
     {
@@ -316,29 +344,43 @@ class EncryptedTransformerLayer {
     y1.clear();
     Mark("LayerNorm 1");
     if (probe_) probe_("LayerNorm 1", z, A);
-    BootAll(z, evk);
+    BootBlock(z, res0, res1, evk);
     Mark("bootstrap (before the feed-forward block)");
+    if (world > 1) {
+      AllGather(z, [&](int j) { return BlockOwner(H, j); });
+      Mark("all-gather: refreshed LayerNorm outputs");
+    }
     if (probe_) probe_("LayerNorm 1, refreshed", z, A);
 
     // ---- feed-forward
     std::vector<Ct> act;
     {
       const double G = cfg_.gelu_range;
+      std::vector<int> cols;
+      for (int j = ffn0; j < ffn1; j++) cols.push_back(j);
+      const int nc = cols.size();
       if (!m_w1_) {
-        std::vector<double> wm(w_.w1);
-        for (auto &v : wm) v *= A / G;
-        m_w1_ = MakeMatrix(wm, H, F, z[0]);
+        std::vector<double> wm((size_t)H * nc);
+        for (int k = 0; k < H; k++)
+          for (int c = 0; c < nc; c++) wm[(size_t)k * nc + c] = w_.w1[(size_t)k * F + cols[c]] * A / G;
+        m_w1_ = MakeMatrix(wm, H, nc, z[0]);
       }
-      std::vector<double> bias(F);
-      for (int j = 0; j < F; j++) bias[j] = w_.b1[j] / G;
-      std::vector<Ct> pre;
-      Project(pre, *m_w1_, Pointers(z), bias);
+      std::vector<double> bias(nc);
+      for (int c = 0; c < nc; c++) bias[c] = w_.b1[cols[c]] / G;
+      std::vector<Ct> pre(F);
+      Project(pre, *m_w1_, Pointers(z), bias, cols);
       Mark("feed-forward projection 1");
       if (probe_) probe_("pre-activation", pre, cfg_.gelu_range);
       act.resize(F);
-      ParallelFor(F, [&](const ConstContextPtr<word> &c, int j) { Poly(c, act[j], pre[j], polys_.gelu_c, mult); });
+      ParallelFor(nc, [&](const ConstContextPtr<word> &c, int i) {
+        Poly(c, act[ffn0 + i], pre[ffn0 + i], polys_.gelu_c, mult);
+      });
       pre.clear();
       Mark("GELU");
+      if (world > 1) {
+        AllGather(act, [&](int j) { return BlockOwner(F, j); });
+        Mark("all-gather: feed-forward activations");
+      }
       if (probe_) probe_("GELU", act, cfg_.gelu_range);
       if (!m_w2_) m_w2_ = MakeMatrix(Centred(w_.w2, F, H, G / A), F, H, act[0]);
     }
@@ -353,8 +395,12 @@ class EncryptedTransformerLayer {
     y2.clear();
     Mark("LayerNorm 2");
     if (probe_) probe_("LayerNorm 2", out, A);
-    BootAll(out, evk);
+    BootBlock(out, res0, res1, evk);
     Mark("bootstrap (end of the layer)");
+    if (world > 1) {
+      AllGather(out, [&](int j) { return BlockOwner(H, j); });
+      Mark("all-gather: layer outputs");
+    }
   }
 
   // seconds per stage of the last Forward (the host synchronises between stages)
@@ -440,8 +486,9 @@ class EncryptedTransformerLayer {
     return m;
   }
   // y = rescale(W x) + bias, one level below x at the canonical scale
+  // out_index (optional): result c is stored in y[out_index[c]] (y keeps its size)
   void Project(std::vector<Ct> &y, const PlainMatrix<word> &m, const std::vector<const Ct *> &x,
-               const std::vector<double> &bias) {
+               const std::vector<double> &bias, const std::vector<int> &out_index = {}) {
     AssertTrue(Level(*x[0]) == m.level(), "Transformer: the matrix was prepared for another level");
     ctx_->AssertSameScale(x[0]->GetScale() * m.scale(),
                           Canon(m.level() - 1) * ctx_->param_.GetRescalePrimeProd(m.level()));
@@ -452,12 +499,64 @@ class EncryptedTransformerLayer {
     ctx_->Synchronize();
     gemm_s_ += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     gemm_macs_ += m.Int8Macs(ctx_->param_.degree_);
-    y.clear();
-    y.resize(raw.size());
+    if (out_index.empty()) {
+      y.clear();
+      y.resize(raw.size());
+    }
     ParallelFor((int)raw.size(), [&](const ConstContextPtr<word> &c, int j) {
-      c->Rescale(y[j], raw[j]);
-      AddConst(c, y[j], bias[j]);
+      Ct &dst = y[out_index.empty() ? j : out_index[j]];
+      c->Rescale(dst, raw[j]);
+      AddConst(c, dst, bias[j]);
     });
+  }
+
+  // ---- ranks: contiguous blocks, the first n % world ranks hold one more
+  std::pair<int, int> Block(int n, int rank) const {
+    const int world = group_->world(), base = n / world, rem = n % world;
+    const int lo = rank * base + Min(rank, rem);
+    return {lo, lo + base + (rank < rem ? 1 : 0)};
+  }
+  int BlockOwner(int n, int i) const {
+    for (int r = 0; r < group_->world(); r++)
+      if (i < Block(n, r).second) return r;
+    return group_->world() - 1;
+  }
+  // Every rank ends with all of v: element i travels from owner(i). Elements
+  // a rank does not own are allocated like the ones it owns (same level,
+  // scale and slot count on every rank).
+  void AllGather(std::vector<Ct> &v, const std::function<int(int)> &owner) {
+    const int rank = group_->rank(), n = v.size();
+    const Ct *like = nullptr;
+    for (int i = 0; i < n && !like; i++)
+      if (owner(i) == rank) like = &v[i];
+    AssertTrue(like != nullptr, "Transformer: a rank owns nothing of a gathered vector");
+    const NPInfo np = like->GetNP();
+    const size_t bytes = (size_t)np.GetNumTotal() * ctx_->param_.degree_ * sizeof(word);
+    void *stream = cfhe_get_stream(ctx_->h_);
+    constexpr int kPerGroup = 256;
+    for (int i0 = 0; i0 < n; i0 += kPerGroup) {
+      const int i1 = Min(n, i0 + kPerGroup);
+      for (int i = i0; i < i1; i++)
+        if (owner(i) != rank) {
+          Ct fresh(np);
+          fresh.SetScale(like->GetScale());
+          fresh.SetNumSlots(like->GetNumSlots());
+          v[i] = std::move(fresh);
+        }
+      group_->Start();
+      for (int i = i0; i < i1; i++) {
+        group_->Broadcast(v[i].bx_.data(), bytes, owner(i), stream);
+        group_->Broadcast(v[i].ax_.data(), bytes, owner(i), stream);
+      }
+      group_->End();
+    }
+  }
+  // BootAll on v[lo, hi)
+  void BootBlock(std::vector<Ct> &v, int lo, int hi, const EvkMap<word> &evk) {
+    std::vector<Ct> mine;
+    for (int i = lo; i < hi; i++) mine.push_back(std::move(v[i]));
+    BootAll(mine, evk);
+    for (int i = lo; i < hi; i++) v[i] = std::move(mine[i - lo]);
   }
   // W (I - 11^T / n_out) * factor: every row loses its mean
   static std::vector<double> Centred(const std::vector<double> &w, int n_in, int n_out, double factor) {
@@ -691,7 +790,9 @@ class EncryptedTransformerLayer {
         dst = std::move(src);
       }
     };
-    const bool pairs = cfg_.pair_boot && n > 1;
+    // statistics go through one by one: they are few, and which heads share a
+    // bootstrap would otherwise depend on how many ranks the heads are spread over
+    const bool pairs = cfg_.pair_boot && n > 1 && !masked;
     const Evk &conj = evk.GetConjugationKey();
     for (size_t i = 0; i < n; i += 2) {
       if (!pairs || i + 1 == n) {
@@ -723,6 +824,7 @@ class EncryptedTransformerLayer {
   TransformerConfig cfg_;
   TransformerWeights w_;
   TransformerPolys polys_;
+  std::shared_ptr<RankGroup> group_;
   int slots_ = 0, lane_ = 0;
   std::unique_ptr<PlainMatrix<word>> m_qkv_, m_wo_, m_w1_, m_w2_;
   Probe probe_;

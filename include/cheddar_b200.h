@@ -64,6 +64,9 @@ CFHE_API void cfhe_context_destroy(cfhe_context *ctx);
  * stream of its own; cfhe_use_own_stream() returns to it. */
 CFHE_API int cfhe_set_stream(cfhe_context *ctx, void *cuda_stream);
 CFHE_API int cfhe_use_own_stream(cfhe_context *ctx);
+/* The cudaStream_t the context's work is enqueued on (for a caller that puts
+ * its own work, e.g. a collective on the context's buffers, in the same order). */
+CFHE_API void *cfhe_get_stream(cfhe_context *ctx);
 CFHE_API int cfhe_synchronize(cfhe_context *ctx);
 /* Two contexts of one GPU work side by side (each on its own stream, with its
  * own workspace and allocation cache): everything submitted to `later` after
