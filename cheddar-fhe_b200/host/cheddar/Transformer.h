@@ -42,11 +42,13 @@
 //
 // Several GPUs (one process each, RankGroup). One layer call is sharded by
 // heads and by blocks of ciphertexts: a rank projects Q, K, V for its heads
-// only and runs their attention; the attention outputs are all-gathered; the
-// output projection, the residual sums and the LayerNorms (cheap, and their
-// statistics need every feature) run on every rank alike; each rank
-// bootstraps its block of the 768 residual ciphertexts and its block of the
-// feed-forward features, with an all-gather after each. Every rank starts
+// only and runs their attention; the attention outputs are all-gathered; from
+// there on a rank owns a block of the residual ciphertexts (its columns of the
+// output projection and of the second feed-forward projection, its share of
+// the residual sums, the LayerNorm products and the bootstraps) and a block of
+// the feed-forward features, with an all-gather where the next stage needs
+// every ciphertext; a LayerNorm's sum of squares gathers one partial sum per
+// rank, and the statistic's bootstrap and series run on every rank alike. Every rank starts
 // from the same ciphertexts and keys and all arithmetic is exact, so the
 // sharded result is bit-identical to the one-GPU result.
 #pragma once
@@ -332,15 +334,18 @@ class EncryptedTransformerLayer {
     {
       // the mean over the features is removed here: C = I - 11^T / H commutes
       // with the residual sum, so C is folded into the weights and the bias
-      if (!m_wo_) m_wo_ = MakeMatrix(Centred(w_.wo, H, H, 1.0 / A), H, H, o[0]);
-      Project(y1, *m_wo_, Pointers(o), CentredBias(w_.bo, 1.0 / A));
+      std::vector<int> cols;
+      for (int j = res0; j < res1; j++) cols.push_back(j);
+      if (!m_wo_) m_wo_ = MakeMatrix(Columns(Centred(w_.wo, H, H, 1.0 / A), H, H, cols), H, cols.size(), o[0]);
+      y1.resize(H);
+      Project(y1, *m_wo_, Pointers(o), Select(CentredBias(w_.bo, 1.0 / A), cols), cols);
       o.clear();
-      AddCentredResidual(y1, x);
+      AddCentredResidual(y1, x, res0, res1);
     }
     Mark("output projection, residual");
     if (probe_) probe_("centred sum 1", y1, A);
     std::vector<Ct> z;
-    LayerNorm(z, y1, w_.gamma1, w_.beta1, evk);
+    LayerNorm(z, y1, w_.gamma1, w_.beta1, evk, res0, res1);
     y1.clear();
     Mark("LayerNorm 1");
     if (probe_) probe_("LayerNorm 1", z, A);
@@ -382,16 +387,21 @@ class EncryptedTransformerLayer {
         Mark("all-gather: feed-forward activations");
       }
       if (probe_) probe_("GELU", act, cfg_.gelu_range);
-      if (!m_w2_) m_w2_ = MakeMatrix(Centred(w_.w2, F, H, G / A), F, H, act[0]);
     }
-    std::vector<Ct> y2;
-    Project(y2, *m_w2_, Pointers(act), CentredBias(w_.b2, 1.0 / A));
+    std::vector<Ct> y2(H);
+    {
+      std::vector<int> cols;
+      for (int j = res0; j < res1; j++) cols.push_back(j);
+      if (!m_w2_)
+        m_w2_ = MakeMatrix(Columns(Centred(w_.w2, F, H, cfg_.gelu_range / A), F, H, cols), F, cols.size(), act[0]);
+      Project(y2, *m_w2_, Pointers(act), Select(CentredBias(w_.b2, 1.0 / A), cols), cols);
+    }
     act.clear();
-    AddCentredResidual(y2, z);
+    AddCentredResidual(y2, z, res0, res1);
     z.clear();
     Mark("feed-forward projection 2, residual");
     if (probe_) probe_("centred sum 2", y2, A);
-    LayerNorm(out, y2, w_.gamma2, w_.beta2, evk);
+    LayerNorm(out, y2, w_.gamma2, w_.beta2, evk, res0, res1);
     y2.clear();
     Mark("LayerNorm 2");
     if (probe_) probe_("LayerNorm 2", out, A);
@@ -531,6 +541,7 @@ class EncryptedTransformerLayer {
       if (owner(i) == rank) like = &v[i];
     AssertTrue(like != nullptr, "Transformer: a rank owns nothing of a gathered vector");
     const NPInfo np = like->GetNP();
+    const bool rx = like->HasRx();
     const size_t bytes = (size_t)np.GetNumTotal() * ctx_->param_.degree_ * sizeof(word);
     void *stream = cfhe_get_stream(ctx_->h_);
     constexpr int kPerGroup = 256;
@@ -538,7 +549,7 @@ class EncryptedTransformerLayer {
       const int i1 = Min(n, i0 + kPerGroup);
       for (int i = i0; i < i1; i++)
         if (owner(i) != rank) {
-          Ct fresh(np);
+          Ct fresh(np, rx);
           fresh.SetScale(like->GetScale());
           fresh.SetNumSlots(like->GetNumSlots());
           v[i] = std::move(fresh);
@@ -547,6 +558,7 @@ class EncryptedTransformerLayer {
       for (int i = i0; i < i1; i++) {
         group_->Broadcast(v[i].bx_.data(), bytes, owner(i), stream);
         group_->Broadcast(v[i].ax_.data(), bytes, owner(i), stream);
+        if (rx) group_->Broadcast(v[i].rx_.data(), bytes, owner(i), stream);
       }
       group_->End();
     }
@@ -569,6 +581,19 @@ class EncryptedTransformerLayer {
     }
     return r;
   }
+  // the listed columns of a row-major [n_in][n_out] matrix
+  static std::vector<double> Columns(const std::vector<double> &w, int n_in, int n_out, const std::vector<int> &cols) {
+    const int nc = cols.size();
+    std::vector<double> r((size_t)n_in * nc);
+    for (int k = 0; k < n_in; k++)
+      for (int c = 0; c < nc; c++) r[(size_t)k * nc + c] = w[(size_t)k * n_out + cols[c]];
+    return r;
+  }
+  static std::vector<double> Select(const std::vector<double> &v, const std::vector<int> &idx) {
+    std::vector<double> r(idx.size());
+    for (size_t c = 0; c < idx.size(); c++) r[c] = v[idx[c]];
+    return r;
+  }
   static std::vector<double> CentredBias(const std::vector<double> &b, double factor) {
     double mean = 0;
     for (double v : b) mean += v;
@@ -577,9 +602,9 @@ class EncryptedTransformerLayer {
     for (size_t j = 0; j < b.size(); j++) r[j] = (b[j] - mean) * factor;
     return r;
   }
-  // y[j] += x[j] - mean_j x[j], x brought down to the level of y
-  void AddCentredResidual(std::vector<Ct> &y, const std::vector<Ct> &x) {
-    const int H = x.size(), lx = Level(x[0]), ly = Level(y[0]);
+  // y[j] += x[j] - mean_j x[j] for j in [lo, hi), x brought down to the level of y
+  void AddCentredResidual(std::vector<Ct> &y, const std::vector<Ct> &x, int lo, int hi) {
+    const int H = x.size(), lx = Level(x[0]), ly = Level(y[lo]);
     AssertTrue(lx > ly, "Transformer: the residual must sit above the block's output");
     Ct sum;
     ctx_->Copy(sum, x[0]);
@@ -590,7 +615,8 @@ class EncryptedTransformerLayer {
     ctx_->encoder().EncodeConstant(inv, lx, s, 1.0 / H);
     Ct mean;
     ctx_->Mult(mean, sum, inv);
-    ParallelFor(H, [&](const ConstContextPtr<word> &cx, int j) {
+    ParallelFor(hi - lo, [&](const ConstContextPtr<word> &cx, int i) {
+      const int j = lo + i;
       Ct t, c;
       cx->Mult(t, x[j], one);
       cx->Sub(t, t, mean);
@@ -706,13 +732,27 @@ class EncryptedTransformerLayer {
 
   // z[j] = gamma_j y[j] / sqrt(var + eps) + beta_j / act_div for centred y
   // (mean already removed), var = (act_div^2 / H) sum_j y[j]^2
+  // This rank holds y[lo, hi) and produces z[lo, hi); the sum of squares
+  // collects the ranks' partial sums (exact modular sums: any grouping gives
+  // the same words), the statistic's bootstrap and series run on every rank.
   void LayerNorm(std::vector<Ct> &z, const std::vector<Ct> &y, const std::vector<double> &gamma,
-                 const std::vector<double> &beta, const EvkMap<word> &evk) {
+                 const std::vector<double> &beta, const EvkMap<word> &evk, int lo, int hi) {
     const int H = y.size();
     const double A = cfg_.act_div, span = cfg_.var_hi - cfg_.var_lo;
     const Evk &mult = evk.GetMultiplicationKey();
     Ct acc, ss, w;
-    ctx_->MultSumUnsafe(acc, Pointers(y), Pointers(y));
+    {
+      std::vector<const Ct *> mine;
+      for (int j = lo; j < hi; j++) mine.push_back(&y[j]);
+      ctx_->MultSumUnsafe(acc, mine, mine);
+    }
+    if (group_->world() > 1) {
+      std::vector<Ct> parts(group_->world());
+      parts[group_->rank()] = std::move(acc);
+      AllGather(parts, [](int r) { return r; });
+      acc = std::move(parts[0]);
+      for (int r = 1; r < group_->world(); r++) ctx_->Add(acc, acc, parts[r]);
+    }
     ctx_->RelinearizeRescale(ss, acc, mult);
     MaskedAffine(w, ss, 2.0 * A * A / (H * span), -(cfg_.var_hi + cfg_.var_lo) / span);
     std::vector<Ct> one(1);
@@ -720,11 +760,12 @@ class EncryptedTransformerLayer {
     BootAll(one, evk, true);
     Ct f;
     Poly(main_, f, one[0], polys_.rsqrt_c, mult);  // 1 / (2 sqrt(var + eps))
-    const int target = Min(Level(f), Level(y[0]) - 1);
+    const int target = Min(Level(f), Level(y[lo]) - 1);
     LevelTo(main_, f, target);
     z.clear();
     z.resize(H);
-    ParallelFor(H, [&](const ConstContextPtr<word> &c, int j) {
+    ParallelFor(hi - lo, [&](const ConstContextPtr<word> &c, int i) {
+      const int j = lo + i;
       Ct t;
       MultConstRescale(c, t, y[j], 2.0 * gamma[j]);
       LevelTo(c, t, target);
