@@ -7,7 +7,9 @@
 // exact non-linear functions and once with each of them replaced by a
 // Chebyshev series handed in by the caller (the series the encrypted layer
 // evaluates). The token offsets of the attention run cyclically over the
-// whole sequence (every token attends to every token: no mask).
+// whole sequence (every token attends to every token: no mask). Pinned on the
+// CPU against PyTorch's float64 softmax / GELU / layer_norm
+// (tests/test_plain_layer_cpu.py).
 #pragma once
 #include <cmath>
 #include <vector>
