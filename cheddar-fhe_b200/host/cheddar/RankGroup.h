@@ -19,6 +19,19 @@
 
 namespace cheddar {
 
+// Contiguous blocks of n items over `world` ranks, the first n % world ranks
+// holding one more: [first, last) of `rank`, and the rank that holds item i.
+inline std::pair<int, int> BlockOfRank(int n, int world, int rank) {
+  const int base = n / world, rem = n % world;
+  const int lo = rank * base + (rank < rem ? rank : rem);
+  return {lo, lo + base + (rank < rem ? 1 : 0)};
+}
+inline int RankOfItem(int n, int world, int i) {
+  for (int r = 0; r < world; r++)
+    if (i < BlockOfRank(n, world, r).second) return r;
+  return world - 1;
+}
+
 class RankGroup {
  public:
   virtual ~RankGroup() = default;

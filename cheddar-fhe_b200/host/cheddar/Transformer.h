@@ -521,16 +521,8 @@ class EncryptedTransformerLayer {
   }
 
   // ---- ranks: contiguous blocks, the first n % world ranks hold one more
-  std::pair<int, int> Block(int n, int rank) const {
-    const int world = group_->world(), base = n / world, rem = n % world;
-    const int lo = rank * base + Min(rank, rem);
-    return {lo, lo + base + (rank < rem ? 1 : 0)};
-  }
-  int BlockOwner(int n, int i) const {
-    for (int r = 0; r < group_->world(); r++)
-      if (i < Block(n, r).second) return r;
-    return group_->world() - 1;
-  }
+  std::pair<int, int> Block(int n, int rank) const { return BlockOfRank(n, group_->world(), rank); }
+  int BlockOwner(int n, int i) const { return RankOfItem(n, group_->world(), i); }
   // Every rank ends with all of v: element i travels from owner(i). Elements
   // a rank does not own are allocated like the ones it owns (same level,
   // scale and slot count on every rank).

@@ -11,11 +11,37 @@
 #include <cstdint>
 #include <cstdio>
 #include <fstream>
+#include <algorithm>
 #include <iostream>
+#include <string>
 
 #include "../../oracle/transformer_plain.h"
+#include "cheddar/RankGroup.h"
+
+// plain_layer --blocks: checks the block partition the sharded layer uses
+// (every item owned exactly once, sizes differ by at most one, owner lookup
+// consistent) for the shapes that occur; prints "blocks ok".
+static int CheckBlocks() {
+  for (int n : {1, 2, 12, 32, 64, 768, 3072})
+    for (int world = 1; world <= 8; world++) {
+      int next = 0, smallest = n, largest = 0;
+      for (int r = 0; r < world; r++) {
+        const auto [lo, hi] = cheddar::BlockOfRank(n, world, r);
+        if (lo != next || hi < lo) return 1;
+        for (int i = lo; i < hi; i++)
+          if (cheddar::RankOfItem(n, world, i) != r) return 1;
+        smallest = std::min(smallest, hi - lo);
+        largest = std::max(largest, hi - lo);
+        next = hi;
+      }
+      if (next != n || largest - smallest > 1) return 1;
+    }
+  std::cout << "blocks ok" << std::endl;
+  return 0;
+}
 
 int main(int argc, char **argv) {
+  if (argc == 2 && std::string(argv[1]) == "--blocks") return CheckBlocks();
   if (argc < 3) return 2;
   std::ifstream in(argv[1], std::ios::binary);
   int32_t head[9];

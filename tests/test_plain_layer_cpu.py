@@ -78,3 +78,11 @@ def test_plain_layer_matches_torch_float64(tmp_path, exact):
     err = np.abs(got - want).max()
     print("max |oracle - torch|", err)
     assert err < (1e-12 if exact else 1e-6)
+
+
+def test_block_partition_of_the_sharded_layer():
+    """Every item of a sharded vector is owned by exactly one rank, block sizes
+    differ by at most one, and the owner lookup agrees (host/cheddar/RankGroup.h)."""
+    subprocess.check_call(["make", "-s", "-C", CPP, "plain_layer"])
+    r = subprocess.run([os.path.join(CPP, "plain_layer"), "--blocks"], capture_output=True, text=True)
+    assert r.returncode == 0 and "blocks ok" in r.stdout
