@@ -352,6 +352,23 @@ class Engine:
         self._check(self.L.cfhe_moddown(self.h, level, kind, self._p(dst), self._p(src), polys,
                                         C.c_longlong(ds), C.c_longlong(ss)))
 
+    def moddown_staged_(self, level, kind, dst, src):
+        """The same as moddown_, composed from the three stage entries
+        (cfhe_intt_for_moddown, cfhe_bconv_for_moddown, cfhe_ntt_for_moddown)."""
+        polys = 1 if src.dim() == 2 else src.shape[0]
+        ss = src.stride(0) if src.dim() == 3 else 0
+        ds = dst.stride(0) if dst.dim() == 3 else 0
+        ns = self.L.cfhe_moddown_source_limbs(self.h, level, kind)
+        if ns < 0:
+            self._check(ns)
+        y = self.torch.empty((polys, ns, self.n), dtype=self.torch.int32, device=src.device)
+        self._check(self.L.cfhe_intt_for_moddown(self.h, level, kind, self._p(y), self._p(src), polys,
+                                                 C.c_longlong(ss)))
+        self._check(self.L.cfhe_bconv_for_moddown(self.h, level, kind, self._p(dst), self._p(y), polys,
+                                                  C.c_longlong(ds)))
+        self._check(self.L.cfhe_ntt_for_moddown(self.h, level, kind, self._p(dst), self._p(src), polys,
+                                                C.c_longlong(ds), C.c_longlong(ss)))
+
     def moddown_noalloc_(self, level, kind, dst, src):
         """One polynomial, [limbs, N]; no device allocation on the call path."""
         self._check(self.L.cfhe_moddown_noalloc(self.h, level, kind, self._p(dst), self._p(src)))

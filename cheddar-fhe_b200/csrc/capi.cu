@@ -996,6 +996,49 @@ int cfhe_moddown(cfhe_context *h, int level, int type, uint32_t *dst,
                      src_poly_stride, h->c.ws);
 }
 
+// the three stages of cfhe_moddown as separate calls
+static const ConvPlan *moddown_plan(cfhe_context *h, int level, int type, int n_polys) {
+  const LevelPlan *lp = get_plan(h, level);
+  if (!lp) return nullptr;
+  if (type < 0 || type > 2) { fail("unknown ModDown type"); return nullptr; }
+  if (type != 0 && !lp->has_rescale) { fail("level cannot be rescaled"); return nullptr; }
+  if (n_polys < 1 || n_polys > kMaxBconvJobs) { fail("invalid n_polys"); return nullptr; }
+  return &lp->down[type];
+}
+
+int cfhe_moddown_source_limbs(cfhe_context *h, int level, int type) {
+  if (!h) return fail("null context");
+  const ConvPlan *cv = moddown_plan(h, level, type, 1);
+  return cv ? (int)cv->src_g.size() : -1;
+}
+
+int cfhe_intt_for_moddown(cfhe_context *h, int level, int type, uint32_t *y, const uint32_t *src, int n_polys,
+                          long long src_poly_stride) {
+  CFHE_ENTER(h);
+  if (!y || !src) return fail("null argument");
+  const ConvPlan *cv = moddown_plan(h, level, type, n_polys);
+  if (!cv) return -1;
+  return run_moddown_intt(h->c, *cv, y, src, n_polys, src_poly_stride);
+}
+
+int cfhe_bconv_for_moddown(cfhe_context *h, int level, int type, uint32_t *dst, uint32_t *y, int n_polys,
+                           long long dst_poly_stride) {
+  CFHE_ENTER(h);
+  if (!dst || !y) return fail("null argument");
+  const ConvPlan *cv = moddown_plan(h, level, type, n_polys);
+  if (!cv) return -1;
+  return run_moddown_bconv(h->c, *cv, dst, y, n_polys, dst_poly_stride);
+}
+
+int cfhe_ntt_for_moddown(cfhe_context *h, int level, int type, uint32_t *dst, const uint32_t *src, int n_polys,
+                         long long dst_poly_stride, long long src_poly_stride) {
+  CFHE_ENTER(h);
+  if (!dst || !src) return fail("null argument");
+  const ConvPlan *cv = moddown_plan(h, level, type, n_polys);
+  if (!cv) return -1;
+  return run_moddown_ntt(h->c, *cv, dst, src, n_polys, dst_poly_stride, src_poly_stride);
+}
+
 int cfhe_evk_inner(cfhe_context *h, int level, uint32_t *acc_b, uint32_t *acc_a,
                    const uint32_t *modup, const uint32_t *c0, const uint32_t *c1,
                    const uint32_t *const *evk_b, const uint32_t *const *evk_a,

@@ -143,16 +143,21 @@ size_t moddown_scratch_words(const ConvPlan &cv, int n_polys) {
   return (size_t)n_polys * cv.src_g.size() * kN;
 }
 
-int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
-                const uint32_t *src, int n_polys, long long dst_stride,
-                long long src_stride, uint32_t *y) {
+static int check_moddown_shape(const ConvPlan &cv, int n_polys) {
   const int ns = (int)cv.src_g.size(), nd = (int)cv.dst_g.size();
   if (ns == 0 || nd == 0 || ns > kMaxBconvSrc || n_polys > kMaxBconvJobs) {
     set_error("ModDown: unsupported shape");
     return -1;
   }
+  return 0;
+}
+
+// 1. inverse transform of the limbs that disappear, y = [n_polys][ns][N]
+int run_moddown_intt(const Context &c, const ConvPlan &cv, uint32_t *y, const uint32_t *src, int n_polys,
+                     long long src_stride) {
+  if (int r = check_moddown_shape(cv, n_polys)) return r;
+  const int ns = (int)cv.src_g.size();
   const bool tc = c.use_tc_bconv && cv.d_tc_table;
-  // 1. inverse transform of the limbs that disappear
   NttArgs a;
   memset(&a, 0, sizeof(a));
   a.dst = y;
@@ -173,7 +178,15 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
   }
   if (int r = launch_ntt(c, a, true)) return r;
   c.mark("moddown_intt");
-  // 2. base conversion into the destination buffers
+  return 0;
+}
+
+// 2. base conversion of y into the destination buffers
+int run_moddown_bconv(const Context &c, const ConvPlan &cv, uint32_t *dst, uint32_t *y, int n_polys,
+                      long long dst_stride) {
+  if (int r = check_moddown_shape(cv, n_polys)) return r;
+  const int ns = (int)cv.src_g.size();
+  const bool tc = c.use_tc_bconv && cv.d_tc_table;
   if (tc) {
     BconvTcArgs b;
     memset(&b, 0, sizeof(b));
@@ -191,7 +204,15 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
     if (int r = launch_bconv(c, b)) return r;
   }
   c.mark("moddown_bconv");
-  // 3. forward transform in place with the fused (pad*x - t) * P^-1 epilogue
+  return 0;
+}
+
+// 3. forward transform in place with the fused (pad*x - t) * P^-1 epilogue
+int run_moddown_ntt(const Context &c, const ConvPlan &cv, uint32_t *dst, const uint32_t *src, int n_polys,
+                    long long dst_stride, long long src_stride) {
+  if (int r = check_moddown_shape(cv, n_polys)) return r;
+  const int nd = (int)cv.dst_g.size();
+  NttArgs a;
   memset(&a, 0, sizeof(a));
   a.dst = dst;
   a.src = dst;
@@ -216,6 +237,14 @@ int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
   if (int r = launch_ntt(c, a, false)) return r;
   c.mark("moddown_ntt");
   return 0;
+}
+
+int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
+                const uint32_t *src, int n_polys, long long dst_stride,
+                long long src_stride, uint32_t *y) {
+  if (int r = run_moddown_intt(c, cv, y, src, n_polys, src_stride)) return r;
+  if (int r = run_moddown_bconv(c, cv, dst, y, n_polys, dst_stride)) return r;
+  return run_moddown_ntt(c, cv, dst, src, n_polys, dst_stride, src_stride);
 }
 
 static int run_inner_impl(const Context &c, const LevelPlan &lp, uint32_t *acc_b,

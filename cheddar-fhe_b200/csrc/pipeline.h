@@ -14,6 +14,12 @@ size_t keyswitch_scratch_words(const LevelPlan &lp, int down_type);
 // mu: beta buffers of ntot limbs (slot = digit number); y: nq limbs scratch
 int run_modup(const Context &c, const LevelPlan &lp, uint32_t *mu,
               const uint32_t *src, bool copy_own, uint32_t *y);
+int run_moddown_intt(const Context &c, const ConvPlan &cv, uint32_t *y, const uint32_t *src, int n_polys,
+                     long long src_stride);
+int run_moddown_bconv(const Context &c, const ConvPlan &cv, uint32_t *dst, uint32_t *y, int n_polys,
+                      long long dst_stride);
+int run_moddown_ntt(const Context &c, const ConvPlan &cv, uint32_t *dst, const uint32_t *src, int n_polys,
+                    long long dst_stride, long long src_stride);
 int run_moddown(const Context &c, const ConvPlan &cv, uint32_t *dst,
                 const uint32_t *src, int n_polys, long long dst_stride,
                 long long src_stride, uint32_t *y);

@@ -295,6 +295,28 @@ CFHE_API int cfhe_pseudo_modup(cfhe_context *ctx, int level, uint32_t *dst, cons
 CFHE_API int cfhe_moddown(cfhe_context *ctx, int level, int type, uint32_t *dst,
                           const uint32_t *src, int n_polys,
                           long long dst_poly_stride, long long src_poly_stride);
+/* The three stages of cfhe_moddown() as separate calls, for a host that
+ * composes its own pipeline as the reference's handlers allow
+ * (NTTHandler::INTTForModDown, src/core/NTT.cu:1018-1127;
+ * ModSwitchHandler's matrix product, src/core/ModSwitch.cu:23-171;
+ * NTTHandler::NTTForModDown with its (src * pad - x) * P^-1 epilogue,
+ * src/core/NTT.cu:889-1016). level / type / n_polys / strides as in
+ * cfhe_moddown; y is a scratch of n_polys * cfhe_moddown_source_limbs() limbs:
+ *   cfhe_intt_for_moddown   y   = inverse transform of the limbs of src that
+ *                                 disappear, times the conversion's constants,
+ *                                 in the form the conversion reads
+ *   cfhe_bconv_for_moddown  dst = base conversion of y onto the limbs that stay
+ *   cfhe_ntt_for_moddown    dst = (pad * src - NTT(dst)) * P^-1, in place
+ * Run in that order they leave the words of cfhe_moddown(). (The forward
+ * transform that skips a digit's own limbs, NTTForModUp, is cfhe_ntt with the
+ * limb list that leaves them out.) */
+CFHE_API int cfhe_moddown_source_limbs(cfhe_context *ctx, int level, int type);
+CFHE_API int cfhe_intt_for_moddown(cfhe_context *ctx, int level, int type, uint32_t *y, const uint32_t *src,
+                                   int n_polys, long long src_poly_stride);
+CFHE_API int cfhe_bconv_for_moddown(cfhe_context *ctx, int level, int type, uint32_t *dst, uint32_t *y,
+                                    int n_polys, long long dst_poly_stride);
+CFHE_API int cfhe_ntt_for_moddown(cfhe_context *ctx, int level, int type, uint32_t *dst, const uint32_t *src,
+                                  int n_polys, long long dst_poly_stride, long long src_poly_stride);
 /* Same result as cfhe_moddown() for ONE polynomial, but the call path never
  * allocates or frees device memory. This entry point has no counterpart in
  * the reference (whose every ModDown takes temporaries from its memory pool,

@@ -154,6 +154,28 @@ def test_moddown_family_matches_oracle(engine40, oracle40, level):
     assert np.array_equal(e.moddown(level, 1, q_only), o.moddown(level, 1, q_only))
 
 
+@pytest.mark.parametrize("level", [28, 16, 3])
+def test_moddown_stage_entries_compose_to_moddown(engine40, oracle40, level):
+    """cfhe_intt_for_moddown, cfhe_bconv_for_moddown and cfhe_ntt_for_moddown run
+    in that order leave the words of the golden model's ModDown, Rescale and
+    ModDownAndRescale (two polynomials at once)."""
+    e, o = engine40, oracle40
+    t = e.torch
+    rng = np.random.default_rng(260 + level)
+    full = e.level_limbs(level, 12)
+    nq = len(full) - 12
+    src = np.stack([rand_limbs(rng, o.primes, full, o.n) for _ in range(2)])
+    for kind in (0, 2, 1):
+        host = src if kind != 1 else np.ascontiguousarray(src[:, :nq])
+        s = e.to_dev(host.reshape(-1, o.n)).reshape(host.shape)
+        nd = len(e.level_limbs(level if kind == 0 else level - 1))
+        d = t.empty((2, nd, o.n), dtype=t.int32, device=s.device)
+        e.moddown_staged_(level, kind, d, s)
+        got = e.to_host(d.reshape(-1, o.n)).reshape(2, nd, o.n)
+        for p in range(2):
+            assert np.array_equal(got[p], o.moddown(level, kind, host[p])), (kind, p)
+
+
 def fake_key(rng, e, o, key_main, beta):
     T = len(e.p["terminal_primes"])
     L = T + len(e.p["main_primes"])
