@@ -821,6 +821,32 @@ int cfhe_encode_coeffs(cfhe_context *h, uint32_t *dst, const double *coeffs, con
   return cfhe_ntt(h, dst, dst, gidx, n_limbs, 1, 0, 0, 1);
 }
 
+int cfhe_decode_coeffs(cfhe_context *h, double *coeffs, const uint32_t *src, const int *gidx, int n_limbs,
+                       const uint32_t *icrt, const uint32_t *hat, const uint32_t *q_low) {
+  if (!h || !coeffs || !src || !gidx || !icrt || !hat || !q_low) return fail("null argument");
+  if (n_limbs < 1 || n_limbs > kMaxLimbs) return fail("too many limbs");
+  void *res = nullptr, *out = nullptr;
+  if (int r = cfhe_malloc(h, &res, (size_t)n_limbs * kN * sizeof(uint32_t))) return r;
+  if (int r = cfhe_malloc(h, &out, (size_t)kN * sizeof(double))) {
+    cfhe_free(h, res);
+    return r;
+  }
+  int rc = cfhe_intt(h, (uint32_t *)res, src, gidx, n_limbs, 1, 0, 0, icrt, 0, 0);
+  if (!rc) {
+    CFHE_ENTER(h);
+    rc = launch_crt_lift(h->c, (double *)out, (const uint32_t *)res, gidx, n_limbs, hat, q_low);
+    h->c.mark("decode");
+    if (!rc) {
+      cudaError_t e = cudaMemcpyAsync(coeffs, out, (size_t)kN * sizeof(double), cudaMemcpyDeviceToHost, h->c.stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(h->c.stream);
+      if (e != cudaSuccess) rc = fail(cudaGetErrorString(e));
+    }
+  }
+  cfhe_free(h, out);
+  cfhe_free(h, res);
+  return rc;
+}
+
 int cfhe_add_evk_part(cfhe_context *h, uint32_t *bx, const uint32_t *s_target, const uint32_t *p_prod,
                       const int *gidx, int n_limbs) {
   CFHE_ENTER(h);

@@ -175,6 +175,8 @@ int launch_sample_uniform(const Context &c, uint32_t *dst, const int *gidx, int 
                           uint32_t stream);
 int launch_sample_error(const Context &c, uint32_t *dst, const int *gidx, int n_limbs, double sigma,
                         uint64_t seed, uint32_t stream);
+int launch_crt_lift(const Context &c, double *out, const uint32_t *res, const int *gidx, int n_limbs,
+                    const uint32_t *hat, const uint32_t *q_low);
 int launch_rns_split(const Context &c, uint32_t *dst, const double *v, const int *gidx, int n_limbs);
 int launch_encrypt(const Context &c, uint32_t *b, const uint32_t *a, const uint32_t *s, const uint32_t *e,
                    const uint32_t *m, const int *gidx, int n_limbs);

@@ -196,6 +196,49 @@ __global__ void __launch_bounds__(kSampleThreads) rns_split_kernel(const __grid_
   a.dst[(size_t)l * kN + i] = r;
 }
 
+// Decoding, device half: the centred integer behind the residues of one
+// coefficient (reference Encoder::Decode, src/core/Encode.cpp:250-275, lifts
+// with big integers on the host). With r_j = x * (Q/q_j)^-1 mod q_j the
+// integer is x = sum_j r_j (Q/q_j) - k Q, k = round(sum_j r_j / q_j): the sum
+// of fractions is within 2^-40 of an integer for any decodable value (|x| is
+// far below Q), so doubles find k; x itself is then computed modulo 2^128,
+// exactly, because |x| < 2^127.
+struct LiftArgs {
+  double *out;
+  const uint32_t *res;  // [n_limbs][N]
+  int n_limbs;
+  uint32_t q[kMaxLimbs];
+  uint32_t hat[kMaxLimbs][4];  // (Q / q_j) mod 2^128, little endian words
+  uint32_t q_low[4];           // Q mod 2^128
+};
+
+__global__ void __launch_bounds__(kSampleThreads) crt_lift_kernel(const __grid_constant__ LiftArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * kSampleThreads + threadIdx.x;
+  unsigned __int128 acc = 0;
+  double frac = 0.0;
+  for (int j = 0; j < a.n_limbs; j++) {
+    const uint32_t r = a.res[(size_t)j * kN + i];
+    const unsigned __int128 h = ((unsigned __int128)(((uint64_t)a.hat[j][3] << 32) | a.hat[j][2]) << 64) |
+                                (((uint64_t)a.hat[j][1] << 32) | a.hat[j][0]);
+    acc += h * r;
+    frac += (double)r / (double)a.q[j];
+  }
+  const unsigned __int128 ql = ((unsigned __int128)(((uint64_t)a.q_low[3] << 32) | a.q_low[2]) << 64) |
+                               (((uint64_t)a.q_low[1] << 32) | a.q_low[0]);
+  const long long k = llrint(frac);
+  acc -= ql * (unsigned __int128)(unsigned long long)k;
+  // to double through the magnitude (a negative value written as hi * 2^64 + lo
+  // with hi = -1 would cancel two numbers near 2^64)
+  const __int128 x = (__int128)acc;
+  const bool negative = x < 0;
+  const unsigned __int128 mag = negative ? (unsigned __int128)(-x) : (unsigned __int128)x;
+  const double v = (double)(unsigned long long)(mag >> 64) * 18446744073709551616.0 +
+                   (double)(unsigned long long)mag;
+  a.out[i] = negative ? -v : v;
+}
+
 int fill_sample(const Context &c, SampleArgs &s, uint32_t *dst, const int *gidx, int n_limbs, uint64_t seed,
                 uint32_t stream) {
   if (!dst || !gidx) {
@@ -280,6 +323,34 @@ int launch_rns_split(const Context &c, uint32_t *dst, const double *v, const int
   }
   CFHE_CUDA(launch_kernel(c.use_pdl, rns_split_kernel, dim3(kN / kSampleThreads, n_limbs), dim3(kSampleThreads), 0,
                           c.stream, x));
+  CFHE_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_crt_lift(const Context &c, double *out, const uint32_t *res, const int *gidx, int n_limbs,
+                    const uint32_t *hat, const uint32_t *q_low) {
+  if (!out || !res || !gidx || !hat || !q_low) {
+    set_error("null argument");
+    return -1;
+  }
+  if (n_limbs < 1 || n_limbs > kMaxLimbs) {
+    set_error("too many limbs");
+    return -1;
+  }
+  LiftArgs x;
+  x.out = out;
+  x.res = res;
+  x.n_limbs = n_limbs;
+  for (int l = 0; l < n_limbs; l++) {
+    if (gidx[l] < 0 || gidx[l] >= c.NP) {
+      set_error("prime index out of range");
+      return -1;
+    }
+    x.q[l] = c.q[gidx[l]];
+    for (int w = 0; w < 4; w++) x.hat[l][w] = hat[4 * l + w];
+  }
+  for (int w = 0; w < 4; w++) x.q_low[w] = q_low[w];
+  CFHE_CUDA(launch_kernel(c.use_pdl, crt_lift_kernel, dim3(kN / kSampleThreads), dim3(kSampleThreads), 0, c.stream, x));
   CFHE_CUDA(cudaGetLastError());
   return 0;
 }

@@ -776,25 +776,57 @@ class Encoder {
     CheckAbi(cfhe_encode_coeffs(h_, ptxt.mx_.data(), coeffs.data(), g.data(), nt));
   }
 
+  // The centred integer coefficients are rebuilt on the device
+  // (cfhe_decode_coeffs: fractions find the multiple of Q, 128-bit wrapping
+  // arithmetic the value); DecodeOnHost is the big-integer form of the same
+  // lift (the reference's, src/core/Encode.cpp:250-275).
   void Decode(std::vector<Complex> &message, const Plaintext<word> &ptxt) const {
     NPInfo np = ptxt.GetNP();
     AssertTrue(np.num_aux_ == 0, "Decode: Aux primes not supported");
     auto primes = param_.GetPrimeVector(np);
     const int nt = np.GetNumTotal(), degree = param_.degree_, half = degree / 2;
     const int num_slots = ptxt.GetNumSlots(), gap = half / num_slots;
-    std::vector<word> icrt(nt);
-    for (int i = 0; i < nt; i++) {
-      word prod = 1;
-      for (int j = 0; j < nt; j++)
-        if (j != i) prod = detail::MulMod(prod, primes[j] % primes[i], primes[i]);
-      prod = detail::MulMod(prod, (word)degree % primes[i], primes[i]);
-      icrt[i] = detail::InvMod(prod, primes[i]);
+    std::vector<word> icrt = InverseCrtConstants(primes, degree);
+    // (Q / q_j) and Q modulo 2^128
+    std::vector<uint32_t> hat((size_t)4 * nt, 0), q_low(4, 0);
+    auto low_words = [](const detail::BigU &b, uint32_t *dst) {
+      for (size_t w = 0; w < 4; w++) dst[w] = w < b.w.size() ? b.w[w] : 0;
+    };
+    detail::BigU Q(1);
+    Q.w[0] = 1;
+    for (int j = 0; j < nt; j++) {
+      Q.mul_small(primes[j]);
+      detail::BigU h(1);
+      h.w[0] = 1;
+      for (int k = 0; k < nt; k++)
+        if (k != j) h.mul_small(primes[k]);
+      low_words(h, &hat[(size_t)4 * j]);
     }
+    low_words(Q, q_low.data());
+    std::vector<double> coeffs(degree);
+    auto g = param_.GetLimbIndices(np);
+    CheckAbi(cfhe_decode_coeffs(h_, coeffs.data(), ptxt.mx_.data(), g.data(), nt, icrt.data(), hat.data(),
+                                q_low.data()));
+    message.resize(num_slots);
+    const double scale = ptxt.GetScale();
+    for (int i = 0; i < num_slots; i++)
+      message[i] = Complex(coeffs[(size_t)i * gap] / scale, coeffs[(size_t)i * gap + half] / scale);
+    SpecialFFT(message);
+  }
+
+  void DecodeOnHost(std::vector<Complex> &message, const Plaintext<word> &ptxt) const {
+    NPInfo np = ptxt.GetNP();
+    AssertTrue(np.num_aux_ == 0, "Decode: Aux primes not supported");
+    auto primes = param_.GetPrimeVector(np);
+    const int nt = np.GetNumTotal(), degree = param_.degree_, half = degree / 2;
+    const int num_slots = ptxt.GetNumSlots(), gap = half / num_slots;
+    std::vector<word> icrt = InverseCrtConstants(primes, degree);
     DeviceVector<word> tmp(nt * degree);
     auto g = param_.GetLimbIndices(np);
     CheckAbi(cfhe_intt(h_, tmp.data(), ptxt.mx_.data(), g.data(), nt, 1, 0, 0, icrt.data(), 0, 0));
     std::vector<word> res;
     CopyDeviceToHost(res, tmp);
+    CheckAbi(cfhe_synchronize(h_));
     std::vector<detail::BigU> hat(nt);
     detail::BigU Q(1);
     Q.w[0] = 1;
@@ -822,6 +854,20 @@ class Encoder {
     for (int i = 0; i < num_slots; i++)
       message[i] = Complex(lift(i * gap) / scale, lift(i * gap + half) / scale);
     SpecialFFT(message);
+  }
+
+  // ((Q / q_i) * degree)^-1 mod q_i: what the inverse transform multiplies by before the lift
+  static std::vector<word> InverseCrtConstants(const std::vector<word> &primes, int degree) {
+    const int nt = primes.size();
+    std::vector<word> icrt(nt);
+    for (int i = 0; i < nt; i++) {
+      word prod = 1;
+      for (int j = 0; j < nt; j++)
+        if (j != i) prod = detail::MulMod(prod, primes[j] % primes[i], primes[i]);
+      prod = detail::MulMod(prod, (word)degree % primes[i], primes[i]);
+      icrt[i] = detail::InvMod(prod, primes[i]);
+    }
+    return icrt;
   }
 
   void EncodeConstant(Constant<word> &constant, int level, double scale, double number,

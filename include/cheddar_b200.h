@@ -252,6 +252,19 @@ CFHE_API int cfhe_add_evk_part(cfhe_context *ctx, uint32_t *bx, const uint32_t *
  * one 512 KiB upload instead of n_limbs * 256 KiB. */
 CFHE_API int cfhe_encode_coeffs(cfhe_context *ctx, uint32_t *dst, const double *coeffs, const int *gidx,
                                 int n_limbs);
+/* Decoding, device half (Encoder::Decode, src/core/Encode.cpp:250-275, before
+ * its special FFT): src is a plaintext on the listed limbs (evaluation domain,
+ * M-form); coeffs, a HOST array of N doubles, receives the centred integer
+ * coefficients of the plaintext polynomial (to be divided by the scale).
+ * The caller supplies the constants of the limb set:
+ *   icrt[j]    = (N * Q / q_j)^-1 mod q_j
+ *   hat[4*j..] = (Q / q_j) mod 2^128, four little-endian 32-bit words
+ *   q_low[4]   = Q mod 2^128
+ * Exact for coefficients below 2^127 in magnitude (any decodable plaintext;
+ * larger values wrap). Synchronises the context's stream. */
+CFHE_API int cfhe_decode_coeffs(cfhe_context *ctx, double *coeffs, const uint32_t *src, const int *gidx,
+                                int n_limbs, const uint32_t *icrt, const uint32_t *hat,
+                                const uint32_t *q_low);
 /* Device-to-device copy and fill on the context's stream (the reference's
  * DeviceVector copies, src/core/DeviceVector.cpp, and cudaMemsetAsync calls). */
 CFHE_API int cfhe_copy_d2d(cfhe_context *ctx, void *dst, const void *src, size_t bytes);

@@ -135,6 +135,39 @@ int main(int argc, char **argv) {
     tb.Decode(res, pt);
     tb.CompareMessages("EncodeDecode", level, m, res);
   });
+  run("DecodeDeviceVsHost", 0, [&](int level) {
+    // the device's lift (fractions + 128-bit wrapping sums) against the
+    // big-integer lift, on a plaintext and on the noisier decryption of a product
+    Msg m, m2, dev, host;
+    tb.GenerateRandomMessage(m);
+    tb.GenerateRandomMessage(m2);
+    Pt pt;
+    tb.Encode(pt, m, level);
+    ctx.encoder().Decode(dev, pt);
+    ctx.encoder().DecodeOnHost(host, pt);
+    double worst = 0;
+    for (size_t i = 0; i < dev.size(); i++) worst = std::max(worst, std::abs(dev[i] - host[i]));
+    const double worst_plain = worst;
+    if (level >= 1) {
+      Ct c1, c2, prod;
+      tb.EncodeAndEncrypt(c1, m, level);
+      tb.EncodeAndEncrypt(c2, m2, level);
+      ctx.Mult(prod, c1, c2);  // unrelinearised, scale squared: the largest integers a decode sees
+      ctx.Relinearize(c1, prod, tb.interface_->GetMultiplicationKey());
+      Pt dec;
+      tb.interface_->Decrypt(dec, c1);
+      ctx.encoder().Decode(dev, dec);
+      ctx.encoder().DecodeOnHost(host, dec);
+      for (size_t i = 0; i < dev.size(); i++) worst = std::max(worst, std::abs(dev[i] - host[i]));
+    }
+    if (!(worst < 1e-9)) {
+      std::cout << std::scientific << "[FAIL] DecodeDeviceVsHost level " << level << ": " << worst << " (plaintext alone "
+                << worst_plain << ")" << std::fixed << std::endl;
+      tb.failures++;
+    } else {
+      std::cout << "[ OK ] DecodeDeviceVsHost level " << level << ": max difference " << worst << std::endl;
+    }
+  });
   run("EncodeEncryptDecryptDecode", 0, [&](int level) {
     Msg m, res;
     tb.GenerateRandomMessage(m);
