@@ -48,9 +48,9 @@
 // the residual sums, the LayerNorm products and the bootstraps) and a block of
 // the feed-forward features, with an all-gather where the next stage needs
 // every ciphertext; a LayerNorm's sum of squares gathers one partial sum per
-// rank, and the statistic's bootstrap and series run on every rank alike. Every rank starts
-// from the same ciphertexts and keys and all arithmetic is exact, so the
-// sharded result is bit-identical to the one-GPU result.
+// rank, and the statistic's bootstrap and series run on every rank alike.
+// Every rank starts from the same ciphertexts and keys and all arithmetic is
+// exact, so the sharded result is bit-identical to the one-GPU result.
 #pragma once
 #include <chrono>
 #include <atomic>
