@@ -129,6 +129,9 @@ struct TransformerPolys {
   std::vector<double> inv_c;    // w -> 1 / (T m),  m = ((hi-lo) w + hi+lo)/2 the mean of the exponentials
   std::vector<double> rsqrt_c;  // w -> 1 / (2 sqrt(v + eps)), v = ((hi-lo) w + hi+lo)/2 the variance
   std::vector<double> gelu_c;   // t -> GELU(G t) / G,          t = a / G
+  // GELU(x) = x / 2 + E(x) with E even, so the series above is t / 2 plus a
+  // series in T_2(t) = 2 t^2 - 1 (T_2k(t) = T_k(T_2(t))): its even coefficients
+  std::vector<double> gelu_even_c;
   explicit TransformerPolys(const TransformerConfig &c) {
     using P = EvalPoly<uint32_t>;
     const double R = c.score_range, T = c.seq_len, G = c.gelu_range;
@@ -147,6 +150,7 @@ struct TransformerPolys {
           return 0.5 * a * (1.0 + std::erf(a / std::sqrt(2.0))) / G;
         },
         c.gelu_degree);
+    for (size_t k = 0; k < gelu_c.size(); k += 2) gelu_even_c.push_back(gelu_c[k]);
   }
 };
 
@@ -377,8 +381,13 @@ class EncryptedTransformerLayer {
       Mark("feed-forward projection 1");
       if (probe_) probe_("pre-activation", pre, cfg_.gelu_range);
       act.resize(F);
+      // only the even part E of GELU(a) = a / 2 + E(a) is evaluated, as a series of
+      // half the degree in 2 t^2 - 1; the linear part a / 2 = (W1^T z + b1) / 2 goes
+      // through the second projection as a linear map of z and joins the residual
       ParallelFor(nc, [&](const ConstContextPtr<word> &c, int i) {
-        Poly(c, act[ffn0 + i], pre[ffn0 + i], polys_.gelu_c, mult);
+        Ct y;
+        EvalPoly<word>::Node(c, y, pre[ffn0 + i], pre[ffn0 + i], nullptr, 1.0, mult);
+        Poly(c, act[ffn0 + i], y, polys_.gelu_even_c, mult);
       });
       pre.clear();
       Mark("GELU");
@@ -394,10 +403,41 @@ class EncryptedTransformerLayer {
       for (int j = res0; j < res1; j++) cols.push_back(j);
       if (!m_w2_)
         m_w2_ = MakeMatrix(Columns(Centred(w_.w2, F, H, cfg_.gelu_range / A), F, H, cols), F, cols.size(), act[0]);
-      Project(y2, *m_w2_, Pointers(act), Select(CentredBias(w_.b2, 1.0 / A), cols), cols);
+      // bias: b2 / A plus the constant of the linear part, W2^T b1 / (2 A), centred
+      std::vector<double> bias(H, 0.0);
+      for (int f = 0; f < F; f++)
+        for (int j = 0; j < H; j++) bias[j] += 0.5 * w_.b1[f] * w_.w2[(size_t)f * H + j];
+      for (int j = 0; j < H; j++) bias[j] += w_.b2[j];
+      Project(y2, *m_w2_, Pointers(act), Select(CentredBias(bias, 1.0 / A), cols), cols);
+      act.clear();
+      // residual and linear part of the GELU in one projection of z: (I + W1 W2 / 2)^T z, centred
+      if (!m_res_) {
+        const auto t0 = std::chrono::steady_clock::now();
+        std::vector<double> m((size_t)H * H, 0.0);
+        for (int k = 0; k < H; k++) {
+          double *row = &m[(size_t)k * H];
+          for (int f = 0; f < F; f++) {
+            const double a = 0.5 * w_.w1[(size_t)k * F + f];
+            const double *w2 = &w_.w2[(size_t)f * H];
+            for (int j = 0; j < H; j++) row[j] += a * w2[j];
+          }
+          row[k] += 1.0;
+        }
+        const auto d = std::chrono::steady_clock::now() - t0;
+        last_ += d;
+        pack_s_ += std::chrono::duration<double>(d).count();
+        m_res_ = MakeMatrix(Columns(Centred(m, H, H, 1.0), H, H, cols), H, cols.size(), z[0]);
+      }
+      std::vector<Ct> lin(H);
+      Project(lin, *m_res_, Pointers(z), std::vector<double>(cols.size(), 0.0), cols);
+      const int ly = Level(y2[res0]);
+      ParallelFor(res1 - res0, [&](const ConstContextPtr<word> &cx, int i) {
+        const int j = res0 + i;
+        Ct low;  // lin[j] belongs to another item's pool: it is read here and freed after the loop
+        cx->LevelDown(low, lin[j], ly);
+        cx->Add(y2[j], y2[j], low);
+      });
     }
-    act.clear();
-    AddCentredResidual(y2, z, res0, res1);
     z.clear();
     Mark("feed-forward projection 2, residual");
     if (probe_) probe_("centred sum 2", y2, A);
@@ -859,7 +899,7 @@ class EncryptedTransformerLayer {
   TransformerPolys polys_;
   std::shared_ptr<RankGroup> group_;
   int slots_ = 0, lane_ = 0;
-  std::unique_ptr<PlainMatrix<word>> m_qkv_, m_wo_, m_w1_, m_w2_;
+  std::unique_ptr<PlainMatrix<word>> m_qkv_, m_wo_, m_w1_, m_w2_, m_res_;
   Probe probe_;
   std::map<std::tuple<int, double, double>, Plaintext<word>> masks_;
   std::vector<double> mask_signs_;

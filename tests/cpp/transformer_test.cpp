@@ -116,7 +116,10 @@ int main(int argc, char **argv) {
       else if (name == "centred sum 1") want = centre(tr->sum1, H);
       else if (name == "LayerNorm 1" || name == "LayerNorm 1, refreshed") want = tr->norm1;
       else if (name == "pre-activation") want = tr->pre;
-      else if (name == "GELU") want = tr->gelu;
+      else if (name == "GELU") {  // the layer evaluates the even part: GELU(a) - a / 2
+        want = tr->gelu;
+        for (size_t i = 0; i < want.size(); i++) want[i] -= 0.5 * tr->pre[i];
+      }
       else if (name == "centred sum 2") want = centre(tr->sum2, H);
       else if (name == "LayerNorm 2") want = *final_out;
       else return;
